@@ -115,7 +115,7 @@ class EltwiseParams(C.Structure):
                 ("mode", C.c_int32),
                 ("stride_x0", C.c_int32), ("stride_y0", C.c_int32),
                 ("stride_x1", C.c_int32), ("stride_y1", C.c_int32),
-                ("calibration", C.c_int32), ("has_o_qf", C.c_int32), ("o_qf", C.c_float),
+                ("quantization", C.c_int32), ("calibration", C.c_int32), ("o_qf", C.c_float),
                 ("act", C.c_int32), ("act_m", C.c_float), ("act_n", C.c_float),
                 ("reserved", C.c_int32 * 4)]
 

@@ -1,0 +1,535 @@
+// conv_i8_tc: 8-bit convolution (u8/s8 activations x s8 weights -> s32) as an
+// implicit GEMM on the sm_100a tensor cores, with the reference's requantising
+// epilogue fused in.  It takes the place of the reference's MMAD / IMAD kernel
+// family (cl_kernels/convolution_gpu_mmad*.cl, fused_conv_eltwise_gpu_imad.cl,
+// convolution_gpu_mmad_32x32sg_128x128wg_slm_int8.cl) while keeping the
+// operation order of the reference kernel fused_conv_eltwise_gpu_ref.cl:148-232.
+//
+// GEMM view:  M = N*P*Q output pixels, N = output features, K = kh*kw*C.
+//   A (M x K): activations, byxf (feature innermost, C a multiple of 32), never
+//              materialised: one TMA copy per (filter tap, channel chunk) brings
+//              the 128 pixels of a tile straight into swizzled shared memory.
+//              Three addressing modes: flat 2-D (1x1, stride 1), TMA im2col
+//              (any filter / stride / padding / dilation, zero fill outside the
+//              image = the reference's skipped taps), and a tiled 4-D box.
+//   B (N x K): weights, oyxi (input features innermost), one TMA box per step.
+//   D        : s32 accumulators in tensor memory, two buffers so the epilogue of
+//              tile t overlaps the main loop of tile t+1.
+// One persistent CTA per SM: warp 0 issues TMA, warp 1 issues tcgen05.mma,
+// warps 2..5 run the epilogue (tcgen05.ld -> bias/dequant/ReLU/requant/round/
+// residual/saturate -> 16-byte stores).
+#include <cuda.h>
+#include <mutex>
+#include "engine.hpp"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+using namespace ptx;
+
+constexpr int kBM = 128;                 // pixels per tile = TMEM lanes
+constexpr int kThreads = 192;
+constexpr int kMaxStages = 8;
+constexpr int kMaxBN = 256;
+constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
+
+enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
+
+struct alignas(64) TcParams {
+    CUtensorMap tmA;
+    CUtensorMap tmB;
+    int32_t a_mode;
+    int32_t N, P, Q;                     // output batch, rows, columns
+    int32_t kh, kw, stride_x, stride_y, pad_x, pad_y, dil_x, dil_y;
+    int32_t bk, chunks, k_steps;         // bytes of K per stage, channel chunks per tap, stages per tile
+    int32_t bn, n_tiles, m_tiles, total_tiles;
+    int64_t M_total;
+    int32_t bw, bh, bb, tiles_w, tiles_h; // tiled mode: box of bw x bh x bb pixels
+    int32_t a_coord_stride_x, a_coord_stride_y; // tiled mode: input step per output step in tensor-map coordinates
+    int32_t stages, a_stage_bytes, b_stage_bytes, a_tx_bytes, b_tx_bytes;
+    uint32_t sbo, layout_type, idesc, tmem_cols;
+    int32_t ofm;
+    // output / residual addressing, in elements
+    int64_t out_px, out_py, out_pb, out_off;
+    int64_t el_px, el_py, el_pb, el_off;
+    int32_t el_sx, el_sy;
+    void* out; const void* eltw; const void* bias; const float* quant; const float* calib; const float* ecal;
+    uint32_t* status;
+    EpiCfg epi;
+};
+
+struct TcSmemAux {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    uint32_t abort;
+    int32_t bias_i[2][kMaxBN];
+    float bias_f[2][kMaxBN];
+    float quant[2][kMaxBN];
+    float calib[2][kMaxBN];
+    float ecal[2][kMaxBN];
+};
+
+__device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int& m_tile, int& n_tile)
+{
+    m_tile = tile / P.n_tiles; n_tile = tile - m_tile * P.n_tiles;
+}
+
+// pixel of row `row` of tile `m_tile`: returns false when the row is padding
+__device__ __forceinline__ bool row_pixel(const TcParams& P, int m_tile, int row, int& n, int& p, int& q)
+{
+    if (P.a_mode == A_TILED) {
+        const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
+        const int th = t2 % P.tiles_h; const int tb = t2 / P.tiles_h;
+        const int rw = row % P.bw; const int r2 = row / P.bw;
+        const int rh = r2 % P.bh; const int rb = r2 / P.bh;
+        q = tw * P.bw + rw; p = th * P.bh + rh; n = tb * P.bb + rb;
+        return rb < P.bb && q < P.Q && p < P.P && n < P.N;
+    }
+    const int64_t m = (int64_t)m_tile * kBM + row;
+    const int pq = P.P * P.Q;
+    n = (int)(m / pq); const int r = (int)(m - (int64_t)n * pq);
+    p = r / P.Q; q = r - p * P.Q;
+    return m < P.M_total;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+conv_i8_tc_kernel(const __grid_constant__ TcParams P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + (uint32_t)(P.stages * P.a_stage_bytes);
+    TcSmemAux* aux = reinterpret_cast<TcSmemAux*>(smem + (size_t)P.stages * (P.a_stage_bytes + P.b_stage_bytes));
+    volatile uint32_t* s_abort = &aux->abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4); }
+        mbar_init(smem_u32(&aux->drain), 1);
+        aux->abort = 0u;
+        mbar_fence_init();
+        prefetch_tensormap(&P.tmA); prefetch_tensormap(&P.tmB);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
+                int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
+                // base coordinates of the tile's first pixel
+                int c_w = 0, c_h = 0, c_n = 0;
+                if (P.a_mode == A_IM2COL) {
+                    int n, p, q; row_pixel(P, m_tile, 0, n, p, q);
+                    c_w = q * P.stride_x - P.pad_x; c_h = p * P.stride_y - P.pad_y; c_n = n;
+                } else if (P.a_mode == A_TILED) {
+                    const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
+                    c_w = tw * P.bw * P.a_coord_stride_x - P.pad_x; c_h = (t2 % P.tiles_h) * P.bh * P.a_coord_stride_y - P.pad_y; c_n = (t2 / P.tiles_h) * P.bb;
+                }
+                int tap = 0, cc = 0, r = 0, s = 0;
+                for (int ks = 0; ks < P.k_steps; ++ks) {
+                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&aux->full[stage]);
+                    mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
+                    const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
+                    const uint32_t b_dst = b_base + (uint32_t)(stage * P.b_stage_bytes);
+                    const int c0 = cc * P.bk;
+                    if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
+                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
+                    else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
+                    tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * P.bn);
+                    ++issued;
+                    if (++cc == P.chunks) { cc = 0; ++tap; if (++s == P.kw) { s = 0; ++r; } }
+                    if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // unwind: let the copies already in flight land before the CTA's shared memory goes away
+                int st = stage; uint32_t ph = phase;
+                const int pending = issued < P.stages ? (int)issued : P.stages;
+                for (int i = 0; i < pending; ++i) {
+                    if (--st < 0) { st = P.stages - 1; ph ^= 1u; }
+                    const uint64_t t0 = globaltimer();
+                    while (!mbar_try_wait(smem_u32(&aux->full[st]), ph) && globaltimer() - t0 < 100000000ull) { }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
+                const int acc = t & 1;
+                if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)t >> 1) & 1u) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.bn);
+                for (int ks = 0; ks < P.k_steps; ++ks) {
+                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(a_base + (uint32_t)(stage * P.a_stage_bytes), P.sbo, P.layout_type);
+                    const uint64_t bdesc = make_smem_desc(b_base + (uint32_t)(stage * P.b_stage_bytes), P.sbo, P.layout_type);
+                    const int kk = P.bk >> 5;                       // one instruction consumes K = 32 bytes
+                    for (int k = 0; k < kk; ++k)
+                        mma_i8_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P.idesc, (ks | k) ? 1u : 0u);
+                    tc_commit(smem_u32(&aux->empty[stage]));        // frees the stage once these MMAs have read it
+                    if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
+            }
+            // drain: every issued MMA must have retired before TMEM is released
+            tc_commit(smem_u32(&aux->drain));
+            const uint64_t t0 = globaltimer();
+            while (!mbar_try_wait(smem_u32(&aux->drain), 0u)) {
+                if (globaltimer() - t0 > kWaitLimitNs) { atomicCAS(P.status, 0u, kErrDrain); break; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int quad = warp & 3;                                  // TMEM lanes 32*quad .. 32*quad+31
+        const int row = quad * 32 + lane;
+        const int et = threadIdx.x - 64;                            // 0..127
+        const EpiCfg& c = P.epi;
+        const bool out8 = is_int8(c.out_dtype);
+        int t = 0; bool ok = true;
+        for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
+            int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
+            const int acc = t & 1;
+            const int n0 = n_tile * P.bn;
+            // per-channel constants of this tile's feature range
+            for (int j = et; j < P.bn; j += 128) {
+                const int f = n0 + j; const bool v = f < P.ofm;
+                int32_t bi = 0; float bf = 0.f;
+                if (v && c.bias_dtype != CLDNN_B200_NONE) {
+                    if (c.bias_dtype == CLDNN_B200_F32) bf = ((const float*)P.bias)[f];
+                    else bi = load_as_int(P.bias, c.bias_dtype, f);
+                }
+                aux->bias_i[acc][j] = bi; aux->bias_f[acc][j] = bf;
+                aux->quant[acc][j] = (v && c.quantization) ? P.quant[f] : 1.f;
+                aux->calib[acc][j] = (v && c.calibration) ? P.calib[f] : 1.f;
+                aux->ecal[acc][j] = (v && c.eltw_calibration) ? P.ecal[f] : 1.f;
+            }
+            named_bar_sync(1, 128);
+            if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue)) { ok = false; break; }
+            tc_fence_after();
+
+            int n, p, q; const bool valid = row_pixel(P, m_tile, row, n, p, q);
+            const int64_t o_pix = P.out_off + (int64_t)n * P.out_pb + (int64_t)p * P.out_py + (int64_t)q * P.out_px;
+            const int64_t e_pix = c.fused_eltw ? P.el_off + (int64_t)n * P.el_pb + (int64_t)p * P.el_sy * P.el_py + (int64_t)q * P.el_sx * P.el_px : 0;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * P.bn);
+
+            for (int c0 = 0; c0 < P.bn; c0 += 32) {
+                if (n0 + c0 >= P.ofm) break;                        // uniform across the CTA
+                uint32_t r[32];
+                tmem_ld_32x32(t_row + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (!valid) continue;
+                const int fbase = n0 + c0;
+                const bool full32 = fbase + 32 <= P.ofm;
+                if (c.quant_path && out8 && full32 && ((o_pix + fbase) & 15) == 0 &&
+                    (!c.fused_eltw || (is_int8(c.eltw_dtype) && ((e_pix + fbase) & 15) == 0))) {
+                    // fast path: 32 features -> two 16-byte stores
+                    uint32_t ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    if (c.fused_eltw) {
+                        const uint4* ep = (const uint4*)((const uint8_t*)P.eltw + e_pix + fbase);
+                        const uint4 e0 = ep[0], e1 = ep[1];
+                        ew[0] = e0.x; ew[1] = e0.y; ew[2] = e0.z; ew[3] = e0.w; ew[4] = e1.x; ew[5] = e1.y; ew[6] = e1.z; ew[7] = e1.w;
+                    }
+                    uint32_t ow[8];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int cj = c0 + j;
+                        const int32_t a = (int32_t)r[j] + aux->bias_i[acc][cj];
+                        float e = 0.f;
+                        if (c.fused_eltw) {
+                            const uint32_t byte = (ew[j >> 2] >> ((j & 3) * 8)) & 0xffu;
+                            e = c.eltw_dtype == CLDNN_B200_U8 ? (float)byte : (float)(int8_t)byte;
+                        }
+                        const float v = epi_quant(c, a, aux->quant[acc][cj], aux->bias_f[acc][cj], aux->calib[acc][cj], e, aux->ecal[acc][cj]);
+                        const int32_t o = c.out_dtype == CLDNN_B200_U8 ? sat_i32_from_float(v, 0, 255) : sat_i32_from_float(v, -128, 127);
+                        if ((j & 3) == 0) ow[j >> 2] = 0;
+                        ow[j >> 2] |= ((uint32_t)o & 0xffu) << ((j & 3) * 8);
+                    }
+                    uint4* op = (uint4*)((uint8_t*)P.out + o_pix + fbase);
+                    op[0] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    op[1] = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+                } else {
+                    // general path: any output type, ragged feature tail, unaligned rows
+#pragma unroll 1
+                    for (int j = 0; j < 32; ++j) {
+                        const int f = fbase + j; if (f >= P.ofm) break;
+                        const int cj = c0 + j;
+                        const int32_t a = (int32_t)r[j] + aux->bias_i[acc][cj];
+                        if (c.quant_path) {
+                            const float e = c.fused_eltw ? load_as_float(P.eltw, c.eltw_dtype, e_pix + f) : 0.f;
+                            const float v = epi_quant(c, a, aux->quant[acc][cj], aux->bias_f[acc][cj], aux->calib[acc][cj], e, aux->ecal[acc][cj]);
+                            store_sat_float(P.out, c.out_dtype, o_pix + f, v);
+                        } else {
+                            // 8-bit fused eltwise without quantisation: integer activation domain
+                            int32_t v = act_int(c.act, a, c.act_m, c.act_n), s;
+                            if (c.has_non_conv_scale) s = (int32_t)__fadd_rn((float)v, __fmul_rn(load_as_float(P.eltw, c.eltw_dtype, e_pix + f), c.non_conv_scale));
+                            else s = v + load_as_int(P.eltw, c.eltw_dtype, e_pix + f);
+                            s = act_int(c.eltw_act, s, c.eltw_m, c.eltw_n);
+                            if (c.eltw_calibration) {
+                                const float tq = __fmul_rn((float)s, aux->ecal[acc][cj]);
+                                if (c.out_is_fp) { store_sat_float(P.out, c.out_dtype, o_pix + f, tq); continue; }
+                                s = (int32_t)round_half_away(tq);
+                            }
+                            store_sat_int(P.out, c.out_dtype, o_pix + f, s);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const int*, const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode_tiled = nullptr;
+static EncodeIm2colFn g_encode_im2col = nullptr;
+
+static bool load_driver_entry_points()
+{
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* fn = nullptr; cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+            g_encode_tiled = (EncodeTiledFn)fn;
+        fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+            g_encode_im2col = (EncodeIm2colFn)fn;
+        (void)cudaGetLastError();
+    });
+    return g_encode_tiled && g_encode_im2col;
+}
+
+struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; };
+
+// tune index -> (addressing mode, feature tile).  0 = automatic choice.
+static const int kTuneBN[4] = {32, 64, 128, 256};
+static int tc_tune_count(const void*) { return 1 + 3 * 4; }
+
+static bool dense_byxf(const cldnn_b200_tensor& t)
+{
+    return t.pf == 1 && t.px % 16 == 0 && t.py % 16 == 0 && t.pb % 16 == 0 && t.offset % 16 == 0 && t.px >= t.f && t.py >= t.px * t.x && t.pb >= t.py * t.y;
+}
+
+// choose a box of bw x bh x bb <= 128 pixels that wastes the fewest tile rows
+static void choose_box(int Q, int Pn, int N, int& bw, int& bh, int& bb)
+{
+    double best = -1.0; bw = 1; bh = 1; bb = 1;
+    for (int w = 1; w <= Q && w <= 128; ++w) {
+        for (int h = 1; h <= Pn && w * h <= 128; ++h) {
+            int b = 128 / (w * h); if (b > N) b = N; if (b < 1) continue; if (b > 128) b = 128;
+            const double tiles = (double)((Q + w - 1) / w) * ((Pn + h - 1) / h) * ((N + b - 1) / b);
+            const double eff = ((double)Q * Pn * N) / (tiles * 128.0);
+            // prefer long contiguous runs when the efficiency ties
+            const double score = eff + 1e-4 * w + 1e-6 * h;
+            if (score > best) { best = score; bw = w; bh = h; bb = b; }
+        }
+    }
+}
+
+static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* why)
+{
+    auto no = [&](const char* m) { if (why) *why = m; return false; };
+    if (!is_int8(p.in.dtype)) return no("activations must be u8 or i8");
+    if (p.w_dtype != CLDNN_B200_I8) return no("weights must be i8");
+    if (p.groups != 1) return no("grouped convolution is handled by other kernels");
+    if (p.kh < 1 || p.kw < 1 || p.kh * p.kw > 255) return no("filter size");
+    if (p.stride_x < 1 || p.stride_y < 1 || p.dil_x < 1 || p.dil_y < 1) return no("stride/dilation");
+    if (p.out.f != p.ofm || p.in.f != p.ifm) return no("feature counts");
+    if (!dense_byxf(p.in)) return no("input must be byxf with 16-byte aligned pitches");
+    if (p.in.px % 32) return no("stored input features must be a multiple of 32");
+    if (p.out.pf != 1) return no("output must be byxf");
+    if (!(is_int8(p.out.dtype) || p.out.dtype == CLDNN_B200_F32 || p.out.dtype == CLDNN_B200_F16 || p.out.dtype == CLDNN_B200_I32)) return no("output type");
+    if (p.w_pi != 1 || p.w_px % 16 || p.w_po % 16 || p.w_offset % 16 || p.w_py != p.w_px * p.kw) return no("weights must be oyxi with 16-byte aligned pitches");
+    if (p.w_px != p.in.px) return no("weights and input must store the same (padded) feature count");
+    const bool quant_path = p.quantization || p.calibration || p.has_o_qf;
+    if (!quant_path && !p.fused_eltw) return no("non-quantised 8-bit convolution accumulates in 8 bits; handled by conv_ref");
+    if (p.fused_eltw && !p.in_out_opt && p.eltw.pf != 1) return no("residual must be byxf");
+    if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32 && p.bias_dtype != CLDNN_B200_F32) return no("bias type");
+    if (!quant_path && p.bias_dtype == CLDNN_B200_F32) return no("float bias needs quantisation");
+    // expected output size
+    const int P_ = (p.in.y + 2 * p.pad_y - ((p.kh - 1) * p.dil_y + 1)) / p.stride_y + 1;
+    const int Q_ = (p.in.x + 2 * p.pad_x - ((p.kw - 1) * p.dil_x + 1)) / p.stride_x + 1;
+    if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
+    if ((int64_t)p.out.b * p.out.y * p.out.x > (int64_t)1 << 31) return no("too many output pixels");
+
+    const int cs = (int)p.in.px;                                    // stored channels = bytes of K per tap
+    pl.bk = cs % 128 == 0 ? 128 : (cs % 64 == 0 ? 64 : 32);
+    const bool is_1x1_s1 = p.kh == 1 && p.kw == 1 && p.stride_x == 1 && p.stride_y == 1 && p.pad_x == 0 && p.pad_y == 0 &&
+                           p.in.py == p.in.px * p.in.x && p.in.pb == p.in.py * p.in.y;
+    const bool pointwise = p.kh == 1 && p.kw == 1 && p.pad_x == 0 && p.pad_y == 0;
+    const bool tiled_ok = (p.stride_x == 1 && p.stride_y == 1) || pointwise;
+    const bool im2col_ok = p.pad_x <= 127 && p.pad_y <= 127 && (p.kw - 1) * p.dil_x <= 255 && (p.kh - 1) * p.dil_y <= 255 &&
+                           p.stride_x <= 8 && p.stride_y <= 8 &&
+                           (int64_t)p.in.b * p.in.pb >= 131072;     // small tensors take the tiled path
+    int tune = p.tune;
+    int mode = -1, bn = 0;
+    if (tune > 0) { mode = (tune - 1) / 4; bn = kTuneBN[(tune - 1) % 4]; }
+    if (mode < 0) mode = is_1x1_s1 ? A_FLAT : (tiled_ok ? A_TILED : A_IM2COL);
+    if (mode == A_FLAT && !is_1x1_s1) return no("flat addressing needs a dense 1x1 stride-1 convolution");
+    if (mode == A_TILED && !tiled_ok) return no("tiled addressing needs stride 1 or a pointwise filter");
+    if (mode == A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded");
+    if (bn == 0) bn = p.ofm > 64 ? 128 : (p.ofm > 32 ? 64 : 32);
+    pl.a_mode = mode; pl.bn = bn;
+    pl.bw = pl.bh = pl.bb = 1;
+    if (mode == A_TILED) choose_box(p.out.x, p.out.y, p.out.b, pl.bw, pl.bh, pl.bb);
+    return true;
+}
+
+static bool tc_supports(const void* vp)
+{
+    TcPlan pl; return tc_plan(*(const cldnn_b200_conv_params*)vp, pl, nullptr);
+}
+
+static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
+    TcPlan pl; std::string why;
+    if (!tc_plan(p, pl, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: " + why);
+    if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: input, output and weights are required");
+    if (p.bias_dtype != CLDNN_B200_NONE && !a->bias) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: bias_dtype set but no bias pointer");
+    if (p.quantization && !a->weights_quantization_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: quantization set but no factors");
+    if (p.calibration && !a->output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: calibration set but no factors");
+    if (p.fused_eltw && !p.in_out_opt && !a->input1) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: fused eltwise needs a second input");
+    if (p.eltw_calibration && !a->eltw_output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: eltwise calibration set but no factors");
+    if (((uintptr_t)a->input0 | (uintptr_t)a->weights) & 15) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: input and weights must be 16-byte aligned");
+    if (!load_driver_entry_points()) return fail(CLDNN_B200_DEVICE_ERROR, "conv_i8_tc: the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
+
+    TcParams P{};
+    P.a_mode = pl.a_mode;
+    P.N = p.out.b; P.P = p.out.y; P.Q = p.out.x;
+    P.kh = p.kh; P.kw = p.kw; P.stride_x = p.stride_x; P.stride_y = p.stride_y; P.pad_x = p.pad_x; P.pad_y = p.pad_y; P.dil_x = p.dil_x; P.dil_y = p.dil_y;
+    const int cs = (int)p.in.px;
+    P.bk = pl.bk; P.chunks = cs / pl.bk; P.k_steps = p.kh * p.kw * P.chunks;
+    P.bn = pl.bn; P.n_tiles = (p.ofm + pl.bn - 1) / pl.bn;
+    P.M_total = (int64_t)P.N * P.P * P.Q;
+    P.bw = pl.bw; P.bh = pl.bh; P.bb = pl.bb;
+    P.a_coord_stride_x = 1; P.a_coord_stride_y = 1;
+    if (pl.a_mode == A_TILED) {
+        P.tiles_w = (P.Q + pl.bw - 1) / pl.bw; P.tiles_h = (P.P + pl.bh - 1) / pl.bh;
+        P.m_tiles = P.tiles_w * P.tiles_h * ((P.N + pl.bb - 1) / pl.bb);
+    } else {
+        P.tiles_w = P.tiles_h = 1;
+        P.m_tiles = (int)((P.M_total + kBM - 1) / kBM);
+    }
+    P.total_tiles = P.m_tiles * P.n_tiles;
+    P.a_stage_bytes = kBM * pl.bk; P.b_stage_bytes = pl.bn * pl.bk;
+    P.a_tx_bytes = (pl.a_mode == A_TILED ? pl.bw * pl.bh * pl.bb : kBM) * pl.bk;
+    P.b_tx_bytes = pl.bn * pl.bk;
+    P.sbo = 8u * (uint32_t)pl.bk;
+    P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
+    const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;     // operand signedness in the instruction descriptor
+    P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(pl.bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    P.tmem_cols = (uint32_t)(2 * pl.bn < 32 ? 32 : 2 * pl.bn);
+    P.ofm = p.ofm;
+    P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
+    if (p.fused_eltw) {
+        const cldnn_b200_tensor& e = p.in_out_opt ? p.out : p.eltw;
+        P.el_px = e.px; P.el_py = e.py; P.el_pb = e.pb; P.el_off = e.offset;
+        P.el_sx = p.in_out_opt ? 1 : p.eltw_stride_x; P.el_sy = p.in_out_opt ? 1 : p.eltw_stride_y;
+    }
+    P.out = a->output; P.eltw = p.in_out_opt ? a->output : a->input1; P.bias = a->bias;
+    P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors; P.ecal = a->eltw_output_calibration_factors;
+    P.status = ctx->d_status;
+    P.epi = make_epi_cfg(p);
+
+    const size_t aux_bytes = sizeof(TcSmemAux);
+    const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
+    const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
+    if (max_smem < 1024 + aux_bytes + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory");
+    int stages = (int)((max_smem - 1024 - aux_bytes) / stage_bytes);
+    if (stages > kMaxStages) stages = kMaxStages;
+    P.stages = stages;
+    size_t smem_bytes = 1024 + (size_t)stages * stage_bytes + aux_bytes;
+    const size_t one_cta_floor = max_smem / 2 + 1024;                // keeps one CTA per SM, so TMEM allocation never waits
+    if (smem_bytes < one_cta_floor) smem_bytes = one_cta_floor;
+    if (smem_bytes > max_smem) smem_bytes = max_smem;
+
+    const CUtensorMapSwizzle sw = pl.bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (pl.bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    void* in_ptr = (char*)const_cast<void*>(a->input0) + p.in.offset;
+    CUresult cr;
+    if (pl.a_mode == A_FLAT) {
+        cuuint64_t dims[2] = {(cuuint64_t)cs, (cuuint64_t)P.M_total};
+        cuuint64_t strides[1] = {(cuuint64_t)p.in.px};
+        cuuint32_t box[2] = {(cuuint32_t)pl.bk, (cuuint32_t)kBM};
+        cuuint32_t es[2] = {1, 1};
+        cr = g_encode_tiled(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, in_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (pl.a_mode == A_IM2COL) {
+        cuuint64_t dims[4] = {(cuuint64_t)cs, (cuuint64_t)p.in.x, (cuuint64_t)p.in.y, (cuuint64_t)p.in.b};
+        cuuint64_t strides[3] = {(cuuint64_t)p.in.px, (cuuint64_t)p.in.py, (cuuint64_t)p.in.pb};
+        int lower[2] = {-p.pad_x, -p.pad_y};
+        int upper[2] = {p.pad_x - (p.kw - 1) * p.dil_x, p.pad_y - (p.kh - 1) * p.dil_y};
+        // the box of base pixels must produce exactly Q x P positions per image
+        const int q_tm = (p.in.x + upper[0] - lower[0] - 1) / p.stride_x + 1, p_tm = (p.in.y + upper[1] - lower[1] - 1) / p.stride_y + 1;
+        if (q_tm != P.Q || p_tm != P.P) return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_i8_tc: im2col traversal does not match the output size");
+        cuuint32_t es[4] = {1, (cuuint32_t)p.stride_x, (cuuint32_t)p.stride_y, 1};
+        cr = g_encode_im2col(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, in_ptr, dims, strides, lower, upper, (cuuint32_t)pl.bk, (cuuint32_t)kBM, es,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        // tiled 4-D box; a pointwise strided convolution reads a strided view of the input
+        const int sx = p.stride_x, sy = p.stride_y;
+        const bool strided_view = sx != 1 || sy != 1;
+        cuuint64_t dims[4] = {(cuuint64_t)cs, (cuuint64_t)(strided_view ? P.Q : p.in.x), (cuuint64_t)(strided_view ? P.P : p.in.y), (cuuint64_t)p.in.b};
+        cuuint64_t strides[3] = {(cuuint64_t)(p.in.px * sx), (cuuint64_t)(p.in.py * sy), (cuuint64_t)p.in.pb};
+        cuuint32_t box[4] = {(cuuint32_t)pl.bk, (cuuint32_t)pl.bw, (cuuint32_t)pl.bh, (cuuint32_t)pl.bb};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        cr = g_encode_tiled(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, in_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_DEVICE_ERROR, "conv_i8_tc: activation tensor map rejected by the driver (CUresult " + std::to_string((int)cr) + ")");
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)cs, (cuuint64_t)(p.kh * p.kw), (cuuint64_t)p.ofm};
+        cuuint64_t strides[2] = {(cuuint64_t)p.w_px, (cuuint64_t)p.w_po};
+        cuuint32_t box[3] = {(cuuint32_t)pl.bk, 1, (cuuint32_t)pl.bn};
+        cuuint32_t es[3] = {1, 1, 1};
+        void* w_ptr = (char*)const_cast<void*>(a->weights) + p.w_offset;
+        cr = g_encode_tiled(&P.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_DEVICE_ERROR, "conv_i8_tc: weights tensor map rejected by the driver (CUresult " + std::to_string((int)cr) + ")");
+    }
+
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_smem));
+
+    int grid = ctx->prop.multiProcessorCount;
+    if (grid > P.total_tiles) grid = P.total_tiles;
+    if (grid < 1) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: empty output");
+    const size_t smem = smem_bytes;
+    out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_tc_kernel<<<grid, kThreads, smem, s>>>(P); return cudaGetLastError(); };
+    out->launches = 1;
+    return CLDNN_B200_SUCCESS;
+}
+
+const KernelDef kdef_conv_i8_tc = {"conv_i8_tc", sizeof(cldnn_b200_conv_params), tc_supports, tc_tune_count, nullptr, tc_prepare};
+
+}  // namespace b200

@@ -1,0 +1,424 @@
+// Context, memory, events and the kernel table of the sm_100a engine: the C ABI
+// that replaces clDNN's OpenCL runtime layer (gpu_toolkit, gpu_buffer,
+// base_event, kernels_cache, gpu::kernel, kernel_runner in src/gpu/).
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+#include "engine.hpp"
+
+namespace b200 {
+
+static thread_local std::string g_last_error;   // like last_err in src/cldnn.cpp:29-33
+
+void set_error(const std::string& msg) { g_last_error = msg; }
+int32_t fail(int32_t code, const std::string& msg) { g_last_error = msg; return code; }
+int32_t cuda_fail(cudaError_t e, const char* what)
+{
+    g_last_error = std::string(what) + ": " + cudaGetErrorName(e) + " (" + cudaGetErrorString(e) + ")";
+    (void)cudaGetLastError();
+    return e == cudaErrorMemoryAllocation ? CLDNN_B200_OUT_OF_RESOURCES : CLDNN_B200_DEVICE_ERROR;
+}
+
+static const KernelDef* const g_kernels[] = {
+    &kdef_conv_i8_tc, &kdef_conv_ref,
+    &kdef_pooling_i8_byxf, &kdef_pooling_ref,
+    &kdef_fc_ref, &kdef_softmax, &kdef_eltwise_ref, &kdef_reorder_ref,
+    &kdef_lrn_ref, &kdef_activation_ref,
+};
+static const int g_kernel_count = (int)(sizeof(g_kernels) / sizeof(g_kernels[0]));
+
+struct DeviceGuard {
+    int prev = -1; bool ok = true;
+    explicit DeviceGuard(int dev) { if (cudaGetDevice(&prev) != cudaSuccess) prev = -1; if (prev != dev) ok = cudaSetDevice(dev) == cudaSuccess; }
+    ~DeviceGuard() { if (prev >= 0) (void)cudaSetDevice(prev); }
+};
+
+}  // namespace b200
+
+using namespace b200;
+
+#define B200_TRY try {
+#define B200_CATCH } catch (const std::bad_alloc&) { return fail(CLDNN_B200_OUT_OF_RESOURCES, "host allocation failed"); } \
+                     catch (const std::exception& e) { return fail(CLDNN_B200_ERROR, e.what()); } \
+                     catch (...) { return fail(CLDNN_B200_ERROR, "unknown error"); }
+
+extern "C" {
+
+const char* cldnn_b200_last_error(void) { return g_last_error.c_str(); }
+
+int32_t cldnn_b200_ctx_create(int32_t device, uint32_t enable_profiling, cldnn_b200_ctx* out)
+{
+    B200_TRY
+    if (!out) return fail(CLDNN_B200_INVALID_ARG, "ctx_create: null out");
+    *out = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        (void)cudaGetLastError();
+        return fail(CLDNN_B200_DEVICE_ERROR, "ctx_create: no CUDA device available (this engine has no CPU fallback)");
+    }
+    if (device < 0 || device >= n) return fail(CLDNN_B200_INVALID_ARG, "ctx_create: device index out of range");
+    B200_CUDA(cudaSetDevice(device));
+    auto* c = new cldnn_b200_ctx_impl();
+    c->device = device; c->profiling = enable_profiling != 0;
+    e = cudaGetDeviceProperties(&c->prop, device);
+    if (e != cudaSuccess) { delete c; return cuda_fail(e, "cudaGetDeviceProperties"); }
+    if (c->prop.major != 10) {
+        std::string m = std::string("ctx_create: device '") + c->prop.name + "' is sm_" + std::to_string(c->prop.major) +
+                        std::to_string(c->prop.minor) + "; this engine ships sm_100a kernels only";
+        delete c; return fail(CLDNN_B200_DEVICE_ERROR, m);
+    }
+    e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) { delete c; return cuda_fail(e, "cudaStreamCreate"); }
+    e = cudaMalloc(&c->d_status, 256);
+    if (e != cudaSuccess) { cudaStreamDestroy(c->stream); delete c; return cuda_fail(e, "cudaMalloc(status)"); }
+    e = cudaMemset(c->d_status, 0, 256);
+    if (e != cudaSuccess) { cudaFree(c->d_status); cudaStreamDestroy(c->stream); delete c; return cuda_fail(e, "cudaMemset(status)"); }
+    *out = c;
+    return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+
+int32_t cldnn_b200_ctx_destroy(cldnn_b200_ctx c)
+{
+    if (!c) return CLDNN_B200_SUCCESS;
+    DeviceGuard g(c->device);
+    (void)cudaStreamSynchronize(c->stream);
+    (void)cudaFree(c->d_status);
+    (void)cudaStreamDestroy(c->stream);
+    delete c;
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_ctx_info(cldnn_b200_ctx c, cldnn_b200_engine_info* info)
+{
+    if (!c || !info) return fail(CLDNN_B200_INVALID_ARG, "ctx_info: null argument");
+    std::memset(info, 0, sizeof(*info));
+    info->cores_count = (uint32_t)c->prop.multiProcessorCount;
+    int khz = 0; (void)cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device);
+    info->core_frequency = (uint32_t)(khz / 1000);
+    info->max_global_mem_size = c->prop.totalGlobalMem;
+    info->max_alloc_mem_size = c->prop.totalGlobalMem;
+    info->max_local_mem_size = c->prop.sharedMemPerBlockOptin;
+    info->max_work_group_size = (uint32_t)c->prop.maxThreadsPerBlock;
+    info->supports_fp16 = 1; info->supports_imad = 1; info->supports_immad = 1;
+    info->compute_major = (uint32_t)c->prop.major; info->compute_minor = (uint32_t)c->prop.minor;
+    std::strncpy(info->name, c->prop.name, sizeof(info->name) - 1);
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_ctx_flush(cldnn_b200_ctx c) { return c ? CLDNN_B200_SUCCESS : fail(CLDNN_B200_INVALID_ARG, "ctx_flush: null ctx"); }
+
+int32_t cldnn_b200_ctx_sync(cldnn_b200_ctx c)
+{
+    if (!c) return fail(CLDNN_B200_INVALID_ARG, "ctx_sync: null ctx");
+    B200_CUDA(cudaStreamSynchronize(c->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_ctx_stream(cldnn_b200_ctx c, void** stream)
+{
+    if (!c || !stream) return fail(CLDNN_B200_INVALID_ARG, "ctx_stream: null argument");
+    *stream = (void*)c->stream; return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_ctx_launch_count(cldnn_b200_ctx c, uint64_t* count)
+{
+    if (!c || !count) return fail(CLDNN_B200_INVALID_ARG, "ctx_launch_count: null argument");
+    *count = c->launches; return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_ctx_device_status(cldnn_b200_ctx c, uint32_t* status)
+{
+    if (!c || !status) return fail(CLDNN_B200_INVALID_ARG, "ctx_device_status: null argument");
+    DeviceGuard g(c->device);
+    B200_CUDA(cudaMemcpyAsync(status, c->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+    B200_CUDA(cudaStreamSynchronize(c->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+// ---- memory ---------------------------------------------------------------------
+int32_t cldnn_b200_mem_alloc(cldnn_b200_ctx c, size_t bytes, cldnn_b200_mem* out)
+{
+    B200_TRY
+    if (!c || !out) return fail(CLDNN_B200_INVALID_ARG, "mem_alloc: null argument");
+    *out = nullptr;
+    if (bytes > c->prop.totalGlobalMem) return fail(CLDNN_B200_ALLOC_SIZE_EXCEEDED, "mem_alloc: exceeded max size of memory object allocation");
+    DeviceGuard g(c->device);
+    auto* m = new cldnn_b200_mem_impl();
+    m->ctx = c; m->bytes = bytes;
+    size_t padded = (bytes + 255) & ~size_t(255);
+    if (padded == 0) padded = 256;
+    cudaError_t e = cudaMalloc(&m->dev, padded);
+    if (e != cudaSuccess) { delete m; return cuda_fail(e, "cudaMalloc"); }
+    e = cudaMemsetAsync(m->dev, 0, padded, c->stream);      // gpu_buffer zero-fills (memory_gpu.cpp:47-50)
+    if (e != cudaSuccess) { cudaFree(m->dev); delete m; return cuda_fail(e, "cudaMemsetAsync"); }
+    *out = m;
+    return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+
+int32_t cldnn_b200_mem_free(cldnn_b200_mem m)
+{
+    if (!m) return CLDNN_B200_SUCCESS;
+    DeviceGuard g(m->ctx->device);
+    (void)cudaStreamSynchronize(m->ctx->stream);
+    if (m->mapped) (void)cudaFreeHost(m->mapped);
+    (void)cudaFree(m->dev);
+    delete m;
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_size(cldnn_b200_mem m, size_t* bytes)
+{
+    if (!m || !bytes) return fail(CLDNN_B200_INVALID_ARG, "mem_size: null argument");
+    *bytes = m->bytes; return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_devptr(cldnn_b200_mem m, void** dev)
+{
+    if (!m || !dev) return fail(CLDNN_B200_INVALID_ARG, "mem_devptr: null argument");
+    *dev = m->dev; return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_map(cldnn_b200_mem m, void** host)
+{
+    if (!m || !host) return fail(CLDNN_B200_INVALID_ARG, "mem_map: null argument");
+    DeviceGuard g(m->ctx->device);
+    if (m->map_count == 0) {
+        B200_CUDA(cudaMallocHost(&m->mapped, m->bytes ? m->bytes : 1));
+        cudaError_t e = cudaMemcpyAsync(m->mapped, m->dev, m->bytes, cudaMemcpyDeviceToHost, m->ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(m->ctx->stream);
+        if (e != cudaSuccess) { cudaFreeHost(m->mapped); m->mapped = nullptr; return cuda_fail(e, "map copy"); }
+    }
+    ++m->map_count;
+    *host = m->mapped;
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_unmap(cldnn_b200_mem m)
+{
+    if (!m) return fail(CLDNN_B200_INVALID_ARG, "mem_unmap: null mem");
+    if (m->map_count == 0) return fail(CLDNN_B200_ERROR, "mem_unmap: memory is not mapped");
+    if (--m->map_count == 0) {
+        DeviceGuard g(m->ctx->device);
+        cudaError_t e = cudaMemcpyAsync(m->dev, m->mapped, m->bytes, cudaMemcpyHostToDevice, m->ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(m->ctx->stream);
+        (void)cudaFreeHost(m->mapped); m->mapped = nullptr;
+        if (e != cudaSuccess) return cuda_fail(e, "unmap copy");
+    }
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_fill(cldnn_b200_mem m, uint8_t pattern)
+{
+    if (!m) return fail(CLDNN_B200_INVALID_ARG, "mem_fill: null mem");
+    DeviceGuard g(m->ctx->device);
+    B200_CUDA(cudaMemsetAsync(m->dev, pattern, m->bytes, m->ctx->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+static int32_t check_range(cldnn_b200_mem m, size_t offset, size_t bytes, const void* host, const char* who)
+{
+    if (!m || (!host && bytes)) return fail(CLDNN_B200_INVALID_ARG, std::string(who) + ": null argument");
+    if (offset > m->bytes || bytes > m->bytes - offset) return fail(CLDNN_B200_INVALID_ARG, std::string(who) + ": range exceeds the memory object");
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_write(cldnn_b200_mem m, size_t offset, const void* host, size_t bytes)
+{
+    int32_t st = check_range(m, offset, bytes, host, "mem_write"); if (st) return st;
+    DeviceGuard g(m->ctx->device);
+    B200_CUDA(cudaMemcpyAsync((char*)m->dev + offset, host, bytes, cudaMemcpyHostToDevice, m->ctx->stream));
+    B200_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_read(cldnn_b200_mem m, size_t offset, void* host, size_t bytes)
+{
+    int32_t st = check_range(m, offset, bytes, host, "mem_read"); if (st) return st;
+    DeviceGuard g(m->ctx->device);
+    B200_CUDA(cudaMemcpyAsync(host, (char*)m->dev + offset, bytes, cudaMemcpyDeviceToHost, m->ctx->stream));
+    B200_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_write_async(cldnn_b200_mem m, size_t offset, const void* host, size_t bytes)
+{
+    int32_t st = check_range(m, offset, bytes, host, "mem_write_async"); if (st) return st;
+    DeviceGuard g(m->ctx->device);
+    B200_CUDA(cudaMemcpyAsync((char*)m->dev + offset, host, bytes, cudaMemcpyHostToDevice, m->ctx->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_mem_read_async(cldnn_b200_mem m, size_t offset, void* host, size_t bytes)
+{
+    int32_t st = check_range(m, offset, bytes, host, "mem_read_async"); if (st) return st;
+    DeviceGuard g(m->ctx->device);
+    B200_CUDA(cudaMemcpyAsync(host, (char*)m->dev + offset, bytes, cudaMemcpyDeviceToHost, m->ctx->stream));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_host_alloc(size_t bytes, void** host)
+{
+    if (!host) return fail(CLDNN_B200_INVALID_ARG, "host_alloc: null out");
+    B200_CUDA(cudaMallocHost(host, bytes ? bytes : 1));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_host_free(void* host)
+{
+    if (host) B200_CUDA(cudaFreeHost(host));
+    return CLDNN_B200_SUCCESS;
+}
+
+// ---- events -----------------------------------------------------------------------
+int32_t cldnn_b200_event_create(cldnn_b200_ctx c, cldnn_b200_event* out)
+{
+    B200_TRY
+    if (!c || !out) return fail(CLDNN_B200_INVALID_ARG, "event_create: null argument");
+    DeviceGuard g(c->device);
+    auto* e = new cldnn_b200_event_impl(); e->ctx = c;
+    cudaError_t ce = cudaEventCreate(&e->ev);
+    if (ce != cudaSuccess) { delete e; return cuda_fail(ce, "cudaEventCreate"); }
+    *out = e; return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+int32_t cldnn_b200_event_record(cldnn_b200_event e)
+{
+    if (!e) return fail(CLDNN_B200_INVALID_ARG, "event_record: null event");
+    DeviceGuard g(e->ctx->device);
+    B200_CUDA(cudaEventRecord(e->ev, e->ctx->stream)); return CLDNN_B200_SUCCESS;
+}
+int32_t cldnn_b200_event_wait(cldnn_b200_event e)
+{
+    if (!e) return fail(CLDNN_B200_INVALID_ARG, "event_wait: null event");
+    B200_CUDA(cudaEventSynchronize(e->ev)); return CLDNN_B200_SUCCESS;
+}
+int32_t cldnn_b200_event_query(cldnn_b200_event e, int32_t* is_set)
+{
+    if (!e || !is_set) return fail(CLDNN_B200_INVALID_ARG, "event_query: null argument");
+    cudaError_t ce = cudaEventQuery(e->ev);
+    if (ce == cudaSuccess) { *is_set = 1; return CLDNN_B200_SUCCESS; }
+    if (ce == cudaErrorNotReady) { (void)cudaGetLastError(); *is_set = 0; return CLDNN_B200_SUCCESS; }
+    return cuda_fail(ce, "cudaEventQuery");
+}
+int32_t cldnn_b200_event_elapsed_ns(cldnn_b200_event a, cldnn_b200_event b, uint64_t* ns)
+{
+    if (!a || !b || !ns) return fail(CLDNN_B200_INVALID_ARG, "event_elapsed_ns: null argument");
+    float ms = 0.f; B200_CUDA(cudaEventElapsedTime(&ms, a->ev, b->ev));
+    *ns = (uint64_t)((double)ms * 1e6); return CLDNN_B200_SUCCESS;
+}
+int32_t cldnn_b200_event_destroy(cldnn_b200_event e)
+{
+    if (!e) return CLDNN_B200_SUCCESS;
+    (void)cudaEventDestroy(e->ev); delete e; return CLDNN_B200_SUCCESS;
+}
+
+// ---- kernels ------------------------------------------------------------------------
+int32_t cldnn_b200_kernel_count(void) { return g_kernel_count; }
+const char* cldnn_b200_kernel_name(int32_t i) { return (i >= 0 && i < g_kernel_count) ? g_kernels[i]->name : nullptr; }
+
+int32_t cldnn_b200_kernel_lookup(cldnn_b200_ctx c, const char* name, cldnn_b200_kernel* out)
+{
+    B200_TRY
+    if (!c || !name || !out) return fail(CLDNN_B200_INVALID_ARG, "kernel_lookup: null argument");
+    *out = nullptr;
+    for (int i = 0; i < g_kernel_count; ++i)
+        if (std::strcmp(g_kernels[i]->name, name) == 0) {
+            auto* k = new cldnn_b200_kernel_impl(); k->ctx = c; k->def = g_kernels[i];
+            *out = k; return CLDNN_B200_SUCCESS;
+        }
+    return fail(CLDNN_B200_ERROR, std::string("kernel_lookup: no kernel named '") + name + "'");
+    B200_CATCH
+}
+
+static int32_t check_params(cldnn_b200_kernel k, const void* params, size_t size, const char* who)
+{
+    if (!k || !params) return fail(CLDNN_B200_INVALID_ARG, std::string(who) + ": null argument");
+    if (size != k->def->params_size)
+        return fail(CLDNN_B200_INVALID_ARG, std::string(who) + ": parameter block of " + std::to_string(size) + " bytes, kernel '" +
+                    k->def->name + "' expects " + std::to_string(k->def->params_size));
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_kernel_supports(cldnn_b200_kernel k, const void* params, size_t size, int32_t* yes)
+{
+    int32_t st = check_params(k, params, size, "kernel_supports"); if (st) return st;
+    if (!yes) return fail(CLDNN_B200_INVALID_ARG, "kernel_supports: null out");
+    *yes = k->def->supports(params) ? 1 : 0; return CLDNN_B200_SUCCESS;
+}
+int32_t cldnn_b200_kernel_tune_count(cldnn_b200_kernel k, const void* params, size_t size, int32_t* count)
+{
+    int32_t st = check_params(k, params, size, "kernel_tune_count"); if (st) return st;
+    if (!count) return fail(CLDNN_B200_INVALID_ARG, "kernel_tune_count: null out");
+    *count = k->def->supports(params) ? k->def->tune_count(params) : 0; return CLDNN_B200_SUCCESS;
+}
+int32_t cldnn_b200_kernel_scratch_bytes(cldnn_b200_kernel k, const void* params, size_t size, size_t* bytes)
+{
+    int32_t st = check_params(k, params, size, "kernel_scratch_bytes"); if (st) return st;
+    if (!bytes) return fail(CLDNN_B200_INVALID_ARG, "kernel_scratch_bytes: null out");
+    *bytes = k->def->scratch_bytes ? k->def->scratch_bytes(params) : 0; return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_prepare(cldnn_b200_kernel k, const void* params, size_t size, const cldnn_b200_args* args, cldnn_b200_prepared* out)
+{
+    B200_TRY
+    int32_t st = check_params(k, params, size, "prepare"); if (st) return st;
+    if (!args || !out) return fail(CLDNN_B200_INVALID_ARG, "prepare: null argument");
+    *out = nullptr;
+    if (!k->def->supports(params))
+        return fail(CLDNN_B200_UNSUPPORTED_FORMAT, std::string("prepare: kernel '") + k->def->name + "' does not support these parameters");
+    DeviceGuard g(k->ctx->device);
+    auto* p = new cldnn_b200_prepared_impl(); p->ctx = k->ctx;
+    st = k->def->prepare(k->ctx, params, args, p);
+    if (st != CLDNN_B200_SUCCESS) { delete p; return st; }
+    *out = p; return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+
+int32_t cldnn_b200_run(cldnn_b200_prepared p)
+{
+    if (!p) return fail(CLDNN_B200_INVALID_ARG, "run: null prepared launch");
+    DeviceGuard g(p->ctx->device);
+    cudaError_t e = p->fn(p->ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(e, "kernel launch");
+    p->ctx->launches += (uint64_t)p->launches;
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_prepared_destroy(cldnn_b200_prepared p) { delete p; return CLDNN_B200_SUCCESS; }
+
+int32_t cldnn_b200_launch(cldnn_b200_kernel k, const void* params, size_t size, const cldnn_b200_args* args)
+{
+    cldnn_b200_prepared p = nullptr;
+    int32_t st = cldnn_b200_prepare(k, params, size, args, &p); if (st) return st;
+    st = cldnn_b200_run(p);
+    cldnn_b200_prepared_destroy(p);
+    return st;
+}
+
+int32_t cldnn_b200_time(cldnn_b200_prepared p, int32_t warmup, int32_t runs, uint64_t* avg_ns)
+{
+    if (!p || !avg_ns || runs <= 0) return fail(CLDNN_B200_INVALID_ARG, "time: bad argument");
+    DeviceGuard g(p->ctx->device);
+    cudaEvent_t a, b;
+    B200_CUDA(cudaEventCreate(&a)); B200_CUDA(cudaEventCreate(&b));
+    cudaError_t e = cudaSuccess;
+    for (int i = 0; i < warmup && e == cudaSuccess; ++i) e = p->fn(p->ctx->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(a, p->ctx->stream);
+    for (int i = 0; i < runs && e == cudaSuccess; ++i) e = p->fn(p->ctx->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(b, p->ctx->stream);
+    if (e == cudaSuccess) e = cudaEventSynchronize(b);
+    float ms = 0.f;
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, a, b);
+    cudaEventDestroy(a); cudaEventDestroy(b);
+    if (e != cudaSuccess) return cuda_fail(e, "time");
+    p->ctx->launches += (uint64_t)p->launches * (uint64_t)(warmup + runs);
+    *avg_ns = (uint64_t)((double)ms * 1e6 / runs);
+    return CLDNN_B200_SUCCESS;
+}
+
+}  // extern "C"

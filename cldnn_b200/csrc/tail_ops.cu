@@ -1,0 +1,426 @@
+// The bandwidth-bound tail of the convolution path: pooling, fully_connected
+// (reference order), softmax, eltwise, reorder, lrn and standalone activation.
+// The *_ref kernels take any layout through pitches; pooling_i8_byxf is the
+// feature-innermost fast path with 16-byte accesses per lane.
+#include "engine.hpp"
+
+namespace b200 {
+
+static inline int grid_for(int64_t total, int threads, const cldnn_b200_ctx_impl* ctx)
+{
+    int64_t blocks = (total + threads - 1) / threads;
+    const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 16;
+    if (blocks > cap) blocks = cap;
+    return blocks < 1 ? 1 : (int)blocks;
+}
+
+// ---------------------------------------------------------------------------------
+// pooling, any layout.  int8: cl_kernels/pooling_gpu_int8_ref.cl:35-131;
+// float: cl_kernels/pooling_gpu_ref.cl:36-201.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pool_divisor(const cldnn_b200_pool_params& p, int ox, int oy, uint32_t n)
+{
+    if (p.div_mode == CLDNN_B200_DIV_DYNAMIC) return n ? n : 1u;
+    if (p.div_mode == CLDNN_B200_DIV_DYNAMIC_WITH_PADDING) {
+        const int hend = min(oy + p.size_y, p.in.y + p.pad_y), wend = min(ox + p.size_x, p.in.x + p.pad_x);
+        const uint32_t d = (uint32_t)((hend - oy) * (wend - ox));
+        return d ? d : 1u;
+    }
+    return (uint32_t)(p.size_x * p.size_y);
+}
+
+__global__ void __launch_bounds__(256)
+pooling_ref_kernel(const __grid_constant__ cldnn_b200_pool_params p, const void* in, void* out)
+{
+    const int64_t total = (int64_t)p.out.b * p.out.f * p.out.y * p.out.x;
+    const bool int_in = is_int8(p.in.dtype);
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int x = (int)(idx % p.out.x); int64_t t = idx / p.out.x;
+        int y = (int)(t % p.out.y); t /= p.out.y;
+        int f = (int)(t % p.out.f); int b = (int)(t / p.out.f);
+        const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
+        if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
+        int32_t ri = p.mode == CLDNN_B200_POOL_MAX ? -128 : 0;
+        float rf = p.mode == CLDNN_B200_POOL_MAX ? (p.in.dtype == CLDNN_B200_F16 ? -65504.0f : -3.402823466e38f) : 0.0f;
+        uint32_t n = 0;
+        for (int j = 0; j < p.size_y; ++j) {
+            const int iy = oy + j; if (iy < 0 || iy >= p.in.y) continue;
+            for (int i = 0; i < p.size_x; ++i) {
+                const int ix = ox + i; if (ix < 0 || ix >= p.in.x) continue;
+                const int64_t ii = tidx(p.in, b, f, iy, ix);
+                if (int_in) { const int32_t v = load_as_int(in, p.in.dtype, ii); ri = p.mode == CLDNN_B200_POOL_MAX ? max(ri, v) : ri + v; }
+                else { const float v = load_as_float(in, p.in.dtype, ii); rf = p.mode == CLDNN_B200_POOL_MAX ? fmaxf(rf, v) : __fadd_rn(rf, v); }
+                ++n;
+            }
+        }
+        const uint32_t div = pool_divisor(p, ox, oy, n);
+        const int64_t oi = tidx(p.out, b, f, y, x);
+        if (int_in) {
+            if (p.mode == CLDNN_B200_POOL_AVG) ri = (int32_t)round_half_away(__fdiv_rn((float)ri, (float)div));
+            if (p.out.dtype == CLDNN_B200_U8) ((uint8_t*)out)[oi] = (uint8_t)act_int(p.act, (int32_t)(uint8_t)ri, p.act_m, p.act_n);
+            else if (p.out.dtype == CLDNN_B200_I8) ((int8_t*)out)[oi] = (int8_t)act_int(p.act, (int32_t)(int8_t)ri, p.act_m, p.act_n);
+            else store_sat_int(out, p.out.dtype, oi, act_int(p.act, ri, p.act_m, p.act_n));
+        } else {
+            if (p.mode == CLDNN_B200_POOL_AVG) rf = __fdiv_rn(rf, (float)div);
+            store_sat_float(out, p.out.dtype, oi, act_float(p.act, rf, p.act_m, p.act_n));
+        }
+    }
+}
+
+static bool pooling_ref_supports(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_pool_params*)vp;
+    return p.size_x >= 1 && p.size_y >= 1 && p.stride_x >= 1 && p.stride_y >= 1 && p.in.f == p.out.f && p.in.b == p.out.b;
+}
+static int one_tune(const void*) { return 1; }
+
+static int32_t pooling_ref_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_pool_params p = *(const cldnn_b200_pool_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "pooling_ref: input and output are required");
+    const void* in = a->input0; void* o = a->output;
+    const int grid = grid_for((int64_t)p.out.b * p.out.f * p.out.y * p.out.x, 256, ctx);
+    out->fn = [p, in, o, grid](cudaStream_t s) { pooling_ref_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_pooling_ref = {"pooling_ref", sizeof(cldnn_b200_pool_params), pooling_ref_supports, one_tune, nullptr, pooling_ref_prepare};
+
+// ---------------------------------------------------------------------------------
+// pooling, 8-bit, feature-innermost (byxf) fast path: each thread owns 16
+// consecutive features of one output pixel and moves them with one 128-bit
+// load per window tap and one 128-bit store.  Same arithmetic as
+// pooling_gpu_int8_ref.cl.
+// ---------------------------------------------------------------------------------
+template <bool kUnsigned>
+__device__ __forceinline__ void unpack16(const uint4& v, int32_t (&e)[16])
+{
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t byte = (w[i >> 2] >> ((i & 3) * 8)) & 0xffu;
+        e[i] = kUnsigned ? (int32_t)byte : (int32_t)(int8_t)byte;
+    }
+}
+
+template <bool kUnsignedIn>
+__global__ void __launch_bounds__(256)
+pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const uint8_t* __restrict__ in, uint8_t* __restrict__ out)
+{
+    const int fv = p.in.f / 16;
+    const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int f16 = (int)(idx % fv); int64_t t = idx / fv;
+        const int x = (int)(t % p.out.x); t /= p.out.x;
+        const int y = (int)(t % p.out.y); const int b = (int)(t / p.out.y);
+        const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
+        if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
+        int32_t r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = p.mode == CLDNN_B200_POOL_MAX ? -128 : 0;
+        uint32_t n = 0;
+        for (int j = 0; j < p.size_y; ++j) {
+            const int iy = oy + j; if (iy < 0 || iy >= p.in.y) continue;
+            for (int i = 0; i < p.size_x; ++i) {
+                const int ix = ox + i; if (ix < 0 || ix >= p.in.x) continue;
+                const uint4 v = __ldg((const uint4*)(in + tidx(p.in, b, f16 * 16, iy, ix)));
+                int32_t e[16]; unpack16<kUnsignedIn>(v, e);
+#pragma unroll
+                for (int k = 0; k < 16; ++k) r[k] = p.mode == CLDNN_B200_POOL_MAX ? max(r[k], e[k]) : r[k] + e[k];
+                ++n;
+            }
+        }
+        const float div = (float)pool_divisor(p, ox, oy, n);
+        uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            int32_t v = r[k];
+            if (p.mode == CLDNN_B200_POOL_AVG) v = (int32_t)round_half_away(__fdiv_rn((float)v, div));
+            // convert_char / convert_uchar wrap, then the activation runs on the 8-bit value
+            v = p.out.dtype == CLDNN_B200_U8 ? (int32_t)(uint8_t)v : (int32_t)(int8_t)v;
+            v = act_int(p.act, v, p.act_m, p.act_n);
+            w[k >> 2] |= ((uint32_t)v & 0xffu) << ((k & 3) * 8);
+        }
+        *(uint4*)(out + tidx(p.out, b, f16 * 16, y, x)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+static bool pooling_i8_byxf_supports(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_pool_params*)vp;
+    if (!pooling_ref_supports(vp)) return false;
+    if (!is_int8(p.in.dtype) || !is_int8(p.out.dtype)) return false;
+    if (p.in.pf != 1 || p.out.pf != 1 || p.in.f % 16) return false;
+    const int64_t pitches[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
+    for (int64_t v : pitches) if (v % 16) return false;
+    return true;
+}
+
+static int32_t pooling_i8_byxf_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_pool_params p = *(const cldnn_b200_pool_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "pooling_i8_byxf: input and output are required");
+    if (((uintptr_t)a->input0 | (uintptr_t)a->output) & 15) return fail(CLDNN_B200_INVALID_ARG, "pooling_i8_byxf: buffers must be 16-byte aligned");
+    const uint8_t* in = (const uint8_t*)a->input0; uint8_t* o = (uint8_t*)a->output;
+    const int grid = grid_for((int64_t)p.out.b * p.out.y * p.out.x * (p.in.f / 16), 256, ctx);
+    const bool uns = p.in.dtype == CLDNN_B200_U8;
+    out->fn = [p, in, o, grid, uns](cudaStream_t s) {
+        if (uns) pooling_i8_byxf_kernel<true><<<grid, 256, 0, s>>>(p, in, o);
+        else pooling_i8_byxf_kernel<false><<<grid, 256, 0, s>>>(p, in, o);
+        return cudaGetLastError();
+    };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_pooling_i8_byxf = {"pooling_i8_byxf", sizeof(cldnn_b200_pool_params), pooling_i8_byxf_supports, one_tune, nullptr, pooling_i8_byxf_prepare};
+
+// ---------------------------------------------------------------------------------
+// fully_connected in the reference's order (cl_kernels/fully_connected_gpu_bfyx_ref.cl:18-84):
+// one warp per output, lanes stride the reduction, shuffle-reduce (integer sums
+// are order-independent; float sums are tolerance-checked).
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+fc_ref_kernel(const __grid_constant__ cldnn_b200_fc_params p, const void* in, const void* w, const void* bias,
+              const float* quant, const float* calib, void* out)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t total = (int64_t)p.out.b * p.out.f;
+    const int K = p.in.f * p.in.y * p.in.x;
+    for (int64_t bo = warp; bo < total; bo += nwarps) {
+        const int b = (int)(bo / p.out.f), o = (int)(bo % p.out.f);
+        int32_t acc_i = 0; float acc_f = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const int x = k % p.in.x, y = (k / p.in.x) % p.in.y, f = k / (p.in.x * p.in.y);
+            const int64_t ii = tidx(p.in, b, f, y, x);
+            const int64_t wi = p.w_offset + (int64_t)o * p.w_po + (int64_t)f * p.w_pi + (int64_t)y * p.w_py + (int64_t)x * p.w_px;
+            if (p.quantization) acc_i += load_as_int(in, p.in.dtype, ii) * load_as_int(w, p.w_dtype, wi);
+            else acc_f += load_as_float(in, p.in.dtype, ii) * load_as_float(w, p.w_dtype, wi);
+        }
+#pragma unroll
+        for (int s = 16; s; s >>= 1) { acc_i += __shfl_xor_sync(0xffffffffu, acc_i, s); acc_f += __shfl_xor_sync(0xffffffffu, acc_f, s); }
+        if (lane) continue;
+        const int64_t oi = tidx(p.out, b, o, 0, 0);
+        if (p.quantization) {
+            int32_t r = acc_i;
+            if (p.bias_dtype != CLDNN_B200_NONE) {
+                float t = __fmul_rn(__fmul_rn((float)acc_i, quant[o]), p.i_qf);
+                t = __fadd_rn(t, load_as_float(bias, p.bias_dtype, o));
+                t = __fmul_rn(t, p.calibration ? calib[o] : p.o_qf);
+                r = sat_i32_from_float(round_half_away(t), -128, 127);
+            } else r = min(127, max(-128, r));
+            store_sat_int(out, p.out.dtype, oi, act_int(p.act, r, p.act_m, p.act_n));
+        } else {
+            float v = acc_f;
+            if (p.bias_dtype != CLDNN_B200_NONE) v += load_as_float(bias, p.bias_dtype, o);
+            store_sat_float(out, p.out.dtype, oi, act_float(p.act, v, p.act_m, p.act_n));
+        }
+    }
+}
+static bool fc_ref_supports(const void* vp) { const auto& p = *(const cldnn_b200_fc_params*)vp; return p.in.b == p.out.b && p.out.f >= 1; }
+static int32_t fc_ref_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_fc_params p = *(const cldnn_b200_fc_params*)vp;
+    if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "fc_ref: input, output and weights are required");
+    if (p.quantization && p.bias_dtype != CLDNN_B200_NONE && !a->weights_quantization_factors) return fail(CLDNN_B200_INVALID_ARG, "fc_ref: quantization factors missing");
+    if (p.calibration && !a->output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "fc_ref: calibration factors missing");
+    const void* in = a->input0; const void* w = a->weights; const void* bias = a->bias; void* o = a->output;
+    const float* q = a->weights_quantization_factors; const float* c = a->output_calibration_factors;
+    const int grid = grid_for((int64_t)p.out.b * p.out.f * 32, 256, ctx);
+    out->fn = [=](cudaStream_t s) { fc_ref_kernel<<<grid, 256, 0, s>>>(p, in, w, bias, q, c, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_fc_ref = {"fc_ref", sizeof(cldnn_b200_fc_params), fc_ref_supports, one_tune, nullptr, fc_ref_prepare};
+
+// ---------------------------------------------------------------------------------
+// softmax over features (cl_kernels/softmax_gpu_ref.cl:22-58): one warp per
+// (b, y, x) row; max, sum and normalise with warp shuffles, float accumulation.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+softmax_kernel(const __grid_constant__ cldnn_b200_softmax_params p, const void* in, void* out)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t rows = (int64_t)p.in.b * p.in.y * p.in.x;
+    for (int64_t r = warp; r < rows; r += nwarps) {
+        const int x = (int)(r % p.in.x), y = (int)((r / p.in.x) % p.in.y), b = (int)(r / ((int64_t)p.in.x * p.in.y));
+        float mx = -3.402823466e38f;
+        for (int f = lane; f < p.in.f; f += 32) mx = fmaxf(mx, load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)));
+#pragma unroll
+        for (int s = 16; s; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        float den = 0.f;
+        for (int f = lane; f < p.in.f; f += 32) den += expf(load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)) - mx);
+#pragma unroll
+        for (int s = 16; s; s >>= 1) den += __shfl_xor_sync(0xffffffffu, den, s);
+        for (int f = lane; f < p.in.f; f += 32) {
+            const float e = expf(load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)) - mx);
+            store_sat_float(out, p.out.dtype, tidx(p.out, b, f, y, x), __fdiv_rn(e, den));
+        }
+    }
+}
+static bool softmax_supports(const void* vp) { const auto& p = *(const cldnn_b200_softmax_params*)vp; return is_fp(p.in.dtype) && is_fp(p.out.dtype) && p.in.f == p.out.f; }
+static int32_t softmax_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_softmax_params p = *(const cldnn_b200_softmax_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "softmax: input and output are required");
+    const void* in = a->input0; void* o = a->output;
+    const int grid = grid_for((int64_t)p.in.b * p.in.y * p.in.x * 32, 256, ctx);
+    out->fn = [=](cudaStream_t s) { softmax_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_softmax = {"softmax", sizeof(cldnn_b200_softmax_params), softmax_supports, one_tune, nullptr, softmax_prepare};
+
+// ---------------------------------------------------------------------------------
+// eltwise (cl_kernels/generic_eltwise_ref.cl:198-330)
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+eltwise_ref_kernel(const __grid_constant__ cldnn_b200_eltwise_params p, const void* in0, const void* in1, const float* calib, void* out)
+{
+    const int64_t total = (int64_t)p.out.b * p.out.f * p.out.y * p.out.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        // iterate in the output's memory order of its innermost axis
+        int b, f, y, x;
+        if (p.out.pf == 1) { f = (int)(idx % p.out.f); int64_t t = idx / p.out.f; x = (int)(t % p.out.x); t /= p.out.x; y = (int)(t % p.out.y); b = (int)(t / p.out.y); }
+        else { x = (int)(idx % p.out.x); int64_t t = idx / p.out.x; y = (int)(t % p.out.y); t /= p.out.y; f = (int)(t % p.out.f); b = (int)(t / p.out.f); }
+        const int64_t i0 = tidx(p.in0, b % p.in0.b, f % p.in0.f, ((int64_t)y * p.stride_y0) % p.in0.y, ((int64_t)x * p.stride_x0) % p.in0.x);
+        const int64_t i1 = tidx(p.in1, b % p.in1.b, f % p.in1.f, ((int64_t)y * p.stride_y1) % p.in1.y, ((int64_t)x * p.stride_x1) % p.in1.x);
+        const int64_t oi = tidx(p.out, b, f, y, x);
+        if (p.quantization) {
+            const int32_t a = load_as_int(in0, p.in0.dtype, i0), c = load_as_int(in1, p.in1.dtype, i1);
+            int32_t r;
+            switch (p.mode) {
+            case CLDNN_B200_ELTW_SUB: r = a - c; break;
+            case CLDNN_B200_ELTW_MAX: r = max(a, c); break;
+            case CLDNN_B200_ELTW_MIN: r = min(a, c); break;
+            case CLDNN_B200_ELTW_PROD: r = a * c; break;
+            default: r = a + c; break;
+            }
+            r = sat_i32_from_float(round_half_away(__fmul_rn((float)r, p.calibration ? calib[f] : p.o_qf)), -128, 127);
+            store_sat_int(out, p.out.dtype, oi, act_int(p.act, r, p.act_m, p.act_n));
+            continue;
+        }
+        const float a = load_as_float(in0, p.in0.dtype, i0), c = load_as_float(in1, p.in1.dtype, i1);
+        float r;
+        switch (p.mode) {
+        case CLDNN_B200_ELTW_SUB: r = __fsub_rn(a, c); break;
+        case CLDNN_B200_ELTW_MAX: r = fmaxf(a, c); break;
+        case CLDNN_B200_ELTW_MIN: r = fminf(a, c); break;
+        case CLDNN_B200_ELTW_PROD: r = __fmul_rn(a, c); break;
+        default: r = __fadd_rn(a, c); break;
+        }
+        if (is_fp(p.out.dtype)) store_sat_float(out, p.out.dtype, oi, act_float(p.act, r, p.act_m, p.act_n));
+        else store_sat_int(out, p.out.dtype, oi, act_int(p.act, (int32_t)r, p.act_m, p.act_n));
+    }
+}
+static bool eltwise_supports(const void* vp) { const auto& p = *(const cldnn_b200_eltwise_params*)vp; return p.stride_x0 >= 1 && p.stride_y0 >= 1 && p.stride_x1 >= 1 && p.stride_y1 >= 1; }
+static int32_t eltwise_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_eltwise_params p = *(const cldnn_b200_eltwise_params*)vp;
+    if (!a->input0 || !a->input1 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "eltwise_ref: two inputs and an output are required");
+    if (p.quantization && p.calibration && !a->output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "eltwise_ref: calibration factors missing");
+    const void* i0 = a->input0; const void* i1 = a->input1; void* o = a->output; const float* c = a->output_calibration_factors;
+    const int grid = grid_for((int64_t)p.out.b * p.out.f * p.out.y * p.out.x, 256, ctx);
+    out->fn = [=](cudaStream_t s) { eltwise_ref_kernel<<<grid, 256, 0, s>>>(p, i0, i1, c, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_eltwise_ref = {"eltwise_ref", sizeof(cldnn_b200_eltwise_params), eltwise_supports, one_tune, nullptr, eltwise_prepare};
+
+// ---------------------------------------------------------------------------------
+// reorder (cl_kernels/reorder_data.cl:72-128).  Threads walk the destination in
+// its own memory order so writes coalesce; a destination feature beyond the
+// source's feature count is written as zero (feature padding of the new layout).
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+reorder_ref_kernel(const __grid_constant__ cldnn_b200_reorder_params p, const void* in, void* out)
+{
+    const int64_t total = (int64_t)p.out.b * p.out.f * p.out.y * p.out.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int b, f, y, x;
+        if (p.out.pf == 1) { f = (int)(idx % p.out.f); int64_t t = idx / p.out.f; x = (int)(t % p.out.x); t /= p.out.x; y = (int)(t % p.out.y); b = (int)(t / p.out.y); }
+        else if (p.out.pb == 1) { b = (int)(idx % p.out.b); int64_t t = idx / p.out.b; f = (int)(t % p.out.f); t /= p.out.f; x = (int)(t % p.out.x); y = (int)(t / p.out.x); }
+        else { x = (int)(idx % p.out.x); int64_t t = idx / p.out.x; y = (int)(t % p.out.y); t /= p.out.y; f = (int)(t % p.out.f); b = (int)(t / p.out.f); }
+        const int64_t oi = tidx(p.out, b, f, y, x);
+        if (f >= p.in.f) { store_sat_int(out, p.out.dtype, oi, 0); continue; }
+        const int64_t ii = tidx(p.in, b, f, y, x);
+        if (!is_fp(p.in.dtype) && !p.has_mean) { store_sat_int(out, p.out.dtype, oi, load_as_int(in, p.in.dtype, ii)); continue; }
+        float v = load_as_float(in, p.in.dtype, ii);
+        if (p.has_mean) v = __fsub_rn(v, p.mean[f < 4 ? f : 3]);
+        store_sat_float(out, p.out.dtype, oi, v);
+    }
+}
+static bool reorder_supports(const void* vp) { const auto& p = *(const cldnn_b200_reorder_params*)vp; return p.in.b == p.out.b && p.in.y == p.out.y && p.in.x == p.out.x && p.out.f >= p.in.f; }
+static int32_t reorder_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_reorder_params p = *(const cldnn_b200_reorder_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "reorder_ref: input and output are required");
+    const void* in = a->input0; void* o = a->output;
+    const int grid = grid_for((int64_t)p.out.b * p.out.f * p.out.y * p.out.x, 256, ctx);
+    out->fn = [=](cudaStream_t s) { reorder_ref_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_reorder_ref = {"reorder_ref", sizeof(cldnn_b200_reorder_params), reorder_supports, one_tune, nullptr, reorder_prepare};
+
+// ---------------------------------------------------------------------------------
+// lrn across channels (cl_kernels/lrn_gpu_across_channel_ref.cl:26-66)
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+lrn_ref_kernel(const __grid_constant__ cldnn_b200_lrn_params p, const void* in, void* out)
+{
+    const int64_t total = (int64_t)p.in.b * p.in.f * p.in.y * p.in.x;
+    const int pad = (p.size - 1) / 2;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int x = (int)(idx % p.in.x); int64_t t = idx / p.in.x;
+        int y = (int)(t % p.in.y); t /= p.in.y;
+        int f = (int)(t % p.in.f); int b = (int)(t / p.in.f);
+        float acc = 0.f;
+        for (int i = 0; i < p.size; ++i) {
+            const int ff = f - pad + i; if (ff < 0 || ff >= p.in.f) continue;
+            const float v = load_as_float(in, p.in.dtype, tidx(p.in, b, ff, y, x));
+            acc = __fadd_rn(acc, __fmul_rn(v, v));
+        }
+        acc = __fadd_rn(__fmul_rn(acc, __fdiv_rn(p.alpha, (float)p.size)), p.k);
+        const float v = load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x));
+        store_sat_float(out, p.out.dtype, tidx(p.out, b, f, y, x), v * powf(acc, -p.beta));
+    }
+}
+static bool lrn_supports(const void* vp) { const auto& p = *(const cldnn_b200_lrn_params*)vp; return p.size >= 1 && is_fp(p.in.dtype); }
+static int32_t lrn_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_lrn_params p = *(const cldnn_b200_lrn_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "lrn_ref: input and output are required");
+    const void* in = a->input0; void* o = a->output;
+    const int grid = grid_for((int64_t)p.in.b * p.in.f * p.in.y * p.in.x, 256, ctx);
+    out->fn = [=](cudaStream_t s) { lrn_ref_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_lrn_ref = {"lrn_ref", sizeof(cldnn_b200_lrn_params), lrn_supports, one_tune, nullptr, lrn_prepare};
+
+// ---------------------------------------------------------------------------------
+// standalone activation (cl_kernels/activation_ref.cl)
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+activation_ref_kernel(const __grid_constant__ cldnn_b200_activation_params p, const void* in, void* out)
+{
+    const int64_t total = (int64_t)p.in.b * p.in.f * p.in.y * p.in.x;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        int x = (int)(idx % p.in.x); int64_t t = idx / p.in.x;
+        int y = (int)(t % p.in.y); t /= p.in.y;
+        int f = (int)(t % p.in.f); int b = (int)(t / p.in.f);
+        const int64_t ii = tidx(p.in, b, f, y, x), oi = tidx(p.out, b, f, y, x);
+        if (is_fp(p.in.dtype)) store_sat_float(out, p.out.dtype, oi, act_float(p.act, load_as_float(in, p.in.dtype, ii), p.act_m, p.act_n));
+        else store_sat_int(out, p.out.dtype, oi, act_int(p.act, load_as_int(in, p.in.dtype, ii), p.act_m, p.act_n));
+    }
+}
+static bool activation_supports(const void*) { return true; }
+static int32_t activation_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_activation_params p = *(const cldnn_b200_activation_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "activation_ref: input and output are required");
+    const void* in = a->input0; void* o = a->output;
+    const int grid = grid_for((int64_t)p.in.b * p.in.f * p.in.y * p.in.x, 256, ctx);
+    out->fn = [=](cudaStream_t s) { activation_ref_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_activation_ref = {"activation_ref", sizeof(cldnn_b200_activation_params), activation_supports, one_tune, nullptr, activation_prepare};
+
+}  // namespace b200

@@ -172,8 +172,8 @@ typedef struct cldnn_b200_softmax_params {
     int32_t reserved[4];
 } cldnn_b200_softmax_params;
 
-/* eltwise (sum / prod / max / min / sub) of two tensors with optional
- * per-feature calibration (cl_kernels/generic_eltwise_ref.cl). */
+/* eltwise (sum / prod / max / min / sub) of two tensors with the optional
+ * int8 requantisation epilogue (cl_kernels/generic_eltwise_ref.cl:198-330). */
 #define CLDNN_B200_ELTW_SUM 0
 #define CLDNN_B200_ELTW_SUB 1
 #define CLDNN_B200_ELTW_MAX 2
@@ -183,8 +183,9 @@ typedef struct cldnn_b200_eltwise_params {
     cldnn_b200_tensor in0, in1, out;
     int32_t mode;
     int32_t stride_x0, stride_y0, stride_x1, stride_y1;
-    int32_t calibration;         /* per-feature output calibration         */
-    int32_t has_o_qf; float o_qf;
+    int32_t quantization;        /* QUANTIZATION_TERM: int op, *factor, round, convert_char_sat */
+    int32_t calibration;         /* factor = calibrations[f], else o_qf    */
+    float   o_qf;
     int32_t act; float act_m, act_n;
     int32_t reserved[4];
 } cldnn_b200_eltwise_params;

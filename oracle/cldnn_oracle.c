@@ -466,10 +466,11 @@ int32_t oracle_softmax(const cldnn_b200_softmax_params* p, const void* in, void*
 }
 
 /*
- * eltwise.  cl_kernels/generic_eltwise_ref.cl with the int8 calibration
- * epilogue: res = op(in0, in1) computed in float for 8-bit inputs when a
- * calibration/quantisation factor is present (round + saturate), otherwise in
- * the widest input type.
+ * eltwise.  KERNEL(eltwise), cl_kernels/generic_eltwise_ref.cl:198-330 with the
+ * operation strings of actual_kernels/eltwise/eltwise_kernel_base.cpp:280-340.
+ * Quantised (:311-326): int op on the 8-bit inputs, (int)round((float)res *
+ * calibrations[f] | O_QF), convert_char_sat, then the activation on the 8-bit
+ * value.  Otherwise the op and the activation run in the unit type.
  */
 int32_t oracle_eltwise(const cldnn_b200_eltwise_params* p, const void* in0, const void* in1, const float* calib, void* out)
 {
@@ -477,10 +478,24 @@ int32_t oracle_eltwise(const cldnn_b200_eltwise_params* p, const void* in0, cons
         for (int f = 0; f < p->out.f; ++f)
             for (int y = 0; y < p->out.y; ++y)
                 for (int x = 0; x < p->out.x; ++x) {
-                    float a = (float)load_elem(in0, p->in0.dtype, tidx(&p->in0, b, f, (int64_t)y * p->stride_y0, (int64_t)x * p->stride_x0));
-                    float c = (float)load_elem(in1, p->in1.dtype, tidx(&p->in1, p->in1.b == 1 ? 0 : b, p->in1.f == 1 ? 0 : f,
-                                               p->in1.y == 1 ? 0 : (int64_t)y * p->stride_y1, p->in1.x == 1 ? 0 : (int64_t)x * p->stride_x1));
-                    float r;
+                    const int64_t i0 = tidx(&p->in0, b % p->in0.b, f % p->in0.f, ((int64_t)y * p->stride_y0) % p->in0.y, ((int64_t)x * p->stride_x0) % p->in0.x);
+                    const int64_t i1 = tidx(&p->in1, b % p->in1.b, f % p->in1.f, ((int64_t)y * p->stride_y1) % p->in1.y, ((int64_t)x * p->stride_x1) % p->in1.x);
+                    const int64_t oi = tidx(&p->out, b, f, y, x);
+                    if (p->quantization) {
+                        int32_t a = load_int(in0, p->in0.dtype, i0), c = load_int(in1, p->in1.dtype, i1), r;
+                        switch (p->mode) {
+                        case CLDNN_B200_ELTW_SUB: r = a - c; break;
+                        case CLDNN_B200_ELTW_MAX: r = a > c ? a : c; break;
+                        case CLDNN_B200_ELTW_MIN: r = a < c ? a : c; break;
+                        case CLDNN_B200_ELTW_PROD: r = a * c; break;
+                        default: r = a + c; break;
+                        }
+                        r = (int32_t)roundf((float)r * (p->calibration ? calib[f] : p->o_qf));
+                        int8_t q = (int8_t)sat_from_int(r, -128, 127);
+                        store_sat_int(out, p->out.dtype, oi, act_int(p->act, q, p->act_m, p->act_n));
+                        continue;
+                    }
+                    float a = (float)load_elem(in0, p->in0.dtype, i0), c = (float)load_elem(in1, p->in1.dtype, i1), r;
                     switch (p->mode) {
                     case CLDNN_B200_ELTW_SUB: r = a - c; break;
                     case CLDNN_B200_ELTW_MAX: r = fmaxf(a, c); break;
@@ -488,11 +503,8 @@ int32_t oracle_eltwise(const cldnn_b200_eltwise_params* p, const void* in0, cons
                     case CLDNN_B200_ELTW_PROD: r = a * c; break;
                     default: r = a + c; break;
                     }
-                    if (p->calibration) r = r * calib[f];
-                    else if (p->has_o_qf) r = r * p->o_qf;
-                    r = act_float(p->act, r, p->act_m, p->act_n);
-                    if (!is_fp(p->out.dtype)) r = roundf(r);
-                    store_sat_float(out, p->out.dtype, tidx(&p->out, b, f, y, x), r);
+                    if (is_fp(p->out.dtype)) store_sat_float(out, p->out.dtype, oi, act_float(p->act, r, p->act_m, p->act_n));
+                    else store_sat_int(out, p->out.dtype, oi, act_int(p->act, (int32_t)r, p->act_m, p->act_n));
                 }
     return CLDNN_B200_SUCCESS;
 }

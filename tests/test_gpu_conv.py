@@ -1,0 +1,149 @@
+"""Parity of the CUDA convolution kernels with the CPU oracle, through the C ABI.
+Integer outputs must be bit-exact."""
+import numpy as np
+import pytest
+
+import cases
+from cldnn_b200 import abi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from cldnn_b200 import engine
+    e = engine.Engine(0)
+    yield e
+    e.close()
+
+
+def _exact(eng, case, kernel, tune=0):
+    want = cases.run_oracle(case)
+    got = cases.run_gpu(eng, case, kernel, tune)
+    n = case.out_elems
+    if want.dtype.kind in "iu":
+        bad = np.flatnonzero(want[:n] != got[:n])
+        assert bad.size == 0, "%d of %d differ; first at %d: want %d got %d" % (bad.size, n, bad[0], want[bad[0]], got[bad[0]])
+    else:
+        np.testing.assert_allclose(got[:n], want[:n], rtol=1e-6, atol=1e-6)
+    return want
+
+
+GEOMS = {
+    # BASELINE config 1: N=1, C=128 -> K=128, 28x28, 3x3 stride 1 pad 1, u8 in, s8 out, ReLU
+    "config1": dict(N=1, C=128, K=128, H=28, W=28),
+    "1x1": dict(N=2, C=64, K=256, H=56, W=56, kh=1, kw=1, pad=0),
+    "1x1_stride2": dict(N=2, C=256, K=128, H=28, W=28, kh=1, kw=1, pad=0, stride=2),
+    "c64_56": dict(N=2, C=64, K=64, H=56, W=56),
+    "ragged_c32_k48": dict(N=3, C=32, K=48, H=9, W=11),
+    "c96_k40": dict(N=1, C=96, K=40, H=7, W=7),
+    "stride2_3x3": dict(N=2, C=64, K=64, H=15, W=15, stride=2),
+    "dilation2": dict(N=1, C=32, K=32, H=12, W=12, dil=2, pad=2),
+    "c512_7x7map": dict(N=4, C=512, K=512, H=7, W=7),
+    "5x5": dict(N=1, C=32, K=32, H=10, W=10, kh=5, kw=5, pad=2),
+    "1x1_map1": dict(N=5, C=2048, K=1000, H=1, W=1, kh=1, kw=1, pad=0),
+    "nopad": dict(N=1, C=32, K=32, H=6, W=6, pad=0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(GEOMS))
+def test_conv_ref_kernel_matches_oracle(eng, name):
+    _exact(eng, cases.make_conv_case(1, **GEOMS[name]), "conv_ref")
+
+
+@pytest.mark.parametrize("name", sorted(GEOMS))
+def test_conv_i8_tc_matches_oracle(eng, name):
+    case = cases.make_conv_case(2, **GEOMS[name])
+    k = eng.kernel("conv_i8_tc")
+    assert k.supports(case.p)
+    want = _exact(eng, case, "conv_i8_tc")
+    assert (want != 0).any() and (want != 127).any()      # the comparison is not on a saturated constant
+
+
+@pytest.mark.parametrize("name", sorted(GEOMS))
+def test_conv_i8_tc_every_tuning_variant(eng, name):
+    """All addressing modes (flat / TMA im2col / tiled box) and feature tiles give the same bits."""
+    k = eng.kernel("conv_i8_tc")
+    case = cases.make_conv_case(3, **GEOMS[name])
+    want = cases.run_oracle(case)
+    ran = 0
+    for tune in range(1, k.tune_count(case.p)):
+        p = cases.copy_params(case.p)
+        p.tune = tune
+        if not k.supports(p):
+            continue
+        got = cases.run_gpu(eng, case, "conv_i8_tc", tune)
+        assert np.array_equal(want[:case.out_elems], got[:case.out_elems]), "tune %d" % tune
+        ran += 1
+    assert ran >= 4
+
+
+EPILOGUES = {
+    "fused_residual_calibrated": dict(fused=True, out_dtype=np.uint8, eltw_calib=True, non_conv_scale=0.5),
+    "fused_residual_plain": dict(fused=True, out_dtype=np.uint8),
+    "fused_residual_in_place": dict(fused=True, out_dtype=np.uint8, in_out_opt=True),
+    "fused_i8_residual": dict(fused=True, out_dtype=np.int8, eltw_dtype=np.int8, non_conv_scale=1.0 / 3.0),
+    "float_bias_and_calibration": dict(bias="f32", calib=True),
+    "i8_in_float_out": dict(in_dtype=np.int8, out_dtype=np.float32),
+    "u8_out": dict(out_dtype=np.uint8),
+    "no_bias": dict(bias="none"),
+    "no_activation": dict(act=abi.ACT_NONE),
+    "relu6_clamp": dict(act=abi.ACT_CLAMP, scale_lo=2.0 ** -13, scale_hi=2.0 ** -12),
+    "leaky": dict(act=abi.ACT_RELU_NEGATIVE_SLOPE),
+    "o_qf": dict(o_qf=0.75),
+    "i_qf": dict(i_qf=0.5),
+    "int_domain_fused": dict(fused=True, quant=False, in_dtype=np.int8, out_dtype=np.uint8, eltw_dtype=np.int8,
+                             eltw_calib=True, w_range=2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(EPILOGUES))
+@pytest.mark.parametrize("kernel", ["conv_ref", "conv_i8_tc"])
+def test_epilogue_variants(eng, name, kernel):
+    kw = dict(EPILOGUES[name])
+    case = cases.make_conv_case(4, N=2, C=64, K=64, H=14, W=14, **kw)
+    if name == "leaky":
+        case.p.act_m = 0.125
+    assert eng.kernel(kernel).supports(case.p)
+    _exact(eng, case, kernel)
+
+
+def test_conv_ref_layouts_and_groups(eng):
+    _exact(eng, cases.make_conv_case(5, 1, 128, 128, 28, 28, fmt="bfyx", f_align=1), "conv_ref")
+    _exact(eng, cases.make_conv_case(6, 2, 16, 24, 9, 9, fmt="yxfb", f_align=1), "conv_ref")
+    _exact(eng, cases.make_conv_case(7, 2, 32, 32, 9, 9, fmt="bfyx", f_align=1, groups=32), "conv_ref")   # depthwise
+    _exact(eng, cases.make_conv_case(8, 2, 32, 64, 9, 9, fmt="bfyx", f_align=1, groups=4), "conv_ref")
+    _exact(eng, cases.make_conv_case(9, 1, 16, 16, 8, 8, in_dtype=np.float32, out_dtype=np.float32, bias="none",
+                                     quant=False, fmt="bfyx", f_align=1), "conv_ref")
+
+
+def test_reference_kats_on_gpu(eng):
+    """The reference's own literal quantised-convolution vectors through the CUDA reference-order kernel."""
+    from golden import kat_conv_quantized
+    from test_oracle_kat import build_kat_conv, _clamp_expected
+    from cldnn_b200 import engine as E
+    for name, case in kat_conv_quantized.CASES.items():
+        in_dt, out_dt = np.dtype(case["in_dtype"]), np.dtype(case["out_dtype"])
+        feats = case["features"]
+        p, inp, w, bias = build_kat_conv(feats, in_dt.type, out_dt.type)
+        p.quantization, p.act = 1, abi.ACT_RELU
+        quant = np.array([f[3] for f in feats], dtype=np.float32)
+        m = [eng.upload(a) for a in (inp.reshape(-1), w.reshape(-1), bias, quant)]
+        out = eng.alloc(len(feats) * 2 * out_dt.itemsize)
+        eng.kernel("conv_ref").launch(p, E.make_args(input0=m[0], weights=m[1], bias=m[2], quant=m[3], output=out))
+        got = out.read(out_dt).reshape(len(feats), 2)
+        pre = np.array([f[4] for f in feats])
+        if out_dt.kind in "iu":
+            np.testing.assert_array_equal(got.astype(np.int64), _clamp_expected(pre, out_dt).astype(np.int64), err_msg=name)
+        else:
+            np.testing.assert_allclose(got, _clamp_expected(pre, out_dt), atol=1e-3)
+
+
+def test_unsupported_parameters_are_refused_not_emulated(eng):
+    from cldnn_b200 import engine as E
+    case = cases.make_conv_case(10, 1, 16, 16, 8, 8, fmt="bfyx", f_align=1)     # bfyx is not a tensor-core layout
+    k = eng.kernel("conv_i8_tc")
+    assert not k.supports(case.p)
+    with pytest.raises(E.EngineError) as e:
+        cases.run_gpu(eng, case, "conv_i8_tc")
+    assert e.value.status == abi.UNSUPPORTED_FORMAT
