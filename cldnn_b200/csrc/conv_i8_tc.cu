@@ -15,9 +15,13 @@
 //   B (N x K): weights, oyxi (input features innermost), one TMA box per step.
 //   D        : s32 accumulators in tensor memory, two buffers so the epilogue of
 //              tile t overlaps the main loop of tile t+1.
-// One persistent CTA per SM: warp 0 issues TMA, warp 1 issues tcgen05.mma,
-// warps 2..5 run the epilogue (tcgen05.ld -> bias/dequant/ReLU/requant/round/
-// residual/saturate -> 16-byte stores).
+// One persistent CTA per SM: warp 0 issues TMA loads (operands and, for the
+// fused residual, the tile of the second input), warp 1 issues tcgen05.mma,
+// warps 2..9 run the epilogue: tcgen05.ld -> bias / dequantise / activation /
+// requantise / round / residual / saturate -> swizzled shared-memory tile ->
+// one TMA store per 128-byte column block (fully coalesced HBM writes).
+// Outputs that TMA cannot address (ragged pitches, float outputs, exotic
+// activations) take a direct-store epilogue instead.
 #include <cuda.h>
 #include <mutex>
 #include "engine.hpp"
@@ -28,7 +32,9 @@ namespace b200 {
 using namespace ptx;
 
 constexpr int kBM = 128;                 // pixels per tile = TMEM lanes
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;
 constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
@@ -36,8 +42,10 @@ constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, 
 enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
 
 struct alignas(64) TcParams {
-    CUtensorMap tmA;
-    CUtensorMap tmB;
+    CUtensorMap tmA;                     // activations
+    CUtensorMap tmB;                     // weights
+    CUtensorMap tmO;                     // output (staged epilogue)
+    CUtensorMap tmE;                     // residual input (staged epilogue, fused)
     int32_t a_mode;
     int32_t N, P, Q;                     // output batch, rows, columns
     int32_t kh, kw, stride_x, stride_y, pad_x, pad_y, dil_x, dil_y;
@@ -45,11 +53,15 @@ struct alignas(64) TcParams {
     int32_t bn, n_tiles, m_tiles, total_tiles;
     int64_t M_total;
     int32_t bw, bh, bb, tiles_w, tiles_h; // tiled mode: box of bw x bh x bb pixels
-    int32_t a_coord_stride_x, a_coord_stride_y; // tiled mode: input step per output step in tensor-map coordinates
     int32_t stages, a_stage_bytes, b_stage_bytes, a_tx_bytes, b_tx_bytes;
     uint32_t sbo, layout_type, idesc, tmem_cols;
     int32_t ofm;
-    // output / residual addressing, in elements
+    // epilogue
+    int32_t staged;                      // 1: shared-memory tile + TMA store, 0: direct stores
+    int32_t fast_epi;                    // quantised, 8-bit output and residual, simple activations
+    int32_t cw, col_blocks, sw_shift, sw_mask, stage_rows;   // staging tile: column block width, 16-byte chunk swizzle
+    int32_t mul_iqf, mul_oqf;
+    // output / residual addressing for the direct path, in elements
     int64_t out_px, out_py, out_pb, out_off;
     int64_t el_px, el_py, el_pb, el_off;
     int32_t el_sx, el_sy;
@@ -63,14 +75,16 @@ struct TcSmemAux {
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t res_full[2];                // residual tile landed in staging buffer
+    uint64_t stage_free[2];              // staging buffer read out by its TMA store
     uint64_t drain;
     uint32_t tmem_base;
     uint32_t abort;
-    int32_t bias_i[2][kMaxBN];
-    float bias_f[2][kMaxBN];
-    float quant[2][kMaxBN];
-    float calib[2][kMaxBN];
-    float ecal[2][kMaxBN];
+    alignas(16) int32_t bias_i[2][kMaxBN];
+    alignas(16) float bias_f[2][kMaxBN];
+    alignas(16) float quant[2][kMaxBN];
+    alignas(16) float calib[2][kMaxBN];
+    alignas(16) float ecal[2][kMaxBN];
 };
 
 __device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int& m_tile, int& n_tile)
@@ -96,6 +110,105 @@ __device__ __forceinline__ bool row_pixel(const TcParams& P, int m_tile, int row
     return m < P.M_total;
 }
 
+// The activations that are cheap enough to inline 32 times in the unrolled epilogue.
+__host__ __device__ inline bool act_is_simple(int32_t fn, float m)
+{
+    return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU || fn == CLDNN_B200_ACT_CLAMP ||
+           (fn == CLDNN_B200_ACT_RELU_NEGATIVE_SLOPE && m == m && m - m == 0.0f);
+}
+__device__ __forceinline__ float act_simple(int32_t fn, float x, float m, float n)
+{
+    if (fn == CLDNN_B200_ACT_RELU) return fmaxf(0.0f, x);
+    if (fn == CLDNN_B200_ACT_NONE) return x;
+    if (fn == CLDNN_B200_ACT_CLAMP) return fmaxf(m, fminf(n, x));
+    return __fadd_rn(fmaxf(x, 0.0f), __fmul_rn(m, fminf(x, 0.0f)));
+}
+
+// round(x) with ties away from zero, returned still as a float whose fraction is
+// not yet dropped: adding +-0.5 with round-toward-zero can never carry the sum
+// across the next integer, so truncating afterwards gives exactly round().
+__device__ __forceinline__ float half_away_pre(float x) { return __fadd_rz(x, copysignf(0.5f, x)); }
+
+// 32 features of one pixel: s32 accumulators -> requantised bytes in eight words.
+// Quantised path, 8-bit output, simple activations; same operation order as
+// epi_quant().  `e` holds the 32 residual bytes when kFused.
+template <bool kFused>
+__device__ __forceinline__ void epi_chunk_fast(const TcParams& P, const TcSmemAux* aux, int acc, int c0, const uint32_t (&r)[32],
+                                               uint4 e0, uint4 e1, uint4& o0, uint4& o1)
+{
+    const EpiCfg& c = P.epi;
+    const bool out_u8 = c.out_dtype == CLDNN_B200_U8;
+    uint32_t ew[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+    float e_bias = 8388608.0f;
+    if (kFused && c.eltw_dtype != CLDNN_B200_U8) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ew[i] ^= 0x80808080u;          // s8 + 128 as an unsigned byte
+        e_bias = 8388736.0f;
+    }
+    uint32_t ow[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const int cj = c0 + 4 * g;
+        const int4 bi = *reinterpret_cast<const int4*>(&aux->bias_i[acc][cj]);
+        const int32_t b4[4] = {bi.x, bi.y, bi.z, bi.w};
+        float q4[4] = {1.f, 1.f, 1.f, 1.f}, bf4[4] = {0.f, 0.f, 0.f, 0.f}, cal4[4], ec4[4] = {1.f, 1.f, 1.f, 1.f};
+        if (c.quantization) { const float4 t = *reinterpret_cast<const float4*>(&aux->quant[acc][cj]); q4[0] = t.x; q4[1] = t.y; q4[2] = t.z; q4[3] = t.w; }
+        if (c.dont_dequantize_bias) { const float4 t = *reinterpret_cast<const float4*>(&aux->bias_f[acc][cj]); bf4[0] = t.x; bf4[1] = t.y; bf4[2] = t.z; bf4[3] = t.w; }
+        if (c.calibration) { const float4 t = *reinterpret_cast<const float4*>(&aux->calib[acc][cj]); cal4[0] = t.x; cal4[1] = t.y; cal4[2] = t.z; cal4[3] = t.w; }
+        else { cal4[0] = cal4[1] = cal4[2] = cal4[3] = c.o_qf; }
+        if (kFused && c.eltw_calibration) { const float4 t = *reinterpret_cast<const float4*>(&aux->ecal[acc][cj]); ec4[0] = t.x; ec4[1] = t.y; ec4[2] = t.z; ec4[3] = t.w; }
+        int32_t o4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float v = __int2float_rn((int32_t)r[4 * g + i] + b4[i]);
+            if (c.quantization) { v = __fmul_rn(v, q4[i]); if (P.mul_iqf) v = __fmul_rn(v, c.i_qf); }
+            if (c.dont_dequantize_bias) v = __fadd_rn(v, bf4[i]);
+            v = act_simple(c.act, v, c.act_m, c.act_n);
+            if (P.mul_oqf) v = __fmul_rn(v, cal4[i]);
+            v = half_away_pre(v);
+            if (kFused) {
+                v = truncf(v);
+                // byte -> float without a conversion instruction: 2^23 + byte, minus 2^23
+                float e = __fadd_rn(__uint_as_float(__byte_perm(ew[g], 0x4B000000u, 0x7450u + i)), -e_bias);
+                if (c.has_non_conv_scale) e = __fmul_rn(e, c.non_conv_scale);
+                v = act_simple(c.eltw_act, __fadd_rn(v, e), c.eltw_m, c.eltw_n);
+                if (c.eltw_calibration) v = __fmul_rn(v, ec4[i]);
+                v = half_away_pre(v);
+            }
+            o4[i] = __float2int_rz(v);
+        }
+        ow[g] = out_u8 ? pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u))
+                       : pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
+    }
+    o0 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    o1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+}
+
+// One output element, every epilogue variant.  Kept out of line: it is the rare path.
+__device__ __noinline__ void epi_general_elem(const TcParams& P, const TcSmemAux* aux, int acc, int cj, int f, int32_t raw,
+                                              int64_t o_pix, int64_t e_pix)
+{
+    const EpiCfg& c = P.epi;
+    const int32_t a = raw + aux->bias_i[acc][cj];
+    if (c.quant_path) {
+        const float e = c.fused_eltw ? load_as_float(P.eltw, c.eltw_dtype, e_pix + f) : 0.f;
+        const float v = epi_quant(c, a, aux->quant[acc][cj], aux->bias_f[acc][cj], aux->calib[acc][cj], e, aux->ecal[acc][cj]);
+        store_sat_float(P.out, c.out_dtype, o_pix + f, v);
+        return;
+    }
+    // 8-bit fused eltwise without quantisation: integer activation domain
+    int32_t v = act_int(c.act, a, c.act_m, c.act_n), s;
+    if (c.has_non_conv_scale) s = (int32_t)__fadd_rn((float)v, __fmul_rn(load_as_float(P.eltw, c.eltw_dtype, e_pix + f), c.non_conv_scale));
+    else s = v + load_as_int(P.eltw, c.eltw_dtype, e_pix + f);
+    s = act_int(c.eltw_act, s, c.eltw_m, c.eltw_n);
+    if (c.eltw_calibration) {
+        const float tq = __fmul_rn((float)s, aux->ecal[acc][cj]);
+        if (c.out_is_fp) { store_sat_float(P.out, c.out_dtype, o_pix + f, tq); return; }
+        s = (int32_t)round_half_away(tq);
+    }
+    store_sat_int(P.out, c.out_dtype, o_pix + f, s);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 conv_i8_tc_kernel(const __grid_constant__ TcParams P)
 {
@@ -105,18 +218,26 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
     uint8_t* smem = smem_raw + (base - raw);
     const uint32_t a_base = base;
     const uint32_t b_base = base + (uint32_t)(P.stages * P.a_stage_bytes);
-    TcSmemAux* aux = reinterpret_cast<TcSmemAux*>(smem + (size_t)P.stages * (P.a_stage_bytes + P.b_stage_bytes));
+    const uint32_t ring_bytes = (uint32_t)(P.stages * (P.a_stage_bytes + P.b_stage_bytes));
+    const uint32_t staging_bytes = P.staged ? (uint32_t)(kBM * P.bn) : 0u;           // per buffer, two buffers
+    uint8_t* staging = smem + ring_bytes;
+    TcSmemAux* aux = reinterpret_cast<TcSmemAux*>(smem + ring_bytes + 2u * staging_bytes);
     volatile uint32_t* s_abort = &aux->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool fused_staged = P.staged && P.epi.fused_eltw;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4); }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), kEpiWarps);
+            mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
+        }
         mbar_init(smem_u32(&aux->drain), 1);
         aux->abort = 0u;
         mbar_fence_init();
         prefetch_tensormap(&P.tmA); prefetch_tensormap(&P.tmB);
+        if (P.staged) { prefetch_tensormap(&P.tmO); if (P.epi.fused_eltw) prefetch_tensormap(&P.tmE); }
     }
     if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
     tc_fence_before();
@@ -127,17 +248,31 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
-            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
+            int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true; int t = 0;
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
                 // base coordinates of the tile's first pixel
-                int c_w = 0, c_h = 0, c_n = 0;
+                int c_w = 0, c_h = 0, c_n = 0, o_w = 0, o_h = 0;
                 if (P.a_mode == A_IM2COL) {
                     int n, p, q; row_pixel(P, m_tile, 0, n, p, q);
                     c_w = q * P.stride_x - P.pad_x; c_h = p * P.stride_y - P.pad_y; c_n = n;
                 } else if (P.a_mode == A_TILED) {
                     const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
-                    c_w = tw * P.bw * P.a_coord_stride_x - P.pad_x; c_h = (t2 % P.tiles_h) * P.bh * P.a_coord_stride_y - P.pad_y; c_n = (t2 / P.tiles_h) * P.bb;
+                    o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
+                    c_w = o_w - P.pad_x; c_h = o_h - P.pad_y;
+                }
+                if (fused_staged) {
+                    // second input of the fused eltwise: same pixels and features as the output tile
+                    const int a = t & 1;
+                    if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)t >> 1) & 1u) ^ 1u, s_abort, P.status, kErrProducer + 1u)) { ok = false; break; }
+                    const uint32_t rf = smem_u32(&aux->res_full[a]);
+                    mbar_expect_tx(rf, (uint32_t)(P.stage_rows * P.cw * P.col_blocks));
+                    for (int cb = 0; cb < P.col_blocks; ++cb) {
+                        const uint32_t dst = smem_u32(staging) + (uint32_t)a * staging_bytes + (uint32_t)(cb * kBM * P.cw);
+                        const int f0 = n_tile * P.bn + cb * P.cw;
+                        if (P.a_mode == A_TILED) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
+                        else tma_load_2d(dst, &P.tmE, rf, f0, m_tile * kBM);
+                    }
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
@@ -199,17 +334,18 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. 32*quad+31
+        const int half = (warp - 2) >> 2;                           // two warps share a lane quadrant, alternate column chunks
         const int row = quad * 32 + lane;
-        const int et = threadIdx.x - 64;                            // 0..127
+        const int et = threadIdx.x - 64;                            // 0..255
         const EpiCfg& c = P.epi;
-        const bool out8 = is_int8(c.out_dtype);
-        int t = 0; bool ok = true;
+        const uint32_t sw = (uint32_t)((row >> P.sw_shift) & P.sw_mask);
+        int t = 0; bool ok = true; int pending_store = -1;
         for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
             int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
             const int acc = t & 1;
             const int n0 = n_tile * P.bn;
             // per-channel constants of this tile's feature range
-            for (int j = et; j < P.bn; j += 128) {
+            for (int j = et; j < P.bn; j += kEpiThreads) {
                 const int f = n0 + j; const bool v = f < P.ofm;
                 int32_t bi = 0; float bf = 0.f;
                 if (v && c.bias_dtype != CLDNN_B200_NONE) {
@@ -221,81 +357,91 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 aux->calib[acc][j] = (v && c.calibration) ? P.calib[f] : 1.f;
                 aux->ecal[acc][j] = (v && c.eltw_calibration) ? P.ecal[f] : 1.f;
             }
-            named_bar_sync(1, 128);
+            named_bar_sync(1, kEpiThreads);
             if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue)) { ok = false; break; }
+            if (fused_staged && !mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue + 1u)) { ok = false; break; }
             tc_fence_after();
-
-            int n, p, q; const bool valid = row_pixel(P, m_tile, row, n, p, q);
-            const int64_t o_pix = P.out_off + (int64_t)n * P.out_pb + (int64_t)p * P.out_py + (int64_t)q * P.out_px;
-            const int64_t e_pix = c.fused_eltw ? P.el_off + (int64_t)n * P.el_pb + (int64_t)p * P.el_sy * P.el_py + (int64_t)q * P.el_sx * P.el_px : 0;
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * P.bn);
 
-            for (int c0 = 0; c0 < P.bn; c0 += 32) {
-                if (n0 + c0 >= P.ofm) break;                        // uniform across the CTA
-                uint32_t r[32];
-                tmem_ld_32x32(t_row + (uint32_t)c0, r);
-                tmem_ld_wait();
-                if (!valid) continue;
-                const int fbase = n0 + c0;
-                const bool full32 = fbase + 32 <= P.ofm;
-                if (c.quant_path && out8 && full32 && ((o_pix + fbase) & 15) == 0 &&
-                    (!c.fused_eltw || (is_int8(c.eltw_dtype) && ((e_pix + fbase) & 15) == 0))) {
-                    // fast path: 32 features -> two 16-byte stores
-                    uint32_t ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (c.fused_eltw) {
-                        const uint4* ep = (const uint4*)((const uint8_t*)P.eltw + e_pix + fbase);
-                        const uint4 e0 = ep[0], e1 = ep[1];
-                        ew[0] = e0.x; ew[1] = e0.y; ew[2] = e0.z; ew[3] = e0.w; ew[4] = e1.x; ew[5] = e1.y; ew[6] = e1.z; ew[7] = e1.w;
+            if (P.staged) {
+                uint8_t* stg = staging + (size_t)acc * staging_bytes;
+                int done = 0;
+                for (int c0 = half * 32; c0 < P.bn; c0 += 64, ++done) {
+                    if (n0 + c0 >= P.ofm) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    // the tile that was stored last must have left its buffer before it is reused two tiles later;
+                    // by now that store has had a whole chunk of time to finish
+                    if (et == 0 && done == 0 && pending_store >= 0) {
+                        bulk_wait_read0();
+                        if (P.epi.fused_eltw) mbar_arrive(smem_u32(&aux->stage_free[pending_store]));
+                        pending_store = -1;
                     }
-                    uint32_t ow[8];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int cj = c0 + j;
-                        const int32_t a = (int32_t)r[j] + aux->bias_i[acc][cj];
-                        float e = 0.f;
+                    const int cb = c0 / P.cw, o = c0 - cb * P.cw;
+                    uint8_t* rowp = stg + (size_t)cb * kBM * P.cw + (size_t)row * P.cw;
+                    uint4* p0 = reinterpret_cast<uint4*>(rowp + ((((uint32_t)o >> 4) ^ sw) << 4));
+                    uint4* p1 = reinterpret_cast<uint4*>(rowp + (((((uint32_t)o >> 4) + 1u) ^ sw) << 4));
+                    uint4 o0, o1;
+                    if (c.fused_eltw) epi_chunk_fast<true>(P, aux, acc, c0, r, *p0, *p1, o0, o1);
+                    else epi_chunk_fast<false>(P, aux, acc, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                    *p0 = o0; *p1 = o1;
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
+                fence_async_smem();
+                named_bar_sync(2, kEpiThreads);
+                if (et == 0) {
+                    if (pending_store >= 0) {                       // tiles narrower than one chunk per warp never ran the wait above
+                        bulk_wait_read0();
+                        if (P.epi.fused_eltw) mbar_arrive(smem_u32(&aux->stage_free[pending_store]));
+                    }
+                    int tw = 0, th = 0, tb = 0;
+                    if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
+                    for (int cb = 0; cb < P.col_blocks; ++cb) {
+                        const int f0 = n0 + cb * P.cw;
+                        if (f0 >= P.ofm) break;
+                        const uint32_t src = smem_u32(stg) + (uint32_t)(cb * kBM * P.cw);
+                        if (P.a_mode == A_TILED) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
+                        else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
+                    }
+                    bulk_commit();
+                    pending_store = acc;
+                }
+            } else {
+                int n, p, q; const bool valid = row_pixel(P, m_tile, row, n, p, q);
+                const int64_t o_pix = P.out_off + (int64_t)n * P.out_pb + (int64_t)p * P.out_py + (int64_t)q * P.out_px;
+                const int64_t e_pix = c.fused_eltw ? P.el_off + (int64_t)n * P.el_pb + (int64_t)p * P.el_sy * P.el_py + (int64_t)q * P.el_sx * P.el_px : 0;
+                for (int c0 = half * 32; c0 < P.bn; c0 += 64) {
+                    if (n0 + c0 >= P.ofm) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    if (!valid) continue;
+                    const int fbase = n0 + c0;
+                    const bool full32 = fbase + 32 <= P.ofm;
+                    if (P.fast_epi && full32 && ((o_pix + fbase) & 15) == 0 && (!c.fused_eltw || ((e_pix + fbase) & 15) == 0)) {
+                        uint4* op = reinterpret_cast<uint4*>((uint8_t*)P.out + o_pix + fbase);
+                        uint4 o0, o1;
                         if (c.fused_eltw) {
-                            const uint32_t byte = (ew[j >> 2] >> ((j & 3) * 8)) & 0xffu;
-                            e = c.eltw_dtype == CLDNN_B200_U8 ? (float)byte : (float)(int8_t)byte;
-                        }
-                        const float v = epi_quant(c, a, aux->quant[acc][cj], aux->bias_f[acc][cj], aux->calib[acc][cj], e, aux->ecal[acc][cj]);
-                        const int32_t o = c.out_dtype == CLDNN_B200_U8 ? sat_i32_from_float(v, 0, 255) : sat_i32_from_float(v, -128, 127);
-                        if ((j & 3) == 0) ow[j >> 2] = 0;
-                        ow[j >> 2] |= ((uint32_t)o & 0xffu) << ((j & 3) * 8);
-                    }
-                    uint4* op = (uint4*)((uint8_t*)P.out + o_pix + fbase);
-                    op[0] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                    op[1] = make_uint4(ow[4], ow[5], ow[6], ow[7]);
-                } else {
-                    // general path: any output type, ragged feature tail, unaligned rows
-#pragma unroll 1
-                    for (int j = 0; j < 32; ++j) {
-                        const int f = fbase + j; if (f >= P.ofm) break;
-                        const int cj = c0 + j;
-                        const int32_t a = (int32_t)r[j] + aux->bias_i[acc][cj];
-                        if (c.quant_path) {
-                            const float e = c.fused_eltw ? load_as_float(P.eltw, c.eltw_dtype, e_pix + f) : 0.f;
-                            const float v = epi_quant(c, a, aux->quant[acc][cj], aux->bias_f[acc][cj], aux->calib[acc][cj], e, aux->ecal[acc][cj]);
-                            store_sat_float(P.out, c.out_dtype, o_pix + f, v);
-                        } else {
-                            // 8-bit fused eltwise without quantisation: integer activation domain
-                            int32_t v = act_int(c.act, a, c.act_m, c.act_n), s;
-                            if (c.has_non_conv_scale) s = (int32_t)__fadd_rn((float)v, __fmul_rn(load_as_float(P.eltw, c.eltw_dtype, e_pix + f), c.non_conv_scale));
-                            else s = v + load_as_int(P.eltw, c.eltw_dtype, e_pix + f);
-                            s = act_int(c.eltw_act, s, c.eltw_m, c.eltw_n);
-                            if (c.eltw_calibration) {
-                                const float tq = __fmul_rn((float)s, aux->ecal[acc][cj]);
-                                if (c.out_is_fp) { store_sat_float(P.out, c.out_dtype, o_pix + f, tq); continue; }
-                                s = (int32_t)round_half_away(tq);
-                            }
-                            store_sat_int(P.out, c.out_dtype, o_pix + f, s);
-                        }
+                            const uint4* ep = reinterpret_cast<const uint4*>((const uint8_t*)P.eltw + e_pix + fbase);
+                            epi_chunk_fast<true>(P, aux, acc, c0, r, ep[0], ep[1], o0, o1);
+                        } else epi_chunk_fast<false>(P, aux, acc, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                        op[0] = o0; op[1] = o1;
+                    } else {
+                        // general path: any output type, any activation, ragged feature tail, unaligned rows
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (fbase + j < P.ofm) epi_general_elem(P, aux, acc, c0 + j, fbase + j, (int32_t)r[j], o_pix, e_pix);
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
         }
+        if (et == 0 && pending_store >= 0) bulk_wait_read0();       // shared memory must outlive the last store's reads
     }
 
     tc_fence_before();
@@ -340,6 +486,7 @@ static bool dense_byxf(const cldnn_b200_tensor& t)
 {
     return t.pf == 1 && t.px % 16 == 0 && t.py % 16 == 0 && t.pb % 16 == 0 && t.offset % 16 == 0 && t.px >= t.f && t.py >= t.px * t.x && t.pb >= t.py * t.y;
 }
+static bool pixel_dense(const cldnn_b200_tensor& t) { return t.py == t.px * t.x && t.pb == t.py * t.y; }
 
 // choose a box of bw x bh x bb <= 128 pixels that wastes the fewest tile rows
 static void choose_box(int Q, int Pn, int N, int& bw, int& bh, int& bb)
@@ -385,8 +532,7 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
 
     const int cs = (int)p.in.px;                                    // stored channels = bytes of K per tap
     pl.bk = cs % 128 == 0 ? 128 : (cs % 64 == 0 ? 64 : 32);
-    const bool is_1x1_s1 = p.kh == 1 && p.kw == 1 && p.stride_x == 1 && p.stride_y == 1 && p.pad_x == 0 && p.pad_y == 0 &&
-                           p.in.py == p.in.px * p.in.x && p.in.pb == p.in.py * p.in.y;
+    const bool is_1x1_s1 = p.kh == 1 && p.kw == 1 && p.stride_x == 1 && p.stride_y == 1 && p.pad_x == 0 && p.pad_y == 0 && pixel_dense(p.in);
     const bool pointwise = p.kh == 1 && p.kw == 1 && p.pad_x == 0 && p.pad_y == 0;
     const bool tiled_ok = (p.stride_x == 1 && p.stride_y == 1) || pointwise;
     const bool im2col_ok = p.pad_x <= 127 && p.pad_y <= 127 && (p.kw - 1) * p.dil_x <= 255 && (p.kh - 1) * p.dil_y <= 255 &&
@@ -395,11 +541,11 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
     int tune = p.tune;
     int mode = -1, bn = 0;
     if (tune > 0) { mode = (tune - 1) / 4; bn = kTuneBN[(tune - 1) % 4]; }
-    if (mode < 0) mode = is_1x1_s1 ? A_FLAT : (tiled_ok ? A_TILED : A_IM2COL);
+    if (mode < 0) mode = is_1x1_s1 ? A_FLAT : (im2col_ok ? A_IM2COL : A_TILED);
     if (mode == A_FLAT && !is_1x1_s1) return no("flat addressing needs a dense 1x1 stride-1 convolution");
     if (mode == A_TILED && !tiled_ok) return no("tiled addressing needs stride 1 or a pointwise filter");
-    if (mode == A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded");
-    if (bn == 0) bn = p.ofm > 64 ? 128 : (p.ofm > 32 ? 64 : 32);
+    if (mode == A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded (or tensor below 128 KiB)");
+    if (bn == 0) bn = p.ofm > 128 ? 256 : (p.ofm > 64 ? 128 : (p.ofm > 32 ? 64 : 32));
     pl.a_mode = mode; pl.bn = bn;
     pl.bw = pl.bh = pl.bb = 1;
     if (mode == A_TILED) choose_box(p.out.x, p.out.y, p.out.b, pl.bw, pl.bh, pl.bb);
@@ -409,6 +555,26 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
 static bool tc_supports(const void* vp)
 {
     TcPlan pl; return tc_plan(*(const cldnn_b200_conv_params*)vp, pl, nullptr);
+}
+
+// tensor map over the pixels x features of an 8-bit byxf tensor, boxed like the tile
+static CUresult encode_pixel_map(CUtensorMap* tm, const TcPlan& pl, void* ptr, const cldnn_b200_tensor& t, int stride_x, int stride_y,
+                                 int cw, CUtensorMapSwizzle sw)
+{
+    if (pl.a_mode == A_TILED) {
+        cuuint64_t dims[4] = {(cuuint64_t)t.f, (cuuint64_t)((t.x + stride_x - 1) / stride_x), (cuuint64_t)((t.y + stride_y - 1) / stride_y), (cuuint64_t)t.b};
+        cuuint64_t strides[3] = {(cuuint64_t)(t.px * stride_x), (cuuint64_t)(t.py * stride_y), (cuuint64_t)t.pb};
+        cuuint32_t box[4] = {(cuuint32_t)cw, (cuuint32_t)pl.bw, (cuuint32_t)pl.bh, (cuuint32_t)pl.bb};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        return g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)t.f, (cuuint64_t)((int64_t)t.b * t.y * t.x)};
+    cuuint64_t strides[1] = {(cuuint64_t)t.px};
+    cuuint32_t box[2] = {(cuuint32_t)cw, (cuuint32_t)kBM};
+    cuuint32_t es[2] = {1, 1};
+    return g_encode_tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 }
 
 static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
@@ -434,7 +600,6 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.bn = pl.bn; P.n_tiles = (p.ofm + pl.bn - 1) / pl.bn;
     P.M_total = (int64_t)P.N * P.P * P.Q;
     P.bw = pl.bw; P.bh = pl.bh; P.bb = pl.bb;
-    P.a_coord_stride_x = 1; P.a_coord_stride_y = 1;
     if (pl.a_mode == A_TILED) {
         P.tiles_w = (P.Q + pl.bw - 1) / pl.bw; P.tiles_h = (P.P + pl.bh - 1) / pl.bh;
         P.m_tiles = P.tiles_w * P.tiles_h * ((P.N + pl.bb - 1) / pl.bb);
@@ -443,8 +608,9 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
         P.m_tiles = (int)((P.M_total + kBM - 1) / kBM);
     }
     P.total_tiles = P.m_tiles * P.n_tiles;
+    P.stage_rows = pl.a_mode == A_TILED ? pl.bw * pl.bh * pl.bb : kBM;
     P.a_stage_bytes = kBM * pl.bk; P.b_stage_bytes = pl.bn * pl.bk;
-    P.a_tx_bytes = (pl.a_mode == A_TILED ? pl.bw * pl.bh * pl.bb : kBM) * pl.bk;
+    P.a_tx_bytes = P.stage_rows * pl.bk;
     P.b_tx_bytes = pl.bn * pl.bk;
     P.sbo = 8u * (uint32_t)pl.bk;
     P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
@@ -453,24 +619,43 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.tmem_cols = (uint32_t)(2 * pl.bn < 32 ? 32 : 2 * pl.bn);
     P.ofm = p.ofm;
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
+    const cldnn_b200_tensor& et = p.in_out_opt ? p.out : p.eltw;
+    const int esx = p.in_out_opt ? 1 : p.eltw_stride_x, esy = p.in_out_opt ? 1 : p.eltw_stride_y;
     if (p.fused_eltw) {
-        const cldnn_b200_tensor& e = p.in_out_opt ? p.out : p.eltw;
-        P.el_px = e.px; P.el_py = e.py; P.el_pb = e.pb; P.el_off = e.offset;
-        P.el_sx = p.in_out_opt ? 1 : p.eltw_stride_x; P.el_sy = p.in_out_opt ? 1 : p.eltw_stride_y;
+        P.el_px = et.px; P.el_py = et.py; P.el_pb = et.pb; P.el_off = et.offset;
+        P.el_sx = esx; P.el_sy = esy;
     }
     P.out = a->output; P.eltw = p.in_out_opt ? a->output : a->input1; P.bias = a->bias;
     P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors; P.ecal = a->eltw_output_calibration_factors;
     P.status = ctx->d_status;
     P.epi = make_epi_cfg(p);
+    P.fast_epi = (P.epi.quant_path && is_int8(p.out.dtype) && act_is_simple(p.act, p.act_m) &&
+                  (!p.fused_eltw || (is_int8(P.epi.eltw_dtype) && act_is_simple(p.eltw_act, p.eltw_m)))) ? 1 : 0;
+    P.mul_iqf = p.i_qf != 1.0f ? 1 : 0;
+    P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
+
+    // staged epilogue: the output (and residual) tile must be addressable by one TMA box per column block
+    auto tma_ok = [&](const cldnn_b200_tensor& t, const void* ptr, int sx, int sy) {
+        if (t.pf != 1 || t.px % 16 || t.py % 16 || t.pb % 16 || t.offset % 16 || ((uintptr_t)ptr & 15)) return false;
+        if (pl.a_mode == A_TILED) return true;
+        return sx == 1 && sy == 1 && pixel_dense(t);
+    };
+    P.staged = (P.fast_epi && tma_ok(p.out, a->output, 1, 1) && (!p.fused_eltw || tma_ok(et, P.eltw, esx, esy))) ? 1 : 0;
+    if (p.fused_eltw && !p.in_out_opt && (et.b != p.out.b || (et.y + esy - 1) / esy < p.out.y || (et.x + esx - 1) / esx < p.out.x || et.f < p.ofm)) P.staged = 0;
+    P.cw = pl.bn < 128 ? pl.bn : 128; P.col_blocks = pl.bn / P.cw;
+    P.sw_shift = P.cw == 128 ? 0 : (P.cw == 64 ? 1 : 2);
+    P.sw_mask = P.cw == 128 ? 7 : (P.cw == 64 ? 3 : 1);
 
     const size_t aux_bytes = sizeof(TcSmemAux);
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
+    size_t staging_total = P.staged ? (size_t)2 * kBM * pl.bn : 0;
+    if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) { P.staged = 0; staging_total = 0; }
     if (max_smem < 1024 + aux_bytes + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory");
-    int stages = (int)((max_smem - 1024 - aux_bytes) / stage_bytes);
+    int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     P.stages = stages;
-    size_t smem_bytes = 1024 + (size_t)stages * stage_bytes + aux_bytes;
+    size_t smem_bytes = 1024 + (size_t)stages * stage_bytes + staging_total + aux_bytes;
     const size_t one_cta_floor = max_smem / 2 + 1024;                // keeps one CTA per SM, so TMEM allocation never waits
     if (smem_bytes < one_cta_floor) smem_bytes = one_cta_floor;
     if (smem_bytes > max_smem) smem_bytes = max_smem;
@@ -517,6 +702,16 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
         cr = g_encode_tiled(&P.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_DEVICE_ERROR, "conv_i8_tc: weights tensor map rejected by the driver (CUresult " + std::to_string((int)cr) + ")");
+    }
+    if (P.staged) {
+        const CUtensorMapSwizzle osw = P.cw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (P.cw == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+        cldnn_b200_tensor ot = p.out; ot.f = p.ofm;
+        cr = encode_pixel_map(&P.tmO, pl, (char*)a->output + p.out.offset, ot, 1, 1, P.cw, osw);
+        if (cr == CUDA_SUCCESS && p.fused_eltw) {
+            cldnn_b200_tensor rt = et; rt.f = p.ofm;
+            cr = encode_pixel_map(&P.tmE, pl, (char*)const_cast<void*>(P.eltw) + et.offset, rt, esx, esy, P.cw, osw);
+        }
+        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_DEVICE_ERROR, "conv_i8_tc: output tensor map rejected by the driver (CUresult " + std::to_string((int)cr) + ")");
     }
 
     B200_CUDA(cudaFuncSetAttribute(conv_i8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)max_smem));

@@ -118,9 +118,10 @@ class Memory:
         _check(self.engine.lib.cldnn_b200_mem_fill(self.handle, byte))
 
     def free(self):
-        if self.handle:
+        # a buffer must not outlive its context: after Engine.close() only drop the handle
+        if self.handle and self.engine.handle:
             self.engine.lib.cldnn_b200_mem_free(self.handle)
-            self.handle = C.c_void_p()
+        self.handle = C.c_void_p()
 
     def __del__(self):
         try:
@@ -144,7 +145,7 @@ class Prepared:
     def destroy(self):
         if self.handle:
             self.engine.lib.cldnn_b200_prepared_destroy(self.handle)
-            self.handle = None
+        self.handle = None
 
     def __del__(self):
         try:

@@ -37,7 +37,7 @@ GEOMS = {
     "c64_56": dict(N=2, C=64, K=64, H=56, W=56),
     "ragged_c32_k48": dict(N=3, C=32, K=48, H=9, W=11),
     "c96_k40": dict(N=1, C=96, K=40, H=7, W=7),
-    "stride2_3x3": dict(N=2, C=64, K=64, H=15, W=15, stride=2),
+    "stride2_3x3": dict(N=10, C=64, K=64, H=15, W=15, stride=2),
     "dilation2": dict(N=1, C=32, K=32, H=12, W=12, dil=2, pad=2),
     "c512_7x7map": dict(N=4, C=512, K=512, H=7, W=7),
     "5x5": dict(N=1, C=32, K=32, H=10, W=10, kh=5, kw=5, pad=2),
