@@ -34,7 +34,8 @@ using namespace ptx;
 constexpr int kBM = 128;                 // pixels per tile = TMEM lanes
 constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kStoreWarp = 2 + kEpiWarps;  // warp that issues the TMA stores of finished tiles
+constexpr int kThreads = 64 + kEpiThreads + 32;
 constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;
 constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
@@ -61,6 +62,7 @@ struct alignas(64) TcParams {
     int32_t fast_epi;                    // quantised, 8-bit output and residual, simple activations
     int32_t cw, col_blocks, sw_shift, sw_mask, stage_rows;   // staging tile: column block width, 16-byte chunk swizzle
     int32_t mul_iqf, mul_oqf;
+    int32_t lean;                        // epilogue configuration covered by the hoisted fast body
     // output / residual addressing for the direct path, in elements
     int64_t out_px, out_py, out_pb, out_off;
     int64_t el_px, el_py, el_pb, el_off;
@@ -77,6 +79,7 @@ struct TcSmemAux {
     uint64_t tmem_empty[2];
     uint64_t res_full[2];                // residual tile landed in staging buffer
     uint64_t stage_free[2];              // staging buffer read out by its TMA store
+    uint64_t out_ready[2];               // staging buffer holds a finished output tile
     uint64_t drain;
     uint32_t tmem_base;
     uint32_t abort;
@@ -89,7 +92,8 @@ struct TcSmemAux {
 
 __device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int& m_tile, int& n_tile)
 {
-    m_tile = tile / P.n_tiles; n_tile = tile - m_tile * P.n_tiles;
+    // feature-tile major: a CTA's successive tiles mostly share their per-channel constants
+    n_tile = tile / P.m_tiles; m_tile = tile - n_tile * P.m_tiles;
 }
 
 // pixel of row `row` of tile `m_tile`: returns false when the row is padding
@@ -132,7 +136,7 @@ __device__ __forceinline__ float half_away_pre(float x) { return __fadd_rz(x, co
 // 32 features of one pixel: s32 accumulators -> requantised bytes in eight words.
 // Quantised path, 8-bit output, simple activations; same operation order as
 // epi_quant().  `e` holds the 32 residual bytes when kFused.
-template <bool kFused>
+template <bool kFused, bool kLean>
 __device__ __forceinline__ void epi_chunk_fast(const TcParams& P, const TcSmemAux* aux, int acc, int c0, const uint32_t (&r)[32],
                                                uint4 e0, uint4 e1, uint4& o0, uint4& o1)
 {
@@ -146,6 +150,38 @@ __device__ __forceinline__ void epi_chunk_fast(const TcParams& P, const TcSmemAu
         e_bias = 8388736.0f;
     }
     uint32_t ow[8];
+    if (kLean) {
+        // The common network configuration, with every uniform decision hoisted out of
+        // the unrolled body: per-channel quantisation only (I_QF = O_QF = 1, integer or
+        // no bias), activations NONE or ReLU, plain residual sum.  ~8 instructions per
+        // feature; max(v, -inf) stands for "no activation".
+        const float lo1 = c.act == CLDNN_B200_ACT_RELU ? 0.0f : __int_as_float(0xff800000);
+        const float lo2 = c.eltw_act == CLDNN_B200_ACT_RELU ? 0.0f : __int_as_float(0xff800000);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const int cj = c0 + 4 * g;
+            const int4 bi = *reinterpret_cast<const int4*>(&aux->bias_i[acc][cj]);
+            const float4 q = *reinterpret_cast<const float4*>(&aux->quant[acc][cj]);
+            const int32_t b4[4] = {bi.x, bi.y, bi.z, bi.w};
+            const float q4[4] = {q.x, q.y, q.z, q.w};
+            int32_t o4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
+                v = half_away_pre(fmaxf(v, lo1));
+                if (kFused) {
+                    const float e = __fadd_rn(__uint_as_float(__byte_perm(ew[g], 0x4B000000u, 0x7450u + i)), -e_bias);
+                    v = half_away_pre(fmaxf(__fadd_rn(truncf(v), e), lo2));
+                }
+                o4[i] = __float2int_rz(v);
+            }
+            ow[g] = out_u8 ? pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u))
+                           : pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
+        }
+        o0 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        o1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+        return;
+    }
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
         const int cj = c0 + 4 * g;
@@ -232,6 +268,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), kEpiWarps);
             mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
+            mbar_init(smem_u32(&aux->out_ready[a]), kEpiWarps);
         }
         mbar_init(smem_u32(&aux->drain), 1);
         aux->abort = 0u;
@@ -331,84 +368,97 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (globaltimer() - t0 > kWaitLimitNs) { atomicCAS(P.status, 0u, kErrDrain); break; }
             }
         }
+    } else if (warp == kStoreWarp) {
+        // ------------------------------ TMA store issuer --------------------------
+        if (lane == 0 && P.staged) {
+            int t = 0;
+            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
+                int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
+                const int a = t & 1;
+                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue + 2u)) break;
+                int tw = 0, th = 0, tb = 0;
+                if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
+                const int n0 = n_tile * P.bn;
+                for (int cb = 0; cb < P.col_blocks; ++cb) {
+                    const int f0 = n0 + cb * P.cw;
+                    if (f0 >= P.ofm) break;
+                    const uint32_t src = smem_u32(staging) + (uint32_t)a * staging_bytes + (uint32_t)(cb * kBM * P.cw);
+                    if (P.a_mode == A_TILED) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
+                    else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
+                }
+                bulk_commit();
+                bulk_wait_read0();                                  // the buffer may be refilled once TMA has read it
+                mbar_arrive(smem_u32(&aux->stage_free[a]));
+            }
+        }
     } else {
         // ------------------------------ epilogue ----------------------------------
+        // Warps run independently: no block-wide synchronisation per tile, only the
+        // mbarriers of the accumulator and staging buffers they touch.
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. 32*quad+31
         const int half = (warp - 2) >> 2;                           // two warps share a lane quadrant, alternate column chunks
         const int row = quad * 32 + lane;
         const int et = threadIdx.x - 64;                            // 0..255
         const EpiCfg& c = P.epi;
         const uint32_t sw = (uint32_t)((row >> P.sw_shift) & P.sw_mask);
-        int t = 0; bool ok = true; int pending_store = -1;
+        int t = 0; bool ok = true; int cur_n_tile = -1;
         for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
             int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
             const int acc = t & 1;
             const int n0 = n_tile * P.bn;
-            // per-channel constants of this tile's feature range
-            for (int j = et; j < P.bn; j += kEpiThreads) {
-                const int f = n0 + j; const bool v = f < P.ofm;
-                int32_t bi = 0; float bf = 0.f;
-                if (v && c.bias_dtype != CLDNN_B200_NONE) {
-                    if (c.bias_dtype == CLDNN_B200_F32) bf = ((const float*)P.bias)[f];
-                    else bi = load_as_int(P.bias, c.bias_dtype, f);
+            if (n_tile != cur_n_tile) {
+                // per-channel constants of this feature range; every warp has left the previous range
+                named_bar_sync(1, kEpiThreads);
+                for (int j = et; j < P.bn; j += kEpiThreads) {
+                    const int f = n0 + j; const bool v = f < P.ofm;
+                    int32_t bi = 0; float bf = 0.f;
+                    if (v && c.bias_dtype != CLDNN_B200_NONE) {
+                        if (c.bias_dtype == CLDNN_B200_F32) bf = ((const float*)P.bias)[f];
+                        else bi = load_as_int(P.bias, c.bias_dtype, f);
+                    }
+                    aux->bias_i[0][j] = bi; aux->bias_f[0][j] = bf;
+                    aux->quant[0][j] = (v && c.quantization) ? P.quant[f] : 1.f;
+                    aux->calib[0][j] = (v && c.calibration) ? P.calib[f] : 1.f;
+                    aux->ecal[0][j] = (v && c.eltw_calibration) ? P.ecal[f] : 1.f;
                 }
-                aux->bias_i[acc][j] = bi; aux->bias_f[acc][j] = bf;
-                aux->quant[acc][j] = (v && c.quantization) ? P.quant[f] : 1.f;
-                aux->calib[acc][j] = (v && c.calibration) ? P.calib[f] : 1.f;
-                aux->ecal[acc][j] = (v && c.eltw_calibration) ? P.ecal[f] : 1.f;
+                named_bar_sync(1, kEpiThreads);
+                cur_n_tile = n_tile;
             }
-            named_bar_sync(1, kEpiThreads);
             if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue)) { ok = false; break; }
-            if (fused_staged && !mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue + 1u)) { ok = false; break; }
+            if (P.staged) {
+                // the staging buffer is ours once its residual tile has landed (fused) or its previous store has read it out
+                const bool got = fused_staged ? mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue + 1u)
+                                              : mbar_wait(smem_u32(&aux->stage_free[acc]), (((uint32_t)t >> 1) & 1u) ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
+                if (!got) { ok = false; break; }
+            }
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * P.bn);
 
             if (P.staged) {
                 uint8_t* stg = staging + (size_t)acc * staging_bytes;
-                int done = 0;
-                for (int c0 = half * 32; c0 < P.bn; c0 += 64, ++done) {
+                for (int c0 = half * 32; c0 < P.bn; c0 += 64) {
                     if (n0 + c0 >= P.ofm) break;
                     uint32_t r[32];
                     tmem_ld_32x32(t_row + (uint32_t)c0, r);
                     tmem_ld_wait();
-                    // the tile that was stored last must have left its buffer before it is reused two tiles later;
-                    // by now that store has had a whole chunk of time to finish
-                    if (et == 0 && done == 0 && pending_store >= 0) {
-                        bulk_wait_read0();
-                        if (P.epi.fused_eltw) mbar_arrive(smem_u32(&aux->stage_free[pending_store]));
-                        pending_store = -1;
-                    }
                     const int cb = c0 / P.cw, o = c0 - cb * P.cw;
                     uint8_t* rowp = stg + (size_t)cb * kBM * P.cw + (size_t)row * P.cw;
                     uint4* p0 = reinterpret_cast<uint4*>(rowp + ((((uint32_t)o >> 4) ^ sw) << 4));
                     uint4* p1 = reinterpret_cast<uint4*>(rowp + (((((uint32_t)o >> 4) + 1u) ^ sw) << 4));
                     uint4 o0, o1;
-                    if (c.fused_eltw) epi_chunk_fast<true>(P, aux, acc, c0, r, *p0, *p1, o0, o1);
-                    else epi_chunk_fast<false>(P, aux, acc, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                    if (P.lean) {
+                        if (c.fused_eltw) epi_chunk_fast<true, true>(P, aux, 0, c0, r, *p0, *p1, o0, o1);
+                        else epi_chunk_fast<false, true>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                    } else {
+                        if (c.fused_eltw) epi_chunk_fast<true, false>(P, aux, 0, c0, r, *p0, *p1, o0, o1);
+                        else epi_chunk_fast<false, false>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                    }
                     *p0 = o0; *p1 = o1;
                 }
                 tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
                 fence_async_smem();
-                named_bar_sync(2, kEpiThreads);
-                if (et == 0) {
-                    if (pending_store >= 0) {                       // tiles narrower than one chunk per warp never ran the wait above
-                        bulk_wait_read0();
-                        if (P.epi.fused_eltw) mbar_arrive(smem_u32(&aux->stage_free[pending_store]));
-                    }
-                    int tw = 0, th = 0, tb = 0;
-                    if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
-                    for (int cb = 0; cb < P.col_blocks; ++cb) {
-                        const int f0 = n0 + cb * P.cw;
-                        if (f0 >= P.ofm) break;
-                        const uint32_t src = smem_u32(stg) + (uint32_t)(cb * kBM * P.cw);
-                        if (P.a_mode == A_TILED) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
-                        else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
-                    }
-                    bulk_commit();
-                    pending_store = acc;
-                }
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(smem_u32(&aux->tmem_empty[acc])); mbar_arrive(smem_u32(&aux->out_ready[acc])); }
             } else {
                 int n, p, q; const bool valid = row_pixel(P, m_tile, row, n, p, q);
                 const int64_t o_pix = P.out_off + (int64_t)n * P.out_pb + (int64_t)p * P.out_py + (int64_t)q * P.out_px;
@@ -426,14 +476,14 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                         uint4 o0, o1;
                         if (c.fused_eltw) {
                             const uint4* ep = reinterpret_cast<const uint4*>((const uint8_t*)P.eltw + e_pix + fbase);
-                            epi_chunk_fast<true>(P, aux, acc, c0, r, ep[0], ep[1], o0, o1);
-                        } else epi_chunk_fast<false>(P, aux, acc, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                            epi_chunk_fast<true, false>(P, aux, 0, c0, r, ep[0], ep[1], o0, o1);
+                        } else epi_chunk_fast<false, false>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
                         op[0] = o0; op[1] = o1;
                     } else {
                         // general path: any output type, any activation, ragged feature tail, unaligned rows
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
-                            if (fbase + j < P.ofm) epi_general_elem(P, aux, acc, c0 + j, fbase + j, (int32_t)r[j], o_pix, e_pix);
+                            if (fbase + j < P.ofm) epi_general_elem(P, aux, 0, c0 + j, fbase + j, (int32_t)r[j], o_pix, e_pix);
                     }
                 }
                 tc_fence_before();
@@ -441,7 +491,6 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
             }
         }
-        if (et == 0 && pending_store >= 0) bulk_wait_read0();       // shared memory must outlive the last store's reads
     }
 
     tc_fence_before();
@@ -633,6 +682,9 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
                   (!p.fused_eltw || (is_int8(P.epi.eltw_dtype) && act_is_simple(p.eltw_act, p.eltw_m)))) ? 1 : 0;
     P.mul_iqf = p.i_qf != 1.0f ? 1 : 0;
     P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
+    auto none_or_relu = [](int32_t fn) { return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU; };
+    P.lean = (P.fast_epi && p.quantization && !P.mul_iqf && !P.mul_oqf && !P.epi.dont_dequantize_bias && none_or_relu(p.act) &&
+              (!p.fused_eltw || (!p.has_non_conv_scale && !p.eltw_calibration && none_or_relu(p.eltw_act)))) ? 1 : 0;
 
     // staged epilogue: the output (and residual) tile must be addressable by one TMA box per column block
     auto tma_ok = [&](const cldnn_b200_tensor& t, const void* ptr, int sx, int sy) {
