@@ -38,6 +38,7 @@ constexpr int kStoreWarp = 2 + kEpiWarps;  // warp that issues the TMA stores of
 constexpr int kThreads = 64 + kEpiThreads + 32;
 constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;
+constexpr int kMaxBufs = 4;               // accumulator / staging buffers in flight per CTA
 constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
 
 enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
@@ -63,6 +64,7 @@ struct alignas(64) TcParams {
     int32_t cw, col_blocks, sw_shift, sw_mask, stage_rows;   // staging tile: column block width, 16-byte chunk swizzle
     int32_t mul_iqf, mul_oqf;
     int32_t lean;                        // epilogue configuration covered by the hoisted fast body
+    int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
     // output / residual addressing for the direct path, in elements
     int64_t out_px, out_py, out_pb, out_off;
     int64_t el_px, el_py, el_pb, el_off;
@@ -75,11 +77,11 @@ struct alignas(64) TcParams {
 struct TcSmemAux {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
-    uint64_t res_full[2];                // residual tile landed in staging buffer
-    uint64_t stage_free[2];              // staging buffer read out by its TMA store
-    uint64_t out_ready[2];               // staging buffer holds a finished output tile
+    uint64_t tmem_full[kMaxBufs];
+    uint64_t tmem_empty[kMaxBufs];
+    uint64_t res_full[kMaxBufs];                // residual tile landed in staging buffer
+    uint64_t stage_free[kMaxBufs];              // staging buffer read out by its TMA store
+    uint64_t out_ready[kMaxBufs];               // staging buffer holds a finished output tile
     uint64_t drain;
     uint32_t tmem_base;
     uint32_t abort;
@@ -257,7 +259,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
     const uint32_t ring_bytes = (uint32_t)(P.stages * (P.a_stage_bytes + P.b_stage_bytes));
     const uint32_t staging_bytes = P.staged ? (uint32_t)(kBM * P.bn) : 0u;           // per buffer, two buffers
     uint8_t* staging = smem + ring_bytes;
-    TcSmemAux* aux = reinterpret_cast<TcSmemAux*>(smem + ring_bytes + 2u * staging_bytes);
+    TcSmemAux* aux = reinterpret_cast<TcSmemAux*>(smem + ring_bytes + (uint32_t)P.nbuf * staging_bytes);
     volatile uint32_t* s_abort = &aux->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,7 +267,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < kMaxBufs; ++a) {
             mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), kEpiWarps);
             mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
             mbar_init(smem_u32(&aux->out_ready[a]), kEpiWarps);
@@ -300,8 +302,8 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 if (fused_staged) {
                     // second input of the fused eltwise: same pixels and features as the output tile
-                    const int a = t & 1;
-                    if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)t >> 1) & 1u) ^ 1u, s_abort, P.status, kErrProducer + 1u)) { ok = false; break; }
+                    const int a = t % P.nbuf;
+                    if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) { ok = false; break; }
                     const uint32_t rf = smem_u32(&aux->res_full[a]);
                     mbar_expect_tx(rf, (uint32_t)(P.stage_rows * P.cw * P.col_blocks));
                     for (int cb = 0; cb < P.col_blocks; ++cb) {
@@ -344,8 +346,8 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
-                const int acc = t & 1;
-                if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)t >> 1) & 1u) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                const int acc = t % P.nbuf;
+                if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.bn);
                 for (int ks = 0; ks < P.k_steps; ++ks) {
@@ -374,8 +376,8 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
             int t = 0;
             for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
-                const int a = t & 1;
-                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue + 2u)) break;
+                const int a = t % P.nbuf;
+                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
                 int tw = 0, th = 0, tb = 0;
                 if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
                 const int n0 = n_tile * P.bn;
@@ -404,7 +406,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         int t = 0; bool ok = true; int cur_n_tile = -1;
         for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
             int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
-            const int acc = t & 1;
+            const int acc = t % P.nbuf;
             const int n0 = n_tile * P.bn;
             if (n_tile != cur_n_tile) {
                 // per-channel constants of this feature range; every warp has left the previous range
@@ -424,11 +426,11 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 named_bar_sync(1, kEpiThreads);
                 cur_n_tile = n_tile;
             }
-            if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue)) { ok = false; break; }
             if (P.staged) {
                 // the staging buffer is ours once its residual tile has landed (fused) or its previous store has read it out
-                const bool got = fused_staged ? mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)t >> 1) & 1u, s_abort, P.status, kErrEpilogue + 1u)
-                                              : mbar_wait(smem_u32(&aux->stage_free[acc]), (((uint32_t)t >> 1) & 1u) ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
+                const bool got = fused_staged ? mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue + 1u)
+                                              : mbar_wait(smem_u32(&aux->stage_free[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
                 if (!got) { ok = false; break; }
             }
             tc_fence_after();
@@ -665,7 +667,8 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
     const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;     // operand signedness in the instruction descriptor
     P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(pl.bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-    P.tmem_cols = (uint32_t)(2 * pl.bn < 32 ? 32 : 2 * pl.bn);
+    P.nbuf = pl.bn >= 256 ? 2 : kMaxBufs;                      // accumulator and staging buffers in flight
+    P.tmem_cols = (uint32_t)(P.nbuf * pl.bn < 32 ? 32 : P.nbuf * pl.bn);
     P.ofm = p.ofm;
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
     const cldnn_b200_tensor& et = p.in_out_opt ? p.out : p.eltw;
@@ -701,7 +704,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     const size_t aux_bytes = sizeof(TcSmemAux);
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
-    size_t staging_total = P.staged ? (size_t)2 * kBM * pl.bn : 0;
+    size_t staging_total = P.staged ? (size_t)P.nbuf * kBM * pl.bn : 0;
     if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) { P.staged = 0; staging_total = 0; }
     if (max_smem < 1024 + aux_bytes + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory");
     int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);

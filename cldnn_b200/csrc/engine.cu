@@ -421,4 +421,48 @@ int32_t cldnn_b200_time(cldnn_b200_prepared p, int32_t warmup, int32_t runs, uin
     return CLDNN_B200_SUCCESS;
 }
 
+int32_t cldnn_b200_graph_begin(cldnn_b200_ctx c)
+{
+    if (!c) return fail(CLDNN_B200_INVALID_ARG, "graph_begin: null ctx");
+    if (c->capturing) return fail(CLDNN_B200_ERROR, "graph_begin: a capture is already in progress");
+    DeviceGuard g(c->device);
+    B200_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    c->capturing = true; c->capture_start_launches = c->launches;
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_graph_end(cldnn_b200_ctx c, cldnn_b200_graph* out)
+{
+    B200_TRY
+    if (!c || !out) return fail(CLDNN_B200_INVALID_ARG, "graph_end: null argument");
+    if (!c->capturing) return fail(CLDNN_B200_ERROR, "graph_end: no capture in progress");
+    DeviceGuard g(c->device);
+    c->capturing = false;
+    cudaGraph_t graph = nullptr;
+    B200_CUDA(cudaStreamEndCapture(c->stream, &graph));
+    auto* gi = new cldnn_b200_graph_impl(); gi->ctx = c; gi->graph = graph;
+    gi->launches = (int)(c->launches - c->capture_start_launches);
+    c->launches = c->capture_start_launches;                 // captured launches have not run yet
+    cudaError_t e = cudaGraphInstantiate(&gi->exec, graph, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(graph); delete gi; return cuda_fail(e, "cudaGraphInstantiate"); }
+    *out = gi; return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+
+int32_t cldnn_b200_graph_launch(cldnn_b200_graph g)
+{
+    if (!g) return fail(CLDNN_B200_INVALID_ARG, "graph_launch: null graph");
+    DeviceGuard dg(g->ctx->device);
+    B200_CUDA(cudaGraphLaunch(g->exec, g->ctx->stream));
+    g->ctx->launches += (uint64_t)g->launches;
+    return CLDNN_B200_SUCCESS;
+}
+
+int32_t cldnn_b200_graph_destroy(cldnn_b200_graph g)
+{
+    if (!g) return CLDNN_B200_SUCCESS;
+    (void)cudaGraphExecDestroy(g->exec); (void)cudaGraphDestroy(g->graph); delete g;
+    return CLDNN_B200_SUCCESS;
+}
+
 }  // extern "C"

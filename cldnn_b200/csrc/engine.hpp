@@ -13,6 +13,8 @@ struct cldnn_b200_ctx_impl {
     cudaStream_t stream = nullptr;
     bool profiling = false;
     uint64_t launches = 0;
+    bool capturing = false;
+    uint64_t capture_start_launches = 0;
     uint32_t* d_status = nullptr;     // device word written by kernels whose bounded wait gave up
     cudaDeviceProp prop{};
 };
@@ -34,6 +36,13 @@ struct cldnn_b200_prepared_impl {
     cldnn_b200_ctx_impl* ctx = nullptr;
     std::function<cudaError_t(cudaStream_t)> fn;   // enqueues the kernel(s)
     int launches = 1;
+};
+
+struct cldnn_b200_graph_impl {
+    cldnn_b200_ctx_impl* ctx = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
 };
 
 namespace b200 {

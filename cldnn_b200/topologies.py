@@ -1,0 +1,144 @@
+"""Synthetic topologies of the benchmark configurations, as engine-independent
+primitive lists (constants are numpy arrays until `realise` uploads them).
+
+ResNet-50 v1, int8: random-init s8 weights uniform in [-127, 127], i32 biases
+uniform in [-4096, 4096], per-output-channel f32 scales uniform in
+[2^-14, 2^-10], u8 224x224x3 inputs uniform in [0, 255]; bottleneck 1x1 / 3x3 /
+1x1 convolutions with the residual sum + ReLU fused into the expanding 1x1
+(fused_conv_eltwise), 3x3/2 max pooling, global average pooling, a 2048 -> 1000
+fully_connected and softmax.  No trained weights or dataset images are involved.
+"""
+import numpy as np
+
+from . import cldnn as cl
+
+
+class Spec:
+    """A topology before upload: primitives in order, numpy constants by id."""
+
+    def __init__(self):
+        self.prims = []
+        self.consts = {}
+        self.input_id = None
+        self.input_layout = None
+        self.outputs = []
+
+    def const(self, id, arr):
+        self.consts[id] = arr
+        self.prims.append(cl.primitive("data", id, array=arr))
+        return id
+
+    def add(self, prim):
+        self.prims.append(prim)
+        return prim.id
+
+    def realise(self, eng):
+        """Upload the constants and return (topology, memories kept alive)."""
+        topo, keep = cl.topology(), []
+        for p in self.prims:
+            if p.kind == "data":
+                m = cl.memory.from_numpy(eng, p.args["array"])
+                keep.append(m)
+                topo.add(cl.data(p.id, m))
+            else:
+                topo.add(p)
+        return topo, keep
+
+
+def _conv_consts(spec, rng, name, cin, cout, k, scale_lo, scale_hi, w_range=127, float_bias=False):
+    w = rng.integers(-w_range, w_range + 1, size=(cout, cin, k, k), dtype=np.int64).astype(np.int8)
+    spec.const(name + "_w", w)
+    if float_bias:
+        spec.const(name + "_b", rng.uniform(-8.0, 8.0, size=cout).astype(np.float32))
+    else:
+        spec.const(name + "_b", rng.integers(-4096, 4097, size=cout, dtype=np.int64).astype(np.int32))
+    spec.const(name + "_q", rng.uniform(scale_lo, scale_hi, size=cout).astype(np.float32))
+
+
+def resnet50_int8(batch, seed=2019, image=224, scale_lo=2.0 ** -14, scale_hi=2.0 ** -10, classes=1000, widths=(64, 128, 256, 512),
+                  blocks=(3, 4, 6, 3), stem=64):
+    rng = np.random.default_rng(seed)
+    s = Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.u8, cl.format.bfyx, cl.tensor(batch, 3, image, image))
+    s.add(cl.input_layout("input", s.input_layout))
+    _conv_consts(s, rng, "conv1", 3, stem, 7, scale_lo, scale_hi)
+    s.add(cl.convolution("conv1", "input", "conv1_w", "conv1_b", "conv1_q", output_data_type=dt.u8, stride=(2, 2), input_offset=(-3, -3),
+                         with_activation=True))
+    s.add(cl.pooling("pool1", "conv1", cl.pooling_mode.max, size=(3, 3), stride=(2, 2)))
+    x, cin = "pool1", stem
+    n_stage = len(widths)
+    for si, (w, nb) in enumerate(zip(widths, blocks)):
+        for b in range(nb):
+            name = "s%d_b%d" % (si + 2, b)
+            stride = 2 if (b == 0 and si > 0) else 1
+            last = si == n_stage - 1 and b == nb - 1
+            _conv_consts(s, rng, name + "_a", cin, w, 1, scale_lo, scale_hi)
+            s.add(cl.convolution(name + "_a", x, name + "_a_w", name + "_a_b", name + "_a_q", output_data_type=dt.u8, stride=(stride, stride),
+                                 with_activation=True))
+            _conv_consts(s, rng, name + "_b", w, w, 3, scale_lo, scale_hi)
+            s.add(cl.convolution(name + "_b", name + "_a", name + "_b_w", name + "_b_b", name + "_b_q", output_data_type=dt.u8,
+                                 input_offset=(-1, -1), with_activation=True))
+            if b == 0:
+                _conv_consts(s, rng, name + "_proj", cin, 4 * w, 1, scale_lo, scale_hi)
+                s.add(cl.convolution(name + "_proj", x, name + "_proj_w", name + "_proj_b", name + "_proj_q", output_data_type=dt.i8,
+                                     stride=(stride, stride)))
+                shortcut = name + "_proj"
+            else:
+                shortcut = x
+            _conv_consts(s, rng, name + "_c", w, 4 * w, 1, scale_lo, scale_hi)
+            s.add(cl.fused_conv_eltwise(name + "_c", name + "_b", shortcut, name + "_c_w", name + "_c_b", name + "_c_q",
+                                        eltw_activation=True, output_data_type=dt.i8 if last else dt.u8))
+            x, cin = name + "_c", 4 * w
+    s.add(cl.pooling("pool5", x, cl.pooling_mode.average, global_pooling=True))
+    rngf = np.random.default_rng(seed + 1)
+    s.const("fc_w", rngf.integers(-127, 128, size=(classes, cin, 1, 1), dtype=np.int64).astype(np.int8))
+    s.const("fc_b", rngf.uniform(-8.0, 8.0, size=classes).astype(np.float32))
+    s.const("fc_q", rngf.uniform(scale_lo, scale_hi, size=classes).astype(np.float32))
+    s.const("fc_c", rngf.uniform(0.03, 0.06, size=classes).astype(np.float32))
+    s.add(cl.fully_connected("fc", "pool5", "fc_w", "fc_b", "fc_q", "fc_c"))
+    s.add(cl.reorder("fc_f32", "fc", cl.format.bfyx, dt.f32))
+    s.add(cl.softmax("prob", "fc_f32"))
+    s.outputs = ["prob", "fc"]
+    return s
+
+
+def conv_ops(spec):
+    """Multiply-add operations x2 of every convolution / fully_connected of a spec, per image (padding taps counted)."""
+    shapes, total = {}, 0
+    lay = spec.input_layout
+    shapes[spec.input_id] = (lay.size.feature, lay.size.y, lay.size.x)
+    per_layer = []
+    for p in spec.prims:
+        a = p.args
+        if p.kind == "data" or p.kind == "input_layout":
+            continue
+        c, h, w = shapes[a["input"]]
+        if p.kind in ("convolution", "fused_conv_eltwise"):
+            wt = spec.consts[a["weights"]]
+            k, _, kh, kw = wt.shape
+            ho = (h - 2 * a["input_offset"][1] - ((kh - 1) * a["dilation"][1] + 1)) // a["stride"][1] + 1
+            wo = (w - 2 * a["input_offset"][0] - ((kw - 1) * a["dilation"][0] + 1)) // a["stride"][0] + 1
+            ops = 2 * k * ho * wo * (c // a.get("groups", 1)) * kh * kw
+            shapes[p.id] = (k, ho, wo)
+            per_layer.append((p.id, p.kind, ops, (c, k, h, kh, a["stride"][0])))
+            total += ops
+        elif p.kind == "fully_connected":
+            wt = spec.consts[a["weights"]]
+            ops = 2 * wt.shape[0] * c * h * w
+            shapes[p.id] = (wt.shape[0], 1, 1)
+            per_layer.append((p.id, p.kind, ops, (c, wt.shape[0], 1, 1, 1)))
+            total += ops
+        elif p.kind == "pooling":
+            if a["global_pooling"]:
+                shapes[p.id] = (c, 1, 1)
+            else:
+                from . import cldnn as _c  # noqa: F401
+                ext_y = max(a["size"][1], a["stride"][1]); ext_x = max(a["size"][0], a["stride"][0])
+                ho = min((h - 2 * a["input_offset"][1] - ext_y + a["stride"][1] - 1) // a["stride"][1] + 1, (h - a["input_offset"][1] - 1) // a["stride"][1] + 1)
+                wo = min((w - 2 * a["input_offset"][0] - ext_x + a["stride"][0] - 1) // a["stride"][0] + 1, (w - a["input_offset"][0] - 1) // a["stride"][0] + 1)
+                shapes[p.id] = (c, ho, wo)
+        else:
+            shapes[p.id] = (c, h, w)
+    return total, per_layer

@@ -219,6 +219,7 @@ typedef struct cldnn_b200_mem_impl*      cldnn_b200_mem;
 typedef struct cldnn_b200_event_impl*    cldnn_b200_event;
 typedef struct cldnn_b200_kernel_impl*   cldnn_b200_kernel;
 typedef struct cldnn_b200_prepared_impl* cldnn_b200_prepared;
+typedef struct cldnn_b200_graph_impl*    cldnn_b200_graph;
 
 /* engine_info_internal (src/gpu/engine_info.cpp:190-231) */
 typedef struct cldnn_b200_engine_info {
@@ -300,6 +301,15 @@ CLDNN_B200_API int32_t cldnn_b200_prepared_destroy(cldnn_b200_prepared p);
 /* kernel_runner::run_kernels (src/gpu/kernel_runner.cpp:112-196): warm-up +
  * `runs` timed replays with CUDA events, average nanoseconds per run         */
 CLDNN_B200_API int32_t cldnn_b200_time(cldnn_b200_prepared p, int32_t warmup, int32_t runs, uint64_t* avg_ns);
+/* Execution-order replay: everything run between graph_begin and graph_end is
+ * recorded instead of executed (CUDA stream capture) and becomes one launchable
+ * object.  This is what network_impl::execute's per-primitive enqueue loop
+ * (src/network.cpp:217-275) collapses to for a fixed-shape network: one
+ * submission per inference.                                                  */
+CLDNN_B200_API int32_t cldnn_b200_graph_begin(cldnn_b200_ctx ctx);
+CLDNN_B200_API int32_t cldnn_b200_graph_end(cldnn_b200_ctx ctx, cldnn_b200_graph* out);
+CLDNN_B200_API int32_t cldnn_b200_graph_launch(cldnn_b200_graph g);
+CLDNN_B200_API int32_t cldnn_b200_graph_destroy(cldnn_b200_graph g);
 /* device-side status word: 0 when the last launches completed normally,
  * otherwise a code written by a kernel whose bounded wait gave up           */
 CLDNN_B200_API int32_t cldnn_b200_ctx_device_status(cldnn_b200_ctx ctx, uint32_t* status);

@@ -1,0 +1,157 @@
+"""Whole topologies through the host layer (topology -> program -> network) on the GPU, against the same topology run
+primitive by primitive on the CPU oracle.  Integer outputs must be bit-exact."""
+import numpy as np
+import pytest
+
+import oracle_net
+from cldnn_b200 import abi, topologies
+from cldnn_b200 import cldnn as cl
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    return cl.engine(0)
+
+
+def _run(eng, spec, x, **opts):
+    topo, keep = spec.realise(eng)
+    net = cl.network(eng, topo, cl.build_options(outputs=spec.outputs, **opts))
+    net.set_input_data(spec.input_id, cl.memory.from_numpy(eng, x))
+    net.execute()
+    return net, {o: net.get_output(o).to_numpy() for o in spec.outputs}
+
+
+def _input(spec, seed=99):
+    lay = spec.input_layout
+    return np.random.default_rng(seed).integers(0, 256, size=(lay.size.batch, lay.size.feature, lay.size.y, lay.size.x)).astype(np.uint8)
+
+
+def _compare(spec, want, got):
+    for k in spec.outputs:
+        if want[k].dtype.kind in "iu":
+            assert np.array_equal(want[k], got[k]), "%s: %d mismatches" % (k, int((want[k] != got[k]).sum()))
+        else:
+            np.testing.assert_allclose(got[k], want[k], rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.parametrize("optimize", [False, True])
+def test_small_residual_network_bit_exact(eng, optimize):
+    spec = topologies.resnet50_int8(3, seed=5, image=64, widths=(32, 64), blocks=(2, 2), stem=32, classes=40)
+    x = _input(spec)
+    stats = {}
+    want = oracle_net.run(spec, {spec.input_id: x}, stats=stats)
+    assert stats["fc:out_of_range"] == 0
+    net, got = _run(eng, spec, x, optimize_data=optimize)
+    _compare(spec, want, got)
+    info = net.primitives_info()
+    convs = [r for r in info if r["type"] in ("convolution", "fused_conv_eltwise", "fully_connected")]
+    if optimize:
+        # the layout optimiser moved the 8-bit path to byxf_af32 and every convolution onto the tensor-core kernel
+        assert all(r["kernel"] == "conv_i8_tc" and r["format"] == "byxf_af32" for r in convs)
+        assert any(r["kernel"] == "pooling_i8_byxf" for r in info)
+    else:
+        # optimize_data(false): reference-order kernels in the caller's layout, like the reference's own tests
+        assert all(r["kernel"] in ("conv_ref", "fc_ref") and r["format"] == "bfyx" for r in convs)
+    # repeated execution replays the captured graph and gives the same bits
+    net.execute()
+    assert np.array_equal(net.get_output("fc").to_numpy(), got["fc"])
+
+
+def test_resnet50_int8_batch2_bit_exact(eng):
+    """BASELINE configuration: ResNet-50 v1 int8, full size (224x224), here at batch 2 so the CPU oracle finishes in seconds."""
+    spec = topologies.resnet50_int8(2)
+    x = _input(spec, seed=7)
+    stats = {}
+    want = oracle_net.run(spec, {spec.input_id: x}, stats=stats)
+    assert stats["fc:out_of_range"] == 0
+    layers = [v for v in stats.values() if isinstance(v, dict)]
+    assert np.mean([v["saturated"] for v in layers]) < 0.2            # the comparison is not on saturated constants
+    net, got = _run(eng, spec, x, optimize_data=True)
+    _compare(spec, want, got)
+    assert (want["fc"] != 0).mean() > 0.5
+    assert net.stats()["launches_per_execute"] >= 53
+
+
+def test_batch_independence_of_the_sharded_path(eng):
+    """Images are independent units: running a batch in two halves gives the bits of the whole batch (the property the
+    multi-GPU data-parallel split relies on)."""
+    spec4 = topologies.resnet50_int8(4, seed=3, image=64, widths=(32, 64), blocks=(1, 1), stem=32, classes=24)
+    spec2 = topologies.resnet50_int8(2, seed=3, image=64, widths=(32, 64), blocks=(1, 1), stem=32, classes=24)
+    x = _input(spec4, seed=1)
+    _, whole = _run(eng, spec4, x, optimize_data=True)
+    _, lo = _run(eng, spec2, x[:2], optimize_data=True)
+    _, hi = _run(eng, spec2, x[2:], optimize_data=True)
+    assert np.array_equal(whole["fc"], np.concatenate([lo["fc"], hi["fc"]]))
+
+
+def test_conv_quantized_kat_through_the_topology_api(eng):
+    """ConvQuantizedTest_u8_to_u8 of the reference (tests/test_cases/convolution_gpu_test.cpp:4133-4166), written the way
+    the reference writes it: input_layout + data + convolution, optimize_data(false), exact integer equality."""
+    from golden import kat_conv_quantized
+    feats = kat_conv_quantized.CASES["u8_to_u8"]["features"]
+    n = len(feats)
+    inp = np.array([f[0] for f in feats], dtype=np.uint8).reshape(1, n, 1, 4)
+    w = np.zeros((n, n, 1, 3), dtype=np.int8)
+    for i, f in enumerate(feats):
+        w[i, i, 0, :] = f[1]
+    input_mem = cl.memory.from_numpy(eng, inp)
+    topo = cl.topology(
+        cl.input_layout("input", input_mem.get_layout()),
+        cl.data("weights", cl.memory.from_numpy(eng, w)),
+        cl.data("biases", cl.memory.from_numpy(eng, np.array([f[2] for f in feats], dtype=np.int32))),
+        cl.data("quantization", cl.memory.from_numpy(eng, np.array([f[3] for f in feats], dtype=np.float32))),
+        cl.convolution("conv", "input", "weights", "biases", "quantization", output_data_type=cl.data_types.u8, with_activation=True))
+    net = cl.network(eng, topo, cl.build_options(optimize_data=False))
+    net.set_input_data("input", input_mem)
+    net.execute()
+    out = net.get_output("conv")
+    lay = out.get_layout()
+    assert (lay.format, lay.size.y, lay.size.x, lay.size.feature, lay.size.batch) == (cl.format.bfyx, 1, 2, n, 1)
+    expected = np.clip(np.array([f[4] for f in feats]), 0, 255)
+    assert np.array_equal(out.to_numpy()[0, :, 0, :].astype(np.int64), expected)
+
+
+def test_activation_and_eltwise_fusing_passes(eng):
+    """conv -> eltwise(sum) -> relu collapses into one fused_conv_eltwise under optimize_data (prepare_primitive_fusing +
+    prepare_conv_eltw_fusing) and computes what the unfused graph computes when nothing saturates."""
+    rng = np.random.default_rng(0)
+    x = rng.integers(0, 8, size=(2, 32, 6, 6)).astype(np.uint8)
+    w = rng.integers(-3, 4, size=(32, 32, 3, 3)).astype(np.int8)
+    other = rng.integers(0, 16, size=(2, 32, 6, 6)).astype(np.uint8)
+    def build(e):
+        xm, om = cl.memory.from_numpy(e, x), cl.memory.from_numpy(e, other)
+        topo = cl.topology(
+            cl.input_layout("input", xm.get_layout()), cl.input_layout("other", om.get_layout()),
+            cl.data("w", cl.memory.from_numpy(e, w)), cl.data("q", cl.memory.from_numpy(e, np.full(32, 0.25, dtype=np.float32))),
+            cl.convolution("conv", "input", "w", "", "q", output_data_type=cl.data_types.i8, input_offset=(-1, -1)),
+            cl.eltwise("sum", "conv", "other", cl.eltwise_mode.sum, quantized=True),
+            cl.activation("relu", "sum", cl.activation_func.relu))
+        return topo, xm, om
+    outs = {}
+    for optimize in (False, True):
+        topo, xm, om = build(eng)
+        net = cl.network(eng, topo, cl.build_options(optimize_data=optimize))
+        net.set_input_data("input", xm); net.set_input_data("other", om)
+        net.execute()
+        outs[optimize] = net.get_output("relu").to_numpy()
+        kinds = [r["type"] for r in net.primitives_info() if r["kernel"]]
+        if optimize:
+            assert "fused_conv_eltwise" in kinds and "eltwise" not in kinds and "activation" not in kinds
+        else:
+            assert kinds.count("convolution") == 1 and "eltwise" in kinds and "activation" in kinds
+    assert np.array_equal(outs[False], outs[True])
+
+
+def test_errors_surface_as_status_codes(eng):
+    xm = cl.memory.from_numpy(eng, np.zeros((1, 8, 4, 4), dtype=np.uint8))
+    bad = cl.topology(cl.input_layout("input", xm.get_layout()),
+                      cl.data("w", cl.memory.from_numpy(eng, np.zeros((8, 4, 3, 3), dtype=np.int8))),      # 4 input features, tensor has 8
+                      cl.convolution("conv", "input", "w"))
+    with pytest.raises(cl.error) as e:
+        cl.network(eng, bad)
+    assert e.value.status == abi.DIMENSION_MISMATCH
+    with pytest.raises(cl.error) as e:
+        cl.network(eng, cl.topology(cl.input_layout("input", xm.get_layout()), cl.softmax("s", "nowhere")))
+    assert e.value.status == abi.INVALID_ARG
