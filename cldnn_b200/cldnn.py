@@ -55,7 +55,9 @@ _SIGNATURES = {
     "cldnn_host_engine_create": (_i, [_i, _u, C.POINTER(_vp)]),
     "cldnn_host_engine_release": (_i, [_vp]),
     "cldnn_host_engine_info": (_i, [_vp, C.POINTER(abi.EngineInfo)]),
+    "cldnn_host_engine_stream": (_i, [_vp, C.POINTER(_vp)]),
     "cldnn_host_memory_allocate": (_i, [_vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "cldnn_host_memory_attach": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, C.POINTER(_vp)]),
     "cldnn_host_memory_release": (_i, [_vp]),
     "cldnn_host_memory_write": (_i, [_vp, _vp, C.c_size_t]),
     "cldnn_host_memory_read": (_i, [_vp, _vp, C.c_size_t]),
@@ -82,6 +84,7 @@ _SIGNATURES = {
     "cldnn_host_network_wait": (_i, [_vp]),
     "cldnn_host_network_get_output": (_i, [_vp, _cp, C.POINTER(_vp)]),
     "cldnn_host_network_info": (_i, [_vp, _cp, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "cldnn_host_network_profiling": (_i, [_vp, _cp, C.c_size_t, C.POINTER(C.c_size_t)]),
     "cldnn_host_network_stats": (_i, [_vp, C.POINTER(C.c_uint64), C.POINTER(C.c_size_t)]),
 }
 
@@ -158,6 +161,11 @@ class engine:
         _check(self.lib.cldnn_host_engine_info(self.handle, C.byref(info)))
         return info
 
+    def stream(self):
+        s = _vp()
+        _check(self.lib.cldnn_host_engine_stream(self.handle, C.byref(s)))
+        return s.value
+
     def release(self):
         if self.handle:
             self.lib.cldnn_host_engine_release(self.handle)
@@ -176,6 +184,14 @@ class memory:
     def allocate(eng, lay):
         h = _vp()
         _check(eng.lib.cldnn_host_memory_allocate(eng.handle, lay.data_type, lay.format, lay.size.batch, lay.size.feature, lay.size.x, lay.size.y, C.byref(h)))
+        return memory(eng.lib, h)
+
+    @staticmethod
+    def attach(eng, lay, device_ptr):
+        """Wrap device memory owned by the caller (cldnn::memory::attach)."""
+        h = _vp()
+        _check(eng.lib.cldnn_host_memory_attach(eng.handle, lay.data_type, lay.format, lay.size.batch, lay.size.feature, lay.size.x, lay.size.y,
+                                                device_ptr, C.byref(h)))
         return memory(eng.lib, h)
 
     @staticmethod
@@ -435,6 +451,14 @@ class network:
             rows.append(dict(id=pid, type=kind, kernel=kernel, tune=int(tune), format=fmt, data_type=int(dt),
                              dims=tuple(int(v) for v in dims.split(",")), fused=[f for f in fused.split(",") if f], is_output=is_out == "1"))
         return rows
+
+    def profiling_info(self):
+        """{primitive id: device nanoseconds} of the last execute (engine created with enable_profiling)."""
+        need = C.c_size_t()
+        _check(self.lib.cldnn_host_network_profiling(self.handle, None, 0, C.byref(need)))
+        buf = C.create_string_buffer(need.value)
+        _check(self.lib.cldnn_host_network_profiling(self.handle, buf, need.value, None))
+        return {l.split("|")[0]: int(l.split("|")[1]) for l in buf.value.decode().splitlines()}
 
     def stats(self):
         launches, pool = C.c_uint64(), C.c_size_t()

@@ -160,13 +160,32 @@ int32_t cldnn_b200_mem_alloc(cldnn_b200_ctx c, size_t bytes, cldnn_b200_mem* out
     B200_CATCH
 }
 
+int32_t cldnn_b200_mem_attach(cldnn_b200_ctx c, void* device_ptr, size_t bytes, cldnn_b200_mem* out)
+{
+    B200_TRY
+    if (!c || !out || !device_ptr) return fail(CLDNN_B200_INVALID_ARG, "mem_attach: null argument");
+    *out = nullptr;
+    cudaPointerAttributes attr{};
+    cudaError_t e = cudaPointerGetAttributes(&attr, device_ptr);
+    if (e != cudaSuccess || (attr.type != cudaMemoryTypeDevice && attr.type != cudaMemoryTypeManaged)) {
+        (void)cudaGetLastError();
+        return fail(CLDNN_B200_INVALID_ARG, "mem_attach: the pointer is not device memory");
+    }
+    if (attr.device != c->device) return fail(CLDNN_B200_INVALID_ARG, "mem_attach: the pointer belongs to another device");
+    auto* m = new cldnn_b200_mem_impl();
+    m->ctx = c; m->dev = device_ptr; m->bytes = bytes; m->attached = true;
+    *out = m;
+    return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+
 int32_t cldnn_b200_mem_free(cldnn_b200_mem m)
 {
     if (!m) return CLDNN_B200_SUCCESS;
     DeviceGuard g(m->ctx->device);
     (void)cudaStreamSynchronize(m->ctx->stream);
     if (m->mapped) (void)cudaFreeHost(m->mapped);
-    (void)cudaFree(m->dev);
+    if (!m->attached) (void)cudaFree(m->dev);
     delete m;
     return CLDNN_B200_SUCCESS;
 }

@@ -23,6 +23,7 @@ struct cldnn_b200_mem_impl {
     cldnn_b200_ctx_impl* ctx = nullptr;
     void* dev = nullptr;
     size_t bytes = 0;
+    bool attached = false;            // wraps memory owned by the caller
     void* mapped = nullptr;           // pinned staging while locked
     int map_count = 0;
 };

@@ -26,6 +26,7 @@ _SIGNATURES = {
     "cldnn_b200_ctx_launch_count": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "cldnn_b200_ctx_device_status": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint32)]),
     "cldnn_b200_mem_alloc": (C.c_int32, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "cldnn_b200_mem_attach": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
     "cldnn_b200_mem_free": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_mem_size": (C.c_int32, [C.c_void_p, C.POINTER(C.c_size_t)]),
     "cldnn_b200_mem_devptr": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),

@@ -36,6 +36,10 @@ int32_t cldnn_host_engine_create(int32_t device, uint32_t prof, cldnn_host_engin
     return guarded([&] { need(out, "engine_create"); *out = nullptr; *out = new cldnn_host_engine_impl{engine(device, prof != 0)}; });
 }
 int32_t cldnn_host_engine_release(cldnn_host_engine e) { delete e; return CLDNN_B200_SUCCESS; }
+int32_t cldnn_host_engine_stream(cldnn_host_engine e, void** stream)
+{
+    return guarded([&] { need(e, "engine_stream"); need(stream, "engine_stream"); *stream = e->e.stream(); });
+}
 int32_t cldnn_host_engine_info(cldnn_host_engine e, cldnn_b200_engine_info* info)
 {
     return guarded([&] { need(e, "engine_info"); need(info, "engine_info"); *info = e->e.get_info(); });
@@ -47,6 +51,13 @@ int32_t cldnn_host_memory_allocate(cldnn_host_engine e, int32_t dt, int32_t fmt,
         need(e, "memory_allocate"); need(out, "memory_allocate"); *out = nullptr;
         if (b < 1 || f < 1 || x < 1 || y < 1) throw error("memory_allocate: sizes must be positive", CLDNN_B200_INVALID_ARG);
         *out = new cldnn_host_memory_impl{memory::allocate(e->e, layout((data_types)dt, fmt, tensor(b, f, x, y)))};
+    });
+}
+int32_t cldnn_host_memory_attach(cldnn_host_engine e, int32_t dt, int32_t fmt, int32_t b, int32_t f, int32_t x, int32_t y, void* dev, cldnn_host_memory* out)
+{
+    return guarded([&] {
+        need(e, "memory_attach"); need(out, "memory_attach"); need(dev, "memory_attach"); *out = nullptr;
+        *out = new cldnn_host_memory_impl{memory::attach(e->e, layout((data_types)dt, fmt, tensor(b, f, x, y)), dev)};
     });
 }
 int32_t cldnn_host_memory_release(cldnn_host_memory m) { delete m; return CLDNN_B200_SUCCESS; }
@@ -189,6 +200,17 @@ int32_t cldnn_host_network_info(cldnn_host_network n, char* buffer, size_t buffe
             ss << i.id << "|" << i.type << "|" << i.kernel << "|" << i.tune << "|" << format::name(i.output.fmt) << "|" << (int)i.output.data_type << "|"
                << i.output.size.batch << "," << i.output.size.feature << "," << i.output.size.y << "," << i.output.size.x << "|" << i.original_ids << "|"
                << (i.is_output ? 1 : 0) << "\n";
+        const std::string s = ss.str();
+        if (needed) *needed = s.size() + 1;
+        if (buffer && buffer_bytes) { const size_t k = std::min(buffer_bytes - 1, s.size()); std::memcpy(buffer, s.data(), k); buffer[k] = 0; }
+    });
+}
+int32_t cldnn_host_network_profiling(cldnn_host_network n, char* buffer, size_t buffer_bytes, size_t* needed)
+{
+    return guarded([&] {
+        need(n, "network_profiling");
+        std::stringstream ss;
+        for (auto& i : n->n.get_profiling_info()) ss << i.first << "|" << i.second << "\n";
         const std::string s = ss.str();
         if (needed) *needed = s.size() + 1;
         if (buffer && buffer_bytes) { const size_t k = std::min(buffer_bytes - 1, s.size()); std::memcpy(buffer, s.data(), k); buffer[k] = 0; }

@@ -67,6 +67,8 @@ class engine {
 public:
     explicit engine(int32_t device = 0, bool enable_profiling = false);
     cldnn_b200_engine_info get_info() const;
+    void* stream() const;                       // cudaStream_t of the engine's queue
+    bool profiling() const;
     std::shared_ptr<engine_impl> impl;
 };
 
@@ -75,6 +77,8 @@ class memory {
 public:
     memory() {}
     static memory allocate(const engine& e, const layout& l);
+    // cldnn::memory::attach for device memory: the caller owns `device_ptr` and keeps it alive
+    static memory attach(const engine& e, const layout& l, void* device_ptr);
     const layout& get_layout() const;
     size_t size() const;
     void write(const void* host, size_t bytes);         // set_values
@@ -187,6 +191,9 @@ public:
     std::vector<std::string> get_output_ids() const;
     std::vector<primitive_info> get_primitives_info() const;   // executed order, with chosen kernels
     uint64_t launches_per_execute() const;
+    // per-primitive device time of the last execute() when the engine was created with profiling enabled
+    // (event::get_profiling_info of the reference, src/gpu/ocl_base_event.cpp:68-92): (primitive id, nanoseconds)
+    std::vector<std::pair<std::string, uint64_t>> get_profiling_info() const;
     size_t device_memory_bytes() const;         // bytes held by the memory pool for intermediates
     void wait();
     std::shared_ptr<network_impl> impl;

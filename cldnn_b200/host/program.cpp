@@ -77,6 +77,7 @@ class engine_impl {
 public:
     cldnn_b200_ctx ctx = nullptr;
     cldnn_b200_engine_info info{};
+    bool profiling = false;
     std::map<std::string, cldnn_b200_kernel> kernels;
     ~engine_impl() { if (ctx) cldnn_b200_ctx_destroy(ctx); }
     cldnn_b200_kernel kernel(const std::string& name)
@@ -94,7 +95,10 @@ engine::engine(int32_t device, bool enable_profiling) : impl(std::make_shared<en
 {
     check(cldnn_b200_ctx_create(device, enable_profiling ? 1u : 0u, &impl->ctx), "engine");
     check(cldnn_b200_ctx_info(impl->ctx, &impl->info), "engine info");
+    impl->profiling = enable_profiling;
 }
+void* engine::stream() const { void* s = nullptr; check(cldnn_b200_ctx_stream(impl->ctx, &s), "engine stream"); return s; }
+bool engine::profiling() const { return impl->profiling; }
 cldnn_b200_engine_info engine::get_info() const { return impl->info; }
 
 // one device allocation; several memory objects may view it over disjoint lifetimes (memory pool)
@@ -121,6 +125,16 @@ memory memory::allocate(const engine& e, const layout& l)
 {
     memory m; m.impl = std::make_shared<memory_impl>();
     m.impl->l = l; m.impl->blk = new_block(e.impl, l.bytes_count());
+    return m;
+}
+memory memory::attach(const engine& e, const layout& l, void* device_ptr)
+{
+    memory m; m.impl = std::make_shared<memory_impl>();
+    m.impl->l = l;
+    auto b = std::make_shared<block>(); b->eng = e.impl; b->bytes = std::max<size_t>(l.bytes_count(), 16);
+    check(cldnn_b200_mem_attach(e.impl->ctx, device_ptr, b->bytes, &b->mem), "memory::attach");
+    b->dev = device_ptr;
+    m.impl->blk = b;
     return m;
 }
 const layout& memory::get_layout() const { return impl->l; }
@@ -253,6 +267,7 @@ public:
     uint64_t launches = 0;
     size_t pool_bytes = 0;
     std::map<std::string, std::pair<std::string, int>> tuning_cache;   // hash -> (kernel, tune)
+    std::vector<std::pair<cldnn_b200_event, cldnn_b200_event>> prof_events;   // per node of `order`, profiling only
     bool cache_dirty = false;
 
     ~network_impl()
@@ -260,6 +275,7 @@ public:
         if (eng && eng->ctx) cldnn_b200_ctx_sync(eng->ctx);
         if (graph) cldnn_b200_graph_destroy(graph);
         for (auto& n : nodes) if (n->prepared) cldnn_b200_prepared_destroy(n->prepared);
+        for (auto& pe : prof_events) { cldnn_b200_event_destroy(pe.first); cldnn_b200_event_destroy(pe.second); }
     }
 
     node* get(const std::string& id)
@@ -843,7 +859,7 @@ void network_impl::execute()
         save_cache();
         check(cldnn_b200_ctx_sync(eng->ctx), "sync");
         launches = 0; for (node* n : order) if (n->prepared) ++launches;
-        if (opts.use_graph) {
+        if (opts.use_graph && !eng->profiling) {
             check(cldnn_b200_graph_begin(eng->ctx), "graph begin");
             try { for (node* n : order) run_prepared(n); }
             catch (...) { cldnn_b200_graph cg = nullptr; cldnn_b200_graph_end(eng->ctx, &cg); if (cg) cldnn_b200_graph_destroy(cg); throw; }
@@ -851,8 +867,20 @@ void network_impl::execute()
         }
         inputs_changed = false;
     }
-    if (graph) check(cldnn_b200_graph_launch(graph), "graph launch");
-    else for (node* n : order) run_prepared(n);
+    if (graph) { check(cldnn_b200_graph_launch(graph), "graph launch"); return; }
+    if (!eng->profiling) { for (node* n : order) run_prepared(n); return; }
+    // profiling: one event pair per primitive, no graph
+    if (prof_events.size() != order.size()) {
+        for (auto& pe : prof_events) { cldnn_b200_event_destroy(pe.first); cldnn_b200_event_destroy(pe.second); }
+        prof_events.assign(order.size(), {nullptr, nullptr});
+        for (auto& pe : prof_events) { check(cldnn_b200_event_create(eng->ctx, &pe.first), "event"); check(cldnn_b200_event_create(eng->ctx, &pe.second), "event"); }
+    }
+    for (size_t i = 0; i < order.size(); ++i) {
+        if (!order[i]->prepared) continue;
+        check(cldnn_b200_event_record(prof_events[i].first), "event record");
+        run_prepared(order[i]);
+        check(cldnn_b200_event_record(prof_events[i].second), "event record");
+    }
 }
 
 // --------------------------------------------------------------------------------------
@@ -894,6 +922,19 @@ std::vector<primitive_info> network::get_primitives_info() const
     return v;
 }
 uint64_t network::launches_per_execute() const { return impl->launches; }
+std::vector<std::pair<std::string, uint64_t>> network::get_profiling_info() const
+{
+    std::vector<std::pair<std::string, uint64_t>> v;
+    if (impl->prof_events.size() != impl->order.size()) return v;
+    check(cldnn_b200_ctx_sync(impl->eng->ctx), "sync");
+    for (size_t i = 0; i < impl->order.size(); ++i) {
+        if (!impl->order[i]->prepared) continue;
+        uint64_t ns = 0;
+        check(cldnn_b200_event_elapsed_ns(impl->prof_events[i].first, impl->prof_events[i].second, &ns), "event elapsed");
+        v.push_back({impl->order[i]->p.id, ns});
+    }
+    return v;
+}
 size_t network::device_memory_bytes() const { return impl->pool_bytes; }
 
 }  // namespace cldnn

@@ -253,6 +253,9 @@ CLDNN_B200_API int32_t cldnn_b200_ctx_launch_count(cldnn_b200_ctx ctx, uint64_t*
 
 /* ---- memory: replaces gpu_buffer (src/gpu/memory_gpu.cpp:37-89) ----------- */
 CLDNN_B200_API int32_t cldnn_b200_mem_alloc(cldnn_b200_ctx ctx, size_t bytes, cldnn_b200_mem* out); /* zero filled */
+/* cldnn_attach_memory (api/C/cldnn.h:770-772), for device memory: wraps a device pointer the caller owns; the caller keeps
+ * it alive for the lifetime of the memory object and of every launch prepared on it.  mem_free releases the wrapper only. */
+CLDNN_B200_API int32_t cldnn_b200_mem_attach(cldnn_b200_ctx ctx, void* device_ptr, size_t bytes, cldnn_b200_mem* out);
 CLDNN_B200_API int32_t cldnn_b200_mem_free(cldnn_b200_mem mem);
 CLDNN_B200_API int32_t cldnn_b200_mem_size(cldnn_b200_mem mem, size_t* bytes);
 CLDNN_B200_API int32_t cldnn_b200_mem_devptr(cldnn_b200_mem mem, void** dev);

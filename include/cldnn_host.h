@@ -44,9 +44,13 @@ CLDNN_B200_API const char* cldnn_host_last_error(void);
 CLDNN_B200_API int32_t cldnn_host_engine_create(int32_t device, uint32_t enable_profiling, cldnn_host_engine* out);
 CLDNN_B200_API int32_t cldnn_host_engine_release(cldnn_host_engine e);
 CLDNN_B200_API int32_t cldnn_host_engine_info(cldnn_host_engine e, cldnn_b200_engine_info* info);
+/* the engine's queue as a cudaStream_t, for callers that order their own copies with the network's work */
+CLDNN_B200_API int32_t cldnn_host_engine_stream(cldnn_host_engine e, void** stream);
 
 /* cldnn_allocate_memory / cldnn_release_memory / cldnn_lock_memory (as explicit copies), api/C/cldnn.h:760-800 */
 CLDNN_B200_API int32_t cldnn_host_memory_allocate(cldnn_host_engine e, int32_t data_type, int32_t format, int32_t b, int32_t f, int32_t x, int32_t y, cldnn_host_memory* out);
+/* cldnn_attach_memory, api/C/cldnn.h:770-772, for a device pointer owned by the caller */
+CLDNN_B200_API int32_t cldnn_host_memory_attach(cldnn_host_engine e, int32_t data_type, int32_t format, int32_t b, int32_t f, int32_t x, int32_t y, void* device_ptr, cldnn_host_memory* out);
 CLDNN_B200_API int32_t cldnn_host_memory_release(cldnn_host_memory m);
 CLDNN_B200_API int32_t cldnn_host_memory_write(cldnn_host_memory m, const void* host, size_t bytes);
 CLDNN_B200_API int32_t cldnn_host_memory_read(cldnn_host_memory m, void* host, size_t bytes);
@@ -114,6 +118,9 @@ CLDNN_B200_API int32_t cldnn_host_network_wait(cldnn_host_network n);
 CLDNN_B200_API int32_t cldnn_host_network_get_output(cldnn_host_network n, const char* id, cldnn_host_memory* out);
 /* executed primitives, one per line: "id|type|kernel|tune|format|dtype|b,f,y,x|fused ids|is_output"; cldnn_get_primitive_info */
 CLDNN_B200_API int32_t cldnn_host_network_info(cldnn_host_network n, char* buffer, size_t buffer_bytes, size_t* needed);
+/* per-primitive device time of the last execute on a profiling engine, one "id|nanoseconds" per line;
+ * cldnn_get_event_profiling_info, src/cldnn.cpp:356 */
+CLDNN_B200_API int32_t cldnn_host_network_profiling(cldnn_host_network n, char* buffer, size_t buffer_bytes, size_t* needed);
 CLDNN_B200_API int32_t cldnn_host_network_stats(cldnn_host_network n, uint64_t* launches_per_execute, size_t* pool_bytes);
 
 #ifdef __cplusplus
