@@ -1,0 +1,310 @@
+// conv_i8_first: the first convolution of an 8-bit network -- few input
+// features (3 for images), planar bfyx input as the caller provides it, large
+// strided filter (7x7 / 2 for ResNet, 11x11 would need kw <= 8) -- computed on
+// the tensor cores without any reordered or padded copy of the input in HBM.
+// It replaces the reference's special first-layer kernels
+// (cl_kernels/convolution_gpu_byxf_fs_bs_yx_bsv4_fsv32.cl,
+// convolution_gpu_byx8_f4__fs_bs_yx_bsv4_fsv32.cl) and the input reorder in
+// front of them; the operation order is that of fused_conv_eltwise_gpu_ref.cl.
+//
+// Each CTA owns tiles of 8 x 16 output pixels.  Per tile the threads copy the
+// small input patch (C x (7*sy+kh) x (15*sx+8) bytes) into shared memory, build
+// the 128 x K im2col operand from it in the tensor core's K-major core-matrix
+// layout -- K ordered (feature, filter row, 8 taps), so every 8-byte group is
+// one shifted read of a patch row -- then one thread issues K/32 tcgen05.mma
+// into tensor memory and all warps run the requantising epilogue, writing byxf
+// (features innermost) for the next layer.  Weights are packed once, at
+// prepare time, into the matching shared-memory image (scratch buffer).
+// Several CTAs share an SM, so the phases of different tiles overlap.
+#include <cuda.h>
+#include "engine.hpp"
+#include "sm100_ptx.cuh"
+#include "conv_epilogue.cuh"
+
+namespace b200 {
+
+using namespace ptx;
+
+constexpr int kFThreads = 256;
+constexpr int kTileH = 8, kTileW = 16;          // 128 output pixels = 128 TMEM lanes
+constexpr int kFMaxOfm = 256;
+constexpr int kFMaxK = 256;
+constexpr uint32_t kErrFirst = 0x50u;
+
+struct FirstParams {
+    int32_t N, C, H, W, P, Q, ofm, kh, kw, sx, sy, pad_x, pad_y;
+    int64_t in_pb, in_pf, in_py, in_off;
+    int32_t groups;                  // C*kh filter rows of 8 taps
+    int32_t Kp;                      // padded K in bytes (multiple of 32)
+    int32_t patch_h, patch_wp;       // patch rows per feature, row pitch in bytes (multiple of 4)
+    int32_t tiles_x, tiles_y, total_tiles;
+    uint32_t idesc, tmem_cols, sbo;
+    int64_t out_px, out_py, out_pb, out_off;
+    int32_t mul_iqf, mul_oqf, lean;
+    const uint8_t* in; uint8_t* out; const uint8_t* wpacked; const void* bias; const float* quant; const float* calib;
+    uint32_t* status;
+    EpiCfg epi;
+};
+
+struct FirstAux {
+    uint64_t mma_done;
+    uint32_t tmem_base;
+    uint32_t abort;
+    alignas(16) int32_t bias_i[1][kFMaxOfm];
+    alignas(16) float bias_f[1][kFMaxOfm];
+    alignas(16) float quant[1][kFMaxOfm];
+    alignas(16) float calib[1][kFMaxOfm];
+    alignas(16) float ecal[1][kFMaxOfm];
+};
+
+// K-major operand without swizzle: 8 x 16-byte core matrices, `lbo` bytes apart along K, `sbo` bytes apart along M/N
+__device__ __forceinline__ uint64_t make_desc_interleaved(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3fffu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3fffu) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+// weights [ofm][C][kh][kw] (any pitches) -> shared-memory image: element (n, k) at (n/8)*sbo + (k/16)*128 + (n%8)*16 + k%16,
+// k = ((c*kh + r)*8 + s); taps s >= kw and k beyond the last group are zero
+__global__ void first_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t pi, int64_t py, int64_t px, int64_t off,
+                                   int ofm, int C, int kh, int kw, int Kp, uint8_t* __restrict__ dst)
+{
+    const int total = ofm * Kp;
+    const int sbo = (Kp / 16) * 128;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int n = i / Kp, k = i - n * Kp;
+        const int g = k >> 3, s = k & 7;
+        int8_t v = 0;
+        if (g < C * kh && s < kw) { const int c = g / kh, r = g - c * kh; v = w[off + n * po + c * pi + r * py + s * px]; }
+        dst[(n >> 3) * sbo + (k >> 4) * 128 + (n & 7) * 16 + (k & 15)] = (uint8_t)v;
+    }
+}
+
+__global__ void __launch_bounds__(kFThreads, 3)
+conv_i8_first_kernel(const __grid_constant__ FirstParams P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 127u) & ~127u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const int a_bytes = 128 * P.Kp, b_bytes = P.ofm * P.Kp;
+    const int patch_bytes = P.C * P.patch_h * P.patch_wp;
+    uint8_t* sA = smem; uint8_t* sB = smem + a_bytes; uint8_t* sPatch = sB + b_bytes;
+    FirstAux* aux = reinterpret_cast<FirstAux*>(sPatch + ((patch_bytes + 15) & ~15));
+    volatile uint32_t* s_abort = &aux->abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const EpiCfg& c = P.epi;
+
+    if (tid == 0) { mbar_init(smem_u32(&aux->mma_done), 1); aux->abort = 0u; mbar_fence_init(); }
+    if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    // weights image and per-feature constants: once per CTA
+    for (int i = tid; i < b_bytes / 16; i += kFThreads) reinterpret_cast<uint4*>(sB)[i] = __ldg(reinterpret_cast<const uint4*>(P.wpacked) + i);
+    for (int j = tid; j < P.ofm; j += kFThreads) {
+        int32_t bi = 0; float bf = 0.f;
+        if (c.bias_dtype != CLDNN_B200_NONE) { if (c.bias_dtype == CLDNN_B200_F32) bf = ((const float*)P.bias)[j]; else bi = load_as_int(P.bias, c.bias_dtype, j); }
+        aux->bias_i[0][j] = bi; aux->bias_f[0][j] = bf;
+        aux->quant[0][j] = c.quantization ? P.quant[j] : 1.f;
+        aux->calib[0][j] = c.calibration ? P.calib[j] : 1.f;
+        aux->ecal[0][j] = 1.f;
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    const uint32_t lbo = 128u, sbo = P.sbo;
+    const int quad = warp & 3, chalf = warp >> 2;
+    const int row = quad * 32 + lane;                 // output pixel of the tile handled by this thread in the epilogue
+    uint32_t phase = 0;
+
+    for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
+        const int tx = tile % P.tiles_x; const int t2 = tile / P.tiles_x;
+        const int ty = t2 % P.tiles_y; const int n = t2 / P.tiles_y;
+        const int x0 = tx * kTileW * P.sx - P.pad_x, y0 = ty * kTileH * P.sy - P.pad_y;
+        const int xa = (x0 >= 0 ? x0 : x0 - 3) / 4 * 4;       // 4-byte aligned patch origin (floor)
+        // ---- input patch: zero outside the image (the reference skips those taps) ----
+        const int words_per_row = P.patch_wp >> 2;
+        const int patch_words = P.C * P.patch_h * words_per_row;
+        for (int i = tid; i < patch_words; i += kFThreads) {
+            const int wq = i % words_per_row; const int r2 = i / words_per_row;
+            const int pr = r2 % P.patch_h, ch = r2 / P.patch_h;
+            const int iy = y0 + pr, ix = xa + wq * 4;
+            uint32_t word = 0;
+            if (iy >= 0 && iy < P.H) {
+                const uint8_t* src = P.in + P.in_off + (int64_t)n * P.in_pb + (int64_t)ch * P.in_pf + (int64_t)iy * P.in_py;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) { const int x = ix + b; if (x >= 0 && x < P.W) word |= (uint32_t)__ldg(src + x) << (8 * b); }
+            }
+            reinterpret_cast<uint32_t*>(sPatch)[i] = word;
+        }
+        __syncthreads();
+        // ---- im2col operand: thread = (pixel m, half of the K chunks) ----
+        {
+            const int m = tid >> 1, h = tid & 1;
+            const int py_ = m / kTileW, px_ = m - py_ * kTileW;
+            const int colb = (x0 - xa) + px_ * P.sx;
+            const int wi = colb >> 2; const uint32_t sh = (uint32_t)(colb & 3) * 8u;
+            const int chunks = P.Kp >> 4, half_chunks = (chunks + 1) >> 1;
+            uint8_t* dstrow = sA + (m >> 3) * sbo + (m & 7) * 16;
+            for (int kc = h * half_chunks; kc < min(chunks, (h + 1) * half_chunks); ++kc) {
+                uint32_t v[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                    const int g = kc * 2 + q;
+                    if (g < P.groups) {
+                        const int ch = g / P.kh, r = g - ch * P.kh;
+                        const uint32_t* rowp = reinterpret_cast<const uint32_t*>(sPatch) + (ch * P.patch_h + py_ * P.sy + r) * words_per_row + wi;
+                        const uint32_t w0 = rowp[0], w1 = rowp[1], w2 = rowp[2];
+                        v[2 * q] = __funnelshift_r(w0, w1, sh); v[2 * q + 1] = __funnelshift_r(w1, w2, sh);
+                    }
+                }
+                *reinterpret_cast<uint4*>(dstrow + kc * 128) = make_uint4(v[0], v[1], v[2], v[3]);
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        // ---- K/32 tensor-core instructions, accumulators in tensor memory ----
+        if (tid == 0) {
+            tc_fence_after();
+            const uint64_t adesc = make_desc_interleaved(smem_u32(sA), lbo, sbo);
+            const uint64_t bdesc = make_desc_interleaved(smem_u32(sB), lbo, sbo);
+            const int kk = P.Kp >> 5;
+            for (int k = 0; k < kk; ++k)          // one instruction consumes two core matrices along K: 2 * lbo bytes
+                mma_i8_ss(tmem_base, adesc + (uint64_t)(k * 16), bdesc + (uint64_t)(k * 16), P.idesc, k ? 1u : 0u);
+            tc_commit(smem_u32(&aux->mma_done));
+        }
+        if (!mbar_wait(smem_u32(&aux->mma_done), phase, s_abort, P.status, kErrFirst)) break;
+        phase ^= 1u;
+        tc_fence_after();
+        // ---- epilogue: warp = (lane quadrant, column half) ----
+        {
+            const int py_ = row / kTileW, px_ = row - py_ * kTileW;
+            const int oy = ty * kTileH + py_, ox = tx * kTileW + px_;
+            const bool valid = oy < P.P && ox < P.Q;
+            const int64_t o_pix = P.out_off + (int64_t)n * P.out_pb + (int64_t)oy * P.out_py + (int64_t)ox * P.out_px;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
+            for (int c0 = chalf * 32; c0 < P.ofm; c0 += 64) {
+                uint32_t r[32];
+                tmem_ld_32x32(t_row + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (!valid) continue;
+                uint4 o0, o1;
+                if (P.lean) epi_chunk_fast<false, true>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                else epi_chunk_fast<false, false>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
+                uint4* op = reinterpret_cast<uint4*>(P.out + o_pix + c0);
+                op[0] = o0; op[1] = o1;
+            }
+        }
+        tc_fence_before();
+        __syncthreads();                               // tensor memory, operand and patch buffers are free again
+        tc_fence_after();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+}
+
+// ------------------------------------------------------------------------------------
+static bool first_plan(const cldnn_b200_conv_params& p, std::string* why)
+{
+    auto no = [&](const char* m) { if (why) *why = m; return false; };
+    if (!is_int8(p.in.dtype) || p.w_dtype != CLDNN_B200_I8) return no("8-bit activations and weights only");
+    if (p.groups != 1 || p.fused_eltw) return no("plain convolution only");
+    if (p.in.px != 1) return no("input must be planar (bfyx)");
+    if (p.out.pf != 1 || !is_int8(p.out.dtype)) return no("output must be 8-bit byxf");
+    if (p.kw > 8 || p.kh < 1 || p.kw < 1) return no("filter width up to 8");
+    if (p.dil_x != 1 || p.dil_y != 1) return no("no dilation");
+    if (p.ifm * p.kh * 8 > kFMaxK) return no("C*kh*8 must not exceed 256");
+    if (p.ofm % 32 || p.ofm > kFMaxOfm || p.out.f != p.ofm || p.in.f != p.ifm) return no("output features: multiple of 32, at most 256");
+    if (p.out.px % 16 || p.out.py % 16 || p.out.pb % 16 || p.out.offset % 16) return no("output pitches must be 16-byte aligned");
+    if (p.stride_x < 1 || p.stride_y < 1 || p.stride_x > 4 || p.stride_y > 4) return no("stride 1..4");
+    const bool quant_path = p.quantization || p.calibration || p.has_o_qf;
+    if (!quant_path) return no("quantised epilogue only");
+    if (!act_is_simple(p.act, p.act_m)) return no("activation not in the fast set");
+    if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32 && p.bias_dtype != CLDNN_B200_F32) return no("bias type");
+    const int P_ = (p.in.y + 2 * p.pad_y - p.kh) / p.stride_y + 1, Q_ = (p.in.x + 2 * p.pad_x - p.kw) / p.stride_x + 1;
+    if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
+    return true;
+}
+static bool first_supports(const void* vp) { return first_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
+static int first_tune_count(const void*) { return 1; }
+static int first_kp(const cldnn_b200_conv_params& p) { return (p.ifm * p.kh * 8 + 31) / 32 * 32; }
+static size_t first_scratch(const void* vp) { const auto& p = *(const cldnn_b200_conv_params*)vp; return (size_t)p.ofm * first_kp(p); }
+
+// Validates the arguments and fills the launch constants; `wpacked` is where the packed weights will live.
+static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p, const cldnn_b200_args* a, void* wpacked, size_t wpacked_bytes,
+                           FirstParams& P, int& grid, size_t& smem)
+{
+    std::string why;
+    if (!first_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_first: " + why);
+    if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: input, output and weights are required");
+    if (p.bias_dtype != CLDNN_B200_NONE && !a->bias) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: bias_dtype set but no bias pointer");
+    if (p.quantization && !a->weights_quantization_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: quantization set but no factors");
+    if (p.calibration && !a->output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: calibration set but no factors");
+    const size_t need = first_scratch(&p);
+    if (!wpacked || wpacked_bytes < need) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: needs " + std::to_string(need) + " bytes of scratch for the packed weights");
+    if (((uintptr_t)wpacked | (uintptr_t)a->output) & 15) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: scratch and output must be 16-byte aligned");
+
+    P = FirstParams{};
+    P.N = p.in.b; P.C = p.ifm; P.H = p.in.y; P.W = p.in.x; P.P = p.out.y; P.Q = p.out.x; P.ofm = p.ofm;
+    P.kh = p.kh; P.kw = p.kw; P.sx = p.stride_x; P.sy = p.stride_y; P.pad_x = p.pad_x; P.pad_y = p.pad_y;
+    P.in_pb = p.in.pb; P.in_pf = p.in.pf; P.in_py = p.in.py; P.in_off = p.in.offset;
+    P.groups = p.ifm * p.kh; P.Kp = first_kp(p);
+    P.patch_h = (kTileH - 1) * p.stride_y + p.kh;
+    P.patch_wp = ((kTileW - 1) * p.stride_x + 8 + 3 + 4 + 3) / 4 * 4;      // window + alignment slack + one spare word for the shifted read
+    P.tiles_x = (P.Q + kTileW - 1) / kTileW; P.tiles_y = (P.P + kTileH - 1) / kTileH; P.total_tiles = P.N * P.tiles_x * P.tiles_y;
+    const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;
+    P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(p.ofm >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    uint32_t cols = 32; while (cols < (uint32_t)p.ofm) cols <<= 1;
+    P.tmem_cols = cols;
+    P.sbo = (uint32_t)(P.Kp / 16) * 128u;
+    P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
+    P.epi = make_epi_cfg(p);
+    P.mul_iqf = p.i_qf != 1.0f ? 1 : 0; P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
+    P.lean = (p.quantization && !P.mul_iqf && !P.mul_oqf && !P.epi.dont_dequantize_bias &&
+              (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU)) ? 1 : 0;
+    P.in = (const uint8_t*)a->input0; P.out = (uint8_t*)a->output; P.wpacked = (const uint8_t*)wpacked;
+    P.bias = a->bias; P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors;
+    P.status = ctx->d_status;
+
+    const int patch_bytes = P.C * P.patch_h * P.patch_wp;
+    smem = 128 + (size_t)128 * P.Kp + (size_t)P.ofm * P.Kp + ((patch_bytes + 15) & ~15) + sizeof(FirstAux);
+    if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory");
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // CTAs per SM: bounded by shared memory and by tensor memory (512 columns per SM)
+    int per_sm = (int)(ctx->prop.sharedMemPerMultiprocessor / (smem + 1024));
+    per_sm = std::min(per_sm, std::min(3, (int)(512 / P.tmem_cols)));
+    if (per_sm < 1) per_sm = 1;
+    grid = ctx->prop.multiProcessorCount * per_sm;
+    if (grid > P.total_tiles) grid = P.total_tiles;
+    return CLDNN_B200_SUCCESS;
+}
+
+static cudaError_t first_pack(const cldnn_b200_conv_params& p, const cldnn_b200_args* a, const FirstParams& P, void* wpacked, cudaStream_t stream)
+{
+    first_pack_weights<<<(p.ofm * P.Kp + 255) / 256, 256, 0, stream>>>((const int8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
+                                                                        p.ofm, p.ifm, p.kh, p.kw, P.Kp, (uint8_t*)wpacked);
+    return cudaGetLastError();
+}
+
+static int32_t first_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
+    FirstParams P; int grid = 0; size_t smem = 0;
+    const int32_t st = first_setup(ctx, p, a, a->scratch, a->scratch_bytes, P, grid, smem);
+    if (st != CLDNN_B200_SUCCESS) return st;
+    // pack the weights once, on the context's stream, before anything that is prepared here can run
+    B200_CUDA(first_pack(p, a, P, a->scratch, ctx->stream));
+    out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_first_kernel<<<grid, kFThreads, smem, s>>>(P); return cudaGetLastError(); };
+    out->launches = 1;
+    return CLDNN_B200_SUCCESS;
+}
+
+const KernelDef kdef_conv_i8_first = {"conv_i8_first", sizeof(cldnn_b200_conv_params), first_supports, first_tune_count, first_scratch, first_prepare};
+
+}  // namespace b200

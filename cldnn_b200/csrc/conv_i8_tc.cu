@@ -26,6 +26,7 @@
 #include <mutex>
 #include "engine.hpp"
 #include "sm100_ptx.cuh"
+#include "conv_epilogue.cuh"
 
 namespace b200 {
 
@@ -114,112 +115,6 @@ __device__ __forceinline__ bool row_pixel(const TcParams& P, int m_tile, int row
     n = (int)(m / pq); const int r = (int)(m - (int64_t)n * pq);
     p = r / P.Q; q = r - p * P.Q;
     return m < P.M_total;
-}
-
-// The activations that are cheap enough to inline 32 times in the unrolled epilogue.
-__host__ __device__ inline bool act_is_simple(int32_t fn, float m)
-{
-    return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU || fn == CLDNN_B200_ACT_CLAMP ||
-           (fn == CLDNN_B200_ACT_RELU_NEGATIVE_SLOPE && m == m && m - m == 0.0f);
-}
-__device__ __forceinline__ float act_simple(int32_t fn, float x, float m, float n)
-{
-    if (fn == CLDNN_B200_ACT_RELU) return fmaxf(0.0f, x);
-    if (fn == CLDNN_B200_ACT_NONE) return x;
-    if (fn == CLDNN_B200_ACT_CLAMP) return fmaxf(m, fminf(n, x));
-    return __fadd_rn(fmaxf(x, 0.0f), __fmul_rn(m, fminf(x, 0.0f)));
-}
-
-// round(x) with ties away from zero, returned still as a float whose fraction is
-// not yet dropped: adding +-0.5 with round-toward-zero can never carry the sum
-// across the next integer, so truncating afterwards gives exactly round().
-__device__ __forceinline__ float half_away_pre(float x) { return __fadd_rz(x, copysignf(0.5f, x)); }
-
-// 32 features of one pixel: s32 accumulators -> requantised bytes in eight words.
-// Quantised path, 8-bit output, simple activations; same operation order as
-// epi_quant().  `e` holds the 32 residual bytes when kFused.
-template <bool kFused, bool kLean>
-__device__ __forceinline__ void epi_chunk_fast(const TcParams& P, const TcSmemAux* aux, int acc, int c0, const uint32_t (&r)[32],
-                                               uint4 e0, uint4 e1, uint4& o0, uint4& o1)
-{
-    const EpiCfg& c = P.epi;
-    const bool out_u8 = c.out_dtype == CLDNN_B200_U8;
-    uint32_t ew[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-    float e_bias = 8388608.0f;
-    if (kFused && c.eltw_dtype != CLDNN_B200_U8) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ew[i] ^= 0x80808080u;          // s8 + 128 as an unsigned byte
-        e_bias = 8388736.0f;
-    }
-    uint32_t ow[8];
-    if (kLean) {
-        // The common network configuration, with every uniform decision hoisted out of
-        // the unrolled body: per-channel quantisation only (I_QF = O_QF = 1, integer or
-        // no bias), activations NONE or ReLU, plain residual sum.  ~8 instructions per
-        // feature; max(v, -inf) stands for "no activation".
-        const float lo1 = c.act == CLDNN_B200_ACT_RELU ? 0.0f : __int_as_float(0xff800000);
-        const float lo2 = c.eltw_act == CLDNN_B200_ACT_RELU ? 0.0f : __int_as_float(0xff800000);
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            const int cj = c0 + 4 * g;
-            const int4 bi = *reinterpret_cast<const int4*>(&aux->bias_i[acc][cj]);
-            const float4 q = *reinterpret_cast<const float4*>(&aux->quant[acc][cj]);
-            const int32_t b4[4] = {bi.x, bi.y, bi.z, bi.w};
-            const float q4[4] = {q.x, q.y, q.z, q.w};
-            int32_t o4[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
-                v = half_away_pre(fmaxf(v, lo1));
-                if (kFused) {
-                    const float e = __fadd_rn(__uint_as_float(__byte_perm(ew[g], 0x4B000000u, 0x7450u + i)), -e_bias);
-                    v = half_away_pre(fmaxf(__fadd_rn(truncf(v), e), lo2));
-                }
-                o4[i] = __float2int_rz(v);
-            }
-            ow[g] = out_u8 ? pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u))
-                           : pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
-        }
-        o0 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-        o1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
-        return;
-    }
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        const int cj = c0 + 4 * g;
-        const int4 bi = *reinterpret_cast<const int4*>(&aux->bias_i[acc][cj]);
-        const int32_t b4[4] = {bi.x, bi.y, bi.z, bi.w};
-        float q4[4] = {1.f, 1.f, 1.f, 1.f}, bf4[4] = {0.f, 0.f, 0.f, 0.f}, cal4[4], ec4[4] = {1.f, 1.f, 1.f, 1.f};
-        if (c.quantization) { const float4 t = *reinterpret_cast<const float4*>(&aux->quant[acc][cj]); q4[0] = t.x; q4[1] = t.y; q4[2] = t.z; q4[3] = t.w; }
-        if (c.dont_dequantize_bias) { const float4 t = *reinterpret_cast<const float4*>(&aux->bias_f[acc][cj]); bf4[0] = t.x; bf4[1] = t.y; bf4[2] = t.z; bf4[3] = t.w; }
-        if (c.calibration) { const float4 t = *reinterpret_cast<const float4*>(&aux->calib[acc][cj]); cal4[0] = t.x; cal4[1] = t.y; cal4[2] = t.z; cal4[3] = t.w; }
-        else { cal4[0] = cal4[1] = cal4[2] = cal4[3] = c.o_qf; }
-        if (kFused && c.eltw_calibration) { const float4 t = *reinterpret_cast<const float4*>(&aux->ecal[acc][cj]); ec4[0] = t.x; ec4[1] = t.y; ec4[2] = t.z; ec4[3] = t.w; }
-        int32_t o4[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float v = __int2float_rn((int32_t)r[4 * g + i] + b4[i]);
-            if (c.quantization) { v = __fmul_rn(v, q4[i]); if (P.mul_iqf) v = __fmul_rn(v, c.i_qf); }
-            if (c.dont_dequantize_bias) v = __fadd_rn(v, bf4[i]);
-            v = act_simple(c.act, v, c.act_m, c.act_n);
-            if (P.mul_oqf) v = __fmul_rn(v, cal4[i]);
-            v = half_away_pre(v);
-            if (kFused) {
-                v = truncf(v);
-                // byte -> float without a conversion instruction: 2^23 + byte, minus 2^23
-                float e = __fadd_rn(__uint_as_float(__byte_perm(ew[g], 0x4B000000u, 0x7450u + i)), -e_bias);
-                if (c.has_non_conv_scale) e = __fmul_rn(e, c.non_conv_scale);
-                v = act_simple(c.eltw_act, __fadd_rn(v, e), c.eltw_m, c.eltw_n);
-                if (c.eltw_calibration) v = __fmul_rn(v, ec4[i]);
-                v = half_away_pre(v);
-            }
-            o4[i] = __float2int_rz(v);
-        }
-        ow[g] = out_u8 ? pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u))
-                       : pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
-    }
-    o0 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-    o1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
 }
 
 // One output element, every epilogue variant.  Kept out of line: it is the rare path.

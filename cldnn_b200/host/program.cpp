@@ -224,6 +224,7 @@ void topology::add(const primitive& p)
 // --------------------------------------------------------------------------------------
 // program nodes
 // --------------------------------------------------------------------------------------
+struct block;
 struct node {
     primitive p;
     std::vector<node*> deps;            // data inputs
@@ -240,6 +241,7 @@ struct node {
     // execution
     memory mem;                         // output memory
     memory packed_weights;              // weights re-laid for the chosen kernel
+    std::shared_ptr<struct block> scratch; // kernel workspace (kernel_scratch_bytes)
     std::string kernel; int32_t tune = 0;
     cldnn_b200_prepared prepared = nullptr;
     int order = -1;
@@ -482,6 +484,13 @@ void network_impl::select_layouts()
         if (t == "fully_connected") return n->wq && n->bias && n->bias->out.data_type == data_types::f32 && n->deps[0]->out.size.x == 1 && n->deps[0]->out.size.y == 1;
         return false;
     };
+    // a convolution over a planar few-feature input (the image) has a kernel that builds its operand from bfyx itself
+    auto first_layer = [&](node* n, node* d) {
+        if (n->p.type != "convolution" || d->out.fmt != format::bfyx || !n->weights) return false;
+        const layout& w = n->weights->out;
+        return w.size.x <= 8 && d->out.size.feature * w.size.y * 8 <= 256 && w.size.batch % 32 == 0 && w.size.batch <= 256 &&
+               n->p.dilation.x == 1 && n->p.dilation.y == 1 && n->act == CLDNN_B200_ACT_NONE && !n->p.activation_negative_slope;
+    };
     std::set<node*> chosen;
     for (node* n : order) {
         if (n->removed || n->constant() || n->p.type == "input_layout" || n->deps.empty()) continue;
@@ -496,6 +505,7 @@ void network_impl::select_layouts()
         if (!chosen.count(n)) continue;
         for (node* d : std::vector<node*>(n->deps)) {
             if (chosen.count(d) || d->out.fmt == format::byxf_af32) continue;
+            if (first_layer(n, d)) continue;                        // conv_i8_first reads the planar input directly
             const std::string rid = d->p.id + "_to_byxf_af32";
             node* r = by_id.count(rid) ? by_id[rid] : add_node(reorder(rid, d->p.id, format::byxf_af32, data_types::none));
             replace_dep(n, d, r);
@@ -716,6 +726,18 @@ void network_impl::prepare_kernel(node* n)
                 return;
             }
             cp.has_o_qf = (!cp.calibration && cp.o_qf != 1.0f) ? 1 : 0;
+        }
+        // first layer: planar 8-bit input, byxf output
+        if (!fc && is_int8(in.data_type) && cp.in.px == 1 && cp.out.pf == 1) {
+            int32_t yes = 0; size_t sbytes = 0;
+            cldnn_b200_kernel k = eng->kernel("conv_i8_first");
+            if (cldnn_b200_kernel_supports(k, &cp, sizeof(cp), &yes) == CLDNN_B200_SUCCESS && yes &&
+                cldnn_b200_kernel_scratch_bytes(k, &cp, sizeof(cp), &sbytes) == CLDNN_B200_SUCCESS) {
+                n->scratch = new_block(eng, sbytes);
+                a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
+                finish({"conv_i8_first"}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
+                return;
+            }
         }
         // tensor-core kernel: needs byxf activations and oyxi weights padded like the activations
         const bool try_tc = is_int8(in.data_type) && w.data_type == data_types::i8 && cp.groups == 1 && cp.in.pf == 1 && cp.in.px % 32 == 0 && cp.out.pf == 1;

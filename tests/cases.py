@@ -32,15 +32,19 @@ def make_conv_case(seed, N, C, K, H, W, kh=3, kw=3, stride=1, pad=1, dil=1,
                    fused=False, eltw_dtype=None, eltw_calib=False, non_conv_scale=1.0,
                    eltw_act=abi.ACT_RELU, in_out_opt=False, eltw_stride=1,
                    i_qf=1.0, o_qf=1.0, scale_lo=2.0 ** -14, scale_hi=2.0 ** -10,
-                   w_layout=None, groups=1, w_range=127):
+                   w_layout=None, groups=1, w_range=127, out_fmt=None):
     rng = np.random.default_rng(seed)
     c = ConvCase()
     p = c.p
     P, Q = conv_out(H, kh, pad, stride, dil), conv_out(W, kw, pad, stride, dil)
     in_dtype, out_dtype = np.dtype(in_dtype), np.dtype(out_dtype)
     p.in_, _ = abi.tensor(abi.dtype_of(in_dtype), N, C, H, W, fmt, f_align)
-    p.out, c.out_elems = abi.tensor(abi.dtype_of(out_dtype), N, K, P, Q, fmt, f_align if fmt == "byxf" else 1)
-    c.out_fmt, c.out_f_align = fmt, (f_align if fmt == "byxf" else 1)
+    ofmt = out_fmt or fmt
+    o_align = 32 if (ofmt == "byxf" and (out_fmt or f_align > 1)) else 1
+    if ofmt == "byxf" and not out_fmt:
+        o_align = f_align
+    p.out, c.out_elems = abi.tensor(abi.dtype_of(out_dtype), N, K, P, Q, ofmt, o_align)
+    c.out_fmt, c.out_f_align = ofmt, o_align
     if in_dtype == np.uint8:
         x = rng.integers(0, 256, size=(N, C, H, W), dtype=np.int64).astype(np.uint8)
     elif in_dtype == np.int8:
@@ -100,8 +104,8 @@ def make_conv_case(seed, N, C, K, H, W, kh=3, kw=3, stride=1, pad=1, dil=1,
             e = rng.integers(-128, 128, size=(N, K, P * eltw_stride, Q * eltw_stride), dtype=np.int64).astype(np.int8)
         else:
             e = rng.standard_normal((N, K, P * eltw_stride, Q * eltw_stride)).astype(edt)
-        p.eltw, _ = abi.tensor(abi.dtype_of(edt), N, K, P * eltw_stride, Q * eltw_stride, fmt, c.out_f_align)
-        c.eltw = abi.to_layout(e, fmt, c.out_f_align)
+        p.eltw, _ = abi.tensor(abi.dtype_of(edt), N, K, P * eltw_stride, Q * eltw_stride, ofmt, c.out_f_align)
+        c.eltw = abi.to_layout(e, ofmt, c.out_f_align)
         p.has_non_conv_scale = int(non_conv_scale != 1.0)
         p.non_conv_scale = non_conv_scale
         p.eltw_act = eltw_act
@@ -140,8 +144,14 @@ def run_gpu(engine, case, kernel="conv_i8_tc", tune=0):
         out = engine.upload(case.eltw.astype(out_dt))
     else:
         out = engine.alloc(case.out_elems * out_dt.itemsize)
+    import ctypes as _C
+    k = engine.kernel(kernel)
+    sb = _C.c_size_t()
+    engine.lib.cldnn_b200_kernel_scratch_bytes(k.handle, _C.byref(p), _C.sizeof(p), _C.byref(sb))
+    scratch = engine.alloc(sb.value) if sb.value else None
+    mems["scratch"] = scratch
     args = eng.make_args(input0=mems["inp"], input1=None if p.in_out_opt else mems["eltw"], output=out, weights=mems["w"],
-                         bias=mems["bias"], quant=mems["quant"], calib=mems["calib"], eltw_calib=mems["ecal"])
+                         bias=mems["bias"], quant=mems["quant"], calib=mems["calib"], eltw_calib=mems["ecal"], scratch=scratch)
     engine.kernel(kernel).launch(p, args)
     engine.sync()
     res = out.read(out_dt, case.out_elems)

@@ -108,6 +108,30 @@ def test_epilogue_variants(eng, name, kernel):
     _exact(eng, case, kernel)
 
 
+FIRST_LAYER = {
+    # ResNet-50 conv1: 3 -> 64, 7x7 stride 2 pad 3, planar u8 image in, byxf out
+    "resnet_conv1": dict(N=2, C=3, K=64, H=224, W=224, kh=7, kw=7, stride=2, pad=3),
+    "ragged_image": dict(N=3, C=3, K=32, H=37, W=45, kh=7, kw=7, stride=2, pad=3),
+    "stride1_5x5": dict(N=1, C=4, K=64, H=20, W=33, kh=5, kw=5, stride=1, pad=2),
+    "one_feature_3x3": dict(N=2, C=1, K=96, H=17, W=18, kh=3, kw=3, stride=1, pad=1),
+    "no_pad_stride3": dict(N=1, C=3, K=128, H=30, W=31, kh=4, kw=6, stride=3, pad=0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FIRST_LAYER))
+@pytest.mark.parametrize("variant", ["relu_u8", "signed_in_calibrated"])
+def test_conv_i8_first_matches_oracle(eng, name, variant):
+    kw = dict(FIRST_LAYER[name])
+    if variant == "relu_u8":
+        case = cases.make_conv_case(21, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, **kw)
+    else:
+        case = cases.make_conv_case(22, fmt="bfyx", f_align=1, out_fmt="byxf", in_dtype=np.int8, out_dtype=np.int8, bias="f32", calib=True,
+                                    act=abi.ACT_NONE, **kw)
+    assert eng.kernel("conv_i8_first").supports(case.p)
+    want = _exact(eng, case, "conv_i8_first")
+    assert (want != 0).any()
+
+
 def test_conv_ref_layouts_and_groups(eng):
     _exact(eng, cases.make_conv_case(5, 1, 128, 128, 28, 28, fmt="bfyx", f_align=1), "conv_ref")
     _exact(eng, cases.make_conv_case(6, 2, 16, 24, 9, 9, fmt="yxfb", f_align=1), "conv_ref")

@@ -49,7 +49,8 @@ def test_small_residual_network_bit_exact(eng, optimize):
     convs = [r for r in info if r["type"] in ("convolution", "fused_conv_eltwise", "fully_connected")]
     if optimize:
         # the layout optimiser moved the 8-bit path to byxf_af32 and every convolution onto the tensor-core kernel
-        assert all(r["kernel"] == "conv_i8_tc" and r["format"] == "byxf_af32" for r in convs)
+        assert all(r["kernel"] in ("conv_i8_tc", "conv_i8_first") and r["format"] == "byxf_af32" for r in convs)
+        assert convs[0]["kernel"] == "conv_i8_first"          # the image is consumed in its planar layout, no input reorder
         assert any(r["kernel"] == "pooling_i8_byxf" for r in info)
     else:
         # optimize_data(false): reference-order kernels in the caller's layout, like the reference's own tests
