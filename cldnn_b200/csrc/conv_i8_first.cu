@@ -17,6 +17,8 @@
 // prepare time, into the matching shared-memory image (scratch buffer).
 // Several CTAs share an SM, so the phases of different tiles overlap.
 #include <cuda.h>
+#include <mutex>
+#include <string>
 #include "engine.hpp"
 #include "sm100_ptx.cuh"
 #include "conv_epilogue.cuh"
@@ -307,4 +309,65 @@ static int32_t first_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cld
 
 const KernelDef kdef_conv_i8_first = {"conv_i8_first", sizeof(cldnn_b200_conv_params), first_supports, first_tune_count, first_scratch, first_prepare};
 
+// ------------------------------------------------------------------------------------
+// Allocation-free variant.  The packed-weights workspace that conv_i8_first normally
+// receives from its caller lives here in a fixed array inside the library image, so a
+// caller that owns no device allocator can still run the first-layer convolution.
+// 32 KiB holds, for example, 128 output features x 256 bytes of padded K (ResNet's 7x7x3 -> 64
+// first layer needs 12 KiB); larger weight images are refused.  Every GPU that loads the
+// library carries the array until exit.
+// ------------------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = 32 * 1024;
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+static void* g_noalloc_ptr[kNoAllocMaxDevices];      // device address of the array, per device ordinal
+static std::mutex g_noalloc_mutex;
+
+// Resolves the array's device address for the context's device.  In host code the
+// symbol name is only a stand-in; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static int32_t noalloc_scratch_address(cldnn_b200_ctx_impl* ctx, void** out)
+{
+    if (ctx->device < 0 || ctx->device >= kNoAllocMaxDevices) return fail(CLDNN_B200_INVALID_ARG, "conv_first_noalloc: device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_ptr[ctx->device]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(conv_first_noalloc scratch)");
+        if (!p) return fail(CLDNN_B200_DEVICE_ERROR, "conv_first_noalloc: the built-in scratch has no device address");
+        g_noalloc_ptr[ctx->device] = p;
+    }
+    *out = g_noalloc_ptr[ctx->device];
+    return CLDNN_B200_SUCCESS;
+}
+
 }  // namespace b200
+
+extern "C" int32_t cldnn_b200_conv_first_noalloc(cldnn_b200_ctx ctx, const cldnn_b200_conv_params* params, const cldnn_b200_args* args)
+{
+    using namespace b200;
+    if (!ctx || !params || !args) return fail(CLDNN_B200_INVALID_ARG, "conv_first_noalloc: null argument");
+    const size_t need = (params->ofm > 0 && params->ifm > 0 && params->kh > 0) ? first_scratch(params) : 0;
+    if (need > kNoAllocScratchBytes)
+        return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_first_noalloc: the packed weights need " + std::to_string(need) + " bytes, the built-in scratch holds " +
+                                                 std::to_string(kNoAllocScratchBytes) + "; use conv_i8_first with caller-provided scratch");
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); prev = -1; }
+    if (prev != ctx->device) B200_CUDA(cudaSetDevice(ctx->device));
+    struct Restore { int prev, cur; ~Restore() { if (prev >= 0 && prev != cur) (void)cudaSetDevice(prev); } } restore{prev, ctx->device};
+
+    void* scratch = nullptr;
+    int32_t st = noalloc_scratch_address(ctx, &scratch);
+    if (st != CLDNN_B200_SUCCESS) return st;
+    FirstParams P; int grid = 0; size_t smem = 0;
+    st = first_setup(ctx, *params, args, scratch, kNoAllocScratchBytes, P, grid, smem);   // validates everything else, refuses what the kernel cannot do
+    if (st != CLDNN_B200_SUCCESS) return st;
+    // The array still holds whatever the previous call packed.  The packing kernel rewrites every byte of the image
+    // this call reads (zero taps and zero K padding included), so nothing stale can leak into the result.
+    B200_CUDA(first_pack(*params, args, P, scratch, ctx->stream));
+    conv_i8_first_kernel<<<grid, kFThreads, smem, ctx->stream>>>(P);
+    B200_CUDA(cudaGetLastError());
+    ctx->launches += 2;
+    return CLDNN_B200_SUCCESS;
+}

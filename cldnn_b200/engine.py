@@ -56,6 +56,7 @@ _SIGNATURES = {
     "cldnn_b200_run": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_prepared_destroy": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_time": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_uint64)]),
+    "cldnn_b200_conv_first_noalloc": (C.c_int32, [C.c_void_p, C.POINTER(abi.ConvParams), C.POINTER(abi.Args)]),
     "cldnn_b200_graph_begin": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_graph_end": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "cldnn_b200_graph_launch": (C.c_int32, [C.c_void_p]),

@@ -313,6 +313,22 @@ CLDNN_B200_API int32_t cldnn_b200_graph_begin(cldnn_b200_ctx ctx);
 CLDNN_B200_API int32_t cldnn_b200_graph_end(cldnn_b200_ctx ctx, cldnn_b200_graph* out);
 CLDNN_B200_API int32_t cldnn_b200_graph_launch(cldnn_b200_graph g);
 CLDNN_B200_API int32_t cldnn_b200_graph_destroy(cldnn_b200_graph g);
+/* First-layer convolution for callers that cannot allocate device memory -- it has no counterpart in the reference.
+ * Some embedders run where cudaMalloc is off limits: a serving process whose device memory is carved up once at start-up
+ * by another allocator, or a latency-critical section that must not take cudaMalloc's device-wide synchronisation.  The
+ * kernel "conv_i8_first" needs a workspace for its packed weights (kernel_scratch_bytes); this entry point keeps that
+ * workspace in a fixed 32 KiB array inside the library image instead, so it calls no cudaMalloc / cudaFree and no
+ * allocating library routine.  The caller passes the same constants and the same input / output / weights / bias /
+ * factor pointers as for "conv_i8_first" (args->scratch is ignored); the two kernels (weights packing, convolution)
+ * are enqueued on the context's stream and the call returns without waiting.
+ *   - Constants whose packed weights exceed 32 KiB (output features x padded C*kh*8) are refused with
+ *     CLDNN_B200_UNSUPPORTED_SIZE; everything "conv_i8_first" refuses is refused here with the same codes.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     before starting any stream capture on the device.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Each call rewrites every
+ *     byte it later reads, so sequential calls are independent; calls whose kernels may overlap on the GPU (other
+ *     streams, other contexts or processes' threads on the same device using this entry point) race on it.        */
+CLDNN_B200_API int32_t cldnn_b200_conv_first_noalloc(cldnn_b200_ctx ctx, const cldnn_b200_conv_params* params, const cldnn_b200_args* args);
 /* device-side status word: 0 when the last launches completed normally,
  * otherwise a code written by a kernel whose bounded wait gave up           */
 CLDNN_B200_API int32_t cldnn_b200_ctx_device_status(cldnn_b200_ctx ctx, uint32_t* status);
