@@ -104,6 +104,27 @@ def cpu_baseline(batch_images, threads=0):
                 sample="full ResNet-50 v1 int8 forward, %d images of 224x224, %.1f s" % (batch_images, dt))
 
 
+def shard_plan(global_images, world):
+    """Images are independent units: rank r takes global_images // world, the remainder goes to the low ranks."""
+    base, rem = divmod(global_images, world)
+    return [base + (1 if r < rem else 0) for r in range(world)]
+
+
+def max_over_ranks(ms, world, device="cpu"):
+    """Device time of the slowest rank (no other collective exists on the path)."""
+    if world == 1:
+        return ms
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_rate(images_per_rank, steps, ms):
+    return sum(images_per_rank) * steps / (ms / 1e3)
+
+
 def run_reference(args, rank):
     """--impl reference: the reference's arithmetic on the box's host cores (rank 0 only)."""
     if rank != 0:
@@ -147,6 +168,7 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG", "WARN")             # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     B = args.batch
@@ -226,11 +248,7 @@ def main():
         torch.cuda.synchronize()
         ms = a.elapsed_time(b)
         barrier()
-        if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return max_over_ranks(ms, world, "cuda")
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -273,8 +291,9 @@ def main():
                 "per_kernel_ms": {kern: sum(v for k, v in acc.items() if info[k]["kernel"] == kern) / reps / 1e6
                                   for kern in sorted(set(r["kernel"] for r in info.values() if r["kernel"]))}}
 
-    images = B * world * args.steps
-    value = images / (ms / 1e3)
+    per_rank = shard_plan(B * world, world)
+    images = sum(per_rank) * args.steps
+    value = whole_job_rate(per_rank, args.steps, ms)
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": "resnet50_v1_int8_b%d" % B, "batch_per_gpu": B, "global_batch": B * world, "image": 224, "parallelism": "dp%d" % world,
