@@ -20,10 +20,11 @@ def _tensor(arr):
     return abi.tensor(abi.dtype_of(arr.dtype), b, f, y, x, "bfyx")[0]
 
 
-def run(spec, inputs, threads=0, stats=None, keep=None):
+def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle"):
     """inputs: {input id: logical [b,f,y,x] array}.  Returns {primitive id: logical array} for spec.outputs
     (or for the ids in `keep`; keep=True keeps everything).  `stats`, if a dict, receives per-primitive
-    fractions of zero / saturated outputs for 8-bit results."""
+    fractions of zero / saturated outputs for 8-bit results.  conv_impl="reference" runs the convolutions on the reference's
+    own kernel source (oracle/_ref) where a variant exists, the C restatement elsewhere."""
     vals = dict(inputs)
     users = {}
     for p in spec.prims:
@@ -79,8 +80,15 @@ def run(spec, inputs, threads=0, stats=None, keep=None):
                 cp.eltw_stride_x, cp.eltw_stride_y = a["eltw_stride"]
             else:
                 cp.has_o_qf = int(cp.o_qf != 1.0 and not cp.calibration)
-            flat = oracle_lib.conv(cp, x.reshape(-1), w.reshape(-1), bias, quant, calib,
-                                   eltw.reshape(-1) if eltw is not None else None, ecal, threads=threads)
+            impl = oracle_lib
+            if conv_impl == "reference":
+                import ref_lib
+                if ref_lib.available(cp):
+                    impl = ref_lib
+                    if stats is not None:
+                        stats["reference_kernel_convs"] = stats.get("reference_kernel_convs", 0) + 1
+            flat = impl.conv(cp, x.reshape(-1), w.reshape(-1), bias, quant, calib,
+                             eltw.reshape(-1) if eltw is not None else None, ecal, threads=threads or oracle_lib.num_threads())
             res = flat.reshape(out.shape)
         elif k == "pooling":
             pp = abi.PoolParams()
