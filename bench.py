@@ -87,7 +87,9 @@ class ClockSampler(threading.Thread):
 
 
 def cpu_baseline(batch_images, threads=0):
-    """The CPU oracle (restatement of the reference kernels) on a bounded sample: whole ResNet-50, `batch_images` images."""
+    """The reference arithmetic on the host cores, on a bounded sample (whole ResNet-50, `batch_images` images): the
+    convolutions run the reference's own kernel source compiled as C++ when oracle/_ref holds the prebuilt variants,
+    otherwise the C restatement; `kind` says which."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import numpy as np
     import oracle_lib
@@ -102,7 +104,7 @@ def cpu_baseline(batch_images, threads=0):
     oracle_net.run(spec, {spec.input_id: x}, threads=cores, stats=stats, conv_impl="reference")
     dt = time.perf_counter() - t0
     nref = stats.get("reference_kernel_convs", 0)
-    # "reference": all 54 convolutions ran the reference's own kernel source (fused_conv_eltwise_gpu_ref.cl compiled as C++);
+    # "reference": all 53 convolutions ran the reference's own kernel source (fused_conv_eltwise_gpu_ref.cl compiled as C++);
     # pooling, the 2048x1000 inner product and softmax (0.05 % of the work) run the C restatement
     return dict(value=batch_images / dt, unit=UNIT, cores=cores, kind="reference" if nref >= 53 else "port",
                 sample="full ResNet-50 v1 int8 forward, %d images of 224x224, %.1f s, %d convolutions on the reference kernel source" % (batch_images, dt, nref))
@@ -146,7 +148,7 @@ def run_reference(args, rank):
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": "resnet50_v1_int8", "batch_per_step": args.cpu_sample, "image": 224,
-                       "note": "CPU restatement of the reference kernels (no OpenCL device exists here); each step is a bounded sample"},
+                       "note": "the reference's convolution kernel source compiled for the host cores (no OpenCL device exists here); each step is a bounded sample"},
             "cpu_baseline": dict(last, value=value),
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
