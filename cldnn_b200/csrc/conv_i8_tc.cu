@@ -24,56 +24,10 @@
 // activations) take a direct-store epilogue instead.
 #include <cuda.h>
 #include <mutex>
-#include "engine.hpp"
-#include "sm100_ptx.cuh"
+#include "conv_i8_tc.hpp"
 #include "conv_epilogue.cuh"
 
 namespace b200 {
-
-using namespace ptx;
-
-constexpr int kBM = 128;                 // pixels per tile = TMEM lanes
-constexpr int kEpiWarps = 8;
-constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kStoreWarp = 2 + kEpiWarps;  // warp that issues the TMA stores of finished tiles
-constexpr int kThreads = 64 + kEpiThreads + 32;
-constexpr int kMaxStages = 8;
-constexpr int kMaxBN = 256;
-constexpr int kMaxBufs = 4;               // accumulator / staging buffers in flight per CTA
-constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
-
-enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
-
-struct alignas(64) TcParams {
-    CUtensorMap tmA;                     // activations
-    CUtensorMap tmB;                     // weights
-    CUtensorMap tmO;                     // output (staged epilogue)
-    CUtensorMap tmE;                     // residual input (staged epilogue, fused)
-    int32_t a_mode;
-    int32_t N, P, Q;                     // output batch, rows, columns
-    int32_t kh, kw, stride_x, stride_y, pad_x, pad_y, dil_x, dil_y;
-    int32_t bk, chunks, k_steps;         // bytes of K per stage, channel chunks per tap, stages per tile
-    int32_t bn, n_tiles, m_tiles, total_tiles;
-    int64_t M_total;
-    int32_t bw, bh, bb, tiles_w, tiles_h; // tiled mode: box of bw x bh x bb pixels
-    int32_t stages, a_stage_bytes, b_stage_bytes, a_tx_bytes, b_tx_bytes;
-    uint32_t sbo, layout_type, idesc, tmem_cols;
-    int32_t ofm;
-    // epilogue
-    int32_t staged;                      // 1: shared-memory tile + TMA store, 0: direct stores
-    int32_t fast_epi;                    // quantised, 8-bit output and residual, simple activations
-    int32_t cw, col_blocks, sw_shift, sw_mask, stage_rows;   // staging tile: column block width, 16-byte chunk swizzle
-    int32_t mul_iqf, mul_oqf;
-    int32_t lean;                        // epilogue configuration covered by the hoisted fast body
-    int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
-    // output / residual addressing for the direct path, in elements
-    int64_t out_px, out_py, out_pb, out_off;
-    int64_t el_px, el_py, el_pb, el_off;
-    int32_t el_sx, el_sy;
-    void* out; const void* eltw; const void* bias; const float* quant; const float* calib; const float* ecal;
-    uint32_t* status;
-    EpiCfg epi;
-};
 
 struct TcSmemAux {
     uint64_t full[kMaxStages];
@@ -92,6 +46,7 @@ struct TcSmemAux {
     alignas(16) float calib[2][kMaxBN];
     alignas(16) float ecal[2][kMaxBN];
 };
+
 
 __device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int& m_tile, int& n_tile)
 {
@@ -159,6 +114,9 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool fused_staged = P.staged && P.epi.fused_eltw;
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 0) atomicMin(&g_tc_time[0], globaltimer());
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
@@ -178,11 +136,15 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 0) atomicMax(&g_tc_time[2], globaltimer());
+#endif
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true; int t = 0;
+            Prof prof; prof.begin();
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
                 // base coordinates of the tile's first pixel
@@ -198,7 +160,9 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (fused_staged) {
                     // second input of the fused eltwise: same pixels and features as the output tile
                     const int a = t % P.nbuf;
+                    prof.start();
                     if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) { ok = false; break; }
+                    prof.stop(1);
                     const uint32_t rf = smem_u32(&aux->res_full[a]);
                     mbar_expect_tx(rf, (uint32_t)(P.stage_rows * P.cw * P.col_blocks));
                     for (int cb = 0; cb < P.col_blocks; ++cb) {
@@ -210,7 +174,9 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
+                    prof.start();
                     if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                    prof.stop(0);
                     const uint32_t full = smem_u32(&aux->full[stage]);
                     mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
                     const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
@@ -225,6 +191,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                     if (++stage == P.stages) { stage = 0; phase ^= 1u; }
                 }
             }
+            prof.flush(0, 2);
             if (!ok) {
                 // unwind: let the copies already in flight land before the CTA's shared memory goes away
                 int st = stage; uint32_t ph = phase;
@@ -240,13 +207,18 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
+            Prof prof; prof.begin();
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t % P.nbuf;
+                prof.start();
                 if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                prof.stop(0);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.bn);
                 for (int ks = 0; ks < P.k_steps; ++ks) {
+                    prof.start();
                     if (!mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    prof.stop(1);
                     tc_fence_after();
                     const uint64_t adesc = make_smem_desc(a_base + (uint32_t)(stage * P.a_stage_bytes), P.sbo, P.layout_type);
                     const uint64_t bdesc = make_smem_desc(b_base + (uint32_t)(stage * P.b_stage_bytes), P.sbo, P.layout_type);
@@ -258,6 +230,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
+            prof.flush(3, 2);
             // drain: every issued MMA must have retired before TMEM is released
             tc_commit(smem_u32(&aux->drain));
             const uint64_t t0 = globaltimer();
@@ -269,10 +242,13 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         // ------------------------------ TMA store issuer --------------------------
         if (lane == 0 && P.staged) {
             int t = 0;
+            Prof prof; prof.begin();
             for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
                 const int a = t % P.nbuf;
+                prof.start();
                 if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
+                prof.stop(0);
                 int tw = 0, th = 0, tb = 0;
                 if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
                 const int n0 = n_tile * P.bn;
@@ -284,9 +260,12 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                     else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
                 }
                 bulk_commit();
+                prof.start();
                 bulk_wait_read0();                                  // the buffer may be refilled once TMA has read it
+                prof.stop(1);
                 mbar_arrive(smem_u32(&aux->stage_free[a]));
             }
+            prof.flush(6, 2);
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
@@ -299,11 +278,13 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         const EpiCfg& c = P.epi;
         const uint32_t sw = (uint32_t)((row >> P.sw_shift) & P.sw_mask);
         int t = 0; bool ok = true; int cur_n_tile = -1;
+        Prof prof; prof.begin();
         for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
             int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
             const int acc = t % P.nbuf;
             const int n0 = n_tile * P.bn;
             if (n_tile != cur_n_tile) {
+                prof.start();
                 // per-channel constants of this feature range; every warp has left the previous range
                 named_bar_sync(1, kEpiThreads);
                 for (int j = et; j < P.bn; j += kEpiThreads) {
@@ -320,14 +301,19 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 named_bar_sync(1, kEpiThreads);
                 cur_n_tile = n_tile;
+                prof.stop(2);
             }
+            prof.start();
             if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue)) { ok = false; break; }
+            prof.stop(0);
+            prof.start();
             if (P.staged) {
                 // the staging buffer is ours once its residual tile has landed (fused) or its previous store has read it out
                 const bool got = fused_staged ? mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue + 1u)
                                               : mbar_wait(smem_u32(&aux->stage_free[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
                 if (!got) { ok = false; break; }
             }
+            prof.stop(1);
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * P.bn);
 
@@ -388,11 +374,18 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
             }
         }
+        if (warp == 2 && lane == 0) prof.flush(9, 3, t);
     }
 
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 64) atomicMin(&g_tc_time[3], globaltimer());
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 0) atomicMax(&g_tc_time[1], globaltimer());
+#endif
 }
 
 // ------------------------------------------------------------------------------------
@@ -426,7 +419,8 @@ struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; };
 
 // tune index -> (addressing mode, feature tile).  0 = automatic choice.
 static const int kTuneBN[4] = {32, 64, 128, 256};
-static int tc_tune_count(const void*) { return 1 + 3 * 4; }
+// Indices 13..24 repeat 1..12 on the general kernel where the specialised one (conv_i8_tc_fast.cu) would be used.
+static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4; }
 
 static bool dense_byxf(const cldnn_b200_tensor& t)
 {
@@ -486,6 +480,7 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
                            (int64_t)p.in.b * p.in.pb >= 131072;     // small tensors take the tiled path
     int tune = p.tune;
     int mode = -1, bn = 0;
+    if (tune > 12) tune -= 12;
     if (tune > 0) { mode = (tune - 1) / 4; bn = kTuneBN[(tune - 1) % 4]; }
     if (mode < 0) mode = is_1x1_s1 ? A_FLAT : (im2col_ok ? A_IM2COL : A_TILED);
     if (mode == A_FLAT && !is_1x1_s1) return no("flat addressing needs a dense 1x1 stride-1 convolution");
@@ -596,7 +591,13 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.sw_shift = P.cw == 128 ? 0 : (P.cw == 64 ? 1 : 2);
     P.sw_mask = P.cw == 128 ? 7 : (P.cw == 64 ? 3 : 1);
 
-    const size_t aux_bytes = sizeof(TcSmemAux);
+    const bool out_u8 = p.out.dtype == CLDNN_B200_U8;
+    const int out_kind = out_u8 ? 0 : ((p.fused_eltw ? p.eltw_act : p.act) == CLDNN_B200_ACT_RELU ? 2 : 1);
+    P.fast_variant = (out_kind << 1) | ((p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) ? 1 : 0);
+    P.acc_bound = (float)p.kh * (float)p.kw * (float)p.ifm * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
+    const bool use_fast = p.tune <= 12 && tc_fast_eligible(P);
+
+    const size_t aux_bytes = use_fast ? tc_fast_aux_bytes() : sizeof(TcSmemAux);
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
     size_t staging_total = P.staged ? (size_t)P.nbuf * kBM * pl.bn : 0;
@@ -670,7 +671,12 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     if (grid > P.total_tiles) grid = P.total_tiles;
     if (grid < 1) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: empty output");
     const size_t smem = smem_bytes;
-    out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_tc_kernel<<<grid, kThreads, smem, s>>>(P); return cudaGetLastError(); };
+    if (use_fast) {
+        if (!P.staged) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory for the staged epilogue");
+        B200_CUDA(tc_fast_configure(P, (int)max_smem));
+        out->fn = [P, grid, smem](cudaStream_t s) { return tc_fast_launch(P, grid, smem, s); };
+    } else
+        out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_tc_kernel<<<grid, kThreads, smem, s>>>(P); return cudaGetLastError(); };
     out->launches = 1;
     return CLDNN_B200_SUCCESS;
 }

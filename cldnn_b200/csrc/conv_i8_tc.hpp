@@ -1,0 +1,91 @@
+// Shared declarations of the tensor-core 8-bit convolution kernels: the launch
+// parameter block the host fills once per prepared launch, and the optional
+// per-role wait-cycle counters of diagnostic builds.
+#pragma once
+#include <cuda.h>
+#include "engine.hpp"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+using namespace ptx;
+
+constexpr int kBM = 128;                 // pixels per tile = TMEM lanes
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kStoreWarp = 2 + kEpiWarps;  // warp that issues the TMA stores of finished tiles
+constexpr int kThreads = 64 + kEpiThreads + 32;
+constexpr int kMaxStages = 8;
+constexpr int kMaxBN = 256;
+constexpr int kMaxBufs = 4;               // accumulator / staging buffers in flight per CTA
+constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
+
+enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
+
+struct alignas(64) TcParams {
+    CUtensorMap tmA;                     // activations
+    CUtensorMap tmB;                     // weights
+    CUtensorMap tmO;                     // output (staged epilogue)
+    CUtensorMap tmE;                     // residual input (staged epilogue, fused)
+    int32_t a_mode;
+    int32_t N, P, Q;                     // output batch, rows, columns
+    int32_t kh, kw, stride_x, stride_y, pad_x, pad_y, dil_x, dil_y;
+    int32_t bk, chunks, k_steps;         // bytes of K per stage, channel chunks per tap, stages per tile
+    int32_t bn, n_tiles, m_tiles, total_tiles;
+    int64_t M_total;
+    int32_t bw, bh, bb, tiles_w, tiles_h; // tiled mode: box of bw x bh x bb pixels
+    int32_t stages, a_stage_bytes, b_stage_bytes, a_tx_bytes, b_tx_bytes;
+    uint32_t sbo, layout_type, idesc, tmem_cols;
+    int32_t ofm;
+    // epilogue
+    int32_t staged;                      // 1: shared-memory tile + TMA store, 0: direct stores
+    int32_t fast_epi;                    // quantised, 8-bit output and residual, simple activations
+    int32_t cw, col_blocks, sw_shift, sw_mask, stage_rows;   // staging tile: column block width, 16-byte chunk swizzle
+    int32_t mul_iqf, mul_oqf;
+    int32_t lean;                        // epilogue configuration covered by the hoisted fast body
+    int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
+    int32_t fast_variant;                // conv_i8_tc_fast: (output kind << 1) | ReLU before the residual sum
+    float acc_bound;                     // K * max|activation| * 128: no accumulator can exceed it in magnitude
+    // output / residual addressing for the direct path, in elements
+    int64_t out_px, out_py, out_pb, out_off;
+    int64_t el_px, el_py, el_pb, el_off;
+    int32_t el_sx, el_sy;
+    void* out; const void* eltw; const void* bias; const float* quant; const float* calib; const float* ecal;
+    uint32_t* status;
+    EpiCfg epi;
+};
+
+// Optional per-role wait-cycle counters (diagnostic builds only, -DCONV_TC_PROFILE).
+#ifdef CONV_TC_PROFILE
+// one copy per translation unit; the debug readers below see the copy of the file that defines them
+static __device__ unsigned long long g_tc_prof[148 * 16];
+struct Prof {
+    long long acc[3] = {0, 0, 0}; long long t = 0, t_begin = 0;
+    __device__ __forceinline__ void begin() { t_begin = clock64(); }
+    __device__ __forceinline__ void start() { t = clock64(); }
+    __device__ __forceinline__ void stop(int i) { acc[i] += clock64() - t; }
+    __device__ __forceinline__ void flush(int slot, int n, long long extra = -1) {
+        if (blockIdx.x >= 148) return;
+        for (int i = 0; i < n; ++i) g_tc_prof[blockIdx.x * 16 + slot + i] = (unsigned long long)acc[i];
+        g_tc_prof[blockIdx.x * 16 + slot + n] = (unsigned long long)(clock64() - t_begin);
+        if (extra >= 0) g_tc_prof[blockIdx.x * 16 + slot + n + 1] = (unsigned long long)extra;
+    }
+};
+static __device__ unsigned long long g_tc_time[4];      // first CTA entry, last CTA exit, last loop begin, first loop end (globaltimer ns)
+#else
+struct Prof {
+    __device__ __forceinline__ void begin() {}
+    __device__ __forceinline__ void start() {}
+    __device__ __forceinline__ void stop(int) {}
+    __device__ __forceinline__ void flush(int, int, long long = -1) {}
+};
+#endif
+
+
+// conv_i8_tc_fast.cu: the specialised kernels for the common network configuration.
+bool tc_fast_eligible(const TcParams& P);
+cudaError_t tc_fast_configure(const TcParams& P, int max_smem);
+cudaError_t tc_fast_launch(const TcParams& P, int grid, size_t smem_bytes, cudaStream_t stream);
+size_t tc_fast_aux_bytes();
+
+}  // namespace b200

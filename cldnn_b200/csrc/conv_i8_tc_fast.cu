@@ -1,0 +1,521 @@
+// conv_i8_tc_fast: the tensor-core 8-bit convolution specialised for the
+// configuration whole quantised networks run in: per-channel dequantisation
+// only (I_QF = O_QF = 1, integer or no bias), activations NONE / ReLU, 8-bit
+// output, optional fused residual sum with a plain 8-bit second input, output
+// features a multiple of the feature tile.  Same main loop and the same
+// operation order as conv_i8_tc (fused_conv_eltwise_gpu_ref.cl:148-232); what
+// differs is the epilogue, which is where those layers spend their time:
+//   * the feature tile is a template parameter, every loop bound is static;
+//   * two groups of four epilogue warps take alternate tiles, each warp owns one
+//     32-row quadrant of its tile for all feature columns and loads the next 32
+//     accumulator columns from tensor memory while it converts the current ones;
+//   * after the first rounding every value is an integer, so the residual sum,
+//     the second ReLU and the saturation run in integer arithmetic:
+//     round(relu(round(v) + e)) == relu(int(round(v)) + e) exactly, as long as
+//     |round(v)| < 2^30.  A bound on |v| is evaluated per feature tile from the
+//     constants ((K * 255 * 128 + |bias|) * |q|); tiles that could exceed it run
+//     the float-domain path;
+//   * unsigned saturation stands in for a ReLU that precedes it.
+// The kernel is launched with programmatic stream serialisation: its prologue
+// (barrier set-up, tensor-memory allocation, descriptor prefetch) overlaps the
+// tail of the previous kernel in the stream; griddepcontrol.wait orders every
+// global-memory access after that kernel's completion.
+#include "conv_i8_tc.hpp"
+
+namespace b200 {
+
+constexpr int kFastThreads = 384;          // warp 0 TMA loads, 1 MMA issue, 2 TMA stores, 3 idle, 4..11 epilogue
+constexpr int kFastEpiWarp0 = 4;
+constexpr int kGroups = 2;                 // epilogue warp groups, alternate tiles
+
+struct FastAux {
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t tmem_full[kMaxBufs];
+    uint64_t tmem_empty[kMaxBufs];
+    uint64_t res_full[kMaxBufs];
+    uint64_t stage_free[kMaxBufs];
+    uint64_t out_ready[kMaxBufs];
+    uint64_t drain;
+    uint32_t tmem_base;
+    uint32_t abort;
+    uint32_t wide[kGroups][4];             // per epilogue warp: a feature of the current tile may leave the integer-safe range
+    alignas(16) int32_t bias_i[kGroups][kMaxBN];
+    alignas(16) float quant[kGroups][kMaxBN];
+};
+
+size_t tc_fast_aux_bytes() { return sizeof(FastAux); }
+
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// c + byte `sel` of the unsigned bytes in `a` (sel = 1 << 8*i picks byte i)
+__device__ __forceinline__ int32_t dp4a_u8(uint32_t a, int32_t sel, int32_t c)
+{
+    int32_t d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(sel), "r"(c)); return d;
+}
+
+// bytes above 127 become 127 (a ReLU'd value saturated to u8, re-saturated to s8)
+__device__ __forceinline__ uint32_t clamp_bytes_127(uint32_t w)
+{
+    const uint32_t m = w & 0x80808080u;
+    return (w | (m - (m >> 7))) & 0x7f7f7f7fu;
+}
+
+constexpr float kMagic = 8388608.0f;             // 2^23: x + 2^23 toward zero leaves floor(x) in the mantissa for 0 <= x < 2^23
+constexpr int32_t kMagicBits = 0x4B000000;
+
+// 32 features of one pixel.  Requires |v| < 2^22 for every dequantised value v
+// (guaranteed per feature tile by the caller), which makes every step exact
+// without a float->int conversion instruction:
+//   round-half-away(v) = sign(v) * floor(|v| + 0.5), floor taken by the 2^23 trick
+//   with round-toward-zero additions (x + 0.5 toward zero never reaches the next integer).
+// kOut: 0 = u8 output (its saturation covers a preceding ReLU), 1 = s8 output,
+// 2 = s8 output after a ReLU.  kRelu1: ReLU between the convolution and the residual sum.
+// e_xor / k_pos / k_neg: the residual word is made unsigned by e_xor (0 or 0x80808080),
+// k_pos = 2^23 bits (+128 for a signed residual), k_neg = 2^23 bits (-128 for a signed residual).
+template <bool kFused, bool kRelu1, int kOut>
+__device__ __forceinline__ void fast_chunk32(const uint32_t (&r)[32], const int32_t* bias, const float* quant,
+                                             uint4* p0, uint4* p1, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+{
+    uint32_t ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (kFused) {
+        const uint4 e0 = *p0, e1 = *p1;
+        ew[0] = e0.x ^ e_xor; ew[1] = e0.y ^ e_xor; ew[2] = e0.z ^ e_xor; ew[3] = e0.w ^ e_xor;
+        ew[4] = e1.x ^ e_xor; ew[5] = e1.y ^ e_xor; ew[6] = e1.z ^ e_xor; ew[7] = e1.w ^ e_xor;
+    }
+    uint32_t ow[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const int4 bi = reinterpret_cast<const int4*>(bias)[g];
+        const float4 q = reinterpret_cast<const float4*>(quant)[g];
+        const int32_t b4[4] = {bi.x, bi.y, bi.z, bi.w};
+        const float q4[4] = {q.x, q.y, q.z, q.w};
+        int32_t o4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
+            int32_t o;
+            if (!kFused && kOut != 1) {
+                // negative values end at 0 either way (unsigned saturation), so no sign handling
+                o = __float_as_int(__fadd_rz(__fadd_rz(v, 0.5f), kMagic)) - kMagicBits;
+            } else if (kFused && kRelu1) {
+                o = __float_as_int(__fadd_rz(__fadd_rz(v, 0.5f), kMagic)) - k_pos;
+                if (v < 0.0f) o = kMagicBits - k_pos;                 // ReLU: the convolution contributes 0
+            } else {
+                const int32_t wb = __float_as_int(__fadd_rz(__fadd_rz(fabsf(v), 0.5f), kMagic));
+                o = wb - (kFused ? k_pos : kMagicBits);
+                if (v < 0.0f) o = (kFused ? k_neg : kMagicBits) - wb;
+            }
+            if (kFused) o = dp4a_u8(ew[g], 1 << (8 * i), o);
+            o4[i] = o;
+        }
+        if (kOut == 1) ow[g] = pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
+        else {
+            ow[g] = pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u));
+            if (kOut == 2) ow[g] = clamp_bytes_127(ow[g]);
+        }
+    }
+    *p0 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    *p1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+}
+
+template <int BN>
+__device__ __forceinline__ void fast_chunk_ptrs(uint8_t* stg, int row, uint32_t sw, int c0, uint4*& p0, uint4*& p1)
+{
+    constexpr int CW = BN < 128 ? BN : 128;
+    const int cb = c0 / CW, o = c0 - cb * CW;
+    uint8_t* rowp = stg + (size_t)cb * kBM * CW + (size_t)row * CW;
+    p0 = reinterpret_cast<uint4*>(rowp + ((((uint32_t)o >> 4) ^ sw) << 4));
+    p1 = reinterpret_cast<uint4*>(rowp + (((((uint32_t)o >> 4) + 1u) ^ sw) << 4));
+}
+
+// One 32-row quadrant of a tile, all BN feature columns.
+template <int BN, bool kFused, bool kRelu1, int kOut>
+__device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
+                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+{
+    const int32_t* bias = aux->bias_i[group];
+    const float* quant = aux->quant[group];
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 64) {
+        uint4 *p0, *p1;
+        tmem_ld_wait();
+        tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);             // in flight while `ra` is converted
+        fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
+        fast_chunk32<kFused, kRelu1, kOut>(ra, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg);
+        tmem_ld_wait();
+        if (c0 + 64 < BN) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
+        else {
+            // the accumulator has been read out: the MMA issuer may reuse it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar);
+        }
+        fast_chunk_ptrs<BN>(stg, row, sw, c0 + 32, p0, p1);
+        fast_chunk32<kFused, kRelu1, kOut>(rb, bias + c0 + 32, quant + c0 + 32, p0, p1, e_xor, k_pos, k_neg);
+    }
+}
+
+// The same tile in float arithmetic, element by element (fused residual only):
+// taken when a feature's value range could leave the integer-safe range.
+template <int BN>
+__device__ __noinline__ void fast_tile_wide(const TcParams& P, const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row,
+                                            uint32_t sw, uint32_t tmem_empty_bar, int lane)
+{
+    const EpiCfg& c = P.epi;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + (uint32_t)c0, r);
+        tmem_ld_wait();
+        uint4 *p0, *p1;
+        fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
+        uint8_t* b0 = reinterpret_cast<uint8_t*>(p0);
+        uint8_t* b1 = reinterpret_cast<uint8_t*>(p1);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            uint8_t* bp = (j < 16 ? b0 : b1) + (j & 15);
+            const float e = c.eltw_dtype == CLDNN_B200_U8 ? (float)*bp : (float)*reinterpret_cast<int8_t*>(bp);
+            const float v = epi_quant(c, (int32_t)r[j] + aux->bias_i[group][c0 + j], aux->quant[group][c0 + j], 0.0f, 1.0f, e, 1.0f);
+            const int32_t i = __float2int_rz(v);
+            *bp = c.out_dtype == CLDNN_B200_U8 ? (uint8_t)min(255, max(0, i)) : (uint8_t)(int8_t)min(127, max(-128, i));
+        }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tmem_empty_bar);
+}
+
+template <int BN, bool kFused>
+__global__ void __launch_bounds__(kFastThreads, 1)
+conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
+{
+    constexpr int NBUF = BN >= 256 ? 2 : 4;
+    constexpr int CW = BN < 128 ? BN : 128;
+    constexpr int COLB = BN / CW;
+    constexpr uint32_t kStagingBytes = (uint32_t)(kBM * BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t a_base = base;
+    const uint32_t b_base = base + (uint32_t)(P.stages * P.a_stage_bytes);
+    const uint32_t ring_bytes = (uint32_t)(P.stages * (P.a_stage_bytes + P.b_stage_bytes));
+    uint8_t* staging = smem + ring_bytes;
+    FastAux* aux = reinterpret_cast<FastAux*>(smem + ring_bytes + (uint32_t)NBUF * kStagingBytes);
+    volatile uint32_t* s_abort = &aux->abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 0) atomicMin(&g_tc_time[0], globaltimer());
+#endif
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
+        for (int a = 0; a < kMaxBufs; ++a) {
+            mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4);
+            mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
+            mbar_init(smem_u32(&aux->out_ready[a]), 4);
+        }
+        mbar_init(smem_u32(&aux->drain), 1);
+        aux->abort = 0u;
+        mbar_fence_init();
+        prefetch_tensormap(&P.tmA); prefetch_tensormap(&P.tmB); prefetch_tensormap(&P.tmO);
+        if (kFused) prefetch_tensormap(&P.tmE);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    griddep_launch_dependents();
+    griddep_wait();                                   // everything below may touch memory the previous kernel wrote or read
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 0) atomicMax(&g_tc_time[2], globaltimer());
+#endif
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true; int t = 0;
+            Prof prof; prof.begin();
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
+                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
+                int c_w = 0, c_h = 0, c_n = 0, o_w = 0, o_h = 0;
+                if (P.a_mode == A_IM2COL) {
+                    const int64_t m = (int64_t)m_tile * kBM; const int pq = P.P * P.Q;
+                    const int n = (int)(m / pq); const int rr = (int)(m - (int64_t)n * pq); const int p = rr / P.Q, q = rr - p * P.Q;
+                    c_w = q * P.stride_x - P.pad_x; c_h = p * P.stride_y - P.pad_y; c_n = n;
+                } else if (P.a_mode == A_TILED) {
+                    const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
+                    o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
+                    c_w = o_w - P.pad_x; c_h = o_h - P.pad_y;
+                }
+                int tap = 0, cc = 0, r = 0, s = 0;
+                for (int ks = 0; ks < P.k_steps; ++ks) {
+                    prof.start();
+                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                    prof.stop(0);
+                    const uint32_t full = smem_u32(&aux->full[stage]);
+                    mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
+                    const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
+                    const uint32_t b_dst = b_base + (uint32_t)(stage * P.b_stage_bytes);
+                    const int c0 = cc * P.bk;
+                    if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
+                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
+                    else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
+                    tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * BN);
+                    ++issued;
+                    if (++cc == P.chunks) { cc = 0; ++tap; if (++s == P.kw) { s = 0; ++r; } }
+                    if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            prof.flush(0, 1);
+            if (!ok) {
+                // unwind: let the copies already in flight land before the CTA's shared memory goes away
+                int st = stage; uint32_t ph = phase;
+                const int pending = issued < P.stages ? (int)issued : P.stages;
+                for (int i = 0; i < pending; ++i) {
+                    if (--st < 0) { st = P.stages - 1; ph ^= 1u; }
+                    const uint64_t t0 = globaltimer();
+                    while (!mbar_try_wait(smem_u32(&aux->full[st]), ph) && globaltimer() - t0 < 100000000ull) { }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
+            Prof prof; prof.begin();
+            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
+                const int acc = t % NBUF;
+                prof.start();
+                if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                prof.stop(0);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int ks = 0; ks < P.k_steps; ++ks) {
+                    prof.start();
+                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    prof.stop(1);
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(a_base + (uint32_t)(stage * P.a_stage_bytes), P.sbo, P.layout_type);
+                    const uint64_t bdesc = make_smem_desc(b_base + (uint32_t)(stage * P.b_stage_bytes), P.sbo, P.layout_type);
+                    const int kk = P.bk >> 5;
+                    for (int k = 0; k < kk; ++k)
+                        mma_i8_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P.idesc, (ks | k) ? 1u : 0u);
+                    tc_commit(smem_u32(&aux->empty[stage]));
+                    if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
+            }
+            prof.flush(3, 2);
+            tc_commit(smem_u32(&aux->drain));
+            const uint64_t t0 = globaltimer();
+            while (!mbar_try_wait(smem_u32(&aux->drain), 0u)) {
+                if (globaltimer() - t0 > kWaitLimitNs) { atomicCAS(P.status, 0u, kErrDrain); break; }
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------ TMA store issuer --------------------------
+        if (lane == 0) {
+            int t = 0;
+            Prof prof; prof.begin();
+            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
+                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
+                const int a = t % NBUF;
+                prof.start();
+                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NBUF) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
+                prof.stop(0);
+                int tw = 0, th = 0, tb = 0;
+                if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
+#pragma unroll
+                for (int cb = 0; cb < COLB; ++cb) {
+                    const int f0 = n_tile * BN + cb * CW;
+                    const uint32_t src = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
+                    if (P.a_mode == A_TILED) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
+                    else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
+                }
+                bulk_commit();
+                prof.start();
+                bulk_wait_read0();                                  // the buffer may be refilled once TMA has read it
+                prof.stop(1);
+                mbar_arrive(smem_u32(&aux->stage_free[a]));
+            }
+            prof.flush(6, 2);
+        }
+    } else if (warp == 3) {
+        // ------------------------------ residual loader ---------------------------
+        // Second input of the fused sum: same pixels and features as the output tile, brought into the
+        // staging buffer the epilogue will overwrite.  Its own warp, so that waiting for a staging buffer
+        // never holds back the operand loads of later tiles.
+        if (kFused && lane == 0) {
+            int t = 0;
+            Prof prof; prof.begin();
+            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
+                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
+                int o_w = 0, o_h = 0, c_n = 0;
+                if (P.a_mode == A_TILED) {
+                    const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
+                    o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
+                }
+                const int a = t % NBUF;
+                prof.start();
+                if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
+                prof.stop(1);
+                const uint32_t rf = smem_u32(&aux->res_full[a]);
+                mbar_expect_tx(rf, (uint32_t)(P.stage_rows * BN));
+#pragma unroll
+                for (int cb = 0; cb < COLB; ++cb) {
+                    const uint32_t dst = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
+                    const int f0 = n_tile * BN + cb * CW;
+                    if (P.a_mode == A_TILED) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
+                    else tma_load_2d(dst, &P.tmE, rf, f0, m_tile * kBM);
+                }
+            }
+        }
+    } else if (warp >= kFastEpiWarp0) {
+        // ------------------------------ epilogue ----------------------------------
+        const int ew = warp - kFastEpiWarp0;
+        const int quad = ew & 3;                                    // TMEM lanes 32*quad .. 32*quad+31 (warp index mod 4)
+        const int group = ew >> 2;
+        const int row = quad * 32 + lane;
+        const int gt = (ew & 3) * 32 + lane;                        // thread index within the group
+        const uint32_t sw = CW == 128 ? ((uint32_t)row & 7u) : (((uint32_t)row >> 1) & 3u);
+        const EpiCfg& c = P.epi;
+        // a signed residual is read as unsigned bytes + 128 and the 128 taken back out of the constants
+        const bool res_s8 = kFused && c.eltw_dtype != CLDNN_B200_U8;
+        const uint32_t e_xor = res_s8 ? 0x80808080u : 0u;
+        const int32_t k_pos = kMagicBits + (res_s8 ? 128 : 0), k_neg = kMagicBits - (res_s8 ? 128 : 0);
+        const int variant = P.fast_variant;
+        int cur_n_tile = -1; bool ok = true; bool wide = false;
+        Prof prof; prof.begin();
+        int t = group;
+        for (int tile = blockIdx.x + group * gridDim.x; tile < P.total_tiles && ok; tile += kGroups * gridDim.x, t += kGroups) {
+            const int n_tile = tile / P.m_tiles;
+            const int acc = t % NBUF;
+            const uint32_t par = (uint32_t)(t / NBUF) & 1u;
+            if (n_tile != cur_n_tile) {
+                prof.start();
+                named_bar_sync(1 + group, 128);                     // every warp of the group has left the previous feature range
+                bool w = false;
+                for (int j = gt; j < BN; j += 128) {
+                    const int f = n_tile * BN + j;
+                    const int32_t bi = c.bias_dtype != CLDNN_B200_NONE ? ((const int32_t*)P.bias)[f] : 0;
+                    const float q = P.quant[f];
+                    aux->bias_i[group][j] = bi; aux->quant[group][j] = q;
+                    w = w || !(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)) < 4.0e6f);
+                }
+                w = __any_sync(0xffffffffu, w);
+                if (lane == 0) aux->wide[group][quad] = w ? 1u : 0u;
+                named_bar_sync(1 + group, 128);
+                wide = (aux->wide[group][0] | aux->wide[group][1] | aux->wide[group][2] | aux->wide[group][3]) != 0u;
+                cur_n_tile = n_tile;
+                prof.stop(2);
+            }
+            prof.start();
+            if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), par, s_abort, P.status, kErrEpilogue)) { ok = false; break; }
+            prof.stop(0);
+            prof.start();
+            // the staging buffer is ours once its residual tile has landed (fused) or its previous store has been read out
+            const bool got = kFused ? mbar_wait(smem_u32(&aux->res_full[acc]), par, s_abort, P.status, kErrEpilogue + 1u)
+                                    : mbar_wait(smem_u32(&aux->stage_free[acc]), par ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
+            if (!got) { ok = false; break; }
+            prof.stop(1);
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+            uint8_t* stg = staging + (size_t)acc * kStagingBytes;
+            const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
+            if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
+            else if (kFused) {
+                switch (variant) {
+                    case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 1: fast_tile<BN, true, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 2: fast_tile<BN, true, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 3: fast_tile<BN, true, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 4: fast_tile<BN, true, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    default: fast_tile<BN, true, true, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                }
+            } else {
+                switch (variant >> 1) {
+                    case 0: fast_tile<BN, false, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 1: fast_tile<BN, false, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    default: fast_tile<BN, false, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->out_ready[acc]));
+        }
+        if (ew == 0 && lane == 0) prof.flush(9, 3, (t - group) / kGroups);
+    }
+
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == kFastEpiWarp0 * 32) atomicMin(&g_tc_time[3], globaltimer());
+#endif
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+#ifdef CONV_TC_PROFILE
+    if (threadIdx.x == 0) atomicMax(&g_tc_time[1], globaltimer());
+#endif
+}
+
+#ifdef CONV_TC_PROFILE
+extern "C" __attribute__((visibility("default"))) int cldnn_b200_debug_tc_prof(unsigned long long* host_out)
+{
+    return (int)cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(g_tc_prof));
+}
+extern "C" __attribute__((visibility("default"))) int cldnn_b200_debug_tc_time(unsigned long long* host_out)
+{
+    cudaDeviceSynchronize();
+    int rc = (int)cudaMemcpyFromSymbol(host_out, g_tc_time, sizeof(g_tc_time));
+    const unsigned long long init[4] = {~0ull, 0ull, 0ull, ~0ull};
+    cudaMemcpyToSymbol(g_tc_time, init, sizeof(init));
+    return rc;
+}
+#endif
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+bool tc_fast_eligible(const TcParams& P)
+{
+    if (!P.lean || !P.staged) return false;
+    if (P.bn != 64 && P.bn != 128 && P.bn != 256) return false;
+    if (P.ofm % P.bn) return false;
+    if (P.epi.bias_dtype != CLDNN_B200_NONE && P.epi.bias_dtype != CLDNN_B200_I32) return false;
+    return true;
+}
+
+static const void* fast_kernel_of(const TcParams& P)
+{
+    const bool f = P.epi.fused_eltw != 0;
+    switch (P.bn) {
+    case 64:  return f ? (const void*)conv_i8_tc_fast_kernel<64, true> : (const void*)conv_i8_tc_fast_kernel<64, false>;
+    case 128: return f ? (const void*)conv_i8_tc_fast_kernel<128, true> : (const void*)conv_i8_tc_fast_kernel<128, false>;
+    default:  return f ? (const void*)conv_i8_tc_fast_kernel<256, true> : (const void*)conv_i8_tc_fast_kernel<256, false>;
+    }
+}
+
+cudaError_t tc_fast_configure(const TcParams& P, int max_smem)
+{
+    return cudaFuncSetAttribute(fast_kernel_of(P), cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+}
+
+cudaError_t tc_fast_launch(const TcParams& P, int grid, size_t smem_bytes, cudaStream_t stream)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(kFastThreads); cfg.dynamicSmemBytes = smem_bytes; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    void* args[1] = {const_cast<TcParams*>(&P)};
+    return cudaLaunchKernelExC(&cfg, fast_kernel_of(P), args);
+}
+
+}  // namespace b200

@@ -108,6 +108,47 @@ def test_epilogue_variants(eng, name, kernel):
     _exact(eng, case, kernel)
 
 
+# The specialised kernels behind conv_i8_tc (per-channel dequantisation only, NONE / ReLU, 8-bit output):
+# every epilogue variant they are compiled for, on every feature tile, and the float-domain path they
+# fall back to when a feature's value range could leave the integer-exact range.
+FAST_VARIANTS = {
+    "plain_u8_none": dict(out_dtype=np.uint8, act=abi.ACT_NONE),
+    "plain_u8_relu": dict(out_dtype=np.uint8),
+    "plain_s8_none": dict(act=abi.ACT_NONE),
+    "plain_s8_relu": dict(),
+    "plain_s8_in": dict(in_dtype=np.int8, act=abi.ACT_NONE),
+    "sum_u8_none_relu": dict(fused=True, out_dtype=np.uint8, act=abi.ACT_NONE),                       # the ResNet block tail
+    "sum_u8_relu_none": dict(fused=True, out_dtype=np.uint8, eltw_act=abi.ACT_NONE),
+    "sum_u8_none_none_s8res": dict(fused=True, out_dtype=np.uint8, act=abi.ACT_NONE, eltw_act=abi.ACT_NONE, eltw_dtype=np.int8),
+    "sum_s8_none_none_s8res": dict(fused=True, out_dtype=np.int8, act=abi.ACT_NONE, eltw_act=abi.ACT_NONE, eltw_dtype=np.int8),
+    "sum_s8_none_relu_s8res": dict(fused=True, out_dtype=np.int8, act=abi.ACT_NONE, eltw_dtype=np.int8),
+    "sum_s8_relu_relu_u8res": dict(fused=True, out_dtype=np.int8, eltw_dtype=np.uint8),
+    "sum_s8_relu_none_u8res": dict(fused=True, out_dtype=np.int8, eltw_act=abi.ACT_NONE, eltw_dtype=np.uint8),
+    "sum_in_place": dict(fused=True, out_dtype=np.uint8, act=abi.ACT_NONE, in_out_opt=True),
+    "sum_no_bias": dict(fused=True, out_dtype=np.uint8, act=abi.ACT_NONE, bias="none"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FAST_VARIANTS))
+@pytest.mark.parametrize("wide", [False, True])
+def test_conv_i8_tc_fast_variants(eng, name, wide):
+    k = eng.kernel("conv_i8_tc")
+    case = cases.make_conv_case(11, N=12, C=64, K=256, H=14, W=14, scale_lo=2.0 ** -13, scale_hi=2.0 ** -11, **FAST_VARIANTS[name])
+    if wide:
+        case.quant[7] = 0.75          # one feature whose values can exceed 2^22: its tile takes the float-domain path
+        case.quant[200] = -3.0
+    want = cases.run_oracle(case)
+    n = case.out_elems
+    assert len(np.unique(want[:n])) > 64
+    for tune in (0, 10, 11, 12, 7):   # automatic, tiled box with 64 / 128 / 256 features per tile, TMA im2col with 128
+        p = cases.copy_params(case.p)
+        p.tune = tune
+        assert k.supports(p)
+        got = cases.run_gpu(eng, case, "conv_i8_tc", tune)
+        bad = np.flatnonzero(want[:n] != got[:n])
+        assert bad.size == 0, "tune %d: %d of %d differ; first at %d: want %d got %d" % (tune, bad.size, n, bad[0], want[bad[0]], got[bad[0]])
+
+
 FIRST_LAYER = {
     # ResNet-50 conv1: 3 -> 64, 7x7 stride 2 pad 3, planar u8 image in, byxf out
     "resnet_conv1": dict(N=2, C=3, K=64, H=224, W=224, kh=7, kw=7, stride=2, pad=3),
