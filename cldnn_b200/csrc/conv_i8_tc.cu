@@ -419,8 +419,10 @@ struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; };
 
 // tune index -> (addressing mode, feature tile).  0 = automatic choice.
 static const int kTuneBN[4] = {32, 64, 128, 256};
-// Indices 13..24 repeat 1..12 on the general kernel where the specialised one (conv_i8_tc_fast.cu) would be used.
-static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4; }
+// Indices 13..24 repeat 1..12 on the general kernel where the specialised one (conv_i8_tc_fast.cu) would be used;
+// 25..28 are the patch mode (resident weights, one activation patch per filter column) of the specialised kernel.
+static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4 + 4; }
+constexpr size_t kPatchWeightBytes = 72 * 1024;       // largest weight tensor the patch mode keeps resident
 
 static bool dense_byxf(const cldnn_b200_tensor& t)
 {
@@ -440,6 +442,38 @@ static void choose_box(int Q, int Pn, int N, int& bw, int& bh, int& bb)
             // prefer long contiguous runs when the efficiency ties
             const double score = eff + 1e-4 * w + 1e-6 * h;
             if (score > best) { best = score; bw = w; bh = h; bb = b; }
+        }
+    }
+}
+
+// The epilogue configuration the specialised kernels cover: per-channel dequantisation only, NONE / ReLU,
+// 8-bit output (and residual), integer or no bias.
+static bool lean_params(const cldnn_b200_conv_params& p)
+{
+    auto none_or_relu = [](int32_t fn) { return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU; };
+    if (!p.quantization || p.i_qf != 1.0f || p.calibration || p.o_qf != 1.0f) return false;
+    if (!is_int8(p.out.dtype) || !none_or_relu(p.act)) return false;
+    if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32) return false;
+    if (p.fused_eltw) {
+        const int32_t edt = p.in_out_opt ? p.out.dtype : p.eltw.dtype;
+        if (!is_int8(edt) || p.has_non_conv_scale || p.eltw_calibration || !none_or_relu(p.eltw_act)) return false;
+    }
+    return true;
+}
+
+// patch mode: a tile of tw x th output pixels of one image (tw * th <= 128); per filter column one patch of
+// (th + kh - 1) x tw input pixels serves the kh taps of that column.  Fewest wasted tile rows first, then least traffic.
+static void choose_patch(int Q, int Pn, int kh, int kw, int& tw, int& th)
+{
+    double best = -1.0; tw = 1; th = 1;
+    for (int w = 1; w <= Q && w <= 128; ++w) {
+        for (int h = 1; h <= Pn && w * h <= 128; ++h) {
+            if (h + kh - 1 > 256) continue;
+            const double tiles = (double)((Q + w - 1) / w) * ((Pn + h - 1) / h);
+            const double eff = ((double)Q * Pn) / (tiles * 128.0);
+            const double traffic = tiles * kw * (h + kh - 1) * w / ((double)Q * Pn * kh * kw);   // relative to one load per tap
+            const double score = eff - 0.25 * traffic;
+            if (score > best) { best = score; tw = w; th = h; }
         }
     }
 }
@@ -480,16 +514,36 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
                            (int64_t)p.in.b * p.in.pb >= 131072;     // small tensors take the tiled path
     int tune = p.tune;
     int mode = -1, bn = 0;
-    if (tune > 12) tune -= 12;
-    if (tune > 0) { mode = (tune - 1) / 4; bn = kTuneBN[(tune - 1) % 4]; }
-    if (mode < 0) mode = is_1x1_s1 ? A_FLAT : (im2col_ok ? A_IM2COL : A_TILED);
+    if (tune > 24) { mode = A_PATCH; bn = kTuneBN[(tune - 25) % 4]; }
+    else {
+        if (tune > 12) tune -= 12;
+        if (tune > 0) { mode = (tune - 1) / 4; bn = kTuneBN[(tune - 1) % 4]; }
+    }
+    // patch mode: stride-1 undilated filters whose weights fit in shared memory, specialised epilogue configuration
+    auto patch_why = [&](int fbn) -> const char* {
+        if (p.stride_x != 1 || p.stride_y != 1 || p.dil_x != 1 || p.dil_y != 1 || p.kh * p.kw == 1) return "patch mode needs a stride-1 undilated filter larger than 1x1";
+        if (fbn < 64 || p.ofm % fbn) return "patch mode needs output features in whole tiles of 64, 128 or 256";
+        if ((size_t)p.kh * p.kw * cs * p.ofm > kPatchWeightBytes) return "patch mode keeps all weights in shared memory: at most 72 KiB";
+        if (!lean_params(p)) return "patch mode exists for the specialised epilogue configuration only";
+        const cldnn_b200_tensor& rt = p.in_out_opt ? p.out : p.eltw;
+        if (p.out.px % 16 || p.out.py % 16 || p.out.pb % 16 || p.out.offset % 16) return "patch mode needs a 16-byte aligned output";
+        if (p.fused_eltw && (rt.pf != 1 || rt.px % 16 || rt.py % 16 || rt.pb % 16 || rt.offset % 16)) return "patch mode needs a 16-byte aligned byxf residual";
+        return nullptr;
+    };
+    if (mode < 0) {
+        const int fbn = p.ofm % 256 == 0 ? 256 : (p.ofm % 128 == 0 ? 128 : 64);
+        if (!patch_why(fbn)) { mode = A_PATCH; bn = fbn; }
+        else mode = is_1x1_s1 ? A_FLAT : (im2col_ok ? A_IM2COL : A_TILED);
+    }
     if (mode == A_FLAT && !is_1x1_s1) return no("flat addressing needs a dense 1x1 stride-1 convolution");
     if (mode == A_TILED && !tiled_ok) return no("tiled addressing needs stride 1 or a pointwise filter");
     if (mode == A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded (or tensor below 128 KiB)");
     if (bn == 0) bn = p.ofm > 128 ? 256 : (p.ofm > 64 ? 128 : (p.ofm > 32 ? 64 : 32));
+    if (mode == A_PATCH) { if (const char* m = patch_why(bn)) return no(m); }
     pl.a_mode = mode; pl.bn = bn;
     pl.bw = pl.bh = pl.bb = 1;
     if (mode == A_TILED) choose_box(p.out.x, p.out.y, p.out.b, pl.bw, pl.bh, pl.bb);
+    if (mode == A_PATCH) choose_patch(p.out.x, p.out.y, p.kh, p.kw, pl.bw, pl.bh);
     return true;
 }
 
@@ -502,7 +556,7 @@ static bool tc_supports(const void* vp)
 static CUresult encode_pixel_map(CUtensorMap* tm, const TcPlan& pl, void* ptr, const cldnn_b200_tensor& t, int stride_x, int stride_y,
                                  int cw, CUtensorMapSwizzle sw)
 {
-    if (pl.a_mode == A_TILED) {
+    if (pl.a_mode == A_TILED || pl.a_mode == A_PATCH) {
         cuuint64_t dims[4] = {(cuuint64_t)t.f, (cuuint64_t)((t.x + stride_x - 1) / stride_x), (cuuint64_t)((t.y + stride_y - 1) / stride_y), (cuuint64_t)t.b};
         cuuint64_t strides[3] = {(cuuint64_t)(t.px * stride_x), (cuuint64_t)(t.py * stride_y), (cuuint64_t)t.pb};
         cuuint32_t box[4] = {(cuuint32_t)cw, (cuuint32_t)pl.bw, (cuuint32_t)pl.bh, (cuuint32_t)pl.bb};
@@ -541,7 +595,8 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.bn = pl.bn; P.n_tiles = (p.ofm + pl.bn - 1) / pl.bn;
     P.M_total = (int64_t)P.N * P.P * P.Q;
     P.bw = pl.bw; P.bh = pl.bh; P.bb = pl.bb;
-    if (pl.a_mode == A_TILED) {
+    const bool boxed = pl.a_mode == A_TILED || pl.a_mode == A_PATCH;
+    if (boxed) {
         P.tiles_w = (P.Q + pl.bw - 1) / pl.bw; P.tiles_h = (P.P + pl.bh - 1) / pl.bh;
         P.m_tiles = P.tiles_w * P.tiles_h * ((P.N + pl.bb - 1) / pl.bb);
     } else {
@@ -549,10 +604,18 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
         P.m_tiles = (int)((P.M_total + kBM - 1) / kBM);
     }
     P.total_tiles = P.m_tiles * P.n_tiles;
-    P.stage_rows = pl.a_mode == A_TILED ? pl.bw * pl.bh * pl.bb : kBM;
+    P.stage_rows = boxed ? pl.bw * pl.bh * pl.bb : kBM;
     P.a_stage_bytes = kBM * pl.bk; P.b_stage_bytes = pl.bn * pl.bk;
     P.a_tx_bytes = P.stage_rows * pl.bk;
     P.b_tx_bytes = pl.bn * pl.bk;
+    if (pl.a_mode == A_PATCH) {
+        // a stage holds the patch; the tensor core reads 128 rows from row r * bw, r < kh, so the stage spans that far
+        const int patch_rows = (pl.bh + p.kh - 1) * pl.bw, read_rows = (p.kh - 1) * pl.bw + kBM;
+        P.k_steps = p.kw * P.chunks;
+        P.a_tx_bytes = patch_rows * pl.bk;
+        P.a_stage_bytes = (((patch_rows > read_rows ? patch_rows : read_rows) * pl.bk) + 1023) / 1024 * 1024;
+        P.b_total_bytes = P.n_tiles * p.kh * p.kw * P.chunks * P.b_stage_bytes;
+    }
     P.sbo = 8u * (uint32_t)pl.bk;
     P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
     const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;     // operand signedness in the instruction descriptor
@@ -582,7 +645,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     // staged epilogue: the output (and residual) tile must be addressable by one TMA box per column block
     auto tma_ok = [&](const cldnn_b200_tensor& t, const void* ptr, int sx, int sy) {
         if (t.pf != 1 || t.px % 16 || t.py % 16 || t.pb % 16 || t.offset % 16 || ((uintptr_t)ptr & 15)) return false;
-        if (pl.a_mode == A_TILED) return true;
+        if (boxed) return true;
         return sx == 1 && sy == 1 && pixel_dense(t);
     };
     P.staged = (P.fast_epi && tma_ok(p.out, a->output, 1, 1) && (!p.fused_eltw || tma_ok(et, P.eltw, esx, esy))) ? 1 : 0;
@@ -595,18 +658,28 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     const int out_kind = out_u8 ? 0 : ((p.fused_eltw ? p.eltw_act : p.act) == CLDNN_B200_ACT_RELU ? 2 : 1);
     P.fast_variant = (out_kind << 1) | ((p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) ? 1 : 0);
     P.acc_bound = (float)p.kh * (float)p.kw * (float)p.ifm * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
-    const bool use_fast = p.tune <= 12 && tc_fast_eligible(P);
+#ifdef CONV_TC_DEBUG
+    if (const char* e = getenv("CLDNN_B200_TC_DEBUG")) P.debug = atoi(e);
+#endif
+    const bool use_fast = (p.tune <= 12 || p.tune > 24) && tc_fast_eligible(P);
 
     const size_t aux_bytes = use_fast ? tc_fast_aux_bytes() : sizeof(TcSmemAux);
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
-    const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
+    const bool patch = pl.a_mode == A_PATCH;
+    if (patch && !use_fast) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: the patch mode exists for the specialised epilogue configuration only");
+    const size_t stage_bytes = (size_t)P.a_stage_bytes + (patch ? 0 : P.b_stage_bytes);
+    const size_t resident = patch ? (size_t)P.b_total_bytes : 0;
     size_t staging_total = P.staged ? (size_t)P.nbuf * kBM * pl.bn : 0;
-    if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) { P.staged = 0; staging_total = 0; }
+    if (max_smem < 1024 + aux_bytes + staging_total + resident + 2 * stage_bytes) {
+        if (patch) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory for the patch mode");
+        P.staged = 0; staging_total = 0;
+    }
     if (max_smem < 1024 + aux_bytes + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory");
-    int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);
+    int stages = (int)((max_smem - 1024 - aux_bytes - staging_total - resident) / stage_bytes);
     if (stages > kMaxStages) stages = kMaxStages;
     P.stages = stages;
-    size_t smem_bytes = 1024 + (size_t)stages * stage_bytes + staging_total + aux_bytes;
+    P.ring_bytes = (int32_t)((size_t)stages * stage_bytes + resident);
+    size_t smem_bytes = 1024 + (size_t)P.ring_bytes + staging_total + aux_bytes;
     const size_t one_cta_floor = max_smem / 2 + 1024;                // keeps one CTA per SM, so TMEM allocation never waits
     if (smem_bytes < one_cta_floor) smem_bytes = one_cta_floor;
     if (smem_bytes > max_smem) smem_bytes = max_smem;
@@ -632,6 +705,13 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
         cuuint32_t es[4] = {1, (cuuint32_t)p.stride_x, (cuuint32_t)p.stride_y, 1};
         cr = g_encode_im2col(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, in_ptr, dims, strides, lower, upper, (cuuint32_t)pl.bk, (cuuint32_t)kBM, es,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (pl.a_mode == A_PATCH) {
+        cuuint64_t dims[4] = {(cuuint64_t)cs, (cuuint64_t)p.in.x, (cuuint64_t)p.in.y, (cuuint64_t)p.in.b};
+        cuuint64_t strides[3] = {(cuuint64_t)p.in.px, (cuuint64_t)p.in.py, (cuuint64_t)p.in.pb};
+        cuuint32_t box[4] = {(cuuint32_t)pl.bk, (cuuint32_t)pl.bw, (cuuint32_t)(pl.bh + p.kh - 1), 1};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        cr = g_encode_tiled(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, in_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         // tiled 4-D box; a pointwise strided convolution reads a strided view of the input
         const int sx = p.stride_x, sy = p.stride_y;

@@ -20,7 +20,7 @@ constexpr int kMaxBN = 256;
 constexpr int kMaxBufs = 4;               // accumulator / staging buffers in flight per CTA
 constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
 
-enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
+enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2, A_PATCH = 3 };
 
 struct alignas(64) TcParams {
     CUtensorMap tmA;                     // activations
@@ -44,6 +44,9 @@ struct alignas(64) TcParams {
     int32_t mul_iqf, mul_oqf;
     int32_t lean;                        // epilogue configuration covered by the hoisted fast body
     int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
+    // patch mode: all weights resident in shared memory, one activation patch per (filter column, channel chunk)
+    int32_t ring_bytes, b_total_bytes;   // operand area: activation ring (+ weight ring or resident weights)
+    int32_t debug;                       // diagnostic builds (-DCONV_TC_DEBUG): what-if switches, 0 otherwise
     int32_t fast_variant;                // conv_i8_tc_fast: (output kind << 1) | ReLU before the residual sum
     float acc_bound;                     // K * max|activation| * 128: no accumulator can exceed it in magnitude
     // output / residual addressing for the direct path, in elements

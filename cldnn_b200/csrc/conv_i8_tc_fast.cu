@@ -9,13 +9,22 @@
 //   * two groups of four epilogue warps take alternate tiles, each warp owns one
 //     32-row quadrant of its tile for all feature columns and loads the next 32
 //     accumulator columns from tensor memory while it converts the current ones;
-//   * after the first rounding every value is an integer, so the residual sum,
-//     the second ReLU and the saturation run in integer arithmetic:
-//     round(relu(round(v) + e)) == relu(int(round(v)) + e) exactly, as long as
-//     |round(v)| < 2^30.  A bound on |v| is evaluated per feature tile from the
-//     constants ((K * 255 * 128 + |bias|) * |q|); tiles that could exceed it run
-//     the float-domain path;
-//   * unsigned saturation stands in for a ReLU that precedes it.
+//   * rounding without conversion instructions (float->int conversions run at a sixth of
+//     the add rate here): round-half-away(v) = sign(v) * floor(|v| + 0.5), the floor taken
+//     from the mantissa of (|v| + 0.5) + 2^23, both additions rounding toward zero.  After
+//     that every value is an integer, so the residual sum (one dp4a that also picks the
+//     byte out of the residual word), the second ReLU and the saturation run in integer
+//     arithmetic: round(relu(round(v) + e)) == relu(int(round(v)) + e).  All of it is exact
+//     while |v| < 2^22; a bound on |v| is evaluated per feature tile from the constants
+//     ((K * 255 * 128 + |bias|) * |q|) and tiles that could exceed it run the float-domain
+//     path of the general kernel, element by element;
+//   * unsigned saturation stands in for a ReLU that precedes it;
+//   * the single thread that issues tcgen05.mma has its descriptors precomputed: at small
+//     feature tiles an MMA runs for 48-64 clocks and the issue loop is the critical path.
+// Patch mode (small 3x3-like filters whose whole weight tensor fits in shared memory): the
+// weights are loaded once per CTA and each filter column needs one activation patch of
+// (tile rows + kh - 1) x tile width pixels; the kh taps of the column read that patch at
+// row offsets through the operand descriptor's start address, instead of kh separate loads.
 // The kernel is launched with programmatic stream serialisation: its prologue
 // (barrier set-up, tensor-memory allocation, descriptor prefetch) overlaps the
 // tail of the previous kernel in the stream; griddepcontrol.wait orders every
@@ -37,6 +46,7 @@ struct FastAux {
     uint64_t stage_free[kMaxBufs];
     uint64_t out_ready[kMaxBufs];
     uint64_t drain;
+    uint64_t b_full;                       // patch mode: the resident weights have landed
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t wide[kGroups][4];             // per epilogue warp: a feature of the current tile may leave the integer-safe range
@@ -46,8 +56,34 @@ struct FastAux {
 
 size_t tc_fast_aux_bytes() { return sizeof(FastAux); }
 
+
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A K-major swizzled operand descriptor split in halves: the high word is constant per launch
+// (8-row group stride, descriptor version, swizzle mode), the low word holds the start address.
+__device__ __forceinline__ uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout_type)
+{
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | ((layout_type & 7u) << 29);
+}
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi)
+{
+    uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi)); return d;
+}
+// KK tensor-core instructions over one channel chunk, 32 bytes of K each
+#ifdef CONV_TC_DEBUG
+#define TC_DEBUG(P, bit) (((P).debug >> (bit)) & 1)
+#else
+#define TC_DEBUG(P, bit) 0
+#endif
+template <int KK>
+__device__ __forceinline__ void mma_chunk(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t acc_first)
+{
+#pragma unroll
+    for (int k = 0; k < KK; ++k)
+        mma_i8_ss(d_tmem, desc64(a_lo + 2u * k, hi), desc64(b_lo + 2u * k, hi), idesc, k ? 1u : acc_first);
+}
+
 // c + byte `sel` of the unsigned bytes in `a` (sel = 1 << 8*i picks byte i)
 __device__ __forceinline__ int32_t dp4a_u8(uint32_t a, int32_t sel, int32_t c)
 {
@@ -203,7 +239,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     uint8_t* smem = smem_raw + (base - raw);
     const uint32_t a_base = base;
     const uint32_t b_base = base + (uint32_t)(P.stages * P.a_stage_bytes);
-    const uint32_t ring_bytes = (uint32_t)(P.stages * (P.a_stage_bytes + P.b_stage_bytes));
+    const uint32_t ring_bytes = (uint32_t)P.ring_bytes;
     uint8_t* staging = smem + ring_bytes;
     FastAux* aux = reinterpret_cast<FastAux*>(smem + ring_bytes + (uint32_t)NBUF * kStagingBytes);
     volatile uint32_t* s_abort = &aux->abort;
@@ -221,6 +257,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             mbar_init(smem_u32(&aux->out_ready[a]), 4);
         }
         mbar_init(smem_u32(&aux->drain), 1);
+        mbar_init(smem_u32(&aux->b_full), 1);
         aux->abort = 0u;
         mbar_fence_init();
         prefetch_tensormap(&P.tmA); prefetch_tensormap(&P.tmB); prefetch_tensormap(&P.tmO);
@@ -249,15 +286,41 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     const int64_t m = (int64_t)m_tile * kBM; const int pq = P.P * P.Q;
                     const int n = (int)(m / pq); const int rr = (int)(m - (int64_t)n * pq); const int p = rr / P.Q, q = rr - p * P.Q;
                     c_w = q * P.stride_x - P.pad_x; c_h = p * P.stride_y - P.pad_y; c_n = n;
-                } else if (P.a_mode == A_TILED) {
+                } else if (P.a_mode == A_TILED || P.a_mode == A_PATCH) {
                     const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
                     o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
                     c_w = o_w - P.pad_x; c_h = o_h - P.pad_y;
                 }
+                if (P.a_mode == A_PATCH) {
+                    if (t == 0) {
+                        // every filter tap of every feature tile, once per CTA
+                        const uint32_t bf = smem_u32(&aux->b_full);
+                        mbar_expect_tx(bf, (uint32_t)P.b_total_bytes);
+                        uint32_t dst = b_base;
+                        for (int nt = 0; nt < P.n_tiles; ++nt)
+                            for (int tp = 0; tp < P.kh * P.kw; ++tp)
+                                for (int ch = 0; ch < P.chunks; ++ch, dst += (uint32_t)P.b_stage_bytes)
+                                    tma_load_3d(dst, &P.tmB, bf, ch * P.bk, tp, nt * BN);
+                    }
+                    // one patch of (bh + kh - 1) x bw pixels per filter column and channel chunk; the kh taps of that
+                    // column read it at row offsets
+                    for (int ks = 0; ks < P.k_steps; ++ks) {
+                        const int s = ks / P.chunks, cc = ks - s * P.chunks;
+                        prof.start();
+                        if (!mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                        prof.stop(0);
+                        const uint32_t full = smem_u32(&aux->full[stage]);
+                        mbar_expect_tx(full, (uint32_t)P.a_tx_bytes);
+                        tma_load_4d(a_base + (uint32_t)(stage * P.a_stage_bytes), &P.tmA, full, cc * P.bk, c_w + s, c_h, c_n);
+                        ++issued;
+                        if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                    }
+                    continue;
+                }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
                     prof.start();
-                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                    if (!mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
                     prof.stop(0);
                     const uint32_t full = smem_u32(&aux->full[stage]);
                     mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
@@ -287,32 +350,64 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
+        // One thread feeds the tensor core; everything it can precompute is precomputed, because at small
+        // feature tiles an MMA runs for only 48-64 clocks and a dependent scalar instruction costs ~4.
         if (lane == 0) {
+            const uint32_t hi = desc_hi(P.sbo, P.layout_type);
+            const uint32_t a_lo0 = desc_lo(a_base), b_lo0 = desc_lo(b_base);
+            const uint32_t a_step = (uint32_t)P.a_stage_bytes >> 4, b_step = (uint32_t)P.b_stage_bytes >> 4;
+            const uint32_t full0 = smem_u32(&aux->full[0]), empty0 = smem_u32(&aux->empty[0]);
+            const int kk = P.bk >> 5, stages = P.stages, k_steps = P.k_steps;
+            const uint32_t idesc = P.idesc;
+            const bool patch = P.a_mode == A_PATCH;
+            const uint32_t row_step = (uint32_t)(P.bw * P.bk) >> 4;                    // patch mode: one filter row further down the patch
+            const uint32_t b_row_step = (uint32_t)(P.kw * P.chunks) * b_step;          //             the weights of the next filter row
+            const int kh = P.kh, chunks = P.chunks;
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;
             Prof prof; prof.begin();
+            if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u);
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t % NBUF;
                 prof.start();
-                if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
                 prof.stop(0);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int ks = 0; ks < P.k_steps; ++ks) {
+                uint32_t accf = 0u;
+                uint32_t b_col = 0u;                                                   // patch mode: weights of (filter column, channel chunk)
+                if (patch) b_col = b_lo0 + (uint32_t)((tile / P.m_tiles) * kh) * b_row_step;
+                for (int ks = 0; ks < k_steps; ++ks) {
                     prof.start();
-                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
                     prof.stop(1);
-                    tc_fence_after();
-                    const uint64_t adesc = make_smem_desc(a_base + (uint32_t)(stage * P.a_stage_bytes), P.sbo, P.layout_type);
-                    const uint64_t bdesc = make_smem_desc(b_base + (uint32_t)(stage * P.b_stage_bytes), P.sbo, P.layout_type);
-                    const int kk = P.bk >> 5;
-                    for (int k = 0; k < kk; ++k)
-                        mma_i8_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P.idesc, (ks | k) ? 1u : 0u);
-                    tc_commit(smem_u32(&aux->empty[stage]));
-                    if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                    prof.start();
+                    if (TC_DEBUG(P, 0)) { }
+                    else if (patch) {
+                        // rows r*bw .. r*bw+127 of the patch are the tile's 128 pixels under filter row r
+                        uint32_t ar = a_lo, br = b_col;
+                        for (int r = 0; r < kh; ++r, ar += row_step, br += b_row_step) {
+                            if (kk == 4) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf);
+                            else if (kk == 2) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf);
+                            else mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf);
+                            accf = 1u;
+                        }
+                        b_col += b_step;
+                    } else {
+                        if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        accf = 1u;
+                    }
+                    prof.stop(2);
+                    tc_commit(empty0 + 8u * (uint32_t)stage);                           // frees the stage once these MMAs have read it
+                    if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
+                    else { a_lo += a_step; b_lo += b_step; }
                 }
                 if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
-            prof.flush(3, 2);
+            prof.flush(2, 3);
+            // drain: every issued MMA must have retired before TMEM is released
             tc_commit(smem_u32(&aux->drain));
             const uint64_t t0 = globaltimer();
             while (!mbar_try_wait(smem_u32(&aux->drain), 0u)) {
@@ -331,12 +426,14 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NBUF) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
                 prof.stop(0);
                 int tw = 0, th = 0, tb = 0;
-                if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
+                const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
+                if (boxed) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
 #pragma unroll
                 for (int cb = 0; cb < COLB; ++cb) {
+                    if (TC_DEBUG(P, 3)) break;
                     const int f0 = n_tile * BN + cb * CW;
                     const uint32_t src = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
-                    if (P.a_mode == A_TILED) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
+                    if (boxed) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
                     else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
                 }
                 bulk_commit();
@@ -358,7 +455,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
                 const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
                 int o_w = 0, o_h = 0, c_n = 0;
-                if (P.a_mode == A_TILED) {
+                const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
+                if (boxed) {
                     const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
                     o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
                 }
@@ -372,7 +470,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 for (int cb = 0; cb < COLB; ++cb) {
                     const uint32_t dst = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
                     const int f0 = n_tile * BN + cb * CW;
-                    if (P.a_mode == A_TILED) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
+                    if (boxed) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
                     else tma_load_2d(dst, &P.tmE, rf, f0, m_tile * kBM);
                 }
             }
@@ -429,7 +527,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
             uint8_t* stg = staging + (size_t)acc * kStagingBytes;
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
-            if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
+            if (TC_DEBUG(P, 1)) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(te); }
+            else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
             else if (kFused) {
                 switch (variant) {
                     case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;

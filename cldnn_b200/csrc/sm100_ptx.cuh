@@ -70,6 +70,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Same contract, for waits that usually succeed at once: one inline poll, the bounded loop out of line.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* s_abort, uint32_t* g_status, uint32_t code)
+{
+    return mbar_wait(bar, parity, s_abort, g_status, code);
+}
+__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, volatile uint32_t* s_abort, uint32_t* g_status, uint32_t code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, s_abort, g_status, code);
+}
+
 // ---- TMA ---------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap)
 {
