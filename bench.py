@@ -32,6 +32,7 @@ def parse():
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tune", type=int, default=1, help="1: pick tile shapes from on-device timings at build")
+    ap.add_argument("--retune", action="store_true", help="ignore the tuning cache shipped with the package: time every tile shape on this device")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample", type=int, default=8, help="images in the CPU baseline sample")
     return ap.parse_args()
@@ -190,7 +191,9 @@ def main():
         cache = os.path.join(ROOT, "gpurun_out", "tuning_cache_rank%d.json" % rank)
         os.makedirs(os.path.dirname(cache), exist_ok=True)
         shipped = os.path.join(ROOT, "cldnn_b200", "cache", "tuning_cache.json")
-        if not os.path.exists(cache) and os.path.exists(shipped):
+        if args.retune and not profiling and os.path.exists(cache):
+            os.remove(cache)
+        if not args.retune and not os.path.exists(cache) and os.path.exists(shipped):
             import shutil
             shutil.copyfile(shipped, cache)
         opts = cl.build_options(optimize_data=True, outputs=["prob"],

@@ -116,4 +116,75 @@ __device__ __forceinline__ void epi_chunk_fast(const ParamsT& P, const AuxT* aux
     o1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
 }
 
+// c + byte `sel` of the unsigned bytes in `a` (sel = 1 << 8*i picks byte i)
+__device__ __forceinline__ int32_t dp4a_u8(uint32_t a, int32_t sel, int32_t c)
+{
+    int32_t d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(sel), "r"(c)); return d;
+}
+
+// bytes above 127 become 127 (a ReLU'd value saturated to u8, re-saturated to s8)
+__device__ __forceinline__ uint32_t clamp_bytes_127(uint32_t w)
+{
+    const uint32_t m = w & 0x80808080u;
+    return (w | (m - (m >> 7))) & 0x7f7f7f7fu;
+}
+
+constexpr float kMagic = 8388608.0f;             // 2^23: x + 2^23 toward zero leaves floor(x) in the mantissa for 0 <= x < 2^23
+constexpr int32_t kMagicBits = 0x4B000000;
+
+// 32 features of one pixel.  Requires |v| < 2^22 for every dequantised value v
+// (guaranteed per feature tile by the caller), which makes every step exact
+// without a float->int conversion instruction:
+//   round-half-away(v) = sign(v) * floor(|v| + 0.5), floor taken by the 2^23 trick
+//   with round-toward-zero additions (x + 0.5 toward zero never reaches the next integer).
+// kOut: 0 = u8 output (its saturation covers a preceding ReLU), 1 = s8 output,
+// 2 = s8 output after a ReLU.  kRelu1: ReLU between the convolution and the residual sum.
+// e_xor / k_pos / k_neg: the residual word is made unsigned by e_xor (0 or 0x80808080),
+// k_pos = 2^23 bits (+128 for a signed residual), k_neg = 2^23 bits (-128 for a signed residual).
+template <bool kFused, bool kRelu1, int kOut>
+__device__ __forceinline__ void fast_chunk32(const uint32_t (&r)[32], const int32_t* bias, const float* quant,
+                                             uint4* p0, uint4* p1, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+{
+    uint32_t ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (kFused) {
+        const uint4 e0 = *p0, e1 = *p1;
+        ew[0] = e0.x ^ e_xor; ew[1] = e0.y ^ e_xor; ew[2] = e0.z ^ e_xor; ew[3] = e0.w ^ e_xor;
+        ew[4] = e1.x ^ e_xor; ew[5] = e1.y ^ e_xor; ew[6] = e1.z ^ e_xor; ew[7] = e1.w ^ e_xor;
+    }
+    uint32_t ow[8];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const int4 bi = reinterpret_cast<const int4*>(bias)[g];
+        const float4 q = reinterpret_cast<const float4*>(quant)[g];
+        const int32_t b4[4] = {bi.x, bi.y, bi.z, bi.w};
+        const float q4[4] = {q.x, q.y, q.z, q.w};
+        int32_t o4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
+            int32_t o;
+            if (!kFused && kOut != 1) {
+                // negative values end at 0 either way (unsigned saturation), so no sign handling
+                o = __float_as_int(__fadd_rz(__fadd_rz(v, 0.5f), kMagic)) - kMagicBits;
+            } else if (kFused && kRelu1) {
+                o = __float_as_int(__fadd_rz(__fadd_rz(v, 0.5f), kMagic)) - k_pos;
+                if (v < 0.0f) o = kMagicBits - k_pos;                 // ReLU: the convolution contributes 0
+            } else {
+                const int32_t wb = __float_as_int(__fadd_rz(__fadd_rz(fabsf(v), 0.5f), kMagic));
+                o = wb - (kFused ? k_pos : kMagicBits);
+                if (v < 0.0f) o = (kFused ? k_neg : kMagicBits) - wb;
+            }
+            if (kFused) o = dp4a_u8(ew[g], 1 << (8 * i), o);
+            o4[i] = o;
+        }
+        if (kOut == 1) ow[g] = pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
+        else {
+            ow[g] = pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u));
+            if (kOut == 2) ow[g] = clamp_bytes_127(ow[g]);
+        }
+    }
+    *p0 = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    *p1 = make_uint4(ow[4], ow[5], ow[6], ow[7]);
+}
+
 }  // namespace b200

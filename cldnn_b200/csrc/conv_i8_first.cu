@@ -27,7 +27,7 @@ namespace b200 {
 
 using namespace ptx;
 
-constexpr int kFThreads = 256;
+constexpr int kFThreads = 288;
 constexpr int kTileH = 8, kTileW = 16;          // 128 output pixels = 128 TMEM lanes
 constexpr int kFMaxOfm = 256;
 constexpr int kFMaxK = 256;
@@ -43,15 +43,19 @@ struct FirstParams {
     uint32_t idesc, tmem_cols, sbo;
     int64_t out_px, out_py, out_pb, out_off;
     int32_t mul_iqf, mul_oqf, lean;
+    float acc_bound;                 // C * kh * kw * max|activation| * 128
+    int32_t ctas_per_sm;
     const uint8_t* in; uint8_t* out; const uint8_t* wpacked; const void* bias; const float* quant; const float* calib;
     uint32_t* status;
     EpiCfg epi;
 };
 
 struct FirstAux {
-    uint64_t mma_done;
+    uint64_t a_full[2], a_empty[2], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     uint32_t abort;
+    uint32_t wide;                   // a feature's values may leave the range the conversion-free epilogue is exact in
+    uint16_t goff[64];               // per (feature, filter row) group: word offset of that row in the patch
     alignas(16) int32_t bias_i[1][kFMaxOfm];
     alignas(16) float bias_f[1][kFMaxOfm];
     alignas(16) float quant[1][kFMaxOfm];
@@ -86,7 +90,95 @@ __global__ void first_pack_weights(const int8_t* __restrict__ w, int64_t po, int
     }
 }
 
-__global__ void __launch_bounds__(kFThreads, 3)
+// ---- pipeline roles ------------------------------------------------------------------
+// warps 0..3 build the im2col operand (two operand buffers), warps 4..7 run the epilogue
+// (two accumulator buffers in tensor memory), warp 8 issues the MMAs.  The phases of
+// consecutive tiles overlap: while the tensor core works on tile t the builders already
+// assemble tile t+1 (with tile t+2's patch words in flight from global memory in their
+// registers) and the epilogue warps requantise tile t-1.
+constexpr int kBuilders = 128;
+constexpr int kMaxPre = 9;                         // patch words a builder thread keeps in flight
+
+// one aligned 4-byte word of the input patch, zero outside the image (the reference skips those taps).
+// `rel` = offset of the word from the patch origin in the image, `pk` = patch row | (byte column << 8): both fixed per thread.
+__device__ __forceinline__ uint32_t patch_word(const FirstParams& P, const uint8_t* origin, int32_t rel, int32_t pk, int y0, int xa)
+{
+    if (pk < 0) return 0u;                                                    // no such word in the patch
+    const int iy = y0 + (pk & 0xff), ix = xa + (pk >> 8);
+    if (iy < 0 || iy >= P.H || ix + 3 < 0 || ix >= P.W) return 0u;
+    const uint8_t* src = origin + rel;
+    if (ix >= 0 && ix + 3 < P.W && (reinterpret_cast<uintptr_t>(src) & 3u) == 0u) return __ldg(reinterpret_cast<const uint32_t*>(src));
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) { const int x = ix + b; if (x >= 0 && x < P.W) word |= (uint32_t)__ldg(src + b) << (8 * b); }
+    return word;
+}
+
+__device__ __forceinline__ void tile_origin(const FirstParams& P, int tile, int& tx, int& ty, int& n, int& x0, int& y0, int& xa)
+{
+    tx = tile % P.tiles_x; const int t2 = tile / P.tiles_x;
+    ty = t2 % P.tiles_y; n = t2 / P.tiles_y;
+    x0 = tx * kTileW * P.sx - P.pad_x; y0 = ty * kTileH * P.sy - P.pad_y;
+    xa = (x0 >= 0 ? x0 : x0 - 3) / 4 * 4;          // 4-byte aligned patch origin (floor)
+}
+
+// epilogue of one 32-row quadrant: kMode 0..2 = the conversion-free variants (u8 / s8 / s8 after ReLU), 3 = general
+template <int kMode>
+__device__ __forceinline__ void first_epi_tile(const FirstParams& P, const FirstAux* aux, uint32_t t_row, uint8_t* out_row, bool valid,
+                                               uint32_t tmem_empty_bar, int lane)
+{
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+    for (int c0 = 0; c0 < P.ofm; c0 += 64) {
+        const bool second = c0 + 32 < P.ofm;
+        tmem_ld_wait();
+        if (second) tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);
+        else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        if (valid) {
+            uint4* op = reinterpret_cast<uint4*>(out_row + c0);
+            if (kMode < 3) fast_chunk32<false, false, kMode < 3 ? kMode : 0>(ra, &aux->bias_i[0][c0], &aux->quant[0][c0], op, op + 1, 0u, kMagicBits, kMagicBits);
+            else { uint4 o0, o1; epi_chunk_fast<false, false>(P, aux, 0, c0, ra, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1); op[0] = o0; op[1] = o1; }
+        }
+        if (!second) break;
+        tmem_ld_wait();
+        if (c0 + 64 < P.ofm) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
+        else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        if (valid) {
+            uint4* op = reinterpret_cast<uint4*>(out_row + c0 + 32);
+            if (kMode < 3) fast_chunk32<false, false, kMode < 3 ? kMode : 0>(rb, &aux->bias_i[0][c0 + 32], &aux->quant[0][c0 + 32], op, op + 1, 0u, kMagicBits, kMagicBits);
+            else { uint4 o0, o1; epi_chunk_fast<false, false>(P, aux, 0, c0 + 32, rb, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1); op[0] = o0; op[1] = o1; }
+        }
+    }
+}
+
+// the same with one register array (load, wait, convert): for launches that keep two CTAs per SM
+template <int kMode>
+__device__ __forceinline__ void first_epi_tile_single(const FirstParams& P, const FirstAux* aux, uint32_t t_row, uint8_t* out_row, bool valid,
+                                                      uint32_t tmem_empty_bar, int lane)
+{
+#pragma unroll 1
+    for (int c0 = 0; c0 < P.ofm; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 >= P.ofm) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        if (valid) {
+            uint4* op = reinterpret_cast<uint4*>(out_row + c0);
+            fast_chunk32<false, false, kMode>(r, &aux->bias_i[0][c0], &aux->quant[0][c0], op, op + 1, 0u, kMagicBits, kMagicBits);
+        }
+    }
+}
+
+// the general (not conversion-free) epilogue, out of line: it is the rare path and must not cost the common one registers
+__device__ __noinline__ void first_epi_tile_general(const FirstParams& P, const FirstAux* aux, uint32_t t_row, uint8_t* out_row, bool valid,
+                                                    uint32_t tmem_empty_bar, int lane)
+{
+    first_epi_tile<3>(P, aux, t_row, out_row, valid, tmem_empty_bar, lane);
+}
+
+template <int kCtas>
+__global__ void __launch_bounds__(kFThreads, kCtas)
 conv_i8_first_kernel(const __grid_constant__ FirstParams P)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -95,120 +187,168 @@ conv_i8_first_kernel(const __grid_constant__ FirstParams P)
     uint8_t* smem = smem_raw + (base - raw);
     const int a_bytes = 128 * P.Kp, b_bytes = P.ofm * P.Kp;
     const int patch_bytes = P.C * P.patch_h * P.patch_wp;
-    uint8_t* sA = smem; uint8_t* sB = smem + a_bytes; uint8_t* sPatch = sB + b_bytes;
+    uint8_t* sA = smem; uint8_t* sB = smem + 2 * a_bytes; uint8_t* sPatch = sB + b_bytes;
     FirstAux* aux = reinterpret_cast<FirstAux*>(sPatch + ((patch_bytes + 15) & ~15));
     volatile uint32_t* s_abort = &aux->abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const EpiCfg& c = P.epi;
 
-    if (tid == 0) { mbar_init(smem_u32(&aux->mma_done), 1); aux->abort = 0u; mbar_fence_init(); }
-    if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&aux->a_full[i]), 1); mbar_init(smem_u32(&aux->a_empty[i]), 1);
+            mbar_init(smem_u32(&aux->tmem_full[i]), 1); mbar_init(smem_u32(&aux->tmem_empty[i]), 4);
+        }
+        aux->abort = 0u; aux->wide = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 8) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    __syncthreads();
     // weights image and per-feature constants: once per CTA
     for (int i = tid; i < b_bytes / 16; i += kFThreads) reinterpret_cast<uint4*>(sB)[i] = __ldg(reinterpret_cast<const uint4*>(P.wpacked) + i);
     for (int j = tid; j < P.ofm; j += kFThreads) {
         int32_t bi = 0; float bf = 0.f;
         if (c.bias_dtype != CLDNN_B200_NONE) { if (c.bias_dtype == CLDNN_B200_F32) bf = ((const float*)P.bias)[j]; else bi = load_as_int(P.bias, c.bias_dtype, j); }
+        const float q = c.quantization ? P.quant[j] : 1.f;
         aux->bias_i[0][j] = bi; aux->bias_f[0][j] = bf;
-        aux->quant[0][j] = c.quantization ? P.quant[j] : 1.f;
+        aux->quant[0][j] = q;
         aux->calib[0][j] = c.calibration ? P.calib[j] : 1.f;
         aux->ecal[0][j] = 1.f;
+        // the conversion-free epilogue is exact while every dequantised value stays below 2^22
+        if (!(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)) < 4.0e6f)) atomicOr(&aux->wide, 1u);
     }
+    for (int g = tid; g < P.groups && g < 64; g += kFThreads) { const int ch = g / P.kh, r = g - ch * P.kh; aux->goff[g] = (uint16_t)((ch * P.patch_h + r) * (P.patch_wp >> 2)); }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
-    const uint32_t lbo = 128u, sbo = P.sbo;
-    const int quad = warp & 3, chalf = warp >> 2;
-    const int row = quad * 32 + lane;                 // output pixel of the tile handled by this thread in the epilogue
-    uint32_t phase = 0;
+    const uint32_t sbo = P.sbo;
+    const int my_tiles = (P.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
-    for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
-        const int tx = tile % P.tiles_x; const int t2 = tile / P.tiles_x;
-        const int ty = t2 % P.tiles_y; const int n = t2 / P.tiles_y;
-        const int x0 = tx * kTileW * P.sx - P.pad_x, y0 = ty * kTileH * P.sy - P.pad_y;
-        const int xa = (x0 >= 0 ? x0 : x0 - 3) / 4 * 4;       // 4-byte aligned patch origin (floor)
-        // ---- input patch: zero outside the image (the reference skips those taps) ----
+    if (warp < 4) {
+        // ------------------------------ builders ----------------------------------
         const int words_per_row = P.patch_wp >> 2;
         const int patch_words = P.C * P.patch_h * words_per_row;
-        for (int i = tid; i < patch_words; i += kFThreads) {
+        // what does not depend on the tile is computed once: where each of this thread's patch words lies relative to
+        // the patch origin, and (in shared memory, by group) where each filter row starts in the patch
+        int32_t rel[kMaxPre], pk[kMaxPre];
+#pragma unroll
+        for (int j = 0; j < kMaxPre; ++j) {
+            const int i = tid + j * kBuilders;
             const int wq = i % words_per_row; const int r2 = i / words_per_row;
             const int pr = r2 % P.patch_h, ch = r2 / P.patch_h;
-            const int iy = y0 + pr, ix = xa + wq * 4;
-            uint32_t word = 0;
-            if (iy >= 0 && iy < P.H) {
-                const uint8_t* src = P.in + P.in_off + (int64_t)n * P.in_pb + (int64_t)ch * P.in_pf + (int64_t)iy * P.in_py;
-#pragma unroll
-                for (int b = 0; b < 4; ++b) { const int x = ix + b; if (x >= 0 && x < P.W) word |= (uint32_t)__ldg(src + x) << (8 * b); }
-            }
-            reinterpret_cast<uint32_t*>(sPatch)[i] = word;
+            rel[j] = (int32_t)(ch * P.in_pf + pr * P.in_py + wq * 4);
+            pk[j] = i < patch_words ? (pr | ((wq * 4) << 8)) : -1;
         }
-        __syncthreads();
-        // ---- im2col operand: thread = (pixel m, half of the K chunks) ----
-        {
-            const int m = tid >> 1, h = tid & 1;
-            const int py_ = m / kTileW, px_ = m - py_ * kTileW;
+        const int m = tid;                                      // output pixel of the tile this thread assembles
+        const int py_ = m / kTileW, px_ = m - py_ * kTileW;
+        const int chunks = P.Kp >> 4;
+        const uint32_t* prow = reinterpret_cast<const uint32_t*>(sPatch) + py_ * P.sy * words_per_row;
+        // patch words of tile `it` of this CTA into a register set (nothing when the CTA has no such tile)
+        auto fetch = [&](int it, uint32_t (&regs)[kMaxPre]) {
+            if (it >= my_tiles) return;
+            int tx, ty, n, x0, y0, xa;
+            tile_origin(P, blockIdx.x + it * gridDim.x, tx, ty, n, x0, y0, xa);
+            const uint8_t* origin = P.in + P.in_off + (int64_t)n * P.in_pb + (int64_t)y0 * P.in_py + xa;
+#pragma unroll
+            for (int j = 0; j < kMaxPre; ++j) regs[j] = patch_word(P, origin, rel[j], pk[j], y0, xa);
+        };
+        // one tile: registers -> patch in shared memory, refill the registers with the tile two ahead (those loads stay
+        // in flight across this and the next tile), assemble the operand
+        auto step = [&](int it, uint32_t (&regs)[kMaxPre]) -> bool {
+            const int buf = it & 1;
+#pragma unroll
+            for (int j = 0; j < kMaxPre; ++j) if (pk[j] >= 0) reinterpret_cast<uint32_t*>(sPatch)[tid + j * kBuilders] = regs[j];
+            named_bar_sync(1, kBuilders);
+            fetch(it + 2, regs);
+            int tx, ty, n, x0, y0, xa;
+            tile_origin(P, blockIdx.x + it * gridDim.x, tx, ty, n, x0, y0, xa);
             const int colb = (x0 - xa) + px_ * P.sx;
-            const int wi = colb >> 2; const uint32_t sh = (uint32_t)(colb & 3) * 8u;
-            const int chunks = P.Kp >> 4, half_chunks = (chunks + 1) >> 1;
-            uint8_t* dstrow = sA + (m >> 3) * sbo + (m & 7) * 16;
-            for (int kc = h * half_chunks; kc < min(chunks, (h + 1) * half_chunks); ++kc) {
+            if (!mbar_wait(smem_u32(&aux->a_empty[buf]), (((uint32_t)(it >> 1) & 1u)) ^ 1u, s_abort, P.status, kErrFirst + 1u)) return false;
+            // im2col row of pixel m: every 8-byte group is one shifted read of a patch row
+            const uint32_t* pw = prow + (colb >> 2); const uint32_t sh = (uint32_t)(colb & 3) * 8u;
+            uint8_t* dstrow = sA + buf * a_bytes + (m >> 3) * sbo + (m & 7) * 16;
+            for (int kc = 0; kc < chunks; ++kc) {
                 uint32_t v[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
                     const int g = kc * 2 + q;
                     if (g < P.groups) {
-                        const int ch = g / P.kh, r = g - ch * P.kh;
-                        const uint32_t* rowp = reinterpret_cast<const uint32_t*>(sPatch) + (ch * P.patch_h + py_ * P.sy + r) * words_per_row + wi;
+                        const uint32_t* rowp = pw + aux->goff[g];
                         const uint32_t w0 = rowp[0], w1 = rowp[1], w2 = rowp[2];
                         v[2 * q] = __funnelshift_r(w0, w1, sh); v[2 * q + 1] = __funnelshift_r(w1, w2, sh);
                     }
                 }
                 *reinterpret_cast<uint4*>(dstrow + kc * 128) = make_uint4(v[0], v[1], v[2], v[3]);
             }
+            fence_async_smem();
+            named_bar_sync(1, kBuilders);                       // operand complete, patch buffer free for the next tile
+            if (tid == 0) mbar_arrive(smem_u32(&aux->a_full[buf]));
+            return true;
+        };
+        uint32_t pre0[kMaxPre], pre1[kMaxPre];
+#pragma unroll
+        for (int j = 0; j < kMaxPre; ++j) { pre0[j] = 0u; pre1[j] = 0u; }
+        fetch(0, pre0); fetch(1, pre1);
+        for (int it = 0; it < my_tiles; it += 2) {
+            if (!step(it, pre0)) break;
+            if (it + 1 < my_tiles && !step(it + 1, pre1)) break;
         }
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();
-        // ---- K/32 tensor-core instructions, accumulators in tensor memory ----
-        if (tid == 0) {
-            tc_fence_after();
-            const uint64_t adesc = make_desc_interleaved(smem_u32(sA), lbo, sbo);
-            const uint64_t bdesc = make_desc_interleaved(smem_u32(sB), lbo, sbo);
+    } else if (warp == 8) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
             const int kk = P.Kp >> 5;
-            for (int k = 0; k < kk; ++k)          // one instruction consumes two core matrices along K: 2 * lbo bytes
-                mma_i8_ss(tmem_base, adesc + (uint64_t)(k * 16), bdesc + (uint64_t)(k * 16), P.idesc, k ? 1u : 0u);
-            tc_commit(smem_u32(&aux->mma_done));
-        }
-        if (!mbar_wait(smem_u32(&aux->mma_done), phase, s_abort, P.status, kErrFirst)) break;
-        phase ^= 1u;
-        tc_fence_after();
-        // ---- epilogue: warp = (lane quadrant, column half) ----
-        {
-            const int py_ = row / kTileW, px_ = row - py_ * kTileW;
-            const int oy = ty * kTileH + py_, ox = tx * kTileW + px_;
-            const bool valid = oy < P.P && ox < P.Q;
-            const int64_t o_pix = P.out_off + (int64_t)n * P.out_pb + (int64_t)oy * P.out_py + (int64_t)ox * P.out_px;
-            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16);
-            for (int c0 = chalf * 32; c0 < P.ofm; c0 += 64) {
-                uint32_t r[32];
-                tmem_ld_32x32(t_row + (uint32_t)c0, r);
-                tmem_ld_wait();
-                if (!valid) continue;
-                uint4 o0, o1;
-                if (P.lean) epi_chunk_fast<false, true>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
-                else epi_chunk_fast<false, false>(P, aux, 0, c0, r, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1);
-                uint4* op = reinterpret_cast<uint4*>(P.out + o_pix + c0);
-                op[0] = o0; op[1] = o1;
+            const uint64_t bdesc = make_desc_interleaved(smem_u32(sB), 128u, sbo);
+            for (int it = 0; it < my_tiles; ++it) {
+                const int buf = it & 1; const uint32_t par = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&aux->tmem_empty[buf]), par ^ 1u, s_abort, P.status, kErrFirst + 2u)) break;
+                if (!mbar_wait(smem_u32(&aux->a_full[buf]), par, s_abort, P.status, kErrFirst + 3u)) break;
+                tc_fence_after();
+                const uint64_t adesc = make_desc_interleaved(smem_u32(sA + buf * a_bytes), 128u, sbo);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.ofm);
+                for (int k = 0; k < kk; ++k)                    // one instruction consumes two core matrices along K: 2 * 128 bytes
+                    mma_i8_ss(d_tmem, adesc + (uint64_t)(k * 16), bdesc + (uint64_t)(k * 16), P.idesc, k ? 1u : 0u);
+                tc_commit(smem_u32(&aux->a_empty[buf]));
+                tc_commit(smem_u32(&aux->tmem_full[buf]));
             }
         }
-        tc_fence_before();
-        __syncthreads();                               // tensor memory, operand and patch buffers are free again
-        tc_fence_after();
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int quad = warp & 3;                              // warps 4..7 -> TMEM lanes 32*quad ..
+        const int row = quad * 32 + lane;
+        const int py_ = row / kTileW, px_ = row - py_ * kTileW;
+        const int mode = (P.lean && !aux->wide) ? (c.out_dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
+        for (int it = 0; it < my_tiles; ++it) {
+            const int buf = it & 1;
+            int tx, ty, n, x0, y0, xa;
+            tile_origin(P, blockIdx.x + it * gridDim.x, tx, ty, n, x0, y0, xa);
+            const int oy = ty * kTileH + py_, ox = tx * kTileW + px_;
+            const bool valid = oy < P.P && ox < P.Q;
+            uint8_t* out_row = P.out + P.out_off + (int64_t)n * P.out_pb + (int64_t)oy * P.out_py + (int64_t)ox * P.out_px;
+            if (!mbar_wait(smem_u32(&aux->tmem_full[buf]), (uint32_t)(it >> 1) & 1u, s_abort, P.status, kErrFirst)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * P.ofm);
+            const uint32_t te = smem_u32(&aux->tmem_empty[buf]);
+            if (kCtas == 1) {
+                switch (mode) {
+                    case 0: first_epi_tile<0>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 1: first_epi_tile<1>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 2: first_epi_tile<2>(P, aux, t_row, out_row, valid, te, lane); break;
+                    default: first_epi_tile_general(P, aux, t_row, out_row, valid, te, lane); break;
+                }
+            } else {
+                switch (mode) {
+                    case 0: first_epi_tile_single<0>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 1: first_epi_tile_single<1>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 2: first_epi_tile_single<2>(P, aux, t_row, out_row, valid, te, lane); break;
+                    default: first_epi_tile_general(P, aux, t_row, out_row, valid, te, lane); break;
+                }
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+    if (warp == 8) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
 }
 
 // ------------------------------------------------------------------------------------
@@ -231,10 +371,13 @@ static bool first_plan(const cldnn_b200_conv_params& p, std::string* why)
     if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32 && p.bias_dtype != CLDNN_B200_F32) return no("bias type");
     const int P_ = (p.in.y + 2 * p.pad_y - p.kh) / p.stride_y + 1, Q_ = (p.in.x + 2 * p.pad_x - p.kw) / p.stride_x + 1;
     if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
+    const int patch_h = (kTileH - 1) * p.stride_y + p.kh, patch_wp = ((kTileW - 1) * p.stride_x + 8 + 3 + 4 + 3) / 4 * 4;
+    if (p.ifm * patch_h * patch_wp / 4 > 128 * 9) return no("the input patch of one tile is too large");
     return true;
 }
 static bool first_supports(const void* vp) { return first_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
-static int first_tune_count(const void*) { return 1; }
+// tune 0 / 2: as many CTAs per SM as fit (at most two), 1: one CTA per SM with the double-buffered epilogue
+static int first_tune_count(const void*) { return 3; }
 static int first_kp(const cldnn_b200_conv_params& p) { return (p.ifm * p.kh * 8 + 31) / 32 * 32; }
 static size_t first_scratch(const void* vp) { const auto& p = *(const cldnn_b200_conv_params*)vp; return (size_t)p.ofm * first_kp(p); }
 
@@ -262,8 +405,9 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     P.tiles_x = (P.Q + kTileW - 1) / kTileW; P.tiles_y = (P.P + kTileH - 1) / kTileH; P.total_tiles = P.N * P.tiles_x * P.tiles_y;
     const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;
     P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(p.ofm >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    uint32_t cols = 32; while (cols < (uint32_t)p.ofm) cols <<= 1;
+    uint32_t cols = 32; while (cols < (uint32_t)(2 * p.ofm)) cols <<= 1;   // two accumulator buffers
     P.tmem_cols = cols;
+    P.acc_bound = (float)p.ifm * (float)p.kh * (float)p.kw * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
     P.sbo = (uint32_t)(P.Kp / 16) * 128u;
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
     P.epi = make_epi_cfg(p);
@@ -275,16 +419,27 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     P.status = ctx->d_status;
 
     const int patch_bytes = P.C * P.patch_h * P.patch_wp;
-    smem = 128 + (size_t)128 * P.Kp + (size_t)P.ofm * P.Kp + ((patch_bytes + 15) & ~15) + sizeof(FirstAux);
+    if (patch_bytes / 4 > kBuilders * kMaxPre) return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_i8_first: the input patch of one tile is too large");
+    smem = 128 + (size_t)2 * 128 * P.Kp + (size_t)P.ofm * P.Kp + ((patch_bytes + 15) & ~15) + sizeof(FirstAux);
     if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory");
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // CTAs per SM: bounded by shared memory and by tensor memory (512 columns per SM)
     int per_sm = (int)(ctx->prop.sharedMemPerMultiprocessor / (smem + 1024));
-    per_sm = std::min(per_sm, std::min(3, (int)(512 / P.tmem_cols)));
+    per_sm = std::min(per_sm, std::min(2, (int)(512 / P.tmem_cols)));
     if (per_sm < 1) per_sm = 1;
+    if (p.tune == 1) per_sm = 1;
+    P.ctas_per_sm = per_sm;
     grid = ctx->prop.multiProcessorCount * per_sm;
     if (grid > P.total_tiles) grid = P.total_tiles;
     return CLDNN_B200_SUCCESS;
+}
+
+static cudaError_t first_launch(const FirstParams& P, int grid, size_t smem, cudaStream_t s)
+{
+    if (P.ctas_per_sm >= 2) conv_i8_first_kernel<2><<<grid, kFThreads, smem, s>>>(P);
+    else conv_i8_first_kernel<1><<<grid, kFThreads, smem, s>>>(P);
+    return cudaGetLastError();
 }
 
 static cudaError_t first_pack(const cldnn_b200_conv_params& p, const cldnn_b200_args* a, const FirstParams& P, void* wpacked, cudaStream_t stream)
@@ -302,7 +457,7 @@ static int32_t first_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cld
     if (st != CLDNN_B200_SUCCESS) return st;
     // pack the weights once, on the context's stream, before anything that is prepared here can run
     B200_CUDA(first_pack(p, a, P, a->scratch, ctx->stream));
-    out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_first_kernel<<<grid, kFThreads, smem, s>>>(P); return cudaGetLastError(); };
+    out->fn = [P, grid, smem](cudaStream_t s) { return first_launch(P, grid, smem, s); };
     out->launches = 1;
     return CLDNN_B200_SUCCESS;
 }
@@ -366,8 +521,7 @@ extern "C" int32_t cldnn_b200_conv_first_noalloc(cldnn_b200_ctx ctx, const cldnn
     // The array still holds whatever the previous call packed.  The packing kernel rewrites every byte of the image
     // this call reads (zero taps and zero K padding included), so nothing stale can leak into the result.
     B200_CUDA(first_pack(*params, args, P, scratch, ctx->stream));
-    conv_i8_first_kernel<<<grid, kFThreads, smem, ctx->stream>>>(P);
-    B200_CUDA(cudaGetLastError());
+    B200_CUDA(first_launch(P, grid, smem, ctx->stream));
     ctx->launches += 2;
     return CLDNN_B200_SUCCESS;
 }

@@ -108,12 +108,31 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
 {
     const int fv = p.in.f / 16;
     const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
+    const bool fast_max = p.mode == CLDNN_B200_POOL_MAX && (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU);
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
         const int f16 = (int)(idx % fv); int64_t t = idx / fv;
         const int x = (int)(t % p.out.x); t /= p.out.x;
         const int y = (int)(t % p.out.y); const int b = (int)(t / p.out.y);
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
+        if (fast_max) {
+            // maximum of the valid taps on packed bytes, no unpacking: the stored bits are the bits of the
+            // largest input (the conversion to the output type wraps), ReLU on a signed output is one more max
+            const int j0 = max(0, -oy), j1 = min(p.size_y, p.in.y - oy), i0 = max(0, -ox), i1 = min(p.size_x, p.in.x - ox);
+            uint4 m = kUnsignedIn ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+            const uint8_t* src = in + tidx(p.in, b, f16 * 16, oy, ox);
+            for (int j = j0; j < j1; ++j) {
+#pragma unroll 3
+                for (int i = i0; i < i1; ++i) {
+                    const uint4 v = __ldg((const uint4*)(src + (int64_t)j * p.in.py + (int64_t)i * p.in.px));
+                    if (kUnsignedIn) { m.x = __vmaxu4(m.x, v.x); m.y = __vmaxu4(m.y, v.y); m.z = __vmaxu4(m.z, v.z); m.w = __vmaxu4(m.w, v.w); }
+                    else { m.x = __vmaxs4(m.x, v.x); m.y = __vmaxs4(m.y, v.y); m.z = __vmaxs4(m.z, v.z); m.w = __vmaxs4(m.w, v.w); }
+                }
+            }
+            if (p.act == CLDNN_B200_ACT_RELU && p.out.dtype == CLDNN_B200_I8) { m.x = __vmaxs4(m.x, 0u); m.y = __vmaxs4(m.y, 0u); m.z = __vmaxs4(m.z, 0u); m.w = __vmaxs4(m.w, 0u); }
+            *(uint4*)(out + tidx(p.out, b, f16 * 16, y, x)) = m;
+            continue;
+        }
         int32_t r[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = p.mode == CLDNN_B200_POOL_MAX ? -128 : 0;

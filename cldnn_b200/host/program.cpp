@@ -591,7 +591,8 @@ void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidat
         }
     }
     set_tune(0);
-    const std::string hash = fnv1a_hex(params, psize, n->p.type);
+    // the key carries the generation of the kernel set: timings taken on older kernels must not be reused
+    const std::string hash = fnv1a_hex(params, psize, n->p.type + "#g2");
     if (opts.tuning != tuning_mode::tuning_disabled) {
         auto it = tuning_cache.find(hash);
         if (it != tuning_cache.end()) {

@@ -171,6 +171,21 @@ def test_conv_i8_first_matches_oracle(eng, name, variant):
     assert eng.kernel("conv_i8_first").supports(case.p)
     want = _exact(eng, case, "conv_i8_first")
     assert (want != 0).any()
+    _exact(eng, case, "conv_i8_first", tune=1)       # one CTA per SM, double-buffered epilogue
+
+
+def test_conv_i8_first_plain_variants(eng):
+    """The conversion-free epilogue variants of the first-layer kernel (u8 / s8 / s8 after ReLU), the float-domain
+    path a large scale forces, and more tiles than CTAs so the operand pipeline wraps several times."""
+    geom = dict(N=6, C=3, K=64, H=97, W=131, kh=7, kw=7, stride=2, pad=3)
+    for out_dtype, act in ((np.uint8, abi.ACT_RELU), (np.uint8, abi.ACT_NONE), (np.int8, abi.ACT_NONE), (np.int8, abi.ACT_RELU)):
+        for wide in (False, True):
+            case = cases.make_conv_case(23, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=out_dtype, act=act,
+                                        scale_lo=2.0 ** -12, scale_hi=2.0 ** -10, **geom)
+            if wide:
+                case.quant[5] = 900.0
+            for tune in (0, 1):
+                _exact(eng, case, "conv_i8_first", tune=tune)
 
 
 def test_conv_ref_layouts_and_groups(eng):
