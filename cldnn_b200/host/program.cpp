@@ -479,7 +479,11 @@ void network_impl::select_layouts()
 {
     auto conv_like = [&](node* n) {
         const std::string& t = n->p.type;
-        if (n->deps.empty() || !is_int8(n->deps[0]->out.data_type)) return false;
+        if (n->deps.empty()) return false;
+        // fp16 convolutions run on the tensor cores from the same feature-innermost padded layout
+        if (n->deps[0]->out.data_type == data_types::f16)
+            return (t == "convolution" || t == "fused_conv_eltwise") && n->p.groups == 1 && n->weights && n->weights->out.data_type == data_types::f16 && !n->wq;
+        if (!is_int8(n->deps[0]->out.data_type)) return false;
         if (t == "convolution" || t == "fused_conv_eltwise") return n->p.groups == 1 && n->wq != nullptr;
         if (t == "fully_connected") return n->wq && n->bias && n->bias->out.data_type == data_types::f32 && n->deps[0]->out.size.x == 1 && n->deps[0]->out.size.y == 1;
         return false;
@@ -495,7 +499,8 @@ void network_impl::select_layouts()
     for (node* n : order) {
         if (n->removed || n->constant() || n->p.type == "input_layout" || n->deps.empty()) continue;
         if (conv_like(n)) chosen.insert(n);
-        else if ((n->p.type == "pooling" || n->p.type == "eltwise" || n->p.type == "activation") && is_int8(n->deps[0]->out.data_type)) {
+        else if ((n->p.type == "pooling" || n->p.type == "eltwise" || n->p.type == "activation") &&
+                 (is_int8(n->deps[0]->out.data_type) || n->deps[0]->out.data_type == data_types::f16)) {
             bool all = true; for (node* d : n->deps) all &= chosen.count(d) > 0;
             if (all) chosen.insert(n);
         }
@@ -741,7 +746,9 @@ void network_impl::prepare_kernel(node* n)
             }
         }
         // tensor-core kernel: needs byxf activations and oyxi weights padded like the activations
-        const bool try_tc = is_int8(in.data_type) && w.data_type == data_types::i8 && cp.groups == 1 && cp.in.pf == 1 && cp.in.px % 32 == 0 && cp.out.pf == 1;
+        const bool half_tc = in.data_type == data_types::f16 && w.data_type == data_types::f16 && n->out.data_type == data_types::f16 && !fc;
+        const bool try_tc = ((is_int8(in.data_type) && w.data_type == data_types::i8) || half_tc) && cp.groups == 1 && cp.in.pf == 1 && cp.in.px % 32 == 0 && cp.out.pf == 1;
+        const char* tc_kernel = half_tc ? "conv_f16_tc" : "conv_i8_tc";
         if (try_tc) {
             cldnn_b200_conv_params tp = cp;
             n->packed_weights = pack_conv_weights(n, (int32_t)cp.in.px);
@@ -749,9 +756,9 @@ void network_impl::prepare_kernel(node* n)
             tp.w_po = pd.pb; tp.w_pi = 1; tp.w_py = pd.py; tp.w_px = pd.px; tp.w_offset = 0;
             cldnn_b200_args ta = a; ta.weights = n->packed_weights.device_ptr();
             int32_t yes = 0;
-            if (cldnn_b200_kernel_supports(eng->kernel("conv_i8_tc"), &tp, sizeof(tp), &yes) == CLDNN_B200_SUCCESS && yes) {
+            if (cldnn_b200_kernel_supports(eng->kernel(tc_kernel), &tp, sizeof(tp), &yes) == CLDNN_B200_SUCCESS && yes) {
                 a = ta; cp = tp;
-                finish({"conv_i8_tc"}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
+                finish({tc_kernel}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
                 return;
             }
             n->packed_weights = memory();

@@ -104,6 +104,53 @@ def resnet50_int8(batch, seed=2019, image=224, scale_lo=2.0 ** -14, scale_hi=2.0
     return s
 
 
+# VGG16 (configuration D): 13 3x3 pad-1 convolutions in five stages, 2x2 max pooling after each stage.
+VGG16_STAGES = ((64, 2), (128, 2), (256, 3), (512, 3), (512, 3))
+
+
+def vgg16_fp16(batch, seed=16, image=224, stages=VGG16_STAGES, classes=1000, fc_width=4096):
+    """fp16 VGG16: weights N(0, sqrt(2 / fan_in)), inputs N(0, 1) supplied by the caller; convolution + ReLU, max pooling,
+    three fully_connected layers and softmax."""
+    rng = np.random.default_rng(seed)
+    s = Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.f16, cl.format.bfyx, cl.tensor(batch, 3, image, image))
+    s.add(cl.input_layout("input", s.input_layout))
+    x, cin, size = "input", 3, image
+    for si, (w, n) in enumerate(stages):
+        for li in range(n):
+            name = "conv%d_%d" % (si + 1, li + 1)
+            s.const(name + "_w", (rng.standard_normal((w, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))).astype(np.float16))
+            s.const(name + "_b", (rng.standard_normal(w) * 0.05).astype(np.float16))
+            s.add(cl.convolution(name, x, name + "_w", name + "_b", input_offset=(-1, -1), with_activation=True))
+            x, cin = name, w
+        s.add(cl.pooling("pool%d" % (si + 1), x, cl.pooling_mode.max, size=(2, 2), stride=(2, 2)))
+        x, size = "pool%d" % (si + 1), size // 2
+    fan = cin * size * size
+    for i, (wout, act) in enumerate(((fc_width, True), (fc_width, True), (classes, False))):
+        name = "fc%d" % (i + 6)
+        shape = (wout, cin, size, size) if i == 0 else (wout, fan, 1, 1)
+        s.const(name + "_w", (rng.standard_normal(shape) * np.sqrt(2.0 / fan)).astype(np.float16))
+        s.const(name + "_b", (rng.standard_normal(wout) * 0.05).astype(np.float16))
+        s.add(cl.fully_connected(name, x, name + "_w", name + "_b", with_activation=act))
+        x, fan = name, wout
+    s.add(cl.softmax("prob", x))
+    s.outputs = ["prob", x]
+    return s
+
+
+def vgg16_conv_layers(image=224, stages=VGG16_STAGES):
+    """(name, input features, output features, map size) of the 13 convolutions: the per-layer sweep."""
+    out, cin, size = [], 3, image
+    for si, (w, n) in enumerate(stages):
+        for li in range(n):
+            out.append(("conv%d_%d" % (si + 1, li + 1), cin, w, size))
+            cin = w
+        size //= 2
+    return out
+
+
 def conv_ops(spec):
     """Multiply-add operations x2 of every convolution / fully_connected of a spec, per image (padding taps counted)."""
     shapes, total = {}, 0

@@ -156,3 +156,24 @@ def test_errors_surface_as_status_codes(eng):
     with pytest.raises(cl.error) as e:
         cl.network(eng, cl.topology(cl.input_layout("input", xm.get_layout()), cl.softmax("s", "nowhere")))
     assert e.value.status == abi.INVALID_ARG
+
+
+@pytest.mark.parametrize("optimize", [False, True])
+def test_small_vgg_fp16_network(eng, optimize):
+    """fp16 VGG-style network (convolution + ReLU, max pooling, fully_connected, softmax) against the oracle, within the
+    fp16 tolerance of 1e-2 relative to each output's scale; with optimize_data every convolution runs on conv_f16_tc."""
+    spec = topologies.vgg16_fp16(2, seed=3, image=32, stages=((16, 1), (32, 2), (64, 1)), classes=10, fc_width=64)
+    lay = spec.input_layout
+    x = np.random.default_rng(7).standard_normal((lay.size.batch, lay.size.feature, lay.size.y, lay.size.x)).astype(np.float16)
+    want = oracle_net.run(spec, {spec.input_id: x})
+    net, got = _run(eng, spec, x, optimize_data=optimize)
+    for k in spec.outputs:
+        w, g = want[k].astype(np.float32), got[k].astype(np.float32)
+        scale = float(np.abs(w).max())
+        assert np.abs(g - w).max() <= 1e-2 * scale, "%s: max abs error %.4g on scale %.4g" % (k, float(np.abs(g - w).max()), scale)
+    convs = [r for r in net.primitives_info() if r["type"] == "convolution"]
+    assert len(convs) == 4
+    if optimize:
+        assert all(r["kernel"] == "conv_f16_tc" for r in convs), [r["kernel"] for r in convs]
+    else:
+        assert all(r["kernel"] == "conv_ref" for r in convs)
