@@ -53,6 +53,7 @@ struct alignas(64) Params {
     int32_t bw, bh, bb, tiles_w, tiles_h;
     int32_t stages, a_stage_bytes, b_stage_bytes, a_tx_bytes, b_tx_bytes, ring_bytes, stage_rows;
     uint32_t sbo, layout_type, idesc, tmem_cols;
+    int32_t batch_tiles;                     // batched GEMM view: tiles per batch, the weight 'tap' is the batch index (0 = plain convolution)
     int32_t ofm, fused, bias_dtype, act, eltw_act;
     float act_m, act_n, eltw_m, eltw_n;
     const void* bias;
@@ -186,7 +187,7 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
                     const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
                     c_w = tw * P.bw - P.pad_x; c_h = (t2 % P.tiles_h) * P.bh - P.pad_y; c_n = (t2 / P.tiles_h) * P.bb;
                 }
-                int tap = 0, cc = 0, r = 0, s = 0;
+                int tap = P.batch_tiles ? m_tile / P.batch_tiles : 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
                     if (!mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErr)) { ok = false; break; }
                     const uint32_t full = smem_u32(&aux->full[stage]);
@@ -588,6 +589,75 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     const size_t smem = smem_bytes; const int ms = (int)max_smem;
     out->fn = [P, grid, smem, ms](cudaStream_t s) { return f16_launch(P, grid, smem, ms, s); };
     out->launches = 1;
+    return CLDNN_B200_SUCCESS;
+}
+
+// Batched GEMM on the same kernel: D[b] (rows x ofm) = A[b] (rows x cs) * B[b] (ofm x cs)^T for b < batches, all fp16 with fp32
+// accumulation; rows per batch a multiple of 128, cs a multiple of 16, every pointer 16-byte aligned.  Used by the Winograd path.
+int32_t f16_batched_gemm_prepare(cldnn_b200_ctx_impl* ctx, const void* A, const void* B, void* D, int batches, int rows, int cs, int ofm,
+                                 std::function<cudaError_t(cudaStream_t)>& fn)
+{
+    if (rows % f16tc::kBM || cs % 16 || ofm % 8 || batches < 1) return fail(CLDNN_B200_INVALID_ARG, "f16 batched gemm: rows % 128, cs % 16, ofm % 8");
+    if (!f16_driver_entry_points()) return fail(CLDNN_B200_DEVICE_ERROR, "conv_f16_tc: the CUDA driver does not export cuTensorMapEncodeTiled/Im2col");
+    F16Plan pl{}; pl.a_mode = f16tc::A_FLAT; pl.bw = pl.bh = pl.bb = 1;
+    pl.bn = ofm > 128 ? 256 : (ofm > 64 ? 128 : 64);
+    pl.bk = cs % 64 == 0 ? 128 : (cs % 32 == 0 ? 64 : 32);
+    if (pl.bn == 256 && pl.bk == 128) pl.bk = 64;
+    Params P{};
+    P.a_mode = f16tc::A_FLAT; P.N = 1; P.P = 1; P.Q = batches * rows;
+    P.kh = P.kw = 1; P.stride_x = P.stride_y = P.dil_x = P.dil_y = 1;
+    const int bke = pl.bk / 2;
+    P.bk = pl.bk; P.chunks = cs / bke; P.k_steps = P.chunks;
+    P.bn = pl.bn; P.n_tiles = (ofm + pl.bn - 1) / pl.bn;
+    P.M_total = (int64_t)batches * rows;
+    P.bw = P.bh = P.bb = 1; P.tiles_w = P.tiles_h = 1;
+    P.m_tiles = (int)(P.M_total / f16tc::kBM); P.total_tiles = P.m_tiles * P.n_tiles;
+    P.batch_tiles = rows / f16tc::kBM;
+    P.stage_rows = f16tc::kBM;
+    P.a_stage_bytes = f16tc::kBM * pl.bk; P.b_stage_bytes = pl.bn * pl.bk;
+    P.a_tx_bytes = P.a_stage_bytes; P.b_tx_bytes = P.b_stage_bytes;
+    P.sbo = 8u * (uint32_t)pl.bk;
+    P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
+    P.idesc = (1u << 4) | ((uint32_t)(pl.bn >> 3) << 17) | ((uint32_t)(f16tc::kBM >> 4) << 24);
+    P.tmem_cols = (uint32_t)((pl.bn >= 256 ? 2 : 4) * pl.bn);
+    P.ofm = ofm; P.bias_dtype = CLDNN_B200_NONE; P.act = CLDNN_B200_ACT_NONE; P.eltw_act = CLDNN_B200_ACT_NONE;
+    P.status = ctx->d_status;
+    const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
+    const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
+    const size_t staging_total = (size_t)2 * f16tc::kBM * pl.bn * 2;
+    const size_t aux_bytes = sizeof(f16tc::Aux);
+    if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_f16_tc: not enough shared memory");
+    int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);
+    if (stages > f16tc::kMaxStages) stages = f16tc::kMaxStages;
+    P.stages = stages; P.ring_bytes = (int32_t)(stages * stage_bytes);
+    size_t smem_bytes = 1024 + (size_t)P.ring_bytes + staging_total + aux_bytes;
+    if (smem_bytes < max_smem / 2 + 1024) smem_bytes = max_smem / 2 + 1024;
+    const CUtensorMapSwizzle sw = pl.bk == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (pl.bk == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    CUresult cr;
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)cs, (cuuint64_t)P.M_total}; cuuint64_t strides[1] = {(cuuint64_t)cs * 2};
+        cuuint32_t box[2] = {(cuuint32_t)bke, (cuuint32_t)f16tc::kBM}; cuuint32_t es[2] = {1, 1};
+        cr = h_encode_tiled(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(A), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (cr == CUDA_SUCCESS) {
+        cuuint64_t dims[3] = {(cuuint64_t)cs, (cuuint64_t)batches, (cuuint64_t)ofm};
+        cuuint64_t strides[2] = {(cuuint64_t)ofm * cs * 2, (cuuint64_t)cs * 2};
+        cuuint32_t box[3] = {(cuuint32_t)bke, 1, (cuuint32_t)pl.bn}; cuuint32_t es[3] = {1, 1, 1};
+        cr = h_encode_tiled(&P.tmB, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(B), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (cr == CUDA_SUCCESS) {
+        cuuint64_t dims[2] = {(cuuint64_t)ofm, (cuuint64_t)P.M_total}; cuuint64_t strides[1] = {(cuuint64_t)ofm * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)f16tc::kBM}; cuuint32_t es[2] = {1, 1};
+        cr = h_encode_tiled(&P.tmO, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, D, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_DEVICE_ERROR, "f16 batched gemm: tensor map rejected by the driver (CUresult " + std::to_string((int)cr) + ")");
+    int grid = ctx->prop.multiProcessorCount;
+    if (grid > P.total_tiles) grid = P.total_tiles;
+    const size_t smem = smem_bytes; const int ms = (int)max_smem;
+    fn = [P, grid, smem, ms](cudaStream_t s) { return f16_launch(P, grid, smem, ms, s); };
     return CLDNN_B200_SUCCESS;
 }
 

@@ -20,14 +20,15 @@ def eng():
     e.close()
 
 
-def _close(eng, case, kernel, tune=0):
+def _close(eng, case, kernel, tune=0, floor=0.05):
     want = cases.run_oracle(case).astype(np.float32)
     got = cases.run_gpu(eng, case, kernel, tune).astype(np.float32)
     n = case.out_elems
     scale = float(np.abs(want[:n]).max())
     assert scale > 0
     err = np.abs(got[:n] - want[:n])
-    bad = np.flatnonzero(err > RTOL * np.maximum(np.abs(want[:n]), 0.05 * scale))
+    # relative to each value, with a floor of `floor` x the output scale under which the error is judged absolutely
+    bad = np.flatnonzero(err > RTOL * np.maximum(np.abs(want[:n]), floor * scale))
     assert bad.size == 0, "%d of %d beyond %.0e relative; worst %.4g vs %.4g" % (bad.size, n, RTOL, got[bad[0]], want[bad[0]])
     return want
 
@@ -97,3 +98,34 @@ def test_conv_f16_ref_kernel_agrees(eng):
     """The generic reference-order kernel on the same fp16 case (any layout): the selector's fallback."""
     case = cases.make_conv_case(34, N=2, C=32, K=48, H=9, W=9, **F16)
     _close(eng, case, "conv_ref")
+
+
+WINOGRAD = {
+    "vgg_64_64": dict(N=2, C=64, K=64, H=56, W=56),
+    "vgg_256_256": dict(N=2, C=256, K=256, H=28, W=28),
+    "vgg_512_512": dict(N=3, C=512, K=512, H=14, W=14),
+    "first_layer_c3": dict(N=2, C=3, K=64, H=40, W=40),
+    "odd_map_ragged_features": dict(N=3, C=48, K=40, H=9, W=11),
+    "no_padding": dict(N=2, C=32, K=32, H=12, W=13, pad=0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WINOGRAD))
+def test_conv_f16_winograd_matches_oracle(eng, name):
+    """Winograd F(2x2, 3x3) against the direct-form oracle: 1e-2 relative, judged absolutely below a quarter of the output
+    scale -- the transformed operands live in fp16 (as in the reference), so small outputs that are differences of large
+    terms carry an absolute error of about 1e-3 of the scale whatever their own size."""
+    case = cases.make_conv_case(41, **WINOGRAD[name], **F16)
+    k = eng.kernel("conv_f16_winograd")
+    assert k.supports(case.p)
+    _close(eng, case, "conv_f16_winograd", floor=0.25)
+
+
+def test_conv_f16_winograd_epilogue_and_refusals(eng):
+    k = eng.kernel("conv_f16_winograd")
+    for extra in (dict(bias="none"), dict(act=abi.ACT_NONE), dict(act=abi.ACT_CLAMP)):
+        kw = dict(F16); kw.update(extra)
+        _close(eng, cases.make_conv_case(42, N=2, C=32, K=64, H=14, W=14, **kw), "conv_f16_winograd", floor=0.25)
+    assert not k.supports(cases.make_conv_case(43, N=1, C=32, K=32, H=8, W=8, stride=2, **F16).p)
+    assert not k.supports(cases.make_conv_case(43, N=1, C=32, K=32, H=8, W=8, kh=1, kw=1, pad=0, **F16).p)
+    assert not k.supports(cases.make_conv_case(43, N=1, C=32, K=32, H=8, W=8).p)            # 8-bit
