@@ -64,6 +64,7 @@ extern const KernelDef kdef_conv_i8_tc;
 extern const KernelDef kdef_conv_i8_first;
 extern const KernelDef kdef_conv_f16_tc;
 extern const KernelDef kdef_conv_f16_winograd;
+extern const KernelDef kdef_conv_i8_dw;
 extern const KernelDef kdef_pooling_ref;
 extern const KernelDef kdef_pooling_i8_byxf;
 extern const KernelDef kdef_fc_ref;

@@ -484,6 +484,9 @@ void network_impl::select_layouts()
         if (n->deps[0]->out.data_type == data_types::f16)
             return (t == "convolution" || t == "fused_conv_eltwise") && n->p.groups == 1 && n->weights && n->weights->out.data_type == data_types::f16 && !n->wq;
         if (!is_int8(n->deps[0]->out.data_type)) return false;
+        // dense convolutions go to the tensor cores, depthwise ones (one feature per group) to the byxf depthwise kernel
+        if (t == "convolution" && n->p.groups > 1) return n->wq != nullptr && n->weights && n->weights->out.size.feature == 1 && n->p.groups == n->deps[0]->out.size.feature &&
+                                                          n->weights->out.size.batch == n->p.groups && n->p.groups % 4 == 0;
         if (t == "convolution" || t == "fused_conv_eltwise") return n->p.groups == 1 && n->wq != nullptr;
         if (t == "fully_connected") return n->wq && n->bias && n->bias->out.data_type == data_types::f32 && n->deps[0]->out.size.x == 1 && n->deps[0]->out.size.y == 1;
         return false;
@@ -763,7 +766,7 @@ void network_impl::prepare_kernel(node* n)
             }
             n->packed_weights = memory();
         }
-        finish({"conv_ref"}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
+        finish({"conv_i8_dw", "conv_ref"}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
         return;
     }
     if (t == "pooling") {

@@ -227,3 +227,33 @@ def test_unsupported_parameters_are_refused_not_emulated(eng):
     with pytest.raises(E.EngineError) as e:
         cases.run_gpu(eng, case, "conv_i8_tc")
     assert e.value.status == abi.UNSUPPORTED_FORMAT
+
+
+DEPTHWISE = {
+    # MobileNet-v2 style: 3x3 depthwise, stride 1 and 2, ReLU6 (CLAMP 0..6 in the dequantised domain)
+    "dw3x3_c32": dict(N=2, C=32, K=32, H=28, W=28, groups=32),
+    "dw3x3_stride2_c96": dict(N=2, C=96, K=96, H=29, W=31, groups=96, stride=2),
+    "dw5x5_dilated_c16": dict(N=1, C=16, K=16, H=13, W=12, groups=16, kh=5, kw=5, pad=4, dil=2),
+    "dw3x3_c960_7x7": dict(N=3, C=960, K=960, H=7, W=7, groups=960),
+}
+
+
+@pytest.mark.parametrize("name", sorted(DEPTHWISE))
+@pytest.mark.parametrize("variant", ["relu6_u8", "signed_calibrated"])
+def test_conv_i8_dw_matches_oracle(eng, name, variant):
+    kw = dict(DEPTHWISE[name])
+    if variant == "relu6_u8":
+        case = cases.make_conv_case(51, out_dtype=np.uint8, act=abi.ACT_CLAMP, scale_lo=2.0 ** -12, scale_hi=2.0 ** -10, **kw)
+    else:
+        case = cases.make_conv_case(52, in_dtype=np.int8, out_dtype=np.int8, bias="f32", calib=True, act=abi.ACT_NONE,
+                                    scale_lo=2.0 ** -11, scale_hi=2.0 ** -9, **kw)
+    assert eng.kernel("conv_i8_dw").supports(case.p)
+    want = _exact(eng, case, "conv_i8_dw")
+    assert len(np.unique(want)) > 4
+    _exact(eng, case, "conv_ref")
+
+
+def test_conv_i8_dw_refuses_dense_and_grouped(eng):
+    k = eng.kernel("conv_i8_dw")
+    assert not k.supports(cases.make_conv_case(53, N=1, C=32, K=32, H=8, W=8).p)
+    assert not k.supports(cases.make_conv_case(53, N=1, C=32, K=32, H=8, W=8, groups=4).p)
