@@ -104,6 +104,66 @@ def resnet50_int8(batch, seed=2019, image=224, scale_lo=2.0 ** -14, scale_hi=2.0
     return s
 
 
+# MobileNet-v2: (expansion, output features, repeats, stride of the first repeat)
+MOBILENET_V2_BLOCKS = ((1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1))
+
+
+def mobilenet_v2_int8(batch, seed=2, image=224, blocks=MOBILENET_V2_BLOCKS, stem=32, head=1280, classes=1000):
+    """int8 MobileNet-v2: 3x3/2 stem, inverted-residual blocks (1x1 expansion, 3x3 depthwise, linear 1x1 projection, residual
+    sum where the shapes allow), 1x1 head, global average pooling, fully_connected, softmax.  s8 weights with per-feature
+    scales sized so the dequantised values spread over ReLU6's range; ReLU6 is an `activation` primitive (clamp 0..6) after
+    each convolution, which the optimising build folds in front of the requantisation (O_QF = 255 / 6 onto u8), as the
+    reference's activation fusing does."""
+    rng = np.random.default_rng(seed)
+    s = Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.u8, cl.format.bfyx, cl.tensor(batch, 3, image, image))
+    s.add(cl.input_layout("input", s.input_layout))
+
+    def conv(name, x, cin, cout, k, stride, groups=1, relu6=True, in_scale=42.5):
+        fan = (cin // groups) * k * k
+        s.const(name + "_w", rng.integers(-127, 128, size=(cout, cin // groups, k, k), dtype=np.int64).astype(np.int8))
+        s.const(name + "_b", rng.integers(-2048, 2049, size=cout, dtype=np.int64).astype(np.int32))
+        # accumulators spread over ~ sqrt(fan) * 73 * (input scale): bring them to a few units
+        sigma = np.sqrt(fan) * 73.0 * (74.0 if in_scale is None else 60.0)
+        s.const(name + "_q", (rng.uniform(1.0, 3.0, size=cout) / sigma).astype(np.float32))
+        pad = -(k // 2)
+        s.add(cl.convolution(name, x, name + "_w", name + "_b", name + "_q", output_data_type=dt.u8 if relu6 else dt.i8, stride=(stride, stride),
+                             input_offset=(pad, pad), groups=groups, output_quantization_factor=42.5 if relu6 else 16.0))
+        if relu6:
+            s.add(cl.activation(name + "_relu6", name, cl.activation_func.clamp, 0.0, 6.0))
+            return name + "_relu6"
+        return name
+
+    x = conv("stem", "input", 3, stem, 3, 2, in_scale=None)
+    cin = stem
+    for bi, (t, c, n, st) in enumerate(blocks):
+        for r in range(n):
+            name = "b%d_%d" % (bi, r)
+            stride = st if r == 0 else 1
+            inp = x
+            h = cin * t
+            y = conv(name + "_exp", x, cin, h, 1, 1) if t != 1 else x
+            y = conv(name + "_dw", y, h, h, 3, stride, groups=h)
+            y = conv(name + "_proj", y, h, c, 1, 1, relu6=False)
+            if stride == 1 and cin == c and inp != "stem_relu6" and not inp.endswith("_relu6"):
+                s.add(cl.eltwise(name + "_sum", y, inp, cl.eltwise_mode.sum))
+                y = name + "_sum"
+            x, cin = y, c
+    x = conv("head", x, cin, head, 1, 1)
+    s.add(cl.pooling("pool", x, cl.pooling_mode.average, global_pooling=True))
+    s.const("fc_w", rng.integers(-127, 128, size=(classes, head, 1, 1), dtype=np.int64).astype(np.int8))
+    s.const("fc_b", rng.uniform(-8.0, 8.0, size=classes).astype(np.float32))
+    s.const("fc_q", (rng.uniform(1.0, 3.0, size=classes) / (np.sqrt(head) * 73.0 * 60.0)).astype(np.float32))
+    s.const("fc_c", rng.uniform(8.0, 16.0, size=classes).astype(np.float32))
+    s.add(cl.fully_connected("fc", "pool", "fc_w", "fc_b", "fc_q", "fc_c"))
+    s.add(cl.reorder("fc_f32", "fc", cl.format.bfyx, dt.f32))
+    s.add(cl.softmax("prob", "fc_f32"))
+    s.outputs = ["prob", "fc"]
+    return s
+
+
 # VGG16 (configuration D): 13 3x3 pad-1 convolutions in five stages, 2x2 max pooling after each stage.
 VGG16_STAGES = ((64, 2), (128, 2), (256, 3), (512, 3), (512, 3))
 

@@ -20,12 +20,38 @@ def _tensor(arr):
     return abi.tensor(abi.dtype_of(arr.dtype), b, f, y, x, "bfyx")[0]
 
 
-def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle"):
+def _fusable_activations(spec):
+    """The activation folding of the optimising build (prepare_primitive_fusing.cpp, fuse_activation): an `activation`
+    whose only producer is a convolution without an activation of its own, consumed by nobody else and not an output,
+    moves into the convolution, where it acts on the dequantised value before the requantisation.
+    Returns {convolution id: (func, a, b)} and {activation id: convolution id}."""
+    users = {}
+    for p in spec.prims:
+        for k in ("input", "input2"):
+            if k in p.args:
+                users.setdefault(p.args[k], []).append(p.id)
+    by_id = {p.id: p for p in spec.prims}
+    into, alias = {}, {}
+    for p in spec.prims:
+        if p.kind != "activation":
+            continue
+        prod = by_id.get(p.args["input"])
+        if prod is None or prod.kind not in ("convolution",) or prod.args["with_activation"]:
+            continue
+        if users.get(prod.id, []) != [p.id] or prod.id in spec.outputs or prod.id in into:
+            continue
+        into[prod.id] = (p.args["func"], p.args["a"], p.args["b"])
+        alias[p.id] = prod.id
+    return into, alias
+
+
+def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle", fuse_activations=False):
     """inputs: {input id: logical [b,f,y,x] array}.  Returns {primitive id: logical array} for spec.outputs
     (or for the ids in `keep`; keep=True keeps everything).  `stats`, if a dict, receives per-primitive
     fractions of zero / saturated outputs for 8-bit results.  conv_impl="reference" runs the convolutions on the reference's
     own kernel source (oracle/_ref) where a variant exists, the C restatement elsewhere."""
     vals = dict(inputs)
+    act_into, act_alias = _fusable_activations(spec) if fuse_activations else ({}, {})
     users = {}
     for p in spec.prims:
         for k in ("input", "input2"):
@@ -40,6 +66,9 @@ def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle"):
             continue
         if k == "input_layout":
             assert p.id in vals, "missing input " + p.id
+            continue
+        if p.id in act_alias:                      # folded into its convolution
+            vals[p.id] = vals[act_alias[p.id]]
             continue
         x = vals[a["input"]]
         if k in ("convolution", "fused_conv_eltwise"):
@@ -65,6 +94,8 @@ def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle"):
             cp.i_qf = a["input_quantization_factor"]
             cp.o_qf = a.get("output_quantization_factor", 1.0)
             cp.act, cp.act_m = _act(a["with_activation"], a["activation_negative_slope"])
+            if p.id in act_into:
+                cp.act, cp.act_m, cp.act_n = act_into[p.id]
             cp.eltw_stride_x = cp.eltw_stride_y = 1
             eltw = ecal = None
             if k == "fused_conv_eltwise":

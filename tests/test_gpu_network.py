@@ -177,3 +177,25 @@ def test_small_vgg_fp16_network(eng, optimize):
         assert all(r["kernel"] == "conv_f16_tc" for r in convs), [r["kernel"] for r in convs]
     else:
         assert all(r["kernel"] == "conv_ref" for r in convs)
+
+
+@pytest.mark.parametrize("optimize", [False, True])
+def test_small_mobilenet_v2_int8_network_bit_exact(eng, optimize):
+    """Inverted-residual blocks: 1x1 expansion and projection on the tensor cores, 3x3 depthwise on conv_i8_dw, ReLU6 as a
+    clamp activation, quantised residual sums.  The optimising build folds each ReLU6 into its convolution, in front of
+    the requantisation (the reference's activation fusing), and is compared with the oracle run the same way; the plain
+    build keeps the activations separate, on the 8-bit values, like the oracle's primitive-by-primitive run."""
+    spec = topologies.mobilenet_v2_int8(3, seed=4, image=48, blocks=((1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 2, 1)), stem=32, head=64, classes=20)
+    x = _input(spec)
+    stats = {}
+    want = oracle_net.run(spec, {spec.input_id: x}, stats=stats, fuse_activations=optimize)
+    assert stats["fc:out_of_range"] == 0
+    net, got = _run(eng, spec, x, optimize_data=optimize)
+    _compare(spec, want, got)
+    info = net.primitives_info()
+    convs = [r for r in info if r["type"] == "convolution"]
+    if optimize:
+        assert any(r["kernel"] == "conv_i8_dw" for r in convs)
+        assert all(r["kernel"] in ("conv_i8_tc", "conv_i8_first", "conv_i8_dw") for r in convs), [(r["id"], r["kernel"]) for r in convs]
+        assert not any(r["type"] == "activation" for r in info if r["kernel"])          # every ReLU6 was folded
+        assert len(np.unique(got["fc"])) > 8
