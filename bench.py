@@ -87,6 +87,12 @@ class ClockSampler(threading.Thread):
         return dict(sm_mhz=s[len(s) // 2] if s else None, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=len(s))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the 53 conv_i8_tc launches of one network execution at batch 256, per image
+# (one ncu capture on a B200; the algorithmic bytes of the same launches are 25.4 MB per image)
+NCU_DRAM_BYTES_PER_IMAGE_CONV_TC = 18.99e6
+NCU_TRAFFIC_BATCH = 256
+
+
 def cpu_baseline(batch_images, threads=0):
     """The reference arithmetic on the host cores, on a bounded sample (whole ResNet-50, `batch_images` images): the
     convolutions run the reference's own kernel source compiled as C++ when oracle/_ref holds the prebuilt variants,
@@ -293,7 +299,10 @@ def main():
         int8_peak = 2.0 * peaks["bf16_sustained"]                    # TOPS; no int8 figure is measured on this pool
         achieved = tc_ops / tc_ns / 1e3                              # ops/ns = Gop/s; /1e3 -> TOPS
         roof = {"bound": "tensor", "kernel": "conv_i8_tc", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s", "frac": achieved / int8_peak,
-                "traffic": None, "peak_source": "2 x bf16_tflops_sustained of %s MEASURED_PEAKS (dense int8 : bf16 = 2 : 1)" % peaks["source"],
+                "traffic": NCU_DRAM_BYTES_PER_IMAGE_CONV_TC * B if B == NCU_TRAFFIC_BATCH else None,
+                "traffic_note": "dram read+write bytes of the conv_i8_tc launches of one step, from the ncu capture summarised in "
+                                "profiles/conv_i8_tc_dram_traffic_b256.md (batch 256; not scaled to other batch sizes because the L2 share changes)",
+                "peak_source": "2 x bf16_tflops_sustained of %s MEASURED_PEAKS (dense int8 : bf16 = 2 : 1)" % peaks["source"],
                 "launches_per_step": sum(1 for k in acc if info[k]["kernel"] == "conv_i8_tc"),
                 "share_of_step": tc_ns / all_ns,
                 "conv3x3_tops": k3_ops / k3_ns / 1e3, "conv3x3_frac": k3_ops / k3_ns / 1e3 / int8_peak,
