@@ -611,9 +611,11 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     if (pl.a_mode == A_PATCH) {
         // a stage holds the patch; the tensor core reads 128 rows from row r * bw, r < kh, so the stage spans that far
         const int patch_rows = (pl.bh + p.kh - 1) * pl.bw, read_rows = (p.kh - 1) * pl.bw + kBM;
-        P.k_steps = p.kw * P.chunks;
-        P.a_tx_bytes = patch_rows * pl.bk;
-        P.a_stage_bytes = (((patch_rows > read_rows ? patch_rows : read_rows) * pl.bk) + 1023) / 1024 * 1024;
+        // one stage = the kw patches (one per filter column) of one channel chunk: one barrier round trip per chunk
+        P.k_steps = P.chunks;
+        P.patch_alloc = (((patch_rows > read_rows ? patch_rows : read_rows) * pl.bk) + 1023) / 1024 * 1024;
+        P.a_tx_bytes = p.kw * patch_rows * pl.bk;
+        P.a_stage_bytes = p.kw * P.patch_alloc;
         P.b_total_bytes = P.n_tiles * p.kh * p.kw * P.chunks * P.b_stage_bytes;
     }
     P.sbo = 8u * (uint32_t)pl.bk;

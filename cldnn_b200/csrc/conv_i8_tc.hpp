@@ -46,6 +46,7 @@ struct alignas(64) TcParams {
     int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
     // patch mode: all weights resident in shared memory, one activation patch per (filter column, channel chunk)
     int32_t ring_bytes, b_total_bytes;   // operand area: activation ring (+ weight ring or resident weights)
+    int32_t patch_alloc;                 // bytes reserved per filter column's patch inside a stage (a stage holds the kw patches of one channel chunk)
     int32_t debug;                       // diagnostic builds (-DCONV_TC_DEBUG): what-if switches, 0 otherwise
     int32_t fast_variant;                // conv_i8_tc_fast: (output kind << 1) | ReLU before the residual sum
     float acc_bound;                     // K * max|activation| * 128: no accumulator can exceed it in magnitude
@@ -62,11 +63,14 @@ struct alignas(64) TcParams {
 #ifdef CONV_TC_PROFILE
 // one copy per translation unit; the debug readers below see the copy of the file that defines them
 static __device__ unsigned long long g_tc_prof[148 * 16];
+// counts, per wait site, how often the barrier was not yet complete at the first poll (reading the clock costs ~70 clocks
+// per read, too much inside the loops); the role's total loop time is taken from two clock reads
 struct Prof {
-    long long acc[3] = {0, 0, 0}; long long t = 0, t_begin = 0;
+    long long acc[3] = {0, 0, 0}; long long t_begin = 0;
     __device__ __forceinline__ void begin() { t_begin = clock64(); }
-    __device__ __forceinline__ void start() { t = clock64(); }
-    __device__ __forceinline__ void stop(int i) { acc[i] += clock64() - t; }
+    __device__ __forceinline__ void start() {}
+    __device__ __forceinline__ void stop(int) {}
+    __device__ __forceinline__ void miss(int i, bool first_poll_ok) { acc[i] += first_poll_ok ? 0 : 1; }
     __device__ __forceinline__ void flush(int slot, int n, long long extra = -1) {
         if (blockIdx.x >= 148) return;
         for (int i = 0; i < n; ++i) g_tc_prof[blockIdx.x * 16 + slot + i] = (unsigned long long)acc[i];
@@ -80,6 +84,7 @@ struct Prof {
     __device__ __forceinline__ void begin() {}
     __device__ __forceinline__ void start() {}
     __device__ __forceinline__ void stop(int) {}
+    __device__ __forceinline__ void miss(int, bool) {}
     __device__ __forceinline__ void flush(int, int, long long = -1) {}
 };
 #endif

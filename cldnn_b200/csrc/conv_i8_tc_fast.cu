@@ -34,7 +34,7 @@
 
 namespace b200 {
 
-constexpr int kFastThreads = 384;          // warp 0 TMA loads, 1 MMA issue, 2 TMA stores, 3 idle, 4..11 epilogue
+constexpr int kFastThreads = 384;          // warp 0 operand loads, 1 MMA issue, 2 TMA stores, 3 residual loads, 4..11 epilogue
 constexpr int kFastEpiWarp0 = 4;
 constexpr int kGroups = 2;                 // epilogue warp groups, alternate tiles
 
@@ -154,6 +154,47 @@ __device__ __noinline__ void fast_tile_wide(const TcParams& P, const FastAux* au
     if (lane == 0) mbar_arrive(tmem_empty_bar);
 }
 
+// The tiles a role visits: tile = first + i * step.  Integer division costs a single thread ~120 clocks, so the
+// decomposition of the tile index (feature tile, pixel tile, and the pixel tile's box or first-pixel coordinates) is kept
+// incrementally: mixed-radix digits advance by the digits of the step, and are recomputed only when the feature tile changes.
+struct TileWalk {
+    int tile, step, n_tile, m_tile;
+    int d0, d1, d2;                 // boxed: box column, box row, box batch; im2col: q, p, n of the tile's first pixel
+    int s0, s1, s2;                 // digits of the step
+    int r0, r1;                     // radices
+    int mode, m_tiles, total;
+    __device__ __forceinline__ void digits(int m)
+    {
+        if (mode == A_IM2COL) { const int64_t px = (int64_t)m * kBM; d0 = (int)(px % r0); const int64_t t = px / r0; d1 = (int)(t % r1); d2 = (int)(t / r1); }
+        else if (mode == A_TILED || mode == A_PATCH) { d0 = m % r0; const int t = m / r0; d1 = t % r1; d2 = t / r1; }
+    }
+    __device__ __forceinline__ void init(const TcParams& P, int first, int stp)
+    {
+        tile = first; step = stp; mode = P.a_mode; m_tiles = P.m_tiles; total = P.total_tiles;
+        const bool im = mode == A_IM2COL;
+        r0 = im ? P.Q : P.tiles_w; r1 = im ? P.P : P.tiles_h;
+        if (r0 < 1) r0 = 1; if (r1 < 1) r1 = 1;
+        const int64_t sm = im ? (int64_t)stp * kBM : (int64_t)stp;
+        s0 = (int)(sm % r0); const int64_t t = sm / r0; s1 = (int)(t % r1); s2 = (int)(t / r1);
+        n_tile = first / m_tiles; m_tile = first - n_tile * m_tiles;
+        d0 = d1 = d2 = 0;
+        if (first < total) digits(m_tile);
+    }
+    __device__ __forceinline__ bool valid() const { return tile < total; }
+    __device__ __forceinline__ void next()
+    {
+        tile += step; m_tile += step;
+        if (m_tile >= m_tiles) {
+            while (m_tile >= m_tiles) { m_tile -= m_tiles; ++n_tile; }
+            if (tile < total) digits(m_tile);
+            return;
+        }
+        d0 += s0; if (d0 >= r0) { d0 -= r0; ++d1; }
+        d1 += s1; if (d1 >= r1) { d1 -= r1; ++d2; }
+        d2 += s2;
+    }
+};
+
 template <int BN, bool kFused>
 __global__ void __launch_bounds__(kFastThreads, 1)
 conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
@@ -206,75 +247,60 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
+        const bool patch = P.a_mode == A_PATCH;
         if (lane == 0) {
-            int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true; int t = 0;
+            if (patch && blockIdx.x < (unsigned)P.total_tiles) {
+                // patch mode: every filter tap of every feature tile, once per CTA
+                const uint32_t bf = smem_u32(&aux->b_full);
+                mbar_expect_tx(bf, (uint32_t)P.b_total_bytes);
+                uint32_t dst = b_base;
+                for (int nt = 0; nt < P.n_tiles; ++nt)
+                    for (int tp = 0; tp < P.kh * P.kw; ++tp)
+                        for (int ch = 0; ch < P.chunks; ++ch, dst += (uint32_t)P.b_stage_bytes)
+                            tma_load_3d(dst, &P.tmB, bf, ch * P.bk, tp, nt * BN);
+            }
+            int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
+            const int stages = P.stages, k_steps = P.k_steps, chunks = P.chunks, bk = P.bk, kw = P.kw;
+            const uint32_t tx = (uint32_t)(patch ? P.a_tx_bytes : P.a_tx_bytes + P.b_tx_bytes);
+            const uint32_t a_stage = (uint32_t)P.a_stage_bytes, b_stage = (uint32_t)P.b_stage_bytes;
+            const uint32_t full0 = smem_u32(&aux->full[0]), empty0 = smem_u32(&aux->empty[0]);
             Prof prof; prof.begin();
-            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
-                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
-                int c_w = 0, c_h = 0, c_n = 0, o_w = 0, o_h = 0;
-                if (P.a_mode == A_IM2COL) {
-                    const int64_t m = (int64_t)m_tile * kBM; const int pq = P.P * P.Q;
-                    const int n = (int)(m / pq); const int rr = (int)(m - (int64_t)n * pq); const int p = rr / P.Q, q = rr - p * P.Q;
-                    c_w = q * P.stride_x - P.pad_x; c_h = p * P.stride_y - P.pad_y; c_n = n;
-                } else if (P.a_mode == A_TILED || P.a_mode == A_PATCH) {
-                    const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
-                    o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
-                    c_w = o_w - P.pad_x; c_h = o_h - P.pad_y;
-                }
-                if (P.a_mode == A_PATCH) {
-                    if (t == 0) {
-                        // every filter tap of every feature tile, once per CTA
-                        const uint32_t bf = smem_u32(&aux->b_full);
-                        mbar_expect_tx(bf, (uint32_t)P.b_total_bytes);
-                        uint32_t dst = b_base;
-                        for (int nt = 0; nt < P.n_tiles; ++nt)
-                            for (int tp = 0; tp < P.kh * P.kw; ++tp)
-                                for (int ch = 0; ch < P.chunks; ++ch, dst += (uint32_t)P.b_stage_bytes)
-                                    tma_load_3d(dst, &P.tmB, bf, ch * P.bk, tp, nt * BN);
+            TileWalk w; w.init(P, blockIdx.x, gridDim.x);
+            for (; w.valid() && ok; w.next()) {
+                int c_w = 0, c_h = 0, c_n = 0;
+                if (P.a_mode == A_IM2COL) { c_w = w.d0 * P.stride_x - P.pad_x; c_h = w.d1 * P.stride_y - P.pad_y; c_n = w.d2; }
+                else if (P.a_mode == A_TILED || patch) { c_w = w.d0 * P.bw - P.pad_x; c_h = w.d1 * P.bh - P.pad_y; c_n = w.d2 * P.bb; }
+                const int m0 = w.m_tile * kBM, n0 = w.n_tile * BN;
+                int tap = 0, cc = 0, r = 0, sx = 0;
+                for (int ks = 0; ks < k_steps; ++ks) {
+                    { bool fp_ = true;
+                    if (!mbar_wait_lean(empty0 + 8u * (uint32_t)stage, phase ^ 1u, s_abort, P.status, kErrProducer, &fp_)) { ok = false; break; }
+                    prof.miss(0, fp_); }
+                    const uint32_t full = full0 + 8u * (uint32_t)stage;
+                    const uint32_t dst = a_base + (uint32_t)stage * a_stage;
+                    mbar_expect_tx(full, tx);
+                    const int c0 = cc * bk;
+                    if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
+                    if (patch) {                                                            // one patch per filter column
+                        for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * P.patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
                     }
-                    // one patch of (bh + kh - 1) x bw pixels per filter column and channel chunk; the kh taps of that
-                    // column read it at row offsets
-                    for (int ks = 0; ks < P.k_steps; ++ks) {
-                        const int s = ks / P.chunks, cc = ks - s * P.chunks;
-                        prof.start();
-                        if (!mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
-                        prof.stop(0);
-                        const uint32_t full = smem_u32(&aux->full[stage]);
-                        mbar_expect_tx(full, (uint32_t)P.a_tx_bytes);
-                        tma_load_4d(a_base + (uint32_t)(stage * P.a_stage_bytes), &P.tmA, full, cc * P.bk, c_w + s, c_h, c_n);
-                        ++issued;
-                        if (++stage == P.stages) { stage = 0; phase ^= 1u; }
-                    }
-                    continue;
-                }
-                int tap = 0, cc = 0, r = 0, s = 0;
-                for (int ks = 0; ks < P.k_steps; ++ks) {
-                    prof.start();
-                    if (!mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
-                    prof.stop(0);
-                    const uint32_t full = smem_u32(&aux->full[stage]);
-                    mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
-                    const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
-                    const uint32_t b_dst = b_base + (uint32_t)(stage * P.b_stage_bytes);
-                    const int c0 = cc * P.bk;
-                    if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
-                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
-                    else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
-                    tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * BN);
+                    else if (P.a_mode == A_FLAT) tma_load_2d(dst, &P.tmA, full, c0, m0);
+                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(sx * P.dil_x), (uint16_t)(r * P.dil_y));
+                    else tma_load_4d(dst, &P.tmA, full, c0, c_w + sx * P.dil_x, c_h + r * P.dil_y, c_n);
                     ++issued;
-                    if (++cc == P.chunks) { cc = 0; ++tap; if (++s == P.kw) { s = 0; ++r; } }
-                    if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                    if (++cc == chunks) { cc = 0; ++tap; if (++sx == kw) { sx = 0; ++r; } }
+                    if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
             prof.flush(0, 1);
             if (!ok) {
                 // unwind: let the copies already in flight land before the CTA's shared memory goes away
                 int st = stage; uint32_t ph = phase;
-                const int pending = issued < P.stages ? (int)issued : P.stages;
+                const int pending = issued < stages ? (int)issued : stages;
                 for (int i = 0; i < pending; ++i) {
-                    if (--st < 0) { st = P.stages - 1; ph ^= 1u; }
+                    if (--st < 0) { st = stages - 1; ph ^= 1u; }
                     const uint64_t t0 = globaltimer();
-                    while (!mbar_try_wait(smem_u32(&aux->full[st]), ph) && globaltimer() - t0 < 100000000ull) { }
+                    while (!mbar_try_wait(full0 + 8u * (uint32_t)st, ph) && globaltimer() - t0 < 100000000ull) { }
                 }
             }
         }
@@ -292,37 +318,43 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const bool patch = P.a_mode == A_PATCH;
             const uint32_t row_step = (uint32_t)(P.bw * P.bk) >> 4;                    // patch mode: one filter row further down the patch
             const uint32_t b_row_step = (uint32_t)(P.kw * P.chunks) * b_step;          //             the weights of the next filter row
-            const int kh = P.kh, chunks = P.chunks;
+            const int kh = P.kh, kw_ = P.kw;
+            const uint32_t patch_step = (uint32_t)P.patch_alloc >> 4;                  //             the next filter column's patch
+            const uint32_t b_tap_step = (uint32_t)P.chunks * b_step;                   //             the weights of the next filter column
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
             Prof prof; prof.begin();
             if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u);
-            for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
+            TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
+            for (; walk.valid() && ok; walk.next(), ++t) {
                 const int acc = t % NBUF;
-                prof.start();
-                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
-                prof.stop(0);
-                tc_fence_after();
+                { bool fp_ = true;
+                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma, &fp_)) { ok = false; break; }
+                prof.miss(0, fp_); }
+                if (!TC_DEBUG(P, 4)) tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 uint32_t accf = 0u;
                 uint32_t b_col = 0u;                                                   // patch mode: weights of (filter column, channel chunk)
-                if (patch) b_col = b_lo0 + (uint32_t)((tile / P.m_tiles) * kh) * b_row_step;
+                if (patch) b_col = b_lo0 + (uint32_t)(walk.n_tile * kh) * b_row_step;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    prof.start();
-                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
-                    prof.stop(1);
+                    { bool fp_ = true;
+                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u, &fp_)) { ok = false; break; }
+                    prof.miss(1, fp_); }
                     prof.start();
                     if (TC_DEBUG(P, 0)) { }
                     else if (patch) {
-                        // rows r*bw .. r*bw+127 of the patch are the tile's 128 pixels under filter row r
-                        uint32_t ar = a_lo, br = b_col;
-                        for (int r = 0; r < kh; ++r, ar += row_step, br += b_row_step) {
-                            if (kk == 4) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf);
-                            else if (kk == 2) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf);
-                            else mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf);
-                            accf = 1u;
+                        // per filter column s one patch; rows r*bw .. r*bw+127 of it are the tile's 128 pixels under filter row r
+                        uint32_t as = a_lo, bs = b_col;
+                        for (int s = 0; s < kw_; ++s, as += patch_step, bs += b_tap_step) {
+                            uint32_t ar = as, br = bs;
+                            for (int r = 0; r < kh; ++r, ar += row_step, br += b_row_step) {
+                                if (kk == 4) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf);
+                                else if (kk == 2) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf);
+                                else mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf);
+                                accf = 1u;
+                            }
                         }
-                        b_col += b_step;
+                        b_col += b_step;                                                     // next channel chunk
                     } else {
                         if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
@@ -349,15 +381,16 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         if (lane == 0) {
             int t = 0;
             Prof prof; prof.begin();
-            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
-                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
+            TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
+            if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;            // the output of an im2col tile is addressed by its first pixel index
+            for (; walk.valid(); walk.next(), ++t) {
+                const int n_tile = walk.n_tile, m_tile = walk.m_tile;
                 const int a = t % NBUF;
                 prof.start();
                 if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NBUF) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
                 prof.stop(0);
-                int tw = 0, th = 0, tb = 0;
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
-                if (boxed) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
+                const int tw = walk.d0, th = walk.d1, tb = walk.d2;
 #pragma unroll
                 for (int cb = 0; cb < COLB; ++cb) {
                     if (TC_DEBUG(P, 3)) break;
@@ -382,14 +415,12 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         if (kFused && lane == 0) {
             int t = 0;
             Prof prof; prof.begin();
-            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
-                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
-                int o_w = 0, o_h = 0, c_n = 0;
+            TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
+            if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;
+            for (; walk.valid(); walk.next(), ++t) {
+                const int n_tile = walk.n_tile, m_tile = walk.m_tile;
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
-                if (boxed) {
-                    const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w;
-                    o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb;
-                }
+                const int o_w = walk.d0 * P.bw, o_h = walk.d1 * P.bh, c_n = walk.d2 * P.bb;
                 const int a = t % NBUF;
                 prof.start();
                 if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
@@ -422,8 +453,10 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         int cur_n_tile = -1; bool ok = true; bool wide = false;
         Prof prof; prof.begin();
         int t = group;
-        for (int tile = blockIdx.x + group * gridDim.x; tile < P.total_tiles && ok; tile += kGroups * gridDim.x, t += kGroups) {
-            const int n_tile = tile / P.m_tiles;
+        TileWalk walk; walk.init(P, blockIdx.x + group * gridDim.x, kGroups * gridDim.x);
+        walk.mode = A_FLAT;                                         // only the feature tile is needed here
+        for (; walk.valid() && ok; walk.next(), t += kGroups) {
+            const int n_tile = walk.n_tile;
             const int acc = t % NBUF;
             const uint32_t par = (uint32_t)(t / NBUF) & 1u;
             if (n_tile != cur_n_tile) {

@@ -75,9 +75,12 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 {
     return mbar_wait(bar, parity, s_abort, g_status, code);
 }
-__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, volatile uint32_t* s_abort, uint32_t* g_status, uint32_t code)
+__device__ __forceinline__ bool mbar_wait_lean(uint32_t bar, uint32_t parity, volatile uint32_t* s_abort, uint32_t* g_status, uint32_t code,
+                                               bool* first_poll_ok = nullptr)
 {
-    if (mbar_try_wait(bar, parity)) return true;
+    const bool ok = mbar_try_wait(bar, parity) != 0u;
+    if (first_poll_ok) *first_poll_ok = ok;
+    if (ok) return true;
     return mbar_wait_slow(bar, parity, s_abort, g_status, code);
 }
 
