@@ -226,9 +226,32 @@ def main():
     out_mem = None
     prob_host = torch.empty((B, 1000), dtype=torch.float32).pin_memory()
 
+    # End to end through the public API: every step's images start in pinned host memory and its probabilities end there.
+    # The host->device copy of step i+1 runs on a copy stream into one of two staging buffers while step i computes; the
+    # network's bound input is refilled from the staging buffer by a device-to-device copy on the compute stream.
+    copy_stream = torch.cuda.Stream(device=local_rank)
+    staging = [torch.empty((B, 3, 224, 224), dtype=torch.uint8, device="cuda") for _ in range(2)]
+    staged = [torch.cuda.Event() for _ in range(2)]       # host->device copy into staging[k] has finished
+    consumed = [torch.cuda.Event() for _ in range(2)]     # staging[k] has been copied into the network input
+    e2e_state = {"primed": -1}
+
+    def _stage(i):
+        k = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[k])
+            staging[k].copy_(host[i % n_resident], non_blocking=True)
+            staged[k].record(copy_stream)
+
     def step_e2e(i):
+        if e2e_state["primed"] != i:                          # first step of a run: nothing was prefetched for it
+            _stage(i)
+        k = i % 2
         with torch.cuda.stream(stream):
-            x_dev.copy_(host[i % n_resident], non_blocking=True)
+            stream.wait_event(staged[k])
+            x_dev.copy_(staging[k], non_blocking=True)
+            consumed[k].record(stream)
+        _stage(i + 1)                                         # next step's images travel while this step computes
+        e2e_state["primed"] = i + 1
         net.execute()
         with torch.cuda.stream(stream):
             prob_host.copy_(prob_dev, non_blocking=True)

@@ -277,6 +277,58 @@ softmax_kernel(const __grid_constant__ cldnn_b200_softmax_params p, const void* 
         }
     }
 }
+// One block per row for long rows (classification heads): every thread keeps its elements in registers, two block
+// reductions (max, sum) through shared memory, one pass over memory in, one out.
+constexpr int kSoftmaxPerThread = 8;
+__global__ void __launch_bounds__(256)
+softmax_row_kernel(const __grid_constant__ cldnn_b200_softmax_params p, const void* in, void* out)
+{
+    __shared__ float red[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t rows = (int64_t)p.in.b * p.in.y * p.in.x;
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int x = (int)(r % p.in.x), y = (int)((r / p.in.x) % p.in.y), b = (int)(r / ((int64_t)p.in.x * p.in.y));
+        float v[kSoftmaxPerThread];
+        float mx = -3.402823466e38f;
+#pragma unroll
+        for (int i = 0; i < kSoftmaxPerThread; ++i) {
+            const int f = threadIdx.x + i * 256;
+            v[i] = f < p.in.f ? load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)) : -3.402823466e38f;
+            mx = fmaxf(mx, v[i]);
+        }
+#pragma unroll
+        for (int s = 16; s; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        if (lane == 0) red[warp] = mx;
+        __syncthreads();
+        mx = red[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
+        __syncthreads();
+        float den = 0.f;
+#pragma unroll
+        for (int i = 0; i < kSoftmaxPerThread; ++i) {
+            const int f = threadIdx.x + i * 256;
+            v[i] = f < p.in.f ? expf(v[i] - mx) : 0.f;
+        }
+        // the reference adds the exponentials of one row in feature order on one work-item; a tree sum differs from it in
+        // the last bits only, inside the tolerance softmax is compared with
+#pragma unroll
+        for (int i = 0; i < kSoftmaxPerThread; ++i) den += v[i];
+#pragma unroll
+        for (int s = 16; s; s >>= 1) den += __shfl_xor_sync(0xffffffffu, den, s);
+        if (lane == 0) red[warp] = den;
+        __syncthreads();
+        den = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) den += red[w];
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kSoftmaxPerThread; ++i) {
+            const int f = threadIdx.x + i * 256;
+            if (f < p.in.f) store_sat_float(out, p.out.dtype, tidx(p.out, b, f, y, x), __fdiv_rn(v[i], den));
+        }
+    }
+}
 static bool softmax_supports(const void* vp) { const auto& p = *(const cldnn_b200_softmax_params*)vp; return is_fp(p.in.dtype) && is_fp(p.out.dtype) && p.in.f == p.out.f; }
 static int32_t softmax_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
@@ -284,7 +336,14 @@ static int32_t softmax_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const c
     if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "softmax: input and output are required");
     const void* in = a->input0; void* o = a->output;
     const int grid = grid_for((int64_t)p.in.b * p.in.y * p.in.x * 32, 256, ctx);
-    out->fn = [=](cudaStream_t s) { softmax_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    const int64_t rows = (int64_t)p.in.b * p.in.y * p.in.x;
+    const bool by_row = p.in.f >= 256 && p.in.f <= 256 * kSoftmaxPerThread && rows <= (int64_t)ctx->prop.multiProcessorCount * 32;
+    const int row_grid = (int)(rows < 1 ? 1 : rows);
+    out->fn = [=](cudaStream_t s) {
+        if (by_row) softmax_row_kernel<<<row_grid, 256, 0, s>>>(p, in, o);
+        else softmax_kernel<<<grid, 256, 0, s>>>(p, in, o);
+        return cudaGetLastError();
+    };
     return CLDNN_B200_SUCCESS;
 }
 const KernelDef kdef_softmax = {"softmax", sizeof(cldnn_b200_softmax_params), softmax_supports, one_tune, nullptr, softmax_prepare};

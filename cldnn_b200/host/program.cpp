@@ -518,12 +518,13 @@ void network_impl::select_layouts()
             node* r = by_id.count(rid) ? by_id[rid] : add_node(reorder(rid, d->p.id, format::byxf_af32, data_types::none));
             replace_dep(n, d, r);
         }
+        // a reorder consumer reads any layout through pitches: it needs no conversion back in front of it
         bool back = n->is_output;
-        for (node* u : n->users) back |= chosen.count(u) == 0;
+        for (node* u : n->users) back |= chosen.count(u) == 0 && u->p.type != "reorder";
         if (back) {
             const int32_t user_fmt = n->out.fmt == format::byxf_af32 ? (int32_t)format::bfyx : n->out.fmt;
             node* r = add_node(reorder(n->p.id + "_from_byxf_af32", n->p.id, user_fmt, data_types::none));
-            for (node* u : std::vector<node*>(n->users)) if (!chosen.count(u)) replace_dep(u, n, r);
+            for (node* u : std::vector<node*>(n->users)) if (!chosen.count(u) && u->p.type != "reorder") replace_dep(u, n, r);
             if (n->is_output) { r->is_output = true; r->answers_for = n->answers_for.empty() ? n->p.id : n->answers_for; n->is_output = false; }
         }
     }
@@ -627,7 +628,9 @@ void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidat
                 cldnn_b200_prepared pr = nullptr;
                 if (cldnn_b200_prepare(k, params, psize, &args, &pr) != CLDNN_B200_SUCCESS) continue;
                 uint64_t ns = 0;
-                const int32_t st = cldnn_b200_time(pr, 2, 3, &ns);   // 3 timed runs, like kernel_runner (src/gpu/kernel_runner.h:37-38)
+                // kernel_runner times 3 runs (src/gpu/kernel_runner.h:37-38); launches here last tens of microseconds, so more
+                // runs are averaged to keep the choice stable
+                const int32_t st = cldnn_b200_time(pr, 3, 12, &ns);
                 cldnn_b200_prepared_destroy(pr);
                 if (st == CLDNN_B200_SUCCESS && ns < best_ns) { best_ns = ns; best_k = cand; best_t = t; }
             }
