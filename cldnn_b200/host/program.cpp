@@ -305,7 +305,7 @@ public:
     void prepare_kernel(node* n);
     void pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t params_size,
                      const cldnn_b200_args& args, const std::function<void(int)>& set_tune);
-    memory pack_conv_weights(node* n, int32_t stored_ifm);
+    memory pack_conv_weights(node* n, int32_t stored_ifm, int32_t groups = 1);
     void load_cache(); void save_cache();
     void execute();
     void run_prepared(node* n) { if (n->prepared) check(cldnn_b200_run(n->prepared), "run " + n->p.id); }
@@ -482,12 +482,12 @@ void network_impl::select_layouts()
         if (n->deps.empty()) return false;
         // fp16 convolutions run on the tensor cores from the same feature-innermost padded layout
         if (n->deps[0]->out.data_type == data_types::f16)
-            return (t == "convolution" || t == "fused_conv_eltwise") && n->p.groups == 1 && n->weights && n->weights->out.data_type == data_types::f16 && !n->wq;
+            return (t == "convolution" || t == "fused_conv_eltwise") && n->p.groups >= 1 && n->p.groups <= 4 && n->weights && n->weights->out.data_type == data_types::f16 && !n->wq;
         if (!is_int8(n->deps[0]->out.data_type)) return false;
         // dense convolutions go to the tensor cores, depthwise ones (one feature per group) to the byxf depthwise kernel
-        if (t == "convolution" && n->p.groups > 1) return n->wq != nullptr && n->weights && n->weights->out.size.feature == 1 && n->p.groups == n->deps[0]->out.size.feature &&
+        if (t == "convolution" && n->p.groups > 4) return n->wq != nullptr && n->weights && n->weights->out.size.feature == 1 && n->p.groups == n->deps[0]->out.size.feature &&
                                                           n->weights->out.size.batch == n->p.groups && n->p.groups % 4 == 0;
-        if (t == "convolution" || t == "fused_conv_eltwise") return n->p.groups == 1 && n->wq != nullptr;
+        if (t == "convolution" || t == "fused_conv_eltwise") return n->p.groups >= 1 && n->p.groups <= 4 && n->wq != nullptr;
         if (t == "fully_connected") return n->wq && n->bias && n->bias->out.data_type == data_types::f32 && n->deps[0]->out.size.x == 1 && n->deps[0]->out.size.y == 1;
         return false;
     };
@@ -653,15 +653,29 @@ void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidat
 // post_optimize_weights (src/graph_optimizer/post_optimize_weights.cpp:36-64) + generic_layer: the chosen kernel's
 // weights layout (oyxi, input features padded to the activation's stored count) is produced once, at build time, by the
 // reorder kernel.
-memory network_impl::pack_conv_weights(node* n, int32_t stored_ifm)
+memory network_impl::pack_conv_weights(node* n, int32_t stored_ifm, int32_t groups)
 {
     const layout& w = n->weights->out;                            // [o = batch][i = feature][y][x], caller's format (bfyx)
     layout packed(w.data_type, format::byxf, tensor(w.size.batch, stored_ifm, w.size.x, w.size.y));
     memory m; m.impl = std::make_shared<memory_impl>(); m.impl->l = packed; m.impl->blk = new_block(eng, packed.bytes_count());
-    cldnn_b200_reorder_params rp{};
-    rp.in = w.desc(); rp.out = packed.desc();
     cldnn_b200_args a{}; a.input0 = n->weights->mem.device_ptr(); a.output = m.device_ptr();
-    check(cldnn_b200_launch(eng->kernel("reorder_ref"), &rp, sizeof(rp), &a), n->p.id + ": weights pre-packing");
+    if (groups <= 1) {
+        cldnn_b200_reorder_params rp{};
+        rp.in = w.desc(); rp.out = packed.desc();
+        check(cldnn_b200_launch(eng->kernel("reorder_ref"), &rp, sizeof(rp), &a), n->p.id + ": weights pre-packing");
+        return m;
+    }
+    // grouped convolution as a dense one: block-diagonal weights over all input features, zeros off the diagonal
+    // (the tensor cores multiply the zeros, which for a few groups costs less than leaving the tensor-core kernel)
+    check(cldnn_b200_mem_fill(m.impl->blk->mem, 0), n->p.id + ": weights pre-packing (zero fill)");
+    const int32_t ofm = w.size.batch / groups, ifm = w.size.feature;
+    for (int32_t g = 0; g < groups; ++g) {
+        cldnn_b200_reorder_params rp{};
+        rp.in = w.desc(); rp.out = packed.desc();
+        rp.in.b = ofm; rp.in.offset += (int64_t)g * ofm * rp.in.pb;
+        rp.out.b = ofm; rp.out.f = ifm; rp.out.offset += (int64_t)g * ofm * rp.out.pb + (int64_t)g * ifm * rp.out.pf;
+        check(cldnn_b200_launch(eng->kernel("reorder_ref"), &rp, sizeof(rp), &a), n->p.id + ": weights pre-packing (group)");
+    }
     return m;
 }
 
@@ -753,11 +767,14 @@ void network_impl::prepare_kernel(node* n)
         }
         // tensor-core kernel: needs byxf activations and oyxi weights padded like the activations
         const bool half_tc = in.data_type == data_types::f16 && w.data_type == data_types::f16 && n->out.data_type == data_types::f16 && !fc;
-        const bool try_tc = ((is_int8(in.data_type) && w.data_type == data_types::i8) || half_tc) && cp.groups == 1 && cp.in.pf == 1 && cp.in.px % 32 == 0 && cp.out.pf == 1;
+        // a convolution in 2..4 groups runs as a dense one on block-diagonal weights (AlexNet's split layers)
+        const bool dense_groups = cp.groups >= 2 && cp.groups <= 4 && !fc;
+        const bool try_tc = ((is_int8(in.data_type) && w.data_type == data_types::i8) || half_tc) && (cp.groups == 1 || dense_groups) && cp.in.pf == 1 && cp.in.px % 32 == 0 && cp.out.pf == 1;
         const char* tc_kernel = half_tc ? "conv_f16_tc" : "conv_i8_tc";
         if (try_tc) {
             cldnn_b200_conv_params tp = cp;
-            n->packed_weights = pack_conv_weights(n, (int32_t)cp.in.px);
+            if (dense_groups) { tp.ofm = cp.ofm * cp.groups; tp.ifm = cp.ifm * cp.groups; tp.groups = 1; }
+            n->packed_weights = pack_conv_weights(n, (int32_t)cp.in.px, dense_groups ? cp.groups : 1);
             const cldnn_b200_tensor pd = n->packed_weights.get_layout().desc();
             tp.w_po = pd.pb; tp.w_pi = 1; tp.w_py = pd.py; tp.w_px = pd.px; tp.w_offset = 0;
             cldnn_b200_args ta = a; ta.weights = n->packed_weights.device_ptr();

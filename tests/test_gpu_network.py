@@ -199,3 +199,35 @@ def test_small_mobilenet_v2_int8_network_bit_exact(eng, optimize):
         assert all(r["kernel"] in ("conv_i8_tc", "conv_i8_first", "conv_i8_dw") for r in convs), [(r["id"], r["kernel"]) for r in convs]
         assert not any(r["type"] == "activation" for r in info if r["kernel"])          # every ReLU6 was folded
         assert len(np.unique(got["fc"])) > 8
+
+
+def test_grouped_convolutions_run_dense_on_block_diagonal_weights(eng):
+    """AlexNet-style split layers (2 groups, 48 / 96 input features per group) through the host layer: the optimising build
+    packs the group filters block-diagonally and runs the dense tensor-core kernel; bit-exact against the grouped oracle."""
+    rng = np.random.default_rng(12)
+    s = topologies.Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.u8, cl.format.bfyx, cl.tensor(3, 96, 13, 13))
+    s.add(cl.input_layout("input", s.input_layout))
+    def conv(name, x, cin, cout, k, groups, out_dt, scale=2.0):
+        s.const(name + "_w", rng.integers(-127, 128, size=(cout, cin // groups, k, k), dtype=np.int64).astype(np.int8))
+        s.const(name + "_b", rng.integers(-4096, 4097, size=cout, dtype=np.int64).astype(np.int32))
+        s.const(name + "_q", (rng.uniform(1.0, 3.0, size=cout) / (np.sqrt(cin // groups * k * k) * 73.0 * scale)).astype(np.float32))
+        s.add(cl.convolution(name, x, name + "_w", name + "_b", name + "_q", output_data_type=out_dt, input_offset=(-(k // 2), -(k // 2)),
+                             groups=groups, with_activation=True))
+        return name
+    x = conv("c2", "input", 96, 256, 5, 2, dt.u8, scale=3.0)
+    x = conv("c3", x, 256, 384, 3, 1, dt.u8)
+    x = conv("c4", x, 384, 384, 3, 2, dt.u8)
+    x = conv("c5", x, 384, 256, 3, 4, dt.i8)
+    s.outputs = [x]
+    xin = _input(s)
+    want = oracle_net.run(s, {s.input_id: xin})
+    for optimize in (False, True):
+        net, got = _run(eng, s, xin, optimize_data=optimize)
+        _compare(s, want, got)
+        convs = [r for r in net.primitives_info() if r["type"] == "convolution"]
+        if optimize:
+            assert all(r["kernel"] == "conv_i8_tc" for r in convs), [(r["id"], r["kernel"]) for r in convs]
+    assert len(np.unique(want["c5"])) > 8
