@@ -1,0 +1,101 @@
+"""The bandwidth-bound tail kernels (pooling, fully_connected, softmax) through the C ABI against the CPU oracle and the
+reference's known-answer vectors.  8-bit results are bit-exact; softmax is compared within 1e-5 relative (the device's
+expf and the summation order differ from the host's in the last bits)."""
+import numpy as np
+import pytest
+
+import oracle_lib
+from cldnn_b200 import abi
+from golden import kat_tail_int8
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from cldnn_b200 import engine
+    e = engine.Engine(0)
+    yield e
+    e.close()
+
+
+def _run(eng, kernel, params, out_elems, out_dtype, **bufs):
+    from cldnn_b200 import engine as E
+    mems = {k: eng.upload(v) for k, v in bufs.items() if v is not None}
+    out = eng.alloc(out_elems * np.dtype(out_dtype).itemsize)
+    k = eng.kernel(kernel)
+    assert k.supports(params), kernel
+    k.launch(params, E.make_args(output=out, **mems))
+    eng.sync()
+    res = out.read(np.dtype(out_dtype), out_elems)
+    assert eng.device_status() == 0
+    for m in list(mems.values()) + [out]:
+        m.free()
+    return res
+
+
+def _pool_params(dtype, N, C, H, W, size, stride, pad, mode, div=abi.DIV_FIXED, act=abi.ACT_NONE, out_dtype=None, fmt="byxf", f_align=32):
+    P = (H + 2 * pad - size) // stride + 1
+    Q = (W + 2 * pad - size) // stride + 1
+    pp = abi.PoolParams()
+    pp.in_, n_in = abi.tensor(abi.dtype_of(np.dtype(dtype)), N, C, H, W, fmt, f_align)
+    pp.out, n_out = abi.tensor(abi.dtype_of(np.dtype(out_dtype or dtype)), N, C, P, Q, fmt, f_align)
+    pp.size_x = pp.size_y = size
+    pp.stride_x = pp.stride_y = stride
+    pp.pad_x = pp.pad_y = pad
+    pp.mode, pp.div_mode, pp.act = mode, div, act
+    return pp, n_in, n_out
+
+
+POOLS = {
+    "resnet_pool1_max3x3s2_u8": dict(dtype=np.uint8, N=2, C=64, H=33, W=35, size=3, stride=2, pad=0, mode=abi.POOL_MAX),
+    "max3x3s2_pad1_s8": dict(dtype=np.int8, N=2, C=32, H=14, W=15, size=3, stride=2, pad=1, mode=abi.POOL_MAX),
+    "max2x2s2_s8_relu": dict(dtype=np.int8, N=1, C=48, H=8, W=8, size=2, stride=2, pad=0, mode=abi.POOL_MAX, act=abi.ACT_RELU),
+    "global_avg_7x7_u8_to_s8": dict(dtype=np.uint8, N=3, C=64, H=7, W=7, size=7, stride=1, pad=0, mode=abi.POOL_AVG, out_dtype=np.int8),
+    "avg3x3s1_pad1_s8_dynamic": dict(dtype=np.int8, N=1, C=16, H=6, W=7, size=3, stride=1, pad=1, mode=abi.POOL_AVG, div=abi.DIV_DYNAMIC),
+}
+
+
+@pytest.mark.parametrize("name", sorted(POOLS))
+@pytest.mark.parametrize("kernel", ["pooling_i8_byxf", "pooling_ref"])
+def test_pooling_int8_matches_oracle(eng, name, kernel):
+    pp, n_in, n_out = _pool_params(**POOLS[name])
+    dt = np.dtype(POOLS[name]["dtype"])
+    rng = np.random.default_rng(61)
+    x = rng.integers(np.iinfo(dt).min, np.iinfo(dt).max + 1, size=n_in, dtype=np.int64).astype(dt)
+    odt = abi.np_dtype_of(pp.out.dtype)
+    want = oracle_lib.pooling(pp, x)
+    got = _run(eng, kernel, pp, n_out, odt, input0=x)
+    assert np.array_equal(want[:n_out], got), "%d differ" % int((want[:n_out] != got).sum())
+    assert len(np.unique(got)) > 8
+
+
+def test_pooling_and_fc_reference_kats_on_gpu(eng):
+    k = kat_tail_int8.POOL_MAX_INT8
+    x = np.trunc(np.array(k["input_f32"], dtype=np.float32)).astype(np.int8)
+    pp, n_in, n_out = _pool_params(np.int8, 1, 1, 3, 3, 3, 1, 0, abi.POOL_MAX, fmt="bfyx", f_align=1)
+    assert _run(eng, "pooling_ref", pp, 1, np.int8, input0=x).astype(np.float32).tolist() == k["expected_f32"]
+    k = kat_tail_int8.FC_NO_BIAS_INT8
+    x = np.trunc(np.array(k["input_f32"], dtype=np.float32)).astype(np.int8)
+    w = np.array(k["weights_i8"], dtype=np.int8).reshape(-1)
+    fp = abi.FcParams()
+    fp.in_, _ = abi.tensor(abi.I8, 1, 1, 1, 3, "bfyx")
+    fp.out, _ = abi.tensor(abi.I8, 1, 4, 1, 1, "bfyx")
+    fp.w_dtype = abi.I8
+    fp.w_px, fp.w_py, fp.w_pi, fp.w_po = 1, 3, 3, 3
+    fp.bias_dtype = abi.NONE
+    fp.i_qf = fp.o_qf = 1.0
+    assert _run(eng, "fc_ref", fp, 4, np.int8, input0=x, weights=w).astype(np.float32).tolist() == k["expected_f32"]
+
+
+@pytest.mark.parametrize("features", [40, 1000, 2048])
+def test_softmax_matches_oracle(eng, features):
+    """40 features: one warp per row; 1000 / 2048: one block per row."""
+    sp = abi.SoftmaxParams()
+    sp.in_, n = abi.tensor(abi.F32, 5, features, 1, 1, "bfyx")
+    sp.out, _ = abi.tensor(abi.F32, 5, features, 1, 1, "bfyx")
+    x = (np.random.default_rng(62).standard_normal(n) * 4.0).astype(np.float32)
+    want = oracle_lib.softmax(sp, x)
+    got = _run(eng, "softmax", sp, n, np.float32, input0=x)
+    np.testing.assert_allclose(got, want[:n], rtol=1e-5, atol=1e-9)
+    np.testing.assert_allclose(got.reshape(5, features).sum(1), 1.0, rtol=1e-5)

@@ -91,3 +91,54 @@ def test_fused_conv_eltwise_kat(name):
         np.testing.assert_array_equal(got.astype(np.int64), _clamp_expected(pre, out_dt).astype(np.int64))
     else:
         np.testing.assert_allclose(got, _clamp_expected(pre, out_dt), atol=1e-3)
+
+
+# ---- int8 pooling and fully_connected KATs (through the oracle's reorder, like the reference's topologies) -------------
+from golden import kat_tail_int8
+
+
+def _reorder(arr, out_dtype, fmt_in="bfyx", fmt_out="bfyx"):
+    b, f, y, x = arr.shape
+    rp = abi.ReorderParams()
+    rp.in_, _ = abi.tensor(abi.dtype_of(arr.dtype), b, f, y, x, fmt_in)
+    rp.out, _ = abi.tensor(abi.dtype_of(np.dtype(out_dtype)), b, f, y, x, fmt_out)
+    return oracle_lib.reorder(rp, np.ascontiguousarray(arr).reshape(-1)).reshape(arr.shape)
+
+
+def _pool_3x3(x_i8, mode):
+    pp = abi.PoolParams()
+    pp.in_, _ = abi.tensor(abi.I8, 1, 1, 3, 3, "bfyx")
+    pp.out, _ = abi.tensor(abi.I8, 1, 1, 1, 1, "bfyx")
+    pp.size_x = pp.size_y = 3
+    pp.stride_x = pp.stride_y = 1
+    pp.mode, pp.div_mode = mode, abi.DIV_FIXED
+    return oracle_lib.pooling(pp, x_i8.reshape(-1)).reshape(1, 1, 1, 1)
+
+
+def test_pooling_int8_kats():
+    k = kat_tail_int8.POOL_MAX_INT8
+    x = _reorder(np.array(k["input_f32"], dtype=np.float32).reshape(1, 1, 3, 3), np.int8, fmt_in="byxf")
+    got = _reorder(_pool_3x3(x, abi.POOL_MAX), np.float32)
+    assert got.reshape(-1).tolist() == k["expected_f32"]
+    k = kat_tail_int8.POOL_AVG_INT8
+    vals = np.array(k["input_f32"], dtype=np.float32)
+    expected = float(np.int8(np.trunc(np.trunc(vals).astype(np.int8).astype(np.float32).sum() / vals.size)))
+    x = _reorder(vals.reshape(1, 1, 3, 3), np.int8, fmt_in="byxf")
+    got = _reorder(_pool_3x3(x, abi.POOL_AVG), np.float32)
+    assert got.reshape(-1).tolist() == [expected]
+
+
+def test_fully_connected_int8_kat():
+    k = kat_tail_int8.FC_NO_BIAS_INT8
+    x = _reorder(np.array(k["input_f32"], dtype=np.float32).reshape(1, 1, 1, 3), np.int8)
+    w = np.array(k["weights_i8"], dtype=np.int8)
+    fp = abi.FcParams()
+    fp.in_, _ = abi.tensor(abi.I8, 1, 1, 1, 3, "bfyx")
+    fp.out, _ = abi.tensor(abi.I8, 1, 4, 1, 1, "bfyx")
+    fp.w_dtype = abi.I8
+    fp.w_px, fp.w_py, fp.w_pi, fp.w_po = 1, 3, 3, 3
+    fp.bias_dtype = abi.NONE
+    fp.i_qf = fp.o_qf = 1.0
+    out, oor = oracle_lib.fc(fp, x.reshape(-1), w.reshape(-1))
+    got = _reorder(out.reshape(1, 4, 1, 1), np.float32)
+    assert got.reshape(-1).tolist() == k["expected_f32"]
