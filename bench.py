@@ -341,7 +341,7 @@ def main():
                        "l2": "each step reads a different one of %d resident batches (%.0f MB total > 126 MB L2); activations per step exceed L2" % (n_resident, n_resident * B * 3 * 224 * 224 / 1e6),
                        "ops_per_image": total_ops},
             "clocks": clocks,
-            "e2e": {"value": images / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": B * 3 * 224 * 224, "d2h_bytes_per_step": B * 1000 * 4,
+            "e2e": {"value": images / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": B * 3 * 224 * 224 * world, "d2h_bytes_per_step": B * 1000 * 4 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches_per_step) * args.steps}
     if rank == 0:

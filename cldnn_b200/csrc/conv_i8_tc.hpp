@@ -44,6 +44,7 @@ struct alignas(64) TcParams {
     int32_t mul_iqf, mul_oqf;
     int32_t lean;                        // epilogue configuration covered by the hoisted fast body
     int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
+    int32_t nstg;                        // conv_i8_tc_fast: staging tiles (>= nbuf when a fused residual is prefetched into them)
     // patch mode: all weights resident in shared memory, one activation patch per (filter column, channel chunk)
     int32_t ring_bytes, b_total_bytes;   // operand area: activation ring (+ weight ring or resident weights)
     int32_t patch_alloc;                 // bytes reserved per filter column's patch inside a stage (a stage holds the kw patches of one channel chunk)

@@ -37,15 +37,16 @@ namespace b200 {
 constexpr int kFastThreads = 384;          // warp 0 operand loads, 1 MMA issue, 2 TMA stores, 3 residual loads, 4..11 epilogue
 constexpr int kFastEpiWarp0 = 4;
 constexpr int kGroups = 2;                 // epilogue warp groups, alternate tiles
+constexpr int kMaxStg = 8;                 // staging tiles
 
 struct FastAux {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[kMaxBufs];
     uint64_t tmem_empty[kMaxBufs];
-    uint64_t res_full[kMaxBufs];
-    uint64_t stage_free[kMaxBufs];
-    uint64_t out_ready[kMaxBufs];
+    uint64_t res_full[kMaxStg];
+    uint64_t stage_free[kMaxStg];
+    uint64_t out_ready[kMaxStg];
     uint64_t drain;
     uint64_t b_full;                       // patch mode: the resident weights have landed
     uint32_t tmem_base;
@@ -203,6 +204,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     constexpr int CW = BN < 128 ? BN : 128;
     constexpr int COLB = BN / CW;
     constexpr uint32_t kStagingBytes = (uint32_t)(kBM * BN);
+    // staging tiles: with a fused residual they also receive the residual tile, whose load has HBM latency in front of the
+    // epilogue; more of them than accumulators (the host decides how many fit) lets those loads run further ahead
+    const int NSTG = P.nstg;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -212,7 +216,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     const uint32_t b_base = base + (uint32_t)(P.stages * P.a_stage_bytes);
     const uint32_t ring_bytes = (uint32_t)P.ring_bytes;
     uint8_t* staging = smem + ring_bytes;
-    FastAux* aux = reinterpret_cast<FastAux*>(smem + ring_bytes + (uint32_t)NBUF * kStagingBytes);
+    FastAux* aux = reinterpret_cast<FastAux*>(smem + ring_bytes + (uint32_t)NSTG * kStagingBytes);
     volatile uint32_t* s_abort = &aux->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -222,8 +226,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
-        for (int a = 0; a < kMaxBufs; ++a) {
-            mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4);
+        for (int a = 0; a < kMaxBufs; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4); }
+        for (int a = 0; a < kMaxStg; ++a) {
             mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
             mbar_init(smem_u32(&aux->out_ready[a]), 4);
         }
@@ -385,9 +389,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;            // the output of an im2col tile is addressed by its first pixel index
             for (; walk.valid(); walk.next(), ++t) {
                 const int n_tile = walk.n_tile, m_tile = walk.m_tile;
-                const int a = t % NBUF;
+                const int a = t % NSTG;
                 prof.start();
-                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NBUF) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
+                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
                 prof.stop(0);
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
                 const int tw = walk.d0, th = walk.d1, tb = walk.d2;
@@ -421,9 +425,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 const int n_tile = walk.n_tile, m_tile = walk.m_tile;
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
                 const int o_w = walk.d0 * P.bw, o_h = walk.d1 * P.bh, c_n = walk.d2 * P.bb;
-                const int a = t % NBUF;
+                const int a = t % NSTG;
                 prof.start();
-                if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
+                if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
                 prof.stop(1);
                 const uint32_t rf = smem_u32(&aux->res_full[a]);
                 mbar_expect_tx(rf, (uint32_t)(P.stage_rows * BN));
@@ -482,13 +486,14 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             prof.stop(0);
             prof.start();
             // the staging buffer is ours once its residual tile has landed (fused) or its previous store has been read out
-            const bool got = kFused ? mbar_wait(smem_u32(&aux->res_full[acc]), par, s_abort, P.status, kErrEpilogue + 1u)
-                                    : mbar_wait(smem_u32(&aux->stage_free[acc]), par ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
+            const int sb = t % NSTG; const uint32_t spar = (uint32_t)(t / NSTG) & 1u;
+            const bool got = kFused ? mbar_wait(smem_u32(&aux->res_full[sb]), spar, s_abort, P.status, kErrEpilogue + 1u)
+                                    : mbar_wait(smem_u32(&aux->stage_free[sb]), spar ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
             if (!got) { ok = false; break; }
             prof.stop(1);
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-            uint8_t* stg = staging + (size_t)acc * kStagingBytes;
+            uint8_t* stg = staging + (size_t)sb * kStagingBytes;
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
             if (TC_DEBUG(P, 1)) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(te); }
             else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
@@ -510,7 +515,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             }
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->out_ready[acc]));
+            if (lane == 0) mbar_arrive(smem_u32(&aux->out_ready[sb]));
         }
         if (ew == 0 && lane == 0) prof.flush(9, 3, (t - group) / kGroups);
     }
