@@ -143,6 +143,20 @@ inline EpiCfg make_epi_cfg(const cldnn_b200_conv_params& p)
     return e;
 }
 
+// A clamp that the unsigned saturating store performs anyway is dropped: with an 8-bit unsigned output, a uniform O_QF > 0,
+// a lower bound <= 0 and an upper bound n with n * O_QF >= 255, clamp(v) * O_QF, rounded and saturated, equals v * O_QF
+// rounded and saturated for every v (values above n land on 255 either way, values below 0 on 0).  ReLU6 in front of a
+// requantisation by 255 / 6 is the common case.  Not applicable in front of a fused residual sum.
+inline cldnn_b200_conv_params simplified_conv_params(const cldnn_b200_conv_params& p0)
+{
+    cldnn_b200_conv_params p = p0;
+    if (p.act == CLDNN_B200_ACT_CLAMP && !p.fused_eltw && p.out.dtype == CLDNN_B200_U8 && !p.calibration && p.has_o_qf && p.o_qf > 0.0f &&
+        p.act_m <= 0.0f && p.act_n * p.o_qf >= 255.0f) {
+        p.act = CLDNN_B200_ACT_NONE; p.act_m = 0.0f; p.act_n = 0.0f;
+    }
+    return p;
+}
+
 // Quantised epilogue in the reference's order
 // (cl_kernels/fused_conv_eltwise_gpu_ref.cl:148-232): i32 bias -> dequantise
 // ((float)acc * q[f]) * I_QF -> (+ f32 bias) -> activation -> * calib[f] | O_QF ->

@@ -48,11 +48,12 @@ __device__ __forceinline__ void epi_chunk_fast(const ParamsT& P, const AuxT* aux
     uint32_t ow[8];
     if (kLean) {
         // The common network configuration, with every uniform decision hoisted out of
-        // the unrolled body: per-channel quantisation only (I_QF = O_QF = 1, integer or
-        // no bias), activations NONE or ReLU, plain residual sum.  ~8 instructions per
+        // the unrolled body: per-channel quantisation, optionally a uniform O_QF (I_QF = 1,
+        // integer or no bias), activations NONE or ReLU, plain residual sum.  ~8 instructions per
         // feature; max(v, -inf) stands for "no activation".
         const float lo1 = c.act == CLDNN_B200_ACT_RELU ? 0.0f : __int_as_float(0xff800000);
         const float lo2 = c.eltw_act == CLDNN_B200_ACT_RELU ? 0.0f : __int_as_float(0xff800000);
+        const bool oq = P.mul_oqf != 0;                             // uniform O_QF (no per-feature calibration on this path)
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
             const int cj = c0 + 4 * g;
@@ -63,8 +64,9 @@ __device__ __forceinline__ void epi_chunk_fast(const ParamsT& P, const AuxT* aux
             int32_t o4[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
-                v = half_away_pre(fmaxf(v, lo1));
+                float v = fmaxf(__fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]), lo1);
+                if (oq) v = __fmul_rn(v, c.o_qf);
+                v = half_away_pre(v);
                 if (kFused) {
                     const float e = __fadd_rn(__uint_as_float(__byte_perm(ew[g], 0x4B000000u, 0x7450u + i)), -e_bias);
                     v = half_away_pre(fmaxf(__fadd_rn(truncf(v), e), lo2));
@@ -132,6 +134,29 @@ __device__ __forceinline__ uint32_t clamp_bytes_127(uint32_t w)
 constexpr float kMagic = 8388608.0f;             // 2^23: x + 2^23 toward zero leaves floor(x) in the mantissa for 0 <= x < 2^23
 constexpr int32_t kMagicBits = 0x4B000000;
 
+// Four features: s32 accumulators (+ integer bias) -> requantised bytes in one word, by the conversion-free steps of
+// fast_chunk32 below (same requirement |v| < 2^22, same kOut / kOqf meaning; no residual).
+template <int kOut, bool kOqf>
+__device__ __forceinline__ uint32_t fast_quad(const int32_t (&acc)[4], const int4 bias, const float4 quant, float oqf)
+{
+    const int32_t b4[4] = {bias.x, bias.y, bias.z, bias.w};
+    const float q4[4] = {quant.x, quant.y, quant.z, quant.w};
+    int32_t o4[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float v = __fmul_rn(__int2float_rn(acc[i] + b4[i]), q4[i]);
+        if (kOqf) v = __fmul_rn(v, oqf);
+        if (kOut != 1) o4[i] = __float_as_int(__fadd_rz(__fadd_rz(v, 0.5f), kMagic)) - kMagicBits;
+        else {
+            const int32_t wb = __float_as_int(__fadd_rz(__fadd_rz(fabsf(v), 0.5f), kMagic));
+            o4[i] = v < 0.0f ? kMagicBits - wb : wb - kMagicBits;
+        }
+    }
+    if (kOut == 1) return pack_sat_s8(o4[1], o4[0], pack_sat_s8(o4[3], o4[2], 0u));
+    const uint32_t w = pack_sat_u8(o4[1], o4[0], pack_sat_u8(o4[3], o4[2], 0u));
+    return kOut == 2 ? clamp_bytes_127(w) : w;
+}
+
 // 32 features of one pixel.  Requires |v| < 2^22 for every dequantised value v
 // (guaranteed per feature tile by the caller), which makes every step exact
 // without a float->int conversion instruction:
@@ -141,9 +166,10 @@ constexpr int32_t kMagicBits = 0x4B000000;
 // 2 = s8 output after a ReLU.  kRelu1: ReLU between the convolution and the residual sum.
 // e_xor / k_pos / k_neg: the residual word is made unsigned by e_xor (0 or 0x80808080),
 // k_pos = 2^23 bits (+128 for a signed residual), k_neg = 2^23 bits (-128 for a signed residual).
-template <bool kFused, bool kRelu1, int kOut>
+// kOqf: the dequantised value is multiplied by the uniform `oqf` (O_QF) before rounding.
+template <bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_chunk32(const uint32_t (&r)[32], const int32_t* bias, const float* quant,
-                                             uint4* p0, uint4* p1, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+                                             uint4* p0, uint4* p1, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f)
 {
     uint32_t ew[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if (kFused) {
@@ -161,7 +187,8 @@ __device__ __forceinline__ void fast_chunk32(const uint32_t (&r)[32], const int3
         int32_t o4[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
+            float v = __fmul_rn(__int2float_rn((int32_t)r[4 * g + i] + b4[i]), q4[i]);
+            if (kOqf) v = __fmul_rn(v, oqf);                           // (a ReLU in front of a positive O_QF commutes with it)
             int32_t o;
             if (!kFused && kOut != 1) {
                 // negative values end at 0 either way (unsigned saturation), so no sign handling

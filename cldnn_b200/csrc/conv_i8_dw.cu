@@ -1,15 +1,26 @@
 // conv_i8_dw: 8-bit depthwise convolution (groups == features, one filter per
 // feature), the MobileNet building block.  A depthwise filter has no reduction
-// over features, so there is nothing for the tensor cores: the kernel is
-// bandwidth-bound CUDA-core code over the feature-innermost (byxf) layout --
-// each thread owns 4 consecutive features of one output pixel, reads one 32-bit
-// word per filter tap (a warp reads 128 contiguous bytes), takes the filter
-// taps from a shared-memory copy laid out [tap][feature], accumulates in s32 and
-// runs the quantised epilogue of fused_conv_eltwise_gpu_ref.cl:148-194 (integer
-// bias, per-feature dequantisation, activation -- ReLU6 is CLAMP(0, 6) --
-// calibration / O_QF, round, saturate).  It stands where the reference uses
+// over features, so there is nothing for the tensor cores: the kernel is CUDA-core
+// code over the feature-innermost (byxf) layout, bounded by instruction issue
+// (one multiply-add per tap and output) and then by HBM.
+//
+// Main kernel (features a multiple of 16): a thread owns 16 consecutive features
+// of two horizontally adjacent output pixels.  Per filter tap it reads one 128-bit
+// word per pixel (a warp reads contiguous memory) and runs one dp4a per feature:
+// the filter tap of feature e is kept in shared memory as a word that holds the
+// weight in byte lane e % 4 and zeros elsewhere, so dp4a(input word, that word, acc)
+// is exactly acc += x[e] * w[e] -- one instruction instead of two byte extractions
+// and a multiply-add.  The weight words are loaded once per tap for both pixels.
+// Epilogue: the quantised epilogue of fused_conv_eltwise_gpu_ref.cl:148-194 (integer
+// bias, per-feature dequantisation, activation -- ReLU6 is CLAMP(0, 6) -- calibration /
+// O_QF, round, saturate); the common configuration (per-feature scale, optional
+// uniform O_QF, NONE / ReLU or a clamp the saturation subsumes) takes the
+// conversion-free form of conv_epilogue.cuh, exact while |value| < 2^22, which a
+// per-CTA scan of the constants checks.  A 4-features-per-thread kernel covers other
+// feature counts.  It stands where the reference uses
 // cl_kernels/convolution_gpu_byxf_af32_depthwise.cl.
 #include "engine.hpp"
+#include "conv_epilogue.cuh"
 
 namespace b200 {
 
@@ -67,6 +78,126 @@ conv_i8_dw_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid
     }
 }
 
+// ---- 16 features x 2 pixels per thread ------------------------------------------------
+struct Dw16Args {
+    const uint8_t* in; const void* bias; const float* quant; const float* calib; uint8_t* out;
+    const uint32_t* wmask;          // [tap][feature]: the weight in byte lane (feature % 4) of a zero word
+    int32_t q2, c16n, lean, mul_oqf; // pixel pairs per row, 16-feature groups, conversion-free epilogue allowed, uniform O_QF present
+    float acc_bound;                // taps * max|activation| * 128
+    uint32_t items;
+};
+
+__global__ void dw_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t py, int64_t px, int64_t off, int C, int kh, int kw, uint32_t* __restrict__ dst)
+{
+    const int total = kh * kw * C;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int f = i % C, t = i / C; const int j = t / kw, s = t - j * kw;
+        dst[i] = ((uint32_t)(uint8_t)w[off + (int64_t)f * po + j * py + s * px]) << (8 * (f & 3));
+    }
+}
+
+template <bool kUnsignedIn>
+__device__ __forceinline__ int32_t dp4a_in(uint32_t x, uint32_t w, int32_t c)
+{
+    int32_t d;
+    if (kUnsignedIn) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(c));
+    else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(c));
+    return d;
+}
+
+template <bool kUnsignedIn>
+__global__ void __launch_bounds__(256)
+conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid_constant__ EpiCfg c, const __grid_constant__ Dw16Args a)
+{
+    extern __shared__ uint4 s_dw[];
+    const int C = p.out.f, taps = p.kh * p.kw;
+    uint4* s_w = s_dw;                                               // [tap][C / 4] groups of 4 masked weight words
+    int32_t* s_bias = reinterpret_cast<int32_t*>(s_dw + taps * (C / 4));
+    float* s_quant = reinterpret_cast<float*>(s_bias + C);
+    __shared__ uint32_t s_wide;
+    if (threadIdx.x == 0) s_wide = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < taps * (C / 4); i += blockDim.x) s_w[i] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
+    bool wide = false;
+    for (int f = threadIdx.x; f < C; f += blockDim.x) {
+        const int32_t bi = (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? load_as_int(a.bias, p.bias_dtype, f) : 0;
+        const float q = p.quantization ? a.quant[f] : 1.0f;
+        s_bias[f] = bi; s_quant[f] = q;
+        wide = wide || !(__fmul_rn(__fmul_rn(__fadd_rn(a.acc_bound, fabsf((float)bi)), fabsf(q)), a.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f);
+    }
+    if (wide) atomicOr(&s_wide, 1u);
+    __syncthreads();
+    // 0..2: conversion-free u8 / s8 / s8 after ReLU, 3: general
+    const int mode = (a.lean && !s_wide) ? (p.out.dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
+    const int c4n = C / 4;
+
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < a.items; idx += gridDim.x * blockDim.x) {
+        const uint32_t g = idx % (uint32_t)a.c16n; uint32_t t = idx / (uint32_t)a.c16n;
+        const uint32_t xq = t % (uint32_t)a.q2; t /= (uint32_t)a.q2;
+        const uint32_t y = t % (uint32_t)p.out.y; const uint32_t b = t / (uint32_t)p.out.y;
+        const int f0 = (int)g * 16, x0 = (int)xq * 2;
+        const bool second = x0 + 1 < p.out.x;
+        const int iy0 = (int)y * p.stride_y - p.pad_y, ix0 = x0 * p.stride_x - p.pad_x, ix1 = ix0 + p.stride_x;
+        int32_t acc0[16], acc1[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) { acc0[e] = 0; acc1[e] = 0; }
+        const uint8_t* src = a.in + p.in.offset + (int64_t)b * p.in.pb + f0;
+        for (int j = 0; j < p.kh; ++j) {
+            const int iy = iy0 + j * p.dil_y; if (iy < 0 || iy >= p.in.y) continue;
+            const uint8_t* rowp = src + (int64_t)iy * p.in.py;
+            for (int s = 0; s < p.kw; ++s) {
+                const int xa = ix0 + s * p.dil_x, xb = ix1 + s * p.dil_x;
+                const bool va = xa >= 0 && xa < p.in.x, vb = second && xb >= 0 && xb < p.in.x;
+                if (!va && !vb) continue;
+                uint4 x_a = make_uint4(0, 0, 0, 0), x_b = make_uint4(0, 0, 0, 0);
+                if (va) x_a = __ldg(reinterpret_cast<const uint4*>(rowp + (int64_t)xa * p.in.px));
+                if (vb) x_b = __ldg(reinterpret_cast<const uint4*>(rowp + (int64_t)xb * p.in.px));
+                const uint32_t xw_a[4] = {x_a.x, x_a.y, x_a.z, x_a.w}, xw_b[4] = {x_b.x, x_b.y, x_b.z, x_b.w};
+                const uint4* wt = s_w + (j * p.kw + s) * c4n + g * 4;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {                          // 4 words of 4 features
+                    const uint4 wm = wt[k];
+                    acc0[4 * k + 0] = dp4a_in<kUnsignedIn>(xw_a[k], wm.x, acc0[4 * k + 0]); acc1[4 * k + 0] = dp4a_in<kUnsignedIn>(xw_b[k], wm.x, acc1[4 * k + 0]);
+                    acc0[4 * k + 1] = dp4a_in<kUnsignedIn>(xw_a[k], wm.y, acc0[4 * k + 1]); acc1[4 * k + 1] = dp4a_in<kUnsignedIn>(xw_b[k], wm.y, acc1[4 * k + 1]);
+                    acc0[4 * k + 2] = dp4a_in<kUnsignedIn>(xw_a[k], wm.z, acc0[4 * k + 2]); acc1[4 * k + 2] = dp4a_in<kUnsignedIn>(xw_b[k], wm.z, acc1[4 * k + 2]);
+                    acc0[4 * k + 3] = dp4a_in<kUnsignedIn>(xw_a[k], wm.w, acc0[4 * k + 3]); acc1[4 * k + 3] = dp4a_in<kUnsignedIn>(xw_b[k], wm.w, acc1[4 * k + 3]);
+                }
+            }
+        }
+        uint8_t* dst = a.out + p.out.offset + (int64_t)b * p.out.pb + (int64_t)y * p.out.py + (int64_t)x0 * p.out.px + f0;
+#pragma unroll
+        for (int px = 0; px < 2; ++px) {
+            if (px == 1 && !second) break;
+            const int32_t (&acc)[16] = px ? acc1 : acc0;
+            uint32_t ow[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int32_t a4[4] = {acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]};
+                const int4 b4 = *reinterpret_cast<const int4*>(s_bias + f0 + 4 * k);
+                const float4 q4 = *reinterpret_cast<const float4*>(s_quant + f0 + 4 * k);
+                if (mode == 0) ow[k] = a.mul_oqf ? fast_quad<0, true>(a4, b4, q4, c.o_qf) : fast_quad<0, false>(a4, b4, q4, 1.0f);
+                else if (mode == 1) ow[k] = a.mul_oqf ? fast_quad<1, true>(a4, b4, q4, c.o_qf) : fast_quad<1, false>(a4, b4, q4, 1.0f);
+                else if (mode == 2) ow[k] = fast_quad<2, false>(a4, b4, q4, 1.0f);
+                else {
+                    uint32_t word = 0;
+                    const int32_t bb[4] = {b4.x, b4.y, b4.z, b4.w}; const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int f = f0 + 4 * k + e;
+                        const float v = epi_quant(c, a4[e] + bb[e], qq[e], c.dont_dequantize_bias ? ((const float*)a.bias)[f] : 0.f,
+                                                  p.calibration ? a.calib[f] : 1.f, 0.f, 1.f);
+                        const int32_t r = __float2int_rz(v);
+                        const int32_t sat = p.out.dtype == CLDNN_B200_U8 ? min(255, max(0, r)) : min(127, max(-128, r));
+                        word |= ((uint32_t)sat & 0xffu) << (8 * e);
+                    }
+                    ow[k] = word;
+                }
+            }
+            *reinterpret_cast<uint4*>(dst + (int64_t)px * p.out.px) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    }
+}
+
 bool dw_plan(const cldnn_b200_conv_params& p, std::string* why)
 {
     auto no = [&](const char* m) { if (why) *why = m; return false; };
@@ -88,9 +219,25 @@ bool dw_plan(const cldnn_b200_conv_params& p, std::string* why)
 bool dw_supports(const void* vp) { return dw_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
 int dw_tune_count(const void*) { return 1; }
 
+// the 16-feature kernel: 16-byte aligned rows of features, its weight words and constants within shared memory
+bool dw16_ok(const cldnn_b200_conv_params& p)
+{
+    if (p.groups % 16) return false;
+    const int64_t al[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
+    for (int64_t v : al) if (v % 16) return false;
+    if ((int64_t)p.kh * p.kw * p.groups * 4 + (int64_t)p.groups * 8 > 96 * 1024) return false;
+    const int64_t items = (int64_t)p.out.b * p.out.y * ((p.out.x + 1) / 2) * (p.groups / 16);
+    return items > 0 && items < 0x7fffffffLL;
+}
+size_t dw_scratch(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_conv_params*)vp;
+    return dw16_ok(p) ? (size_t)p.kh * p.kw * p.groups * 4 : 0;
+}
+
 int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
-    const cldnn_b200_conv_params p = *(const cldnn_b200_conv_params*)vp;
+    const cldnn_b200_conv_params p = simplified_conv_params(*(const cldnn_b200_conv_params*)vp);
     std::string why;
     if (!dw_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_dw: " + why);
     if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_dw: input, output and weights are required");
@@ -99,6 +246,38 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
     if (p.calibration && !a->output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_dw: calibration set but no factors");
     if (((uintptr_t)a->input0 | (uintptr_t)a->output) & 3) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_dw: buffers must be 4-byte aligned");
     const EpiCfg c = make_epi_cfg(p);
+    const bool uns_in = p.in.dtype == CLDNN_B200_U8;
+    if (dw16_ok(p) && a->scratch && a->scratch_bytes >= dw_scratch(&p) && !(((uintptr_t)a->input0 | (uintptr_t)a->output | (uintptr_t)a->scratch) & 15)) {
+        Dw16Args d{};
+        d.in = (const uint8_t*)a->input0; d.bias = a->bias; d.quant = a->weights_quantization_factors; d.calib = a->output_calibration_factors;
+        d.out = (uint8_t*)a->output; d.wmask = (const uint32_t*)a->scratch;
+        d.q2 = (p.out.x + 1) / 2; d.c16n = p.groups / 16;
+        d.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
+        const bool oqf_ok = !d.mul_oqf || (!p.calibration && p.o_qf > 0.0f && (p.out.dtype == CLDNN_B200_U8 || p.act != CLDNN_B200_ACT_RELU));
+        d.lean = (p.quantization && p.i_qf == 1.0f && oqf_ok && !c.dont_dequantize_bias && (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU) &&
+                  (p.bias_dtype == CLDNN_B200_NONE || p.bias_dtype == CLDNN_B200_I32)) ? 1 : 0;
+        d.acc_bound = (float)(p.kh * p.kw) * (uns_in ? 255.0f : 128.0f) * 128.0f;
+        d.items = (uint32_t)((int64_t)p.out.b * p.out.y * d.q2 * d.c16n);
+        // the weight words once, on the context's stream, before anything that is prepared here can run
+        const int taps_c = p.kh * p.kw * p.groups;
+        dw_pack_weights<<<(taps_c + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_py, p.w_px, p.w_offset, p.groups, p.kh, p.kw, (uint32_t*)a->scratch);
+        B200_CUDA(cudaGetLastError());
+        const size_t smem = (size_t)taps_c * 4 + (size_t)p.groups * 8;
+        if (smem > 48 * 1024) {
+            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        }
+        int64_t blocks = ((int64_t)d.items + 255) / 256; const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 8;
+        if (blocks > cap) blocks = cap;
+        const int grid = (int)blocks;
+        out->fn = [p, c, d, grid, smem, uns_in](cudaStream_t s) {
+            if (uns_in) conv_i8_dw16_kernel<true><<<grid, 256, smem, s>>>(p, c, d);
+            else conv_i8_dw16_kernel<false><<<grid, 256, smem, s>>>(p, c, d);
+            return cudaGetLastError();
+        };
+        out->launches = 1;
+        return CLDNN_B200_SUCCESS;
+    }
     DwArgs d{(const uint8_t*)a->input0, (const int8_t*)a->weights, a->bias, a->weights_quantization_factors, a->output_calibration_factors, (uint8_t*)a->output};
     const int64_t items = (int64_t)p.out.b * p.out.y * p.out.x * (p.out.f / 4);
     int64_t blocks = (items + 255) / 256; const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 8;
@@ -116,6 +295,6 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
 
 }  // namespace
 
-const KernelDef kdef_conv_i8_dw = {"conv_i8_dw", sizeof(cldnn_b200_conv_params), dw_supports, dw_tune_count, nullptr, dw_prepare};
+const KernelDef kdef_conv_i8_dw = {"conv_i8_dw", sizeof(cldnn_b200_conv_params), dw_supports, dw_tune_count, dw_scratch, dw_prepare};
 
 }  // namespace b200

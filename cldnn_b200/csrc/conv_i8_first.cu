@@ -123,10 +123,11 @@ __device__ __forceinline__ void tile_origin(const FirstParams& P, int tile, int&
 }
 
 // epilogue of one 32-row quadrant: kMode 0..2 = the conversion-free variants (u8 / s8 / s8 after ReLU), 3 = general
-template <int kMode>
+template <int kMode, bool kOqf = false>
 __device__ __forceinline__ void first_epi_tile(const FirstParams& P, const FirstAux* aux, uint32_t t_row, uint8_t* out_row, bool valid,
                                                uint32_t tmem_empty_bar, int lane)
 {
+    const float oqf = P.epi.o_qf;
     uint32_t ra[32], rb[32];
     tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
@@ -137,7 +138,7 @@ __device__ __forceinline__ void first_epi_tile(const FirstParams& P, const First
         else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
         if (valid) {
             uint4* op = reinterpret_cast<uint4*>(out_row + c0);
-            if (kMode < 3) fast_chunk32<false, false, kMode < 3 ? kMode : 0>(ra, &aux->bias_i[0][c0], &aux->quant[0][c0], op, op + 1, 0u, kMagicBits, kMagicBits);
+            if (kMode < 3) fast_chunk32<false, false, kMode < 3 ? kMode : 0, kOqf>(ra, &aux->bias_i[0][c0], &aux->quant[0][c0], op, op + 1, 0u, kMagicBits, kMagicBits, oqf);
             else { uint4 o0, o1; epi_chunk_fast<false, false>(P, aux, 0, c0, ra, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1); op[0] = o0; op[1] = o1; }
         }
         if (!second) break;
@@ -146,17 +147,18 @@ __device__ __forceinline__ void first_epi_tile(const FirstParams& P, const First
         else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
         if (valid) {
             uint4* op = reinterpret_cast<uint4*>(out_row + c0 + 32);
-            if (kMode < 3) fast_chunk32<false, false, kMode < 3 ? kMode : 0>(rb, &aux->bias_i[0][c0 + 32], &aux->quant[0][c0 + 32], op, op + 1, 0u, kMagicBits, kMagicBits);
+            if (kMode < 3) fast_chunk32<false, false, kMode < 3 ? kMode : 0, kOqf>(rb, &aux->bias_i[0][c0 + 32], &aux->quant[0][c0 + 32], op, op + 1, 0u, kMagicBits, kMagicBits, oqf);
             else { uint4 o0, o1; epi_chunk_fast<false, false>(P, aux, 0, c0 + 32, rb, make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), o0, o1); op[0] = o0; op[1] = o1; }
         }
     }
 }
 
 // the same with one register array (load, wait, convert): for launches that keep two CTAs per SM
-template <int kMode>
+template <int kMode, bool kOqf = false>
 __device__ __forceinline__ void first_epi_tile_single(const FirstParams& P, const FirstAux* aux, uint32_t t_row, uint8_t* out_row, bool valid,
                                                       uint32_t tmem_empty_bar, int lane)
 {
+    const float oqf = P.epi.o_qf;
 #pragma unroll 1
     for (int c0 = 0; c0 < P.ofm; c0 += 32) {
         uint32_t r[32];
@@ -165,7 +167,7 @@ __device__ __forceinline__ void first_epi_tile_single(const FirstParams& P, cons
         if (c0 + 32 >= P.ofm) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
         if (valid) {
             uint4* op = reinterpret_cast<uint4*>(out_row + c0);
-            fast_chunk32<false, false, kMode>(r, &aux->bias_i[0][c0], &aux->quant[0][c0], op, op + 1, 0u, kMagicBits, kMagicBits);
+            fast_chunk32<false, false, kMode, kOqf>(r, &aux->bias_i[0][c0], &aux->quant[0][c0], op, op + 1, 0u, kMagicBits, kMagicBits, oqf);
         }
     }
 }
@@ -214,7 +216,7 @@ conv_i8_first_kernel(const __grid_constant__ FirstParams P)
         aux->calib[0][j] = c.calibration ? P.calib[j] : 1.f;
         aux->ecal[0][j] = 1.f;
         // the conversion-free epilogue is exact while every dequantised value stays below 2^22
-        if (!(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)) < 4.0e6f)) atomicOr(&aux->wide, 1u);
+        if (!(__fmul_rn(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)), P.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f)) atomicOr(&aux->wide, 1u);
     }
     for (int g = tid; g < P.groups && g < 64; g += kFThreads) { const int ch = g / P.kh, r = g - ch * P.kh; aux->goff[g] = (uint16_t)((ch * P.patch_h + r) * (P.patch_wp >> 2)); }
     fence_async_smem();
@@ -317,7 +319,8 @@ conv_i8_first_kernel(const __grid_constant__ FirstParams P)
         const int quad = warp & 3;                              // warps 4..7 -> TMEM lanes 32*quad ..
         const int row = quad * 32 + lane;
         const int py_ = row / kTileW, px_ = row - py_ * kTileW;
-        const int mode = (P.lean && !aux->wide) ? (c.out_dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
+        // modes 0..2: conversion-free (u8 / s8 / s8 after ReLU), +4: with a uniform O_QF (modes 0 and 1 only), 3: general
+        const int mode = (P.lean && !aux->wide) ? ((c.out_dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) + (P.mul_oqf ? 4 : 0)) : 3;
         for (int it = 0; it < my_tiles; ++it) {
             const int buf = it & 1;
             int tx, ty, n, x0, y0, xa;
@@ -334,6 +337,8 @@ conv_i8_first_kernel(const __grid_constant__ FirstParams P)
                     case 0: first_epi_tile<0>(P, aux, t_row, out_row, valid, te, lane); break;
                     case 1: first_epi_tile<1>(P, aux, t_row, out_row, valid, te, lane); break;
                     case 2: first_epi_tile<2>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 4: first_epi_tile_single<0, true>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 5: first_epi_tile_single<1, true>(P, aux, t_row, out_row, valid, te, lane); break;
                     default: first_epi_tile_general(P, aux, t_row, out_row, valid, te, lane); break;
                 }
             } else {
@@ -341,6 +346,8 @@ conv_i8_first_kernel(const __grid_constant__ FirstParams P)
                     case 0: first_epi_tile_single<0>(P, aux, t_row, out_row, valid, te, lane); break;
                     case 1: first_epi_tile_single<1>(P, aux, t_row, out_row, valid, te, lane); break;
                     case 2: first_epi_tile_single<2>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 4: first_epi_tile_single<0, true>(P, aux, t_row, out_row, valid, te, lane); break;
+                    case 5: first_epi_tile_single<1, true>(P, aux, t_row, out_row, valid, te, lane); break;
                     default: first_epi_tile_general(P, aux, t_row, out_row, valid, te, lane); break;
                 }
             }
@@ -382,9 +389,10 @@ static int first_kp(const cldnn_b200_conv_params& p) { return (p.ifm * p.kh * 8 
 static size_t first_scratch(const void* vp) { const auto& p = *(const cldnn_b200_conv_params*)vp; return (size_t)p.ofm * first_kp(p); }
 
 // Validates the arguments and fills the launch constants; `wpacked` is where the packed weights will live.
-static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p, const cldnn_b200_args* a, void* wpacked, size_t wpacked_bytes,
+static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p_in, const cldnn_b200_args* a, void* wpacked, size_t wpacked_bytes,
                            FirstParams& P, int& grid, size_t& smem)
 {
+    const cldnn_b200_conv_params p = simplified_conv_params(p_in);
     std::string why;
     if (!first_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_first: " + why);
     if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: input, output and weights are required");
@@ -412,7 +420,9 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
     P.epi = make_epi_cfg(p);
     P.mul_iqf = p.i_qf != 1.0f ? 1 : 0; P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
-    P.lean = (p.quantization && !P.mul_iqf && !P.mul_oqf && !P.epi.dont_dequantize_bias &&
+    // a uniform positive O_QF is part of the conversion-free epilogue in front of an unsigned or a plain signed saturation
+    const bool oqf_ok = !P.mul_oqf || (!p.calibration && p.o_qf > 0.0f && (p.out.dtype == CLDNN_B200_U8 || p.act != CLDNN_B200_ACT_RELU));
+    P.lean = (p.quantization && !P.mul_iqf && oqf_ok && !P.epi.dont_dequantize_bias &&
               (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU)) ? 1 : 0;
     P.in = (const uint8_t*)a->input0; P.out = (uint8_t*)a->output; P.wpacked = (const uint8_t*)wpacked;
     P.bias = a->bias; P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors;

@@ -451,8 +451,13 @@ static void choose_box(int Q, int Pn, int N, int& bw, int& bh, int& bb)
 static bool lean_params(const cldnn_b200_conv_params& p)
 {
     auto none_or_relu = [](int32_t fn) { return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU; };
-    if (!p.quantization || p.i_qf != 1.0f || p.calibration || p.o_qf != 1.0f) return false;
+    if (!p.quantization || p.i_qf != 1.0f || p.calibration) return false;
     if (!is_int8(p.out.dtype) || !none_or_relu(p.act)) return false;
+    if (p.o_qf != 1.0f) {
+        // a uniform O_QF: positive, in front of an unsigned or a plain signed saturation, no ReLU in front of a residual sum
+        const int32_t last = p.fused_eltw ? p.eltw_act : p.act;
+        if (!(p.o_qf > 0.0f) || (p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) || (p.out.dtype != CLDNN_B200_U8 && last == CLDNN_B200_ACT_RELU)) return false;
+    }
     if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32) return false;
     if (p.fused_eltw) {
         const int32_t edt = p.in_out_opt ? p.out.dtype : p.eltw.dtype;
@@ -552,7 +557,7 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
 
 static bool tc_supports(const void* vp)
 {
-    TcPlan pl; return tc_plan(*(const cldnn_b200_conv_params*)vp, pl, nullptr);
+    TcPlan pl; return tc_plan(simplified_conv_params(*(const cldnn_b200_conv_params*)vp), pl, nullptr);
 }
 
 // tensor map over the pixels x features of an 8-bit byxf tensor, boxed like the tile
@@ -577,7 +582,7 @@ static CUresult encode_pixel_map(CUtensorMap* tm, const TcPlan& pl, void* ptr, c
 
 static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
-    const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
+    const cldnn_b200_conv_params p = simplified_conv_params(*(const cldnn_b200_conv_params*)vp);
     TcPlan pl; std::string why;
     if (!tc_plan(p, pl, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: " + why);
     if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: input, output and weights are required");
@@ -644,7 +649,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.mul_iqf = p.i_qf != 1.0f ? 1 : 0;
     P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
     auto none_or_relu = [](int32_t fn) { return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU; };
-    P.lean = (P.fast_epi && p.quantization && !P.mul_iqf && !P.mul_oqf && !P.epi.dont_dequantize_bias && none_or_relu(p.act) &&
+    P.lean = (P.fast_epi && p.quantization && !P.mul_iqf && (!P.mul_oqf || !p.calibration) && !P.epi.dont_dequantize_bias && none_or_relu(p.act) &&
               (!p.fused_eltw || (!p.has_non_conv_scale && !p.eltw_calibration && none_or_relu(p.eltw_act)))) ? 1 : 0;
 
     // staged epilogue: the output (and residual) tile must be addressable by one TMA box per column block
@@ -661,7 +666,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
 
     const bool out_u8 = p.out.dtype == CLDNN_B200_U8;
     const int out_kind = out_u8 ? 0 : ((p.fused_eltw ? p.eltw_act : p.act) == CLDNN_B200_ACT_RELU ? 2 : 1);
-    P.fast_variant = (out_kind << 1) | ((p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) ? 1 : 0);
+    P.fast_variant = (out_kind << 1) | ((p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) ? 1 : 0) | (P.mul_oqf ? 8 : 0);
     P.acc_bound = (float)p.kh * (float)p.kw * (float)p.ifm * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
 #ifdef CONV_TC_DEBUG
     if (const char* e = getenv("CLDNN_B200_TC_DEBUG")) P.debug = atoi(e);

@@ -97,23 +97,24 @@ __device__ __forceinline__ void fast_chunk_ptrs(uint8_t* stg, int row, uint32_t 
 }
 
 // One 32-row quadrant of a tile, all BN feature columns.
-template <int BN, bool kFused, bool kRelu1, int kOut>
+// `cols` (a multiple of 64, <= BN): columns that hold features of the tensor; the last feature tile of a ragged count stops there.
+template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, int cols, float oqf = 1.0f)
 {
     const int32_t* bias = aux->bias_i[group];
     const float* quant = aux->quant[group];
     uint32_t ra[32], rb[32];
     tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 64) {
+    for (int c0 = 0; c0 < cols; c0 += 64) {
         uint4 *p0, *p1;
         tmem_ld_wait();
         tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);             // in flight while `ra` is converted
         fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
-        fast_chunk32<kFused, kRelu1, kOut>(ra, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg);
+        fast_chunk32<kFused, kRelu1, kOut, kOqf>(ra, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg, oqf);
         tmem_ld_wait();
-        if (c0 + 64 < BN) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
+        if (c0 + 64 < cols) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
         else {
             // the accumulator has been read out: the MMA issuer may reuse it
             tc_fence_before();
@@ -121,7 +122,7 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
             if (lane == 0) mbar_arrive(tmem_empty_bar);
         }
         fast_chunk_ptrs<BN>(stg, row, sw, c0 + 32, p0, p1);
-        fast_chunk32<kFused, kRelu1, kOut>(rb, bias + c0 + 32, quant + c0 + 32, p0, p1, e_xor, k_pos, k_neg);
+        fast_chunk32<kFused, kRelu1, kOut, kOqf>(rb, bias + c0 + 32, quant + c0 + 32, p0, p1, e_xor, k_pos, k_neg, oqf);
     }
 }
 
@@ -129,11 +130,11 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
 // taken when a feature's value range could leave the integer-safe range.
 template <int BN>
 __device__ __noinline__ void fast_tile_wide(const TcParams& P, const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row,
-                                            uint32_t sw, uint32_t tmem_empty_bar, int lane)
+                                            uint32_t sw, uint32_t tmem_empty_bar, int lane, int cols)
 {
     const EpiCfg& c = P.epi;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = 0; c0 < cols; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + (uint32_t)c0, r);
         tmem_ld_wait();
@@ -399,6 +400,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 for (int cb = 0; cb < COLB; ++cb) {
                     if (TC_DEBUG(P, 3)) break;
                     const int f0 = n_tile * BN + cb * CW;
+                    if (f0 >= P.ofm) break;                         // ragged feature count: nothing of the tensor in this block
                     const uint32_t src = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
                     if (boxed) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
                     else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
@@ -430,11 +432,15 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
                 prof.stop(1);
                 const uint32_t rf = smem_u32(&aux->res_full[a]);
-                mbar_expect_tx(rf, (uint32_t)(P.stage_rows * BN));
+                int cbs = 0;                                        // column blocks that hold features of the tensor
+#pragma unroll
+                for (int cb = 0; cb < COLB; ++cb) if (n_tile * BN + cb * CW < P.ofm) ++cbs;
+                mbar_expect_tx(rf, (uint32_t)(P.stage_rows * CW * cbs));
 #pragma unroll
                 for (int cb = 0; cb < COLB; ++cb) {
                     const uint32_t dst = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
                     const int f0 = n_tile * BN + cb * CW;
+                    if (f0 >= P.ofm) break;
                     if (boxed) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
                     else tma_load_2d(dst, &P.tmE, rf, f0, m_tile * kBM);
                 }
@@ -453,8 +459,10 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         const bool res_s8 = kFused && c.eltw_dtype != CLDNN_B200_U8;
         const uint32_t e_xor = res_s8 ? 0x80808080u : 0u;
         const int32_t k_pos = kMagicBits + (res_s8 ? 128 : 0), k_neg = kMagicBits - (res_s8 ? 128 : 0);
-        const int variant = P.fast_variant;
-        int cur_n_tile = -1; bool ok = true; bool wide = false;
+        const int variant = P.fast_variant & 7;
+        const bool with_oqf = (P.fast_variant & 8) != 0;            // uniform O_QF after the dequantisation
+        const float oqf = c.o_qf, oqf_abs = with_oqf ? fabsf(c.o_qf) : 1.0f;
+        int cur_n_tile = -1; bool ok = true; bool wide = false; int cols = BN;
         Prof prof; prof.begin();
         int t = group;
         TileWalk walk; walk.init(P, blockIdx.x + group * gridDim.x, kGroups * gridDim.x);
@@ -469,15 +477,19 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 bool w = false;
                 for (int j = gt; j < BN; j += 128) {
                     const int f = n_tile * BN + j;
-                    const int32_t bi = c.bias_dtype != CLDNN_B200_NONE ? ((const int32_t*)P.bias)[f] : 0;
-                    const float q = P.quant[f];
+                    // columns past the last feature (ragged count): zero accumulators (their weight rows are out of the
+                    // tensor map's range), neutral constants, and the store clips them
+                    const bool real = f < P.ofm;
+                    const int32_t bi = (real && c.bias_dtype != CLDNN_B200_NONE) ? ((const int32_t*)P.bias)[f] : 0;
+                    const float q = real ? P.quant[f] : 1.0f;
                     aux->bias_i[group][j] = bi; aux->quant[group][j] = q;
-                    w = w || !(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)) < 4.0e6f);
+                    w = w || !(__fmul_rn(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)), oqf_abs) < 4.0e6f);
                 }
                 w = __any_sync(0xffffffffu, w);
                 if (lane == 0) aux->wide[group][quad] = w ? 1u : 0u;
                 named_bar_sync(1 + group, 128);
                 wide = (aux->wide[group][0] | aux->wide[group][1] | aux->wide[group][2] | aux->wide[group][3]) != 0u;
+                cols = min(BN, (P.ofm - n_tile * BN + 63) & ~63);
                 cur_n_tile = n_tile;
                 prof.stop(2);
             }
@@ -496,21 +508,31 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             uint8_t* stg = staging + (size_t)sb * kStagingBytes;
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
             if (TC_DEBUG(P, 1)) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(te); }
-            else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
+            else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane, cols);
+            else if (with_oqf) {
+                // u8 or plain s8 output, no ReLU between convolution and residual sum (the host admits nothing else here)
+                if (kFused) {
+                    if ((variant >> 1) == 0) fast_tile<BN, true, false, 0, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
+                    else fast_tile<BN, true, false, 1, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
+                } else {
+                    if ((variant >> 1) == 0) fast_tile<BN, false, false, 0, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
+                    else fast_tile<BN, false, false, 1, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
+                }
+            }
             else if (kFused) {
                 switch (variant) {
-                    case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 1: fast_tile<BN, true, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 2: fast_tile<BN, true, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 3: fast_tile<BN, true, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 4: fast_tile<BN, true, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    default: fast_tile<BN, true, true, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 1: fast_tile<BN, true, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 2: fast_tile<BN, true, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 3: fast_tile<BN, true, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 4: fast_tile<BN, true, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    default: fast_tile<BN, true, true, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
                 }
             } else {
                 switch (variant >> 1) {
-                    case 0: fast_tile<BN, false, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 1: fast_tile<BN, false, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    default: fast_tile<BN, false, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 0: fast_tile<BN, false, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 1: fast_tile<BN, false, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    default: fast_tile<BN, false, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
                 }
             }
             fence_async_smem();
@@ -553,7 +575,11 @@ bool tc_fast_eligible(const TcParams& P)
 {
     if (!P.lean || !P.staged) return false;
     if (P.bn != 64 && P.bn != 128 && P.bn != 256) return false;
-    if (P.ofm % P.bn) return false;
+    // a uniform O_QF: positive, and only in front of an unsigned or plain signed saturation
+    if (P.mul_oqf) {
+        if (P.epi.calibration || !(P.epi.o_qf > 0.0f)) return false;
+        if ((P.fast_variant & 1) || ((P.fast_variant >> 1) & 3) == 2) return false;
+    }
     if (P.epi.bias_dtype != CLDNN_B200_NONE && P.epi.bias_dtype != CLDNN_B200_I32) return false;
     return true;
 }

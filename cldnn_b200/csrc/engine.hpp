@@ -62,6 +62,7 @@ struct KernelDef {
 extern const KernelDef kdef_conv_ref;
 extern const KernelDef kdef_conv_i8_tc;
 extern const KernelDef kdef_conv_i8_first;
+extern const KernelDef kdef_conv_first_tc;
 extern const KernelDef kdef_conv_f16_tc;
 extern const KernelDef kdef_conv_f16_winograd;
 extern const KernelDef kdef_conv_i8_dw;

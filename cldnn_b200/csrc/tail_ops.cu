@@ -29,15 +29,22 @@ __device__ __forceinline__ uint32_t pool_divisor(const cldnn_b200_pool_params& p
     return (uint32_t)(p.size_x * p.size_y);
 }
 
+// element index -> coordinates, x innermost (planar layouts) or f innermost (byxf)
+__device__ __forceinline__ void decode_bfyx(int64_t idx, int F, int Y, int X, bool f_inner, int& b, int& f, int& y, int& x)
+{
+    if (f_inner) { f = (int)(idx % F); int64_t t = idx / F; x = (int)(t % X); t /= X; y = (int)(t % Y); b = (int)(t / Y); }
+    else { x = (int)(idx % X); int64_t t = idx / X; y = (int)(t % Y); t /= Y; f = (int)(t % F); b = (int)(t / F); }
+}
+
 __global__ void __launch_bounds__(256)
 pooling_ref_kernel(const __grid_constant__ cldnn_b200_pool_params p, const void* in, void* out)
 {
     const int64_t total = (int64_t)p.out.b * p.out.f * p.out.y * p.out.x;
     const bool int_in = is_int8(p.in.dtype);
+    const bool f_inner = p.in.pf == 1 && p.out.pf == 1;             // consecutive threads follow the innermost dimension of the layout
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        int x = (int)(idx % p.out.x); int64_t t = idx / p.out.x;
-        int y = (int)(t % p.out.y); t /= p.out.y;
-        int f = (int)(t % p.out.f); int b = (int)(t / p.out.f);
+        int b, f, y, x;
+        decode_bfyx(idx, p.out.f, p.out.y, p.out.x, f_inner, b, f, y, x);
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
         int32_t ri = p.mode == CLDNN_B200_POOL_MAX ? -128 : 0;
@@ -447,9 +454,8 @@ lrn_ref_kernel(const __grid_constant__ cldnn_b200_lrn_params p, const void* in, 
     const int64_t total = (int64_t)p.in.b * p.in.f * p.in.y * p.in.x;
     const int pad = (p.size - 1) / 2;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        int x = (int)(idx % p.in.x); int64_t t = idx / p.in.x;
-        int y = (int)(t % p.in.y); t /= p.in.y;
-        int f = (int)(t % p.in.f); int b = (int)(t / p.in.f);
+        int b, f, y, x;
+        decode_bfyx(idx, p.in.f, p.in.y, p.in.x, p.in.pf == 1 && p.out.pf == 1, b, f, y, x);
         float acc = 0.f;
         for (int i = 0; i < p.size; ++i) {
             const int ff = f - pad + i; if (ff < 0 || ff >= p.in.f) continue;

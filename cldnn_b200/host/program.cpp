@@ -477,32 +477,47 @@ void network_impl::fuse_conv_eltwise()
 // byxf_af32 (features innermost, padded to 32), the layout the tensor-core kernel reads with TMA.
 void network_impl::select_layouts()
 {
+    // an inner product whose weights have the input's feature and map sizes is a GEMM over the flattened byxf input
+    auto fc_weights_match = [&](node* n) {
+        if (!n->weights) return false;
+        const layout& in = n->deps[0]->out; const layout& w = n->weights->out;
+        return w.size.feature == in.size.feature && w.size.x == in.size.x && w.size.y == in.size.y;
+    };
     auto conv_like = [&](node* n) {
         const std::string& t = n->p.type;
         if (n->deps.empty()) return false;
-        // fp16 convolutions run on the tensor cores from the same feature-innermost padded layout
-        if (n->deps[0]->out.data_type == data_types::f16)
+        // fp16 convolutions and inner products run on the tensor cores from the same feature-innermost padded layout
+        if (n->deps[0]->out.data_type == data_types::f16) {
+            if (t == "fully_connected") return n->weights && n->weights->out.data_type == data_types::f16 && !n->wq && fc_weights_match(n);
             return (t == "convolution" || t == "fused_conv_eltwise") && n->p.groups >= 1 && n->p.groups <= 4 && n->weights && n->weights->out.data_type == data_types::f16 && !n->wq;
+        }
         if (!is_int8(n->deps[0]->out.data_type)) return false;
         // dense convolutions go to the tensor cores, depthwise ones (one feature per group) to the byxf depthwise kernel
         if (t == "convolution" && n->p.groups > 4) return n->wq != nullptr && n->weights && n->weights->out.size.feature == 1 && n->p.groups == n->deps[0]->out.size.feature &&
                                                           n->weights->out.size.batch == n->p.groups && n->p.groups % 4 == 0;
         if (t == "convolution" || t == "fused_conv_eltwise") return n->p.groups >= 1 && n->p.groups <= 4 && n->wq != nullptr;
-        if (t == "fully_connected") return n->wq && n->bias && n->bias->out.data_type == data_types::f32 && n->deps[0]->out.size.x == 1 && n->deps[0]->out.size.y == 1;
+        if (t == "fully_connected") return n->wq && n->bias && n->bias->out.data_type == data_types::f32 && fc_weights_match(n);
         return false;
     };
     // a convolution over a planar few-feature input (the image) has a kernel that builds its operand from bfyx itself
+    // (conv_i8_first: 8-bit, filters up to 8 taps wide; conv_first_tc: fp16 or 8-bit, K = C*kh*kw packed densely)
     auto first_layer = [&](node* n, node* d) {
-        if (n->p.type != "convolution" || d->out.fmt != format::bfyx || !n->weights) return false;
+        if (n->p.type != "convolution" || d->out.fmt != format::bfyx || !n->weights || n->p.groups != 1) return false;
         const layout& w = n->weights->out;
-        return w.size.x <= 8 && d->out.size.feature * w.size.y * 8 <= 256 && w.size.batch % 32 == 0 && w.size.batch <= 256 &&
-               n->p.dilation.x == 1 && n->p.dilation.y == 1 && n->act == CLDNN_B200_ACT_NONE && !n->p.activation_negative_slope;
+        const bool i8 = is_int8(d->out.data_type) && n->wq != nullptr && w.data_type == data_types::i8;
+        const bool f16 = d->out.data_type == data_types::f16 && w.data_type == data_types::f16 && !n->wq;
+        if ((!i8 && !f16) || w.size.batch % 32 || w.size.batch > 256) return false;
+        const bool simple_act = (n->act == CLDNN_B200_ACT_NONE || n->act == CLDNN_B200_ACT_RELU || n->act == CLDNN_B200_ACT_CLAMP) && !n->p.activation_negative_slope;
+        if (i8 && w.size.x <= 8 && d->out.size.feature * w.size.y * 8 <= 256 && n->p.dilation.x == 1 && n->p.dilation.y == 1 && simple_act) return true;
+        const int64_t k = (int64_t)d->out.size.feature * w.size.y * w.size.x;
+        const int64_t image = w.size.batch * ((k + 31) / 32 * 32) * (f16 ? 2 : 1);       // resident weights in shared memory
+        return d->out.size.feature <= 4 && k <= 1024 && image <= 120 * 1024 && (f16 || simple_act);
     };
     std::set<node*> chosen;
     for (node* n : order) {
         if (n->removed || n->constant() || n->p.type == "input_layout" || n->deps.empty()) continue;
         if (conv_like(n)) chosen.insert(n);
-        else if ((n->p.type == "pooling" || n->p.type == "eltwise" || n->p.type == "activation") &&
+        else if ((n->p.type == "pooling" || n->p.type == "eltwise" || n->p.type == "activation" || n->p.type == "lrn") &&
                  (is_int8(n->deps[0]->out.data_type) || n->deps[0]->out.data_type == data_types::f16)) {
             bool all = true; for (node* d : n->deps) all &= chosen.count(d) > 0;
             if (all) chosen.insert(n);
@@ -735,13 +750,23 @@ void network_impl::prepare_kernel(node* n)
             cp.eltw_stride_x = p.eltw_stride.x; cp.eltw_stride_y = p.eltw_stride.y;
             cp.in_out_opt = 0;
         }
+        std::function<void()> fc_fallback;
         if (fc) {
             // fully_connected_gpu_bfyx_ref.cl:68-81: round(((float)acc*q*I_QF + bias) * calib|O_QF), activation on the 8-bit
             // value.  With a float bias this is the convolution epilogue with DONT_DEQUANTIZE_BIAS; ReLU commutes with
-            // the rounding and the saturating store.
-            const bool as_conv = cp.quantization && n->bias && n->bias->out.data_type == data_types::f32 && n->out.data_type == data_types::i8 &&
-                                 (cp.act == CLDNN_B200_ACT_NONE || cp.act == CLDNN_B200_ACT_RELU) && in.size.x == 1 && in.size.y == 1;
-            if (!as_conv) {
+            // the rounding and the saturating store.  The fp16 form is bias + activation, the fp16 convolution's epilogue.
+            // A byxf input without padding between pixels is one row of y*x*stored-features values per image, and the
+            // weights packed oyxi are the matching rows: the inner product is a 1x1 convolution over a 1x1 map.
+            const bool flat = cp.in.pf == 1 && cp.in.py == cp.in.px * cp.in.x && cp.in.pb == cp.in.py * cp.in.y && cp.out.pf == 1 &&
+                              w.size.feature == in.size.feature && w.size.x == in.size.x && w.size.y == in.size.y;
+            // (the reference saturates the rounded value to s8 whatever the output type; written to an unsigned output that
+            // leaves 0..127 -- the bytes an s8 store after a ReLU produces)
+            const bool i8_conv = cp.quantization && n->bias && n->bias->out.data_type == data_types::f32 && is_int8(n->out.data_type) &&
+                                 (cp.act == CLDNN_B200_ACT_NONE || cp.act == CLDNN_B200_ACT_RELU) && is_int8(in.data_type);
+            const bool f16_conv = in.data_type == data_types::f16 && w.data_type == data_types::f16 && n->out.data_type == data_types::f16 && !cp.quantization &&
+                                  !cp.calibration && cp.o_qf == 1.0f;
+            const bool as_conv = flat && (i8_conv || f16_conv);
+            auto plain_fc = [&]() {
                 cldnn_b200_fc_params fp{};
                 fp.in = in.desc(); fp.out = n->out.desc();
                 const cldnn_b200_tensor wd = w.desc();
@@ -749,24 +774,33 @@ void network_impl::prepare_kernel(node* n)
                 fp.bias_dtype = cp.bias_dtype; fp.quantization = cp.quantization; fp.i_qf = cp.i_qf; fp.calibration = cp.calibration; fp.o_qf = cp.o_qf;
                 fp.act = cp.act; fp.act_m = cp.act_m; fp.act_n = cp.act_n;
                 finish({"fc_ref"}, &fp, sizeof(fp), [](int) {});
-                return;
-            }
+            };
+            fc_fallback = plain_fc;
+            if (!as_conv) { plain_fc(); return; }
             cp.has_o_qf = (!cp.calibration && cp.o_qf != 1.0f) ? 1 : 0;
+            if (i8_conv && n->out.data_type == data_types::u8) { cp.out.dtype = CLDNN_B200_I8; cp.act = CLDNN_B200_ACT_RELU; }
         }
-        // first layer: planar 8-bit input, byxf output
-        if (!fc && is_int8(in.data_type) && cp.in.px == 1 && cp.out.pf == 1) {
-            int32_t yes = 0; size_t sbytes = 0;
-            cldnn_b200_kernel k = eng->kernel("conv_i8_first");
-            if (cldnn_b200_kernel_supports(k, &cp, sizeof(cp), &yes) == CLDNN_B200_SUCCESS && yes &&
-                cldnn_b200_kernel_scratch_bytes(k, &cp, sizeof(cp), &sbytes) == CLDNN_B200_SUCCESS) {
-                n->scratch = new_block(eng, sbytes);
-                a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
-                finish({"conv_i8_first"}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
-                return;
+        // first layer: planar input as the caller provides it, byxf output
+        if (!fc && (is_int8(in.data_type) || in.data_type == data_types::f16) && cp.in.px == 1 && cp.out.pf == 1) {
+            for (const char* kn : {"conv_i8_first", "conv_first_tc"}) {
+                int32_t yes = 0; size_t sbytes = 0;
+                cldnn_b200_kernel k = eng->kernel(kn);
+                if (cldnn_b200_kernel_supports(k, &cp, sizeof(cp), &yes) == CLDNN_B200_SUCCESS && yes &&
+                    cldnn_b200_kernel_scratch_bytes(k, &cp, sizeof(cp), &sbytes) == CLDNN_B200_SUCCESS) {
+                    n->scratch = new_block(eng, sbytes);
+                    a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
+                    finish({kn}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
+                    return;
+                }
             }
         }
         // tensor-core kernel: needs byxf activations and oyxi weights padded like the activations
-        const bool half_tc = in.data_type == data_types::f16 && w.data_type == data_types::f16 && n->out.data_type == data_types::f16 && !fc;
+        const bool half_tc = in.data_type == data_types::f16 && w.data_type == data_types::f16 && n->out.data_type == data_types::f16;
+        const int32_t stored_ifm = (int32_t)cp.in.px;
+        if (fc) {                                                       // the flattened view (the weights are packed from the original one)
+            const int64_t kflat = cp.in.pb;
+            cp.in.f = (int32_t)kflat; cp.in.x = cp.in.y = 1; cp.in.px = cp.in.py = kflat; cp.ifm = (int32_t)kflat;
+        }
         // a convolution in 2..4 groups runs as a dense one on block-diagonal weights (AlexNet's split layers)
         const bool dense_groups = cp.groups >= 2 && cp.groups <= 4 && !fc;
         const bool try_tc = ((is_int8(in.data_type) && w.data_type == data_types::i8) || half_tc) && (cp.groups == 1 || dense_groups) && cp.in.pf == 1 && cp.in.px % 32 == 0 && cp.out.pf == 1;
@@ -774,9 +808,10 @@ void network_impl::prepare_kernel(node* n)
         if (try_tc) {
             cldnn_b200_conv_params tp = cp;
             if (dense_groups) { tp.ofm = cp.ofm * cp.groups; tp.ifm = cp.ifm * cp.groups; tp.groups = 1; }
-            n->packed_weights = pack_conv_weights(n, (int32_t)cp.in.px, dense_groups ? cp.groups : 1);
+            n->packed_weights = pack_conv_weights(n, stored_ifm, dense_groups ? cp.groups : 1);
             const cldnn_b200_tensor pd = n->packed_weights.get_layout().desc();
             tp.w_po = pd.pb; tp.w_pi = 1; tp.w_py = pd.py; tp.w_px = pd.px; tp.w_offset = 0;
+            if (fc) tp.w_px = tp.w_py = pd.pb;                         // one tap holding the whole flattened row
             cldnn_b200_args ta = a; ta.weights = n->packed_weights.device_ptr();
             int32_t yes = 0;
             if (cldnn_b200_kernel_supports(eng->kernel(tc_kernel), &tp, sizeof(tp), &yes) == CLDNN_B200_SUCCESS && yes) {
@@ -785,6 +820,16 @@ void network_impl::prepare_kernel(node* n)
                 return;
             }
             n->packed_weights = memory();
+        }
+        if (fc) { fc_fallback(); return; }
+        {   // the depthwise kernel keeps its weights as one word per (tap, feature) in a scratch buffer
+            int32_t yes = 0; size_t sbytes = 0;
+            cldnn_b200_kernel k = eng->kernel("conv_i8_dw");
+            if (cldnn_b200_kernel_supports(k, &cp, sizeof(cp), &yes) == CLDNN_B200_SUCCESS && yes &&
+                cldnn_b200_kernel_scratch_bytes(k, &cp, sizeof(cp), &sbytes) == CLDNN_B200_SUCCESS && sbytes) {
+                n->scratch = new_block(eng, sbytes);
+                a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
+            }
         }
         finish({"conv_i8_dw", "conv_ref"}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
         return;

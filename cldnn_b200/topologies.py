@@ -211,6 +211,46 @@ def vgg16_conv_layers(image=224, stages=VGG16_STAGES):
     return out
 
 
+# AlexNet (one-tower weights with the original two-group layers): (features, filter, stride, pad, groups, lrn + pool after)
+ALEXNET_CONVS = ((96, 11, 4, 0, 1, True), (256, 5, 1, 2, 2, True), (384, 3, 1, 1, 1, False), (384, 3, 1, 1, 2, False), (256, 3, 1, 1, 2, False))
+
+
+def alexnet_fp16(batch, seed=12, image=227, convs=ALEXNET_CONVS, classes=1000, fc_width=4096, w_std=0.01):
+    """fp16 AlexNet: 11x11 stride-4 first convolution, grouped conv2 / conv4 / conv5, LRN (5, k=1, alpha=1e-4, beta=0.75) and
+    3x3 stride-2 max pooling after conv1 and conv2, max pooling after conv5, three fully_connected layers, softmax.
+    Weights N(0, w_std), small positive biases so the ReLUs stay alive, inputs N(0, 1) supplied by the caller."""
+    rng = np.random.default_rng(seed)
+    s = Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.f16, cl.format.bfyx, cl.tensor(batch, 3, image, image))
+    s.add(cl.input_layout("input", s.input_layout))
+    x, cin, size = "input", 3, image
+    for i, (w, k, stride, pad, groups, norm) in enumerate(convs):
+        name = "conv%d" % (i + 1)
+        s.const(name + "_w", (rng.standard_normal((w, cin // groups, k, k)) * w_std).astype(np.float16))
+        s.const(name + "_b", (rng.standard_normal(w) * 0.02 + 0.1).astype(np.float16))
+        s.add(cl.convolution(name, x, name + "_w", name + "_b", stride=(stride, stride), input_offset=(-pad, -pad), with_activation=True, groups=groups))
+        x, cin, size = name, w, (size + 2 * pad - k) // stride + 1
+        if norm:
+            s.add(cl.lrn("norm%d" % (i + 1), x, size=5, k=1.0, alpha=1e-4, beta=0.75))
+            x = "norm%d" % (i + 1)
+        if norm or i == len(convs) - 1:
+            s.add(cl.pooling("pool%d" % (i + 1), x, cl.pooling_mode.max, size=(3, 3), stride=(2, 2)))
+            x, size = "pool%d" % (i + 1), (size - 3) // 2 + 1
+    fan = cin * size * size
+    for i, (wout, act) in enumerate(((fc_width, True), (fc_width, True), (classes, False))):
+        name = "fc%d" % (i + 6)
+        shape = (wout, cin, size, size) if i == 0 else (wout, fan, 1, 1)
+        s.const(name + "_w", (rng.standard_normal(shape) * w_std).astype(np.float16))
+        s.const(name + "_b", (rng.standard_normal(wout) * 0.02 + 0.1).astype(np.float16))
+        s.add(cl.fully_connected(name, x, name + "_w", name + "_b", with_activation=act))
+        x, fan = name, wout
+    s.add(cl.softmax("prob", x))
+    s.outputs = ["prob", x]
+    return s
+
+
 def conv_ops(spec):
     """Multiply-add operations x2 of every convolution / fully_connected of a spec, per image (padding taps counted)."""
     shapes, total = {}, 0

@@ -149,6 +149,57 @@ def test_conv_i8_tc_fast_variants(eng, name, wide):
         assert bad.size == 0, "tune %d: %d of %d differ; first at %d: want %d got %d" % (tune, bad.size, n, bad[0], want[bad[0]], got[bad[0]])
 
 
+REQUANT = {
+    # a uniform O_QF behind the per-feature scale (MobileNet's layers), on feature counts that do not fill the tiles
+    "relu6_requantised_u8": dict(out_dtype=np.uint8, act=abi.ACT_CLAMP, o_qf=42.5),
+    "linear_s8_oqf16": dict(act=abi.ACT_NONE, o_qf=16.0),
+    "relu_u8_oqf": dict(out_dtype=np.uint8, o_qf=2.5),
+    "sum_s8_oqf16": dict(fused=True, act=abi.ACT_NONE, eltw_act=abi.ACT_NONE, eltw_dtype=np.int8, o_qf=16.0),
+    "sum_u8_oqf_relu_after": dict(fused=True, out_dtype=np.uint8, act=abi.ACT_NONE, o_qf=4.0),
+    "clamp_not_subsumed": dict(out_dtype=np.uint8, act=abi.ACT_CLAMP, o_qf=20.0),
+    "relu_s8_oqf": dict(o_qf=8.0),                                                            # s8 after ReLU with O_QF: general kernel
+}
+
+
+@pytest.mark.parametrize("name", sorted(REQUANT))
+@pytest.mark.parametrize("features", [16, 24, 96, 144, 320])
+def test_conv_i8_tc_requantised_ragged_features(eng, name, features):
+    k = eng.kernel("conv_i8_tc")
+    case = cases.make_conv_case(12, N=5, C=64, K=features, H=14, W=14, kh=1, kw=1, pad=0, scale_lo=2.0 ** -13, scale_hi=2.0 ** -11, **REQUANT[name])
+    want = cases.run_oracle(case)
+    n = case.out_elems
+    assert len(np.unique(want[:n])) > 32
+    ran = 0
+    for tune in (0, 2, 3, 4, 10, 11, 7, 15):     # automatic; flat with 64 / 128 / 256 features per tile; tiled 64 / 128; im2col 128; general kernel
+        p = cases.copy_params(case.p)
+        p.tune = tune
+        if not k.supports(p):
+            continue
+        got = cases.run_gpu(eng, case, "conv_i8_tc", tune)
+        bad = np.flatnonzero(want[:n] != got[:n])
+        assert bad.size == 0, "tune %d: %d of %d differ; first at %d: want %d got %d" % (tune, bad.size, n, bad[0], want[bad[0]], got[bad[0]])
+        ran += 1
+    assert ran >= 5
+
+
+def test_conv_i8_tc_requantised_3x3_and_wide(eng):
+    k = eng.kernel("conv_i8_tc")
+    for name in ("relu6_requantised_u8", "linear_s8_oqf16", "sum_s8_oqf16"):
+        for wide in (False, True):
+            case = cases.make_conv_case(13, N=3, C=32, K=96, H=15, W=13, scale_lo=2.0 ** -13, scale_hi=2.0 ** -11, **REQUANT[name])
+            if wide:
+                case.quant[70] = 0.5
+            want = cases.run_oracle(case)
+            n = case.out_elems
+            for tune in (0, 10, 11, 6, 26):
+                p = cases.copy_params(case.p)
+                p.tune = tune
+                if not k.supports(p):
+                    continue
+                got = cases.run_gpu(eng, case, "conv_i8_tc", tune)
+                assert np.array_equal(want[:n], got[:n]), "%s wide=%s tune %d" % (name, wide, tune)
+
+
 FIRST_LAYER = {
     # ResNet-50 conv1: 3 -> 64, 7x7 stride 2 pad 3, planar u8 image in, byxf out
     "resnet_conv1": dict(N=2, C=3, K=64, H=224, W=224, kh=7, kw=7, stride=2, pad=3),
@@ -172,6 +223,20 @@ def test_conv_i8_first_matches_oracle(eng, name, variant):
     want = _exact(eng, case, "conv_i8_first")
     assert (want != 0).any()
     _exact(eng, case, "conv_i8_first", tune=1)       # one CTA per SM, double-buffered epilogue
+
+
+def test_conv_i8_first_requantised(eng):
+    """MobileNet's stem: 3x3 stride 2, ReLU6 folded in front of a requantisation by 255/6 (conversion-free with a uniform O_QF),
+    a linear s8 output with O_QF, and a clamp the saturation does not subsume."""
+    geom = dict(N=3, C=3, K=32, H=65, W=71, kh=3, kw=3, stride=2, pad=1)
+    for extra in (dict(out_dtype=np.uint8, act=abi.ACT_CLAMP, o_qf=42.5), dict(act=abi.ACT_NONE, o_qf=16.0), dict(out_dtype=np.uint8, act=abi.ACT_CLAMP, o_qf=20.0)):
+        for kernel in ("conv_i8_first", "conv_first_tc"):
+            case = cases.make_conv_case(24, fmt="bfyx", f_align=1, out_fmt="byxf", scale_lo=2.0 ** -13, scale_hi=2.0 ** -11, **geom, **extra)
+            assert eng.kernel(kernel).supports(case.p)
+            want = _exact(eng, case, kernel)
+            assert len(np.unique(want[:case.out_elems])) > 16
+            if kernel == "conv_i8_first":
+                _exact(eng, case, kernel, tune=1)
 
 
 def test_conv_i8_first_plain_variants(eng):
@@ -251,6 +316,29 @@ def test_conv_i8_dw_matches_oracle(eng, name, variant):
     want = _exact(eng, case, "conv_i8_dw")
     assert len(np.unique(want)) > 4
     _exact(eng, case, "conv_ref")
+
+
+DW_FAST = {
+    # the configurations the conversion-free epilogue of the 16-feature kernel covers
+    "relu6_requantised_u8": dict(out_dtype=np.uint8, act=abi.ACT_CLAMP, o_qf=42.5),          # clamp(0, 6) * 255/6: the saturation subsumes it
+    "relu_u8": dict(out_dtype=np.uint8),
+    "none_s8": dict(act=abi.ACT_NONE),
+    "relu_s8": dict(),
+    "none_s8_oqf16": dict(act=abi.ACT_NONE, o_qf=16.0),
+    "s8_in_none_u8": dict(in_dtype=np.int8, out_dtype=np.uint8, act=abi.ACT_NONE, o_qf=3.0),
+    "clamp_not_subsumed": dict(out_dtype=np.uint8, act=abi.ACT_CLAMP, o_qf=20.0),             # 6 * 20 < 255: the clamp stays (general path)
+}
+
+
+@pytest.mark.parametrize("name", sorted(DW_FAST))
+@pytest.mark.parametrize("wide", [False, True])
+def test_conv_i8_dw_conversion_free_variants(eng, name, wide):
+    for geom in (dict(N=3, C=48, K=48, H=17, W=19, groups=48), dict(N=2, C=144, K=144, H=15, W=14, groups=144, stride=2)):
+        case = cases.make_conv_case(54, scale_lo=2.0 ** -11, scale_hi=2.0 ** -9, **geom, **DW_FAST[name])
+        if wide:
+            case.quant[5] = 700.0          # a feature whose values can exceed 2^22: the CTA takes the float-domain path
+        want = _exact(eng, case, "conv_i8_dw")
+        assert len(np.unique(want[:case.out_elems])) > 8
 
 
 def test_conv_i8_dw_refuses_dense_and_grouped(eng):

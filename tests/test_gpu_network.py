@@ -162,7 +162,7 @@ def test_errors_surface_as_status_codes(eng):
 def test_small_vgg_fp16_network(eng, optimize):
     """fp16 VGG-style network (convolution + ReLU, max pooling, fully_connected, softmax) against the oracle, within the
     fp16 tolerance of 1e-2 relative to each output's scale; with optimize_data every convolution runs on conv_f16_tc."""
-    spec = topologies.vgg16_fp16(2, seed=3, image=32, stages=((16, 1), (32, 2), (64, 1)), classes=10, fc_width=64)
+    spec = topologies.vgg16_fp16(2, seed=3, image=32, stages=((32, 1), (32, 2), (64, 1)), classes=10, fc_width=64)
     lay = spec.input_layout
     x = np.random.default_rng(7).standard_normal((lay.size.batch, lay.size.feature, lay.size.y, lay.size.x)).astype(np.float16)
     want = oracle_net.run(spec, {spec.input_id: x})
@@ -173,10 +173,40 @@ def test_small_vgg_fp16_network(eng, optimize):
         assert np.abs(g - w).max() <= 1e-2 * scale, "%s: max abs error %.4g on scale %.4g" % (k, float(np.abs(g - w).max()), scale)
     convs = [r for r in net.primitives_info() if r["type"] == "convolution"]
     assert len(convs) == 4
+    fcs = [r for r in net.primitives_info() if r["type"] == "fully_connected"]
     if optimize:
-        assert all(r["kernel"] == "conv_f16_tc" for r in convs), [r["kernel"] for r in convs]
+        # the image layer is gathered in place from the planar input, the rest (inner products included) are tensor-core GEMMs
+        assert [r["kernel"] for r in convs] == ["conv_first_tc"] + ["conv_f16_tc"] * 3, [r["kernel"] for r in convs]
+        assert all(r["kernel"] == "conv_f16_tc" for r in fcs), [r["kernel"] for r in fcs]
     else:
         assert all(r["kernel"] == "conv_ref" for r in convs)
+        assert all(r["kernel"] == "fc_ref" for r in fcs)
+
+
+@pytest.mark.parametrize("optimize", [False, True])
+def test_small_alexnet_fp16_network(eng, optimize):
+    """fp16 AlexNet-style network: 11x11 stride-4 first convolution, two-group convolutions, LRN, 3x3 stride-2 max
+    pooling, three fully_connected layers (the first over a 3x3 map), softmax; 1e-2 relative to each output's scale."""
+    spec = topologies.alexnet_fp16(3, seed=5, image=99, convs=((32, 11, 4, 0, 1, True), (64, 5, 1, 2, 2, True), (96, 3, 1, 1, 1, False),
+                                                                (96, 3, 1, 1, 2, False), (64, 3, 1, 1, 2, False)),
+                                   classes=10, fc_width=64, w_std=0.05)
+    lay = spec.input_layout
+    x = np.random.default_rng(8).standard_normal((lay.size.batch, lay.size.feature, lay.size.y, lay.size.x)).astype(np.float16)
+    want = oracle_net.run(spec, {spec.input_id: x})
+    net, got = _run(eng, spec, x, optimize_data=optimize)
+    for k in spec.outputs:
+        w, g = want[k].astype(np.float32), got[k].astype(np.float32)
+        scale = float(np.abs(w).max())
+        assert scale > 0 and np.abs(g - w).max() <= 1e-2 * scale, "%s: max abs error %.4g on scale %.4g" % (k, float(np.abs(g - w).max()), scale)
+    info = net.primitives_info()
+    convs = [r for r in info if r["type"] == "convolution"]
+    fcs = [r for r in info if r["type"] == "fully_connected"]
+    assert len(convs) == 5 and len(fcs) == 3
+    if optimize:
+        assert [r["kernel"] for r in convs] == ["conv_first_tc"] + ["conv_f16_tc"] * 4, [r["kernel"] for r in convs]
+        assert all(r["kernel"] == "conv_f16_tc" for r in fcs), [r["kernel"] for r in fcs]
+        # LRN and pooling stay in the feature-innermost layout: no reorder between the first convolution and the last pooling
+        assert sum(1 for r in info if r["type"] == "reorder" and r["kernel"]) <= 2, [(r["id"], r["kernel"]) for r in info if r["type"] == "reorder"]
 
 
 @pytest.mark.parametrize("optimize", [False, True])
