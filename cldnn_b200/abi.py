@@ -107,7 +107,10 @@ class FcParams(C.Structure):
 
 
 class SoftmaxParams(C.Structure):
-    _fields_ = [("in_", Tensor), ("out", Tensor), ("reserved", C.c_int32 * 4)]
+    _fields_ = [("in_", Tensor), ("out", Tensor), ("dimension", C.c_int32), ("reserved", C.c_int32 * 3)]
+
+
+SOFTMAX_F, SOFTMAX_X, SOFTMAX_Y, SOFTMAX_FYX = 0, 1, 2, 3
 
 
 class EltwiseParams(C.Structure):

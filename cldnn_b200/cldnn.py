@@ -76,6 +76,7 @@ _SIGNATURES = {
     "cldnn_host_add_pooling": (_i, [_vp, _cp, _cp, _i, _u, _i, _i, _i, _i, _i, _i]),
     "cldnn_host_add_fully_connected": (_i, [_vp, _cp, _cp, _cp, _cp, _cp, _cp, _f, _f, _u, _f]),
     "cldnn_host_add_softmax": (_i, [_vp, _cp, _cp]),
+    "cldnn_host_add_softmax_dim": (_i, [_vp, _cp, _cp, C.c_int32]),
     "cldnn_host_add_lrn": (_i, [_vp, _cp, _cp, _u, _f, _f, _f]),
     "cldnn_host_network_build": (_i, [_vp, _vp, C.POINTER(_BuildOptions), C.POINTER(_vp)]),
     "cldnn_host_network_release": (_i, [_vp]),
@@ -326,8 +327,13 @@ def fully_connected(id, input, weights, bias="", weights_quantization_factors=""
                      activation_negative_slope=activation_negative_slope)
 
 
-def softmax(id, input):
-    return primitive("softmax", id, input=input)
+class softmax_dimension:
+    """softmax::dimension_t (api/CPP/softmax.hpp:44-50)."""
+    normalize_f, normalize_x, normalize_y, normalize_fyx = 0, 1, 2, 3
+
+
+def softmax(id, input, dimension=softmax_dimension.normalize_fyx):
+    return primitive("softmax", id, input=input, dimension=dimension)
 
 
 def lrn(id, input, size=5, k=1.0, alpha=1e-4, beta=0.75):
@@ -387,7 +393,7 @@ class topology:
                                                             _b(a["output_calibration_factors"]), a["input_quantization_factor"], a["output_quantization_factor"],
                                                             int(a["with_activation"]), a["activation_negative_slope"])
                 elif k == "softmax":
-                    st = lib.cldnn_host_add_softmax(h, _b(p.id), _b(a["input"]))
+                    st = lib.cldnn_host_add_softmax_dim(h, _b(p.id), _b(a["input"]), int(a.get("dimension", 3)))
                 elif k == "lrn":
                     st = lib.cldnn_host_add_lrn(h, _b(p.id), _b(a["input"]), a["size"], a["k"], a["alpha"], a["beta"])
                 else:

@@ -38,6 +38,7 @@ constexpr int kBuilders = kBuildWarps * 32;
 constexpr int kMmaWarp = kBuildWarps + kEpiWarps;
 constexpr int kThreads = (kBuildWarps + kEpiWarps + 1) * 32;
 constexpr int kStages = 4;
+constexpr int kAccBufs = 4;                       // most accumulator buffers in tensor memory (ofm columns each)
 constexpr int kStageBytes = 128 * 128;            // 128 pixels x 8 cores x 16 bytes
 constexpr int kMaxK = 1024;                       // table entries (elements of K)
 constexpr int kMaxOfm = 256;
@@ -52,14 +53,22 @@ struct Params {
     int64_t out_px, out_py, out_pb, out_off;         // elements
     uint32_t idesc, tmem_cols, sbo_b;
     int32_t bias_dtype, act; float act_m, act_n;     // fp16 epilogue
+    int32_t nacc;                                    // accumulator buffers in tensor memory: up to kAccBufs of ofm columns each
+    int32_t debug;                                   // diagnostic builds (-DCONV_TC_DEBUG): what-if switches, 0 otherwise
     int32_t mul_iqf, mul_oqf, lean;                  // 8-bit epilogue (lean: per-feature scale, optional uniform O_QF, NONE / ReLU, integer bias)
     const void* in; void* out; const uint8_t* wpacked; const int2* table; const void* bias; const float* quant; const float* calib;
     uint32_t* status;
     EpiCfg epi;
 };
 
+#ifdef CONV_TC_DEBUG
+#define FTC_DEBUG(P, bit) (((P).debug >> (bit)) & 1)
+#else
+#define FTC_DEBUG(P, bit) 0
+#endif
+
 struct Aux {
-    uint64_t a_full[kStages], a_empty[kStages], tmem_full[2], tmem_empty[2];
+    uint64_t a_full[kStages], a_empty[kStages], tmem_full[kAccBufs], tmem_empty[kAccBufs];
     uint32_t tmem_base, abort;
     alignas(16) int32_t bias_i[1][kMaxOfm];
     alignas(16) float bias_f[1][kMaxOfm];
@@ -107,6 +116,23 @@ __global__ void first_tc_pack(const T* __restrict__ w, int64_t po, int64_t pi, i
     }
 }
 
+// (image, row, column) of one output pixel, advanced by a fixed number of pixels per tile without divisions
+struct PixelWalk {
+    int n, p, q, dn, dp, dq, Pn, Q;
+    __device__ __forceinline__ void init(uint32_t first, uint32_t step, int Pn_, int Q_)
+    {
+        Pn = Pn_; Q = Q_;
+        q = (int)(first % (uint32_t)Q); uint32_t t = first / (uint32_t)Q; p = (int)(t % (uint32_t)Pn); n = (int)(t / (uint32_t)Pn);
+        dq = (int)(step % (uint32_t)Q); t = step / (uint32_t)Q; dp = (int)(t % (uint32_t)Pn); dn = (int)(t / (uint32_t)Pn);
+    }
+    __device__ __forceinline__ void next()
+    {
+        q += dq; if (q >= Q) { q -= Q; ++p; }
+        p += dp; if (p >= Pn) { p -= Pn; ++n; }
+        n += dn;
+    }
+};
+
 __device__ __forceinline__ uint32_t load_elem(const __half* p) { return (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p)); }
 __device__ __forceinline__ uint32_t load_elem(const uint8_t* p) { return (uint32_t)__ldg(p); }
 
@@ -137,8 +163,8 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
     const EpiCfg& c = P.epi;
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&aux->a_full[i]), kBuilders); mbar_init(smem_u32(&aux->a_empty[i]), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&aux->tmem_full[i]), 1); mbar_init(smem_u32(&aux->tmem_empty[i]), kEpiWarps); }
+        for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&aux->a_full[i]), kBuildWarps); mbar_init(smem_u32(&aux->a_empty[i]), 1); }
+        for (int i = 0; i < kAccBufs; ++i) { mbar_init(smem_u32(&aux->tmem_full[i]), 1); mbar_init(smem_u32(&aux->tmem_empty[i]), kEpiWarps); }
         aux->abort = 0u;
         mbar_fence_init();
     }
@@ -161,7 +187,6 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
     const int my_tiles = (P.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int pq = P.Pn * P.Q;
 
     if (warp < kBuildWarps) {
         // ------------------------------ gather ------------------------------------
@@ -169,21 +194,28 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
         const T* in = reinterpret_cast<const T*>(P.in) + P.in_off;
         uint8_t* dst0 = sA + (m >> 3) * 1024 + (m & 7) * 16;
         int stage = 0; uint32_t phase = 0; bool ok = true;
-        for (int it = 0; it < my_tiles && ok; ++it) {
-            const int64_t mg = (int64_t)(blockIdx.x + it * gridDim.x) * 128 + m;
-            const bool valid = mg < P.M_total;
-            const int n = (int)(mg / pq); const int rr = (int)(mg - (int64_t)n * pq); const int p = rr / P.Q, q = rr - p * P.Q;
+        PixelWalk px; px.init(blockIdx.x * 128u + (uint32_t)m, gridDim.x * 128u, P.Pn, P.Q);      // the host admits fewer than 2^31 pixels
+        for (int it = 0; it < my_tiles && ok; ++it, px.next()) {
+            const bool valid = px.n < P.N;
+            const int n = px.n, p = px.p, q = px.q;
             const int y0 = p * P.sy - P.pad_y, x0 = q * P.sx - P.pad_x;
             const T* src = in + (int64_t)n * P.in_pb + (int64_t)y0 * P.in_py + (int64_t)x0 * P.in_px;   // dereferenced only at taps inside the image
             const bool interior = valid && y0 >= 0 && y0 + P.ext_y < P.H && x0 >= 0 && x0 + P.ext_x < P.W;
             for (int ch = 0; ch < P.chunks; ++ch) {
-                if (!mbar_wait(smem_u32(&aux->a_empty[stage]), phase ^ 1u, s_abort, P.status, kErr + 1u)) { ok = false; break; }
+                // one lane per warp polls the barrier, and one arrives for the warp: 256 threads on one shared-memory word serialise
+                if (lane == 0) ok = mbar_wait(smem_u32(&aux->a_empty[stage]), phase ^ 1u, s_abort, P.status, kErr + 1u);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                __syncwarp();
+                if (!ok) break;
                 const int ncore = min(8, P.cores - ch * 8);
                 uint8_t* dst = dst0 + stage * kStageBytes;
                 for (int j = half; j < ncore; j += 2) {
                     const int kb = (ch * 8 + j) * EPC;
                     uint32_t e[EPC];
-                    if (interior && kb + EPC <= P.K) {
+                    if (FTC_DEBUG(P, 0)) {
+#pragma unroll
+                        for (int i = 0; i < EPC; ++i) e[i] = (uint32_t)(kb + i);
+                    } else if (interior && kb + EPC <= P.K) {
 #pragma unroll
                         for (int i = 0; i < EPC; i += 2) {
                             const int4 t = *reinterpret_cast<const int4*>(&sTab[kb + i]);
@@ -209,7 +241,8 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
                     *reinterpret_cast<uint4*>(dst + j * 128) = v;
                 }
                 fence_async_smem();
-                mbar_arrive(smem_u32(&aux->a_full[stage]));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->a_full[stage]));
                 if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -218,7 +251,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; bool ok = true;
             for (int it = 0; it < my_tiles && ok; ++it) {
-                const int buf = it & 1; const uint32_t par = (uint32_t)(it >> 1) & 1u;
+                const int buf = it % P.nacc; const uint32_t par = (uint32_t)(it / P.nacc) & 1u;
                 if (!mbar_wait(smem_u32(&aux->tmem_empty[buf]), par ^ 1u, s_abort, P.status, kErr + 2u)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.ofm);
@@ -229,6 +262,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
                     const uint64_t adesc = desc_interleaved(smem_u32(sA + stage * kStageBytes), 128u, 1024u);
                     const uint64_t bdesc = desc_interleaved(smem_u32(sB + ch * 8 * 128), 128u, P.sbo_b);
                     for (int i = 0; i < nm; ++i) {
+                        if (FTC_DEBUG(P, 2)) break;
                         if (kHalf) mma_f16_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
                         else mma_i8_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
                     }
@@ -242,13 +276,13 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
         // ------------------------------ epilogue ----------------------------------
         const int quad = warp & 3;                              // warps 8..11 -> TMEM lanes 32*quad ..
         const int row = quad * 32 + lane;
-        for (int it = 0; it < my_tiles; ++it) {
-            const int buf = it & 1;
-            const int64_t mg = (int64_t)(blockIdx.x + it * gridDim.x) * 128 + row;
-            const bool valid = mg < P.M_total;
-            const int n = (int)(mg / pq); const int rr = (int)(mg - (int64_t)n * pq); const int p = rr / P.Q, q = rr - p * P.Q;
+        PixelWalk px; px.init(blockIdx.x * 128u + (uint32_t)row, gridDim.x * 128u, P.Pn, P.Q);
+        for (int it = 0; it < my_tiles; ++it, px.next()) {
+            const int buf = it % P.nacc;
+            const bool valid = px.n < P.N;
+            const int n = px.n, p = px.p, q = px.q;
             T* out_row = reinterpret_cast<T*>(P.out) + P.out_off + (int64_t)n * P.out_pb + (int64_t)p * P.out_py + (int64_t)q * P.out_px;
-            if (!mbar_wait(smem_u32(&aux->tmem_full[buf]), (uint32_t)(it >> 1) & 1u, s_abort, P.status, kErr)) break;
+            if (!mbar_wait(smem_u32(&aux->tmem_full[buf]), (uint32_t)(it / P.nacc) & 1u, s_abort, P.status, kErr)) break;
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * P.ofm);
 #pragma unroll 1
@@ -257,7 +291,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
                 tmem_ld_32x32(t_row + (uint32_t)c0, r);
                 tmem_ld_wait();
                 if (c0 + 32 >= P.ofm) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[buf])); }
-                if (!valid) continue;
+                if (!valid || FTC_DEBUG(P, 1)) continue;
                 if (kHalf) {
                     uint4* op = reinterpret_cast<uint4*>(out_row + c0);
 #pragma unroll
@@ -333,6 +367,7 @@ static bool ftc_plan(const cldnn_b200_conv_params& p, std::string* why)
     const int Q_ = (p.in.x + 2 * p.pad_x - ((p.kw - 1) * p.dil_x + 1)) / p.stride_x + 1;
     if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
     if (ftc_smem(p) > 200 * 1024) return no("weights do not fit in shared memory");
+    if ((int64_t)p.out.b * p.out.y * p.out.x + 128 >= 0x7fffffffLL) return no("too many output pixels");
     // the gather table holds 32-bit element offsets from the window origin
     if ((int64_t)p.ifm * p.in.pf + (int64_t)p.kh * p.dil_y * p.in.py + (int64_t)p.kw * p.dil_x * p.in.px > 0x7fffffffLL) return no("input too large");
     return true;
@@ -374,7 +409,13 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
     if (half) P.idesc = (1u << 4) | ((uint32_t)(p.ofm >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);          // f16 x f16 -> f32
     else P.idesc = (2u << 4) | ((p.in.dtype == CLDNN_B200_U8 ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(p.ofm >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    uint32_t cols = 32; while (cols < (uint32_t)(2 * p.ofm)) cols <<= 1;   // two accumulator buffers
+    // CTAs per SM and accumulator buffers: two CTAs (when shared memory holds two) with at least two accumulators each
+    // inside half of the SM's 512 columns of tensor memory, else one CTA with up to four
+    const size_t smem = ftc_smem(p);
+    if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_first_tc: not enough shared memory");
+    int per_sm = (ctx->prop.sharedMemPerMultiprocessor / (smem + 1024) >= 2 && 256 / p.ofm >= 2) ? 2 : 1;
+    P.nacc = std::min(firsttc::kAccBufs, (per_sm == 2 ? 256 : 512) / p.ofm);
+    uint32_t cols = 32; while (cols < (uint32_t)(P.nacc * p.ofm)) cols <<= 1;
     P.tmem_cols = cols;
     P.sbo_b = (uint32_t)P.cores * 128u;
     P.bias_dtype = p.bias_dtype; P.act = p.act; P.act_m = p.act_m; P.act_n = p.act_n;
@@ -386,9 +427,10 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.table = (const int2*)((const uint8_t*)a->scratch + ftc_table_offset(p));
     P.bias = a->bias; P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors;
     P.status = ctx->d_status;
+#ifdef CONV_TC_DEBUG
+    if (const char* e = getenv("CLDNN_B200_TC_DEBUG")) P.debug = atoi(e);
+#endif
 
-    const size_t smem = ftc_smem(p);
-    if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_first_tc: not enough shared memory");
     // pack the weights and build the table once, on the context's stream, before anything that is prepared here can run
     const int pack_blocks = (p.ofm * P.cores * (16 / es) + 255) / 256;
     if (half) {
@@ -401,10 +443,6 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
                                                                                P.cores, (uint8_t*)a->scratch, (int2*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     }
     B200_CUDA(cudaGetLastError());
-    // CTAs per SM: bounded by shared memory, tensor memory (512 columns) and the register file
-    int per_sm = (int)(ctx->prop.sharedMemPerMultiprocessor / (smem + 1024));
-    per_sm = std::min(per_sm, std::min(2, (int)(512 / P.tmem_cols)));
-    if (per_sm < 1) per_sm = 1;
     int grid = ctx->prop.multiProcessorCount * per_sm;
     if (grid > P.total_tiles) grid = P.total_tiles;
     out->fn = [P, grid, smem, half](cudaStream_t s) {

@@ -111,13 +111,16 @@ conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __gr
 {
     extern __shared__ uint4 s_dw[];
     const int C = p.out.f, taps = p.kh * p.kw;
-    uint4* s_w = s_dw;                                               // [tap][C / 4] groups of 4 masked weight words
+    uint4* s_w = s_dw;                                               // [tap][k][C / 16]: the 4 weight words of features 16 g + 4 k .. + 3 (threads of a warp differ in g: consecutive 16-byte reads)
     int32_t* s_bias = reinterpret_cast<int32_t*>(s_dw + taps * (C / 4));
     float* s_quant = reinterpret_cast<float*>(s_bias + C);
     __shared__ uint32_t s_wide;
     if (threadIdx.x == 0) s_wide = 0u;
     __syncthreads();
-    for (int i = threadIdx.x; i < taps * (C / 4); i += blockDim.x) s_w[i] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
+    for (int i = threadIdx.x; i < taps * (C / 4); i += blockDim.x) {
+        const int tap = i / (C / 4), r = i - tap * (C / 4);          // global order [tap][g][k]
+        s_w[(tap * 4 + (r & 3)) * a.c16n + (r >> 2)] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
+    }
     bool wide = false;
     for (int f = threadIdx.x; f < C; f += blockDim.x) {
         const int32_t bi = (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? load_as_int(a.bias, p.bias_dtype, f) : 0;
@@ -153,10 +156,10 @@ conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __gr
                 if (va) x_a = __ldg(reinterpret_cast<const uint4*>(rowp + (int64_t)xa * p.in.px));
                 if (vb) x_b = __ldg(reinterpret_cast<const uint4*>(rowp + (int64_t)xb * p.in.px));
                 const uint32_t xw_a[4] = {x_a.x, x_a.y, x_a.z, x_a.w}, xw_b[4] = {x_b.x, x_b.y, x_b.z, x_b.w};
-                const uint4* wt = s_w + (j * p.kw + s) * c4n + g * 4;
+                const uint4* wt = s_w + (j * p.kw + s) * c4n + g;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {                          // 4 words of 4 features
-                    const uint4 wm = wt[k];
+                    const uint4 wm = wt[k * a.c16n];
                     acc0[4 * k + 0] = dp4a_in<kUnsignedIn>(xw_a[k], wm.x, acc0[4 * k + 0]); acc1[4 * k + 0] = dp4a_in<kUnsignedIn>(xw_b[k], wm.x, acc1[4 * k + 0]);
                     acc0[4 * k + 1] = dp4a_in<kUnsignedIn>(xw_a[k], wm.y, acc0[4 * k + 1]); acc1[4 * k + 1] = dp4a_in<kUnsignedIn>(xw_b[k], wm.y, acc1[4 * k + 1]);
                     acc0[4 * k + 2] = dp4a_in<kUnsignedIn>(xw_a[k], wm.z, acc0[4 * k + 2]); acc1[4 * k + 2] = dp4a_in<kUnsignedIn>(xw_b[k], wm.z, acc1[4 * k + 2]);

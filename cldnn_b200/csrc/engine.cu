@@ -23,9 +23,9 @@ int32_t cuda_fail(cudaError_t e, const char* what)
 
 static const KernelDef* const g_kernels[] = {
     &kdef_conv_i8_tc, &kdef_conv_i8_first, &kdef_conv_first_tc, &kdef_conv_f16_tc, &kdef_conv_f16_winograd, &kdef_conv_i8_dw, &kdef_conv_ref,
-    &kdef_pooling_i8_byxf, &kdef_pooling_ref,
+    &kdef_pooling_i8_byxf, &kdef_pooling_f16_byxf, &kdef_pooling_ref,
     &kdef_fc_ref, &kdef_softmax, &kdef_eltwise_ref, &kdef_reorder_ref,
-    &kdef_lrn_ref, &kdef_activation_ref,
+    &kdef_lrn_f16_byxf, &kdef_lrn_ref, &kdef_activation_ref,
 };
 static const int g_kernel_count = (int)(sizeof(g_kernels) / sizeof(g_kernels[0]));
 

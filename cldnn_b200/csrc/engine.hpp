@@ -68,6 +68,8 @@ extern const KernelDef kdef_conv_f16_winograd;
 extern const KernelDef kdef_conv_i8_dw;
 extern const KernelDef kdef_pooling_ref;
 extern const KernelDef kdef_pooling_i8_byxf;
+extern const KernelDef kdef_pooling_f16_byxf;
+extern const KernelDef kdef_lrn_f16_byxf;
 extern const KernelDef kdef_fc_ref;
 extern const KernelDef kdef_softmax;
 extern const KernelDef kdef_eltwise_ref;

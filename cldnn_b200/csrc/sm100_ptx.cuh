@@ -60,7 +60,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     const uint64_t t0 = globaltimer();
 #pragma unroll 1
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
+        // the clock is read once per batch of polls: reading it costs far more than a poll and would delay the wake-up
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) if (mbar_try_wait(bar, parity)) return true;
         if (*s_abort) return false;
         if (globaltimer() - t0 > kWaitLimitNs) {
             *s_abort = 1u;

@@ -2,6 +2,7 @@
 // (reference order), softmax, eltwise, reorder, lrn and standalone activation.
 // The *_ref kernels take any layout through pitches; pooling_i8_byxf is the
 // feature-innermost fast path with 16-byte accesses per lane.
+#include <cuda_fp16.h>
 #include "engine.hpp"
 
 namespace b200 {
@@ -199,6 +200,84 @@ static int32_t pooling_i8_byxf_prepare(cldnn_b200_ctx_impl* ctx, const void* vp,
 const KernelDef kdef_pooling_i8_byxf = {"pooling_i8_byxf", sizeof(cldnn_b200_pool_params), pooling_i8_byxf_supports, one_tune, nullptr, pooling_i8_byxf_prepare};
 
 // ---------------------------------------------------------------------------------
+// pooling, fp16, feature-innermost (byxf): each thread owns 8 consecutive features of one
+// output pixel, one 128-bit load per window tap and one 128-bit store; the maximum on
+// packed halves, the average accumulated in fp32.  Same arithmetic as pooling_gpu_ref.cl
+// (its half accumulator for the average is replaced by a float one: tolerance parity).
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+pooling_f16_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const __half* __restrict__ in, __half* __restrict__ out)
+{
+    const int fv = p.in.f / 8;
+    const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
+    const bool is_max = p.mode == CLDNN_B200_POOL_MAX;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int f8 = (int)(idx % fv); int64_t t = idx / fv;
+        const int x = (int)(t % p.out.x); t /= p.out.x;
+        const int y = (int)(t % p.out.y); const int b = (int)(t / p.out.y);
+        const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
+        if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
+        const int j0 = max(0, -oy), j1 = min(p.size_y, p.in.y - oy), i0 = max(0, -ox), i1 = min(p.size_x, p.in.x - ox);
+        const __half* src = in + tidx(p.in, b, f8 * 8, oy, ox);
+        const __half2 lowest = __half2half2(__ushort_as_half((unsigned short)0xfbffu));      // -65504, the reference's HALF_MIN start value
+        __half2 m[4] = {lowest, lowest, lowest, lowest};
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint32_t n = 0;
+        for (int j = j0; j < j1; ++j) {
+            for (int i = i0; i < i1; ++i) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)j * p.in.py + (int64_t)i * p.in.px));
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+                if (is_max) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) m[k] = __hmax2(m[k], h[k]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); acc[2 * k] += f.x; acc[2 * k + 1] += f.y; }
+                }
+                ++n;
+            }
+        }
+        float r[8];
+        if (is_max) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(m[k]); r[2 * k] = f.x; r[2 * k + 1] = f.y; }
+        } else {
+            const float div = (float)pool_divisor(p, ox, oy, n);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) r[k] = __fdiv_rn(acc[k], div);
+        }
+        __half2 o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            o[k] = __floats2half2_rn(act_float(p.act, r[2 * k], p.act_m, p.act_n), act_float(p.act, r[2 * k + 1], p.act_m, p.act_n));
+        *reinterpret_cast<uint4*>(out + tidx(p.out, b, f8 * 8, y, x)) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
+static bool pooling_f16_byxf_supports(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_pool_params*)vp;
+    if (!pooling_ref_supports(vp)) return false;
+    if (p.in.dtype != CLDNN_B200_F16 || p.out.dtype != CLDNN_B200_F16) return false;
+    if (p.in.pf != 1 || p.out.pf != 1 || p.in.f % 8) return false;
+    const int64_t pitches[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
+    for (int64_t v : pitches) if (v % 8) return false;
+    return true;
+}
+
+static int32_t pooling_f16_byxf_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_pool_params p = *(const cldnn_b200_pool_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "pooling_f16_byxf: input and output are required");
+    if (((uintptr_t)a->input0 | (uintptr_t)a->output) & 15) return fail(CLDNN_B200_INVALID_ARG, "pooling_f16_byxf: buffers must be 16-byte aligned");
+    const __half* in = (const __half*)a->input0; __half* o = (__half*)a->output;
+    const int grid = grid_for((int64_t)p.out.b * p.out.y * p.out.x * (p.in.f / 8), 256, ctx);
+    out->fn = [p, in, o, grid](cudaStream_t s) { pooling_f16_byxf_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_pooling_f16_byxf = {"pooling_f16_byxf", sizeof(cldnn_b200_pool_params), pooling_f16_byxf_supports, one_tune, nullptr, pooling_f16_byxf_prepare};
+
+// ---------------------------------------------------------------------------------
 // fully_connected in the reference's order (cl_kernels/fully_connected_gpu_bfyx_ref.cl:18-84):
 // one warp per output, lanes stride the reduction, shuffle-reduce (integer sums
 // are order-independent; float sums are tolerance-checked).
@@ -261,24 +340,47 @@ const KernelDef kdef_fc_ref = {"fc_ref", sizeof(cldnn_b200_fc_params), fc_ref_su
 // softmax over features (cl_kernels/softmax_gpu_ref.cl:22-58): one warp per
 // (b, y, x) row; max, sum and normalise with warp shuffles, float accumulation.
 // ---------------------------------------------------------------------------------
+// set index + position inside the set -> coordinates, by the scope of normalisation (api/C/softmax.h:34-40)
+__device__ __forceinline__ void softmax_coords(const cldnn_b200_softmax_params& p, int64_t set, int i, int& b, int& f, int& y, int& x)
+{
+    const int F = p.in.f, Y = p.in.y, X = p.in.x;
+    switch (p.dimension) {
+    case CLDNN_B200_SOFTMAX_X:   x = i; y = (int)(set % Y); f = (int)((set / Y) % F); b = (int)(set / ((int64_t)Y * F)); break;
+    case CLDNN_B200_SOFTMAX_Y:   y = i; x = (int)(set % X); f = (int)((set / X) % F); b = (int)(set / ((int64_t)X * F)); break;
+    case CLDNN_B200_SOFTMAX_FYX: x = i % X; y = (i / X) % Y; f = i / (X * Y); b = (int)set; break;
+    default:                     f = i; x = (int)(set % X); y = (int)((set / X) % Y); b = (int)(set / ((int64_t)X * Y)); break;
+    }
+}
+__host__ __device__ inline int64_t softmax_len(const cldnn_b200_softmax_params& p)
+{
+    switch (p.dimension) {
+    case CLDNN_B200_SOFTMAX_X: return p.in.x;
+    case CLDNN_B200_SOFTMAX_Y: return p.in.y;
+    case CLDNN_B200_SOFTMAX_FYX: return (int64_t)p.in.f * p.in.y * p.in.x;
+    default: return p.in.f;
+    }
+}
+
 __global__ void __launch_bounds__(256)
 softmax_kernel(const __grid_constant__ cldnn_b200_softmax_params p, const void* in, void* out)
 {
     const int lane = threadIdx.x & 31;
     const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-    const int64_t rows = (int64_t)p.in.b * p.in.y * p.in.x;
-    for (int64_t r = warp; r < rows; r += nwarps) {
-        const int x = (int)(r % p.in.x), y = (int)((r / p.in.x) % p.in.y), b = (int)(r / ((int64_t)p.in.x * p.in.y));
+    const int len = (int)softmax_len(p);
+    const int64_t sets = len > 0 ? ((int64_t)p.in.b * p.in.f * p.in.y * p.in.x) / len : 0;
+    for (int64_t r = warp; r < sets; r += nwarps) {
+        int b, f, y, x;
         float mx = -3.402823466e38f;
-        for (int f = lane; f < p.in.f; f += 32) mx = fmaxf(mx, load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)));
+        for (int i = lane; i < len; i += 32) { softmax_coords(p, r, i, b, f, y, x); mx = fmaxf(mx, load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x))); }
 #pragma unroll
         for (int s = 16; s; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
         float den = 0.f;
-        for (int f = lane; f < p.in.f; f += 32) den += expf(load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)) - mx);
+        for (int i = lane; i < len; i += 32) { softmax_coords(p, r, i, b, f, y, x); den += expf(load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)) - mx); }
 #pragma unroll
         for (int s = 16; s; s >>= 1) den += __shfl_xor_sync(0xffffffffu, den, s);
-        for (int f = lane; f < p.in.f; f += 32) {
+        for (int i = lane; i < len; i += 32) {
+            softmax_coords(p, r, i, b, f, y, x);
             const float e = expf(load_as_float(in, p.in.dtype, tidx(p.in, b, f, y, x)) - mx);
             store_sat_float(out, p.out.dtype, tidx(p.out, b, f, y, x), __fdiv_rn(e, den));
         }
@@ -336,15 +438,24 @@ softmax_row_kernel(const __grid_constant__ cldnn_b200_softmax_params p, const vo
         }
     }
 }
-static bool softmax_supports(const void* vp) { const auto& p = *(const cldnn_b200_softmax_params*)vp; return is_fp(p.in.dtype) && is_fp(p.out.dtype) && p.in.f == p.out.f; }
+static bool softmax_supports(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_softmax_params*)vp;
+    return is_fp(p.in.dtype) && is_fp(p.out.dtype) && p.in.f == p.out.f && p.in.x == p.out.x && p.in.y == p.out.y && p.in.b == p.out.b &&
+           p.dimension >= CLDNN_B200_SOFTMAX_F && p.dimension <= CLDNN_B200_SOFTMAX_FYX && softmax_len(p) < 0x7fffffffLL;
+}
 static int32_t softmax_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
     const cldnn_b200_softmax_params p = *(const cldnn_b200_softmax_params*)vp;
     if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "softmax: input and output are required");
     const void* in = a->input0; void* o = a->output;
-    const int grid = grid_for((int64_t)p.in.b * p.in.y * p.in.x * 32, 256, ctx);
+    const int64_t len = softmax_len(p);
+    const int64_t sets = len > 0 ? ((int64_t)p.in.b * p.in.f * p.in.y * p.in.x) / len : 0;
+    const int grid = grid_for(sets * 32, 256, ctx);
+    // the block-per-row kernel normalises over f; over a 1x1 map the whole-image scope is the same thing
+    const bool over_f = p.dimension == CLDNN_B200_SOFTMAX_F || (p.dimension == CLDNN_B200_SOFTMAX_FYX && p.in.x == 1 && p.in.y == 1);
     const int64_t rows = (int64_t)p.in.b * p.in.y * p.in.x;
-    const bool by_row = p.in.f >= 256 && p.in.f <= 256 * kSoftmaxPerThread && rows <= (int64_t)ctx->prop.multiProcessorCount * 32;
+    const bool by_row = over_f && p.in.f >= 256 && p.in.f <= 256 * kSoftmaxPerThread && rows <= (int64_t)ctx->prop.multiProcessorCount * 32;
     const int row_grid = (int)(rows < 1 ? 1 : rows);
     out->fn = [=](cudaStream_t s) {
         if (by_row) softmax_row_kernel<<<row_grid, 256, 0, s>>>(p, in, o);
@@ -467,6 +578,67 @@ lrn_ref_kernel(const __grid_constant__ cldnn_b200_lrn_params p, const void* in, 
         store_sat_float(out, p.out.dtype, tidx(p.out, b, f, y, x), v * powf(acc, -p.beta));
     }
 }
+// The same for fp16 in the feature-innermost (byxf) layout, window 5: a thread owns 8 consecutive features of one pixel,
+// reads them with one 128-bit load and the two neighbours on either side with one 32-bit load each, keeps the squares
+// in fp32 and writes 8 halves; x^-beta = exp2(-beta * log2(x)) on the special-function unit (the reference's
+// native_powr is as loosely specified).
+__global__ void __launch_bounds__(256)
+lrn_f16_byxf_kernel(const __grid_constant__ cldnn_b200_lrn_params p, const __half* __restrict__ in, __half* __restrict__ out)
+{
+    const int fv = p.in.f / 8;
+    const int64_t total = (int64_t)p.in.b * p.in.y * p.in.x * fv;
+    const float scale = __fdiv_rn(p.alpha, (float)p.size);
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int f8 = (int)(idx % fv); int64_t t = idx / fv;
+        const int x = (int)(t % p.in.x); t /= p.in.x;
+        const int y = (int)(t % p.in.y); const int b = (int)(t / p.in.y);
+        const int f0 = f8 * 8;
+        const __half* src = in + tidx(p.in, b, f0, y, x);
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+        float val[12];                                               // features f0 - 2 .. f0 + 9
+        {
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __half22float2(h[k]); val[2 + 2 * k] = f.x; val[3 + 2 * k] = f.y; }
+            float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+            if (f0 >= 2) lo = __half22float2(__ldg(reinterpret_cast<const __half2*>(src - 2)));
+            if (f0 + 8 < p.in.f) hi = __half22float2(__ldg(reinterpret_cast<const __half2*>(src + 8)));
+            if (f0 + 9 >= p.in.f) hi.y = 0.f;
+            val[0] = lo.x; val[1] = lo.y; val[10] = hi.x; val[11] = hi.y;
+        }
+        float sq[12];
+#pragma unroll
+        for (int k = 0; k < 12; ++k) sq[k] = val[k] * val[k];
+        __half2 o[4];
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) {
+            const float a0 = fmaf(sq[k] + sq[k + 1] + sq[k + 2] + sq[k + 3] + sq[k + 4], scale, p.k);
+            const float a1 = fmaf(sq[k + 1] + sq[k + 2] + sq[k + 3] + sq[k + 4] + sq[k + 5], scale, p.k);
+            o[k >> 1] = __floats2half2_rn(val[k + 2] * exp2f(-p.beta * __log2f(a0)), val[k + 3] * exp2f(-p.beta * __log2f(a1)));
+        }
+        *reinterpret_cast<uint4*>(out + tidx(p.out, b, f0, y, x)) = *reinterpret_cast<const uint4*>(o);
+    }
+}
+static bool lrn_f16_byxf_supports(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_lrn_params*)vp;
+    if (p.size != 5 || p.in.dtype != CLDNN_B200_F16 || p.out.dtype != CLDNN_B200_F16) return false;
+    if (p.in.pf != 1 || p.out.pf != 1 || p.in.f % 8) return false;
+    const int64_t pitches[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
+    for (int64_t v : pitches) if (v % 8) return false;
+    return true;
+}
+static int32_t lrn_f16_byxf_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_lrn_params p = *(const cldnn_b200_lrn_params*)vp;
+    if (!a->input0 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "lrn_f16_byxf: input and output are required");
+    if (((uintptr_t)a->input0 | (uintptr_t)a->output) & 15) return fail(CLDNN_B200_INVALID_ARG, "lrn_f16_byxf: buffers must be 16-byte aligned");
+    const __half* in = (const __half*)a->input0; __half* o = (__half*)a->output;
+    const int grid = grid_for((int64_t)p.in.b * p.in.y * p.in.x * (p.in.f / 8), 256, ctx);
+    out->fn = [p, in, o, grid](cudaStream_t s) { lrn_f16_byxf_kernel<<<grid, 256, 0, s>>>(p, in, o); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+
 static bool lrn_supports(const void* vp) { const auto& p = *(const cldnn_b200_lrn_params*)vp; return p.size >= 1 && is_fp(p.in.dtype); }
 static int32_t lrn_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
@@ -478,6 +650,7 @@ static int32_t lrn_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     return CLDNN_B200_SUCCESS;
 }
 const KernelDef kdef_lrn_ref = {"lrn_ref", sizeof(cldnn_b200_lrn_params), lrn_supports, one_tune, nullptr, lrn_prepare};
+const KernelDef kdef_lrn_f16_byxf = {"lrn_f16_byxf", sizeof(cldnn_b200_lrn_params), lrn_f16_byxf_supports, one_tune, nullptr, lrn_f16_byxf_prepare};
 
 // ---------------------------------------------------------------------------------
 // standalone activation (cl_kernels/activation_ref.cl)

@@ -160,6 +160,10 @@ int32_t cldnn_host_add_softmax(cldnn_host_topology t, const char* id, const char
 {
     return guarded([&] { need(t, "add_softmax"); t->t.add(softmax(str(id), str(input))); });
 }
+int32_t cldnn_host_add_softmax_dim(cldnn_host_topology t, const char* id, const char* input, int32_t dimension)
+{
+    return guarded([&] { need(t, "add_softmax_dim"); t->t.add(softmax(str(id), str(input), dimension)); });
+}
 int32_t cldnn_host_add_lrn(cldnn_host_topology t, const char* id, const char* input, uint32_t size, float k, float alpha, float beta)
 {
     return guarded([&] { need(t, "add_lrn"); t->t.add(lrn(str(id), str(input), size, k, alpha, beta)); });

@@ -120,6 +120,7 @@ struct primitive {
     int32_t activation_func = CLDNN_B200_ACT_NONE; float act_a = 0.0f, act_b = 0.0f;
     pooling_mode pool_mode = pooling_mode::max; tensor size{1, 1, 1, 1}; bool global_pooling = false;
     uint32_t lrn_size = 5; float lrn_k = 1.0f, lrn_alpha = 1e-4f, lrn_beta = 0.75f;
+    int32_t softmax_dimension = 3;                                  // softmax::dimension_t: normalize_f 0, _x 1, _y 2, _fyx 3 (the default, api/CPP/softmax.hpp:59)
     layout target;                                        // reorder output layout / input_layout layout
     std::vector<float> subtract_per_feature;              // reorder mean values
     memory mem;                                           // data
@@ -151,7 +152,8 @@ primitive global_pooling(const std::string& id, const std::string& input, poolin
 primitive fully_connected(const std::string& id, const std::string& input, const std::string& weights, const std::string& bias,
                           const std::string& w_quantization_factor, const std::string& output_calibration_factors,
                           float i_quantization_factor, bool with_activation = false, float activation_slp = 0.0f);
-primitive softmax(const std::string& id, const std::string& input);
+enum softmax_dimension : int32_t { normalize_f = 0, normalize_x = 1, normalize_y = 2, normalize_fyx = 3 };   // api/CPP/softmax.hpp:44-50
+primitive softmax(const std::string& id, const std::string& input, int32_t dimension = normalize_fyx);
 primitive lrn(const std::string& id, const std::string& input, uint32_t size, float k, float alpha, float beta);
 
 // cldnn::topology -- api/CPP/topology.hpp

@@ -208,7 +208,10 @@ primitive fully_connected(const std::string& id, const std::string& input, const
     p.output_calibration_factors = oc; p.input_quantization_factor = iqf; p.with_activation = with_activation; p.activation_negative_slope = slp;
     return p;
 }
-primitive softmax(const std::string& id, const std::string& input) { primitive p; p.type = "softmax"; p.id = id; p.input = {input}; return p; }
+primitive softmax(const std::string& id, const std::string& input, int32_t dimension)
+{
+    primitive p; p.type = "softmax"; p.id = id; p.input = {input}; p.softmax_dimension = dimension; return p;
+}
 primitive lrn(const std::string& id, const std::string& input, uint32_t size, float k, float alpha, float beta)
 {
     primitive p; p.type = "lrn"; p.id = id; p.input = {input}; p.lrn_size = size; p.lrn_k = k; p.lrn_alpha = alpha; p.lrn_beta = beta; return p;
@@ -849,11 +852,13 @@ void network_impl::prepare_kernel(node* n)
         if (p.pool_mode == pooling_mode::average && dyn) pp.div_mode = CLDNN_B200_DIV_DYNAMIC_WITH_PADDING;
         else pp.div_mode = p.pool_mode == pooling_mode::average_no_padding ? CLDNN_B200_DIV_DYNAMIC : CLDNN_B200_DIV_FIXED;
         pp.act = n->act; pp.act_m = n->act_m; pp.act_n = n->act_n;
-        finish({"pooling_i8_byxf", "pooling_ref"}, &pp, sizeof(pp), [](int) {});
+        finish({"pooling_i8_byxf", "pooling_f16_byxf", "pooling_ref"}, &pp, sizeof(pp), [](int) {});
         return;
     }
     if (t == "softmax") {
         cldnn_b200_softmax_params sp{}; sp.in = n->deps[0]->out.desc(); sp.out = n->out.desc();
+        if (p.softmax_dimension < 0 || p.softmax_dimension > 3) throw error(p.id + ": wrong API - no such softmax dimension", CLDNN_B200_INVALID_ARG);
+        sp.dimension = p.softmax_dimension;
         finish({"softmax"}, &sp, sizeof(sp), [](int) {});
         return;
     }
@@ -881,7 +886,7 @@ void network_impl::prepare_kernel(node* n)
     if (t == "lrn") {
         cldnn_b200_lrn_params lp{}; lp.in = n->deps[0]->out.desc(); lp.out = n->out.desc();
         lp.size = (int32_t)p.lrn_size; lp.k = p.lrn_k; lp.alpha = p.lrn_alpha; lp.beta = p.lrn_beta;
-        finish({"lrn_ref"}, &lp, sizeof(lp), [](int) {});
+        finish({"lrn_f16_byxf", "lrn_ref"}, &lp, sizeof(lp), [](int) {});
         return;
     }
     if (t == "activation") {

@@ -165,11 +165,17 @@ typedef struct cldnn_b200_fc_params {
     int32_t reserved[4];
 } cldnn_b200_fc_params;
 
-/* softmax over the feature axis of a [b][f] (x=y=1) or over f for each (b,y,x)
- * (cl_kernels/softmax_gpu_ref.cl:22-58). */
+/* softmax (cl_kernels/softmax_gpu_ref.cl:22-58).  `dimension` is the scope of normalisation, with the values of
+ * cldnn_softmax_dimension (api/C/softmax.h:34-40): 0 over f for each (b, y, x), 1 over x for each (b, f, y),
+ * 2 over y for each (b, f, x), 3 over the whole f*y*x image of each batch. */
+#define CLDNN_B200_SOFTMAX_F 0
+#define CLDNN_B200_SOFTMAX_X 1
+#define CLDNN_B200_SOFTMAX_Y 2
+#define CLDNN_B200_SOFTMAX_FYX 3
 typedef struct cldnn_b200_softmax_params {
     cldnn_b200_tensor in, out;
-    int32_t reserved[4];
+    int32_t dimension;
+    int32_t reserved[3];
 } cldnn_b200_softmax_params;
 
 /* eltwise (sum / prod / max / min / sub) of two tensors with the optional

@@ -93,7 +93,9 @@ CLDNN_B200_API int32_t cldnn_host_add_fully_connected(cldnn_host_topology t, con
                                                       const char* weights_quantization_factors, const char* output_calibration_factors,
                                                       float input_quantization_factor, float output_quantization_factor,
                                                       uint32_t with_activation, float activation_negative_slope);
-CLDNN_B200_API int32_t cldnn_host_add_softmax(cldnn_host_topology t, const char* id, const char* input);
+CLDNN_B200_API int32_t cldnn_host_add_softmax(cldnn_host_topology t, const char* id, const char* input);   /* normalize_fyx, the reference's default */
+/* dimension: cldnn_softmax_dimension (api/C/softmax.h:34-40): 0 normalize_f, 1 normalize_x, 2 normalize_y, 3 normalize_fyx */
+CLDNN_B200_API int32_t cldnn_host_add_softmax_dim(cldnn_host_topology t, const char* id, const char* input, int32_t dimension);
 CLDNN_B200_API int32_t cldnn_host_add_lrn(cldnn_host_topology t, const char* id, const char* input, uint32_t size, float k, float alpha, float beta);
 
 /* build options, api/C/cldnn.h:207-232 */

@@ -444,24 +444,48 @@ int32_t oracle_fc(const cldnn_b200_fc_params* p, const cldnn_b200_args* a, int32
 }
 
 /*
- * softmax over features.  KERNEL(softmax), cl_kernels/softmax_gpu_ref.cl:22-58:
- * max-subtract, exp, float denominator, divide.  native_exp is
- * implementation-defined on the device, so parity is tolerance-based.
+ * softmax.  KERNEL(softmax), cl_kernels/softmax_gpu_ref.cl:22-58: per set of
+ * values -- max-subtract, exp, float denominator, divide.  The sets follow
+ * `dimension` (actual_kernels/softmax/softmax_items_class_kernel_base.cpp:45-99: the
+ * class axis is x, y or f, the other two axes and the batch enumerate the sets;
+ * src/gpu/softmax_gpu.cpp:42-63: normalize_fyx flattens f, y, x into one class axis).  native_exp is implementation-defined on the
+ * device, so parity is tolerance-based.
  */
+static void softmax_coords(const cldnn_b200_softmax_params* p, int64_t set, int64_t i, int* b, int* f, int* y, int* x)
+{
+    const int F = p->in.f, Y = p->in.y, X = p->in.x;
+    switch (p->dimension) {
+    case CLDNN_B200_SOFTMAX_X:   *x = (int)i; *y = (int)(set % Y); *f = (int)((set / Y) % F); *b = (int)(set / ((int64_t)Y * F)); break;
+    case CLDNN_B200_SOFTMAX_Y:   *y = (int)i; *x = (int)(set % X); *f = (int)((set / X) % F); *b = (int)(set / ((int64_t)X * F)); break;
+    case CLDNN_B200_SOFTMAX_FYX: *x = (int)(i % X); *y = (int)((i / X) % Y); *f = (int)(i / ((int64_t)X * Y)); *b = (int)set; break;
+    default:                     *f = (int)i; *x = (int)(set % X); *y = (int)((set / X) % Y); *b = (int)(set / ((int64_t)X * Y)); break;
+    }
+}
+
 int32_t oracle_softmax(const cldnn_b200_softmax_params* p, const void* in, void* out)
 {
-    for (int b = 0; b < p->in.b; ++b)
-        for (int y = 0; y < p->in.y; ++y)
-            for (int x = 0; x < p->in.x; ++x) {
-                float mx = -3.402823466e38f;
-                for (int f = 0; f < p->in.f; ++f) mx = fmaxf(mx, (float)load_elem(in, p->in.dtype, tidx(&p->in, b, f, y, x)));
-                float den = 0.0f;
-                for (int f = 0; f < p->in.f; ++f) den += expf((float)load_elem(in, p->in.dtype, tidx(&p->in, b, f, y, x)) - mx);
-                for (int f = 0; f < p->in.f; ++f) {
-                    float e = expf((float)load_elem(in, p->in.dtype, tidx(&p->in, b, f, y, x)) - mx);
-                    store_sat_float(out, p->out.dtype, tidx(&p->out, b, f, y, x), e / den);
-                }
-            }
+    const int64_t all = (int64_t)p->in.b * p->in.f * p->in.y * p->in.x;
+    int64_t len;
+    switch (p->dimension) {
+    case CLDNN_B200_SOFTMAX_F:   len = p->in.f; break;
+    case CLDNN_B200_SOFTMAX_X:   len = p->in.x; break;
+    case CLDNN_B200_SOFTMAX_Y:   len = p->in.y; break;
+    case CLDNN_B200_SOFTMAX_FYX: len = (int64_t)p->in.f * p->in.y * p->in.x; break;
+    default: return CLDNN_B200_INVALID_ARG;
+    }
+    if (len <= 0) return CLDNN_B200_SUCCESS;
+    for (int64_t set = 0; set < all / len; ++set) {
+        int b, f, y, x;
+        float mx = -3.402823466e38f;
+        for (int64_t i = 0; i < len; ++i) { softmax_coords(p, set, i, &b, &f, &y, &x); mx = fmaxf(mx, (float)load_elem(in, p->in.dtype, tidx(&p->in, b, f, y, x))); }
+        float den = 0.0f;
+        for (int64_t i = 0; i < len; ++i) { softmax_coords(p, set, i, &b, &f, &y, &x); den += expf((float)load_elem(in, p->in.dtype, tidx(&p->in, b, f, y, x)) - mx); }
+        for (int64_t i = 0; i < len; ++i) {
+            softmax_coords(p, set, i, &b, &f, &y, &x);
+            float e = expf((float)load_elem(in, p->in.dtype, tidx(&p->in, b, f, y, x)) - mx);
+            store_sat_float(out, p->out.dtype, tidx(&p->out, b, f, y, x), e / den);
+        }
+    }
     return CLDNN_B200_SUCCESS;
 }
 

@@ -164,6 +164,7 @@ def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle", fuse
             sp = abi.SoftmaxParams()
             sp.in_ = _tensor(x)
             sp.out = _tensor(x)
+            sp.dimension = int(a.get("dimension", abi.SOFTMAX_FYX))
             res = oracle_lib.softmax(sp, x.reshape(-1)).reshape(x.shape)
         elif k == "reorder":
             odt = abi.np_dtype_of(a["out_data_type"]) if a["out_data_type"] != abi.NONE else x.dtype

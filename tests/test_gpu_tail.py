@@ -99,3 +99,65 @@ def test_softmax_matches_oracle(eng, features):
     got = _run(eng, "softmax", sp, n, np.float32, input0=x)
     np.testing.assert_allclose(got, want[:n], rtol=1e-5, atol=1e-9)
     np.testing.assert_allclose(got.reshape(5, features).sum(1), 1.0, rtol=1e-5)
+
+
+F16_POOLS = {
+    "alexnet_max3x3s2": dict(dtype=np.float16, N=2, C=96, H=27, W=27, size=3, stride=2, pad=0, mode=abi.POOL_MAX, f_align=8),
+    "vgg_max2x2s2": dict(dtype=np.float16, N=2, C=64, H=14, W=16, size=2, stride=2, pad=0, mode=abi.POOL_MAX, f_align=16),
+    "max3x3s1_pad1_relu": dict(dtype=np.float16, N=1, C=40, H=9, W=7, size=3, stride=1, pad=1, mode=abi.POOL_MAX, act=abi.ACT_RELU, f_align=8),
+    "global_avg_7x7": dict(dtype=np.float16, N=3, C=256, H=7, W=7, size=7, stride=1, pad=0, mode=abi.POOL_AVG, f_align=32),
+    "avg3x3s2_pad1_dynamic": dict(dtype=np.float16, N=2, C=24, H=11, W=12, size=3, stride=2, pad=1, mode=abi.POOL_AVG, div=abi.DIV_DYNAMIC, f_align=8),
+}
+
+
+@pytest.mark.parametrize("name", sorted(F16_POOLS))
+@pytest.mark.parametrize("kernel", ["pooling_f16_byxf", "pooling_ref"])
+def test_pooling_fp16_matches_oracle(eng, name, kernel):
+    """fp16 pooling in the feature-innermost layout: the maximum is exact, the average within fp16 rounding (1e-3 relative)."""
+    pp, n_in, n_out = _pool_params(**F16_POOLS[name])
+    rng = np.random.default_rng(62)
+    x = rng.standard_normal(n_in).astype(np.float16)
+    want = oracle_lib.pooling(pp, x).astype(np.float32)
+    got = _run(eng, kernel, pp, n_out, np.float16, input0=x).astype(np.float32)
+    if F16_POOLS[name]["mode"] == abi.POOL_MAX:
+        assert np.array_equal(want[:n_out], got)
+    else:
+        assert np.abs(want[:n_out] - got).max() <= 2e-3 * max(1.0, float(np.abs(want).max()))
+    assert len(np.unique(got)) > 8
+
+
+@pytest.mark.parametrize("kernel", ["lrn_f16_byxf", "lrn_ref"])
+@pytest.mark.parametrize("shape", [(2, 96, 13, 14), (1, 256, 5, 6), (3, 8, 4, 4)])
+def test_lrn_fp16_across_channels_matches_oracle(eng, kernel, shape):
+    """AlexNet's local response normalisation (window 5, k = 1, alpha = 1e-4, beta = 0.75; and a strong alpha so the
+    neighbours matter) in the feature-innermost layout; 2e-3 relative to the output scale (fp16 output, device pow)."""
+    N, C, H, W = shape
+    for alpha in (1e-4, 0.5):
+        lp = abi.LrnParams()
+        lp.in_, n = abi.tensor(abi.F16, N, C, H, W, "byxf", 8)
+        lp.out, _ = abi.tensor(abi.F16, N, C, H, W, "byxf", 8)
+        lp.size, lp.k, lp.alpha, lp.beta = 5, 1.0, alpha, 0.75
+        x = (np.random.default_rng(63).standard_normal(n) * 3).astype(np.float16)
+        want = oracle_lib.lrn(lp, x).astype(np.float32)
+        got = _run(eng, kernel, lp, n, np.float16, input0=x).astype(np.float32)
+        assert np.abs(want - got).max() <= 2e-3 * float(np.abs(want).max())
+        assert float(np.abs(want).max()) > 0.5
+
+
+def test_softmax_reference_kats_all_scopes_on_gpu(eng):
+    """The reference's softmax vectors for normalize_f / _y / _fyx (and normalize_x against numpy) through the GPU kernel."""
+    from test_oracle_kat import softmax_scope_checks
+    softmax_scope_checks(lambda sp, x: _run(eng, "softmax", sp, x.size, np.float32, input0=x))
+
+
+def test_softmax_whole_image_scope_matches_oracle(eng):
+    """normalize_fyx on a feature-innermost fp16 tensor: one set of f*y*x values per batch."""
+    sp = abi.SoftmaxParams()
+    sp.in_, n = abi.tensor(abi.F16, 3, 21, 9, 7, "byxf", 8)
+    sp.out, _ = abi.tensor(abi.F32, 3, 21, 9, 7, "bfyx", 1)
+    sp.dimension = abi.SOFTMAX_FYX
+    x = (np.random.default_rng(64).standard_normal(n) * 2).astype(np.float16)
+    want = oracle_lib.softmax(sp, x)
+    got = _run(eng, "softmax", sp, 3 * 21 * 9 * 7, np.float32, input0=x)
+    assert np.allclose(got, want[:got.size], rtol=1e-4, atol=1e-8)
+    assert np.allclose(got.reshape(3, -1).sum(axis=1), 1.0, atol=1e-4)

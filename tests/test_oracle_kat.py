@@ -142,3 +142,38 @@ def test_fully_connected_int8_kat():
     out, oor = oracle_lib.fc(fp, x.reshape(-1), w.reshape(-1))
     got = _reorder(out.reshape(1, 4, 1, 1), np.float32)
     assert got.reshape(-1).tolist() == k["expected_f32"]
+
+
+def _softmax_scope(dimension, x_bfyx):
+    from golden import kat_softmax  # noqa: F401
+    sp = abi.SoftmaxParams()
+    N, F, Y, X = x_bfyx.shape
+    sp.in_, n = abi.tensor(abi.F32, N, F, Y, X, "bfyx", 1)
+    sp.out, _ = abi.tensor(abi.F32, N, F, Y, X, "bfyx", 1)
+    sp.dimension = dimension
+    return sp, n
+
+
+def softmax_scope_checks(run):
+    """Shared by the oracle and the GPU test: `run(params, flat input) -> flat output`."""
+    from golden import kat_softmax as K
+    x = np.array(K.VALUES_BATCH_WISE["input"], dtype=np.float32).reshape(1, 10, 1, 1)
+    for dim in (abi.SOFTMAX_F, abi.SOFTMAX_FYX):
+        sp, n = _softmax_scope(dim, x)
+        got = run(sp, x.reshape(-1))
+        assert np.allclose(got, np.array(K.VALUES_BATCH_WISE["expected"], dtype=np.float32), rtol=1e-5, atol=1e-7)
+    x = np.array(K.SCOPES_INPUT_BFYX, dtype=np.float32).reshape(2, 3, 2, 2)
+    for dim, expected, axes in ((abi.SOFTMAX_FYX, K.EXPECTED_MAX_FYX, (1, 2, 3)), (abi.SOFTMAX_Y, K.EXPECTED_MAX_Y, (2,)), (abi.SOFTMAX_F, K.EXPECTED_MAX_F, (1,))):
+        sp, n = _softmax_scope(dim, x)
+        got = run(sp, x.reshape(-1)).reshape(x.shape)
+        assert np.allclose(got.sum(axis=axes), 1.0, atol=1e-5)
+        mx = got.max(axis=axes).reshape(-1)                          # remaining axes in b, f, y, x order: the reference's walk
+        assert np.allclose(mx, np.array(expected, dtype=np.float32), rtol=1e-5, atol=1e-6), (dim, mx, expected)
+    sp, n = _softmax_scope(abi.SOFTMAX_X, x)                         # no literal vector in the reference: sums and a numpy restatement
+    got = run(sp, x.reshape(-1)).reshape(x.shape)
+    e = np.exp(x - x.max(axis=3, keepdims=True))
+    assert np.allclose(got, e / e.sum(axis=3, keepdims=True), rtol=1e-5, atol=1e-7)
+
+
+def test_softmax_reference_kats_all_scopes():
+    softmax_scope_checks(lambda sp, x: oracle_lib.softmax(sp, x))
