@@ -97,24 +97,25 @@ __device__ __forceinline__ void fast_chunk_ptrs(uint8_t* stg, int row, uint32_t 
 }
 
 // One 32-row quadrant of a tile, all BN feature columns.
-// `cols` (a multiple of 64, <= BN): columns that hold features of the tensor; the last feature tile of a ragged count stops there.
+// (The last feature tile of a ragged feature count is converted in full: its surplus columns hold zero accumulators and
+// neutral constants, and the store clips them.)
 template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, int cols, float oqf = 1.0f)
+                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f)
 {
     const int32_t* bias = aux->bias_i[group];
     const float* quant = aux->quant[group];
     uint32_t ra[32], rb[32];
     tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
-    for (int c0 = 0; c0 < cols; c0 += 64) {
+    for (int c0 = 0; c0 < BN; c0 += 64) {
         uint4 *p0, *p1;
         tmem_ld_wait();
         tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);             // in flight while `ra` is converted
         fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
         fast_chunk32<kFused, kRelu1, kOut, kOqf>(ra, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg, oqf);
         tmem_ld_wait();
-        if (c0 + 64 < cols) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
+        if (c0 + 64 < BN) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
         else {
             // the accumulator has been read out: the MMA issuer may reuse it
             tc_fence_before();
@@ -126,15 +127,23 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
     }
 }
 
+// The variants with a uniform O_QF stay out of line, so that the common ones keep their registers and code layout.
+template <int BN, bool kFused, int kOut>
+__device__ __noinline__ void fast_tile_oqf(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
+                                           uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf)
+{
+    fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf);
+}
+
 // The same tile in float arithmetic, element by element (fused residual only):
 // taken when a feature's value range could leave the integer-safe range.
 template <int BN>
 __device__ __noinline__ void fast_tile_wide(const TcParams& P, const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row,
-                                            uint32_t sw, uint32_t tmem_empty_bar, int lane, int cols)
+                                            uint32_t sw, uint32_t tmem_empty_bar, int lane)
 {
     const EpiCfg& c = P.epi;
 #pragma unroll 1
-    for (int c0 = 0; c0 < cols; c0 += 32) {
+    for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + (uint32_t)c0, r);
         tmem_ld_wait();
@@ -462,7 +471,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         const int variant = P.fast_variant & 7;
         const bool with_oqf = (P.fast_variant & 8) != 0;            // uniform O_QF after the dequantisation
         const float oqf = c.o_qf, oqf_abs = with_oqf ? fabsf(c.o_qf) : 1.0f;
-        int cur_n_tile = -1; bool ok = true; bool wide = false; int cols = BN;
+        int cur_n_tile = -1; bool ok = true; bool wide = false;
         Prof prof; prof.begin();
         int t = group;
         TileWalk walk; walk.init(P, blockIdx.x + group * gridDim.x, kGroups * gridDim.x);
@@ -489,7 +498,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 if (lane == 0) aux->wide[group][quad] = w ? 1u : 0u;
                 named_bar_sync(1 + group, 128);
                 wide = (aux->wide[group][0] | aux->wide[group][1] | aux->wide[group][2] | aux->wide[group][3]) != 0u;
-                cols = min(BN, (P.ofm - n_tile * BN + 63) & ~63);
                 cur_n_tile = n_tile;
                 prof.stop(2);
             }
@@ -508,31 +516,31 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             uint8_t* stg = staging + (size_t)sb * kStagingBytes;
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
             if (TC_DEBUG(P, 1)) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(te); }
-            else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane, cols);
+            else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
             else if (with_oqf) {
                 // u8 or plain s8 output, no ReLU between convolution and residual sum (the host admits nothing else here)
                 if (kFused) {
-                    if ((variant >> 1) == 0) fast_tile<BN, true, false, 0, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
-                    else fast_tile<BN, true, false, 1, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    else fast_tile_oqf<BN, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
                 } else {
-                    if ((variant >> 1) == 0) fast_tile<BN, false, false, 0, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
-                    else fast_tile<BN, false, false, 1, true>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols, oqf);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    else fast_tile_oqf<BN, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
                 }
             }
             else if (kFused) {
                 switch (variant) {
-                    case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    case 1: fast_tile<BN, true, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    case 2: fast_tile<BN, true, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    case 3: fast_tile<BN, true, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    case 4: fast_tile<BN, true, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    default: fast_tile<BN, true, true, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 1: fast_tile<BN, true, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 2: fast_tile<BN, true, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 3: fast_tile<BN, true, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 4: fast_tile<BN, true, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    default: fast_tile<BN, true, true, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
                 }
             } else {
                 switch (variant >> 1) {
-                    case 0: fast_tile<BN, false, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    case 1: fast_tile<BN, false, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
-                    default: fast_tile<BN, false, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, cols); break;
+                    case 0: fast_tile<BN, false, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 1: fast_tile<BN, false, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    default: fast_tile<BN, false, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
                 }
             }
             fence_async_smem();

@@ -129,7 +129,7 @@ def vgg16_fp16(batch=32, runs=20, out=sys.stdout):
     direct = sum(min(r["conv_f16_tc"]["us"], r.get("conv_first_tc", r["conv_f16_tc"])["us"]) for r in rows)
     best = sum(min(r["conv_f16_tc"]["us"], r.get("conv_first_tc", r["conv_f16_tc"])["us"], r.get("conv_f16_winograd", r["conv_f16_tc"])["us"]) for r in rows)
     total = sum(r["gflop"] for r in rows)
-    print(json.dumps({"summary": "vgg16_fp16", "batch": batch, "direct_us": direct, "direct_tflops": total / direct * 1e-3 * 1e3,
+    print(json.dumps({"summary": "vgg16_fp16", "batch": batch, "direct_us": direct, "direct_tflops": total / direct * 1e3,
                       "best_of_both_us": best, "winograd_wins": [r["layer"] for r in rows if "conv_f16_winograd" in r and r["conv_f16_winograd"]["us"] < r["conv_f16_tc"]["us"]]}),
           file=out, flush=True)
     E.close()
