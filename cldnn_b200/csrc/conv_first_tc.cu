@@ -4,21 +4,30 @@
 // straight from the caller's input layout (planar bfyx as images arrive, or any
 // other pitches) with no padded or reordered copy of the input in HBM.  With 3
 // input features the generic tensor-core kernels would pad every filter tap to
-// 16 / 32 features and multiply mostly zeros; here K = C*kh*kw is packed densely.
-// It stands where the reference uses its first-layer kernels
+// 16 / 32 features and multiply mostly zeros; here only the filter rows are
+// padded, to 8 bytes.  It stands where the reference uses its first-layer kernels
 // (cl_kernels/convolution_gpu_bfyx_os_iyx_osv16.cl for fp16 images,
 // convolution_gpu_byxf_fs_bs_yx_bsv4_fsv32.cl for 8-bit ones) behind a reorder.
 //
-// M = N*P*Q output pixels, 128 consecutive ones per tile (= TMEM lanes); K is
-// cut into chunks of 8 core matrices (128 bytes per pixel).  Warps 0..7 gather:
-// thread (pixel m, half h) assembles every second 16-byte core of its pixel's
-// im2col row -- element k = (c*kh + r)*kw + s read at an offset taken from a
-// table in shared memory, zero outside the image -- into a ring of operand
-// stages in the K-major no-swizzle core-matrix layout; warp 12 issues
-// tcgen05.mma (kind::f16 / kind::i8) against the resident weight image, two
-// accumulator buffers in tensor memory; warps 8..11 run the epilogue (fp16:
-// bias + activation; 8-bit: the quantised epilogue of
-// fused_conv_eltwise_gpu_ref.cl:148-198) and write byxf for the next layer.
+// M = N*P*Q output pixels, 128 consecutive ones per tile (= TMEM lanes).  K is
+// ordered (feature, filter row, filter column) with every filter row padded to
+// whole 8-byte quanta (4 halves / 8 bytes; the padding taps carry zero
+// weights), so each quantum of a pixel's im2col row is one run of consecutive
+// input elements.
+//   warps 0..15  gather, in four groups of four warps; a group builds every
+//                fourth operand stage on its own (thread = pixel): it issues the
+//                aligned 64-bit loads around the runs of four 16-byte cores (two
+//                words per run, which starts at any element; only words that
+//                hold a tap inside the image are read), then funnel-shifts them
+//                into place and clears padding and border taps.  Four stages are
+//                under construction at once, which hides the load latency.
+//                Dilated or non-contiguous inputs go element by element.  Stages
+//                hold 8 cores in the K-major no-swizzle core-matrix layout.
+//   warps 16..19 epilogue (fp16: bias + activation; 8-bit: the quantised
+//                epilogue of fused_conv_eltwise_gpu_ref.cl:148-198), writing byxf
+//                for the next layer.
+//   warp 20      issues tcgen05.mma (kind::f16 / kind::i8) against the resident
+//                weight image; up to four accumulator buffers in tensor memory.
 // Every barrier wait is bounded and reports through the device status word.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -33,20 +42,21 @@ using namespace ptx;
 
 namespace firsttc {
 
-constexpr int kBuildWarps = 8, kEpiWarps = 4;
+constexpr int kBuildWarps = 16, kEpiWarps = 4;          // gather warps: four groups of four, one operand stage per group
 constexpr int kBuilders = kBuildWarps * 32;
 constexpr int kMmaWarp = kBuildWarps + kEpiWarps;
 constexpr int kThreads = (kBuildWarps + kEpiWarps + 1) * 32;
 constexpr int kStages = 4;
 constexpr int kAccBufs = 4;                       // most accumulator buffers in tensor memory (ofm columns each)
 constexpr int kStageBytes = 128 * 128;            // 128 pixels x 8 cores x 16 bytes
-constexpr int kMaxK = 1024;                       // table entries (elements of K)
+constexpr int kMaxCores = 256;                    // table entries: 16-byte cores of the padded K
 constexpr int kMaxOfm = 256;
 constexpr uint32_t kErr = 0x70u;
 
 struct Params {
-    int32_t N, H, W, Pn, Q, ofm, K, cores, chunks;   // cores = 16-byte groups of the padded K (even), chunks = ceil(cores / 8)
-    int32_t sx, sy, pad_x, pad_y, ext_x, ext_y;      // ext = (kw-1)*dil_x, (kh-1)*dil_y
+    int32_t N, H, W, Pn, Q, ofm, runs, cores, chunks; // runs = C*kh*(quanta per filter row): 8-byte quanta that hold taps; cores = 16-byte groups of the padded K (even); chunks = ceil(cores / 8)
+    int32_t run_len, fast_ok;                        // elements of one padded filter row; 1: contiguous undilated rows (the shifted-word gather applies)
+    int32_t sx, sy, pad_x, pad_y, ext_x, ext_y, dil_x; // ext = (kw-1)*dil_x, (kh-1)*dil_y
     int32_t total_tiles;
     int64_t M_total;
     int64_t in_pb, in_py, in_px, in_off;             // elements
@@ -56,7 +66,7 @@ struct Params {
     int32_t nacc;                                    // accumulator buffers in tensor memory: up to kAccBufs of ofm columns each
     int32_t debug;                                   // diagnostic builds (-DCONV_TC_DEBUG): what-if switches, 0 otherwise
     int32_t mul_iqf, mul_oqf, lean;                  // 8-bit epilogue (lean: per-feature scale, optional uniform O_QF, NONE / ReLU, integer bias)
-    const void* in; void* out; const uint8_t* wpacked; const int2* table; const void* bias; const float* quant; const float* calib;
+    const void* in; void* out; const uint8_t* wpacked; const int4* table; const void* bias; const float* quant; const float* calib;
     uint32_t* status;
     EpiCfg epi;
 };
@@ -88,31 +98,40 @@ __device__ __forceinline__ uint64_t desc_interleaved(uint32_t smem_addr, uint32_
     return d;
 }
 
-// weights [ofm][C][kh][kw] (any pitches) -> shared-memory image: element (n, k), k = (c*kh + r)*kw + s, at
-// (n/8)*sbo + (k/EPC)*128 + (n%8)*16 + (k%EPC)*sizeof(T), zero for k >= K; and the gather table: entry k = (offset of
-// the tap from the window origin in elements, row shift | column shift << 16)
+// weights [ofm][C][kh][kw] (any pitches) -> shared-memory image: element (n, k), k = ((c*kh + r)*qpr + j)*QE + e for tap
+// s = j*QE + e of filter row (c, r) (qpr quanta of QE = 8 / sizeof(T) taps per row), at
+// (n/8)*sbo + (k/EPC)*128 + (n%8)*16 + (k%EPC)*sizeof(T); zero for s >= kw and beyond the last row.  And the gather table,
+// one entry per quantum: (offset of its first tap from the window origin in elements, row shift | column shift << 12 |
+// taps in the quantum << 24, byte masks of its two 32-bit words that keep the filter row's taps).
 template <typename T>
 __global__ void first_tc_pack(const T* __restrict__ w, int64_t po, int64_t pi, int64_t py, int64_t px, int64_t off,
                               int ofm, int C, int kh, int kw, int cores, T* __restrict__ dst,
-                              int2* __restrict__ table, int64_t in_pf, int64_t in_py, int64_t in_px, int dil_x, int dil_y)
+                              int4* __restrict__ table, int64_t in_pf, int64_t in_py, int64_t in_px, int dil_x, int dil_y)
 {
-    constexpr int EPC = 16 / (int)sizeof(T);
-    const int K = C * kh * kw, Kp = cores * EPC;
+    constexpr int EPC = 16 / (int)sizeof(T), QE = EPC / 2;
+    const int qpr = (kw + QE - 1) / QE, quanta = C * kh * qpr, Kp = cores * EPC;
     const int sbo = cores * 128 / (int)sizeof(T);                       // in elements
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ofm * Kp; i += gridDim.x * blockDim.x) {
         const int n = i / Kp, k = i - n * Kp;
+        const int g = k / QE, e = k - g * QE;
         T v = T(0);
-        if (k < K) { const int s = k % kw, t = k / kw; const int r = t % kh, c = t / kh; v = w[off + n * po + c * pi + r * py + s * px]; }
+        if (g < quanta) {
+            const int j = g % qpr, t = g / qpr; const int r = t % kh, c = t / kh; const int s_ = j * QE + e;
+            if (s_ < kw) v = w[off + n * po + c * pi + r * py + s_ * px];
+        }
         dst[(n >> 3) * sbo + (k / EPC) * (128 / (int)sizeof(T)) + (n & 7) * EPC + (k % EPC)] = v;
     }
-    for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < Kp; k += gridDim.x * blockDim.x) {
-        int2 e = make_int2(0, 0);
-        if (k < K) {
-            const int s = k % kw, t = k / kw; const int r = t % kh, c = t / kh;
-            e.x = (int)(c * in_pf + (int64_t)r * dil_y * in_py + (int64_t)s * dil_x * in_px);
-            e.y = (r * dil_y) | ((s * dil_x) << 16);
+    for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < 2 * cores; g += gridDim.x * blockDim.x) {
+        int4 ent = make_int4(0, 0, 0, 0);
+        if (g < quanta) {
+            const int j = g % qpr, t = g / qpr; const int r = t % kh, c = t / kh; const int s0 = j * QE;
+            const int nv = min(QE, kw - s0), nb = nv * (int)sizeof(T);    // taps / bytes of the quantum that belong to the filter row
+            ent.x = (int)(c * in_pf + (int64_t)r * dil_y * in_py + (int64_t)s0 * dil_x * in_px);
+            ent.y = (r * dil_y) | ((s0 * dil_x) << 12) | (nv << 24);
+            ent.z = (int)(nb >= 4 ? 0xffffffffu : ((1u << (8 * nb)) - 1u));                        // byte masks of the two words
+            ent.w = (int)(nb >= 8 ? 0xffffffffu : (nb <= 4 ? 0u : ((1u << (8 * (nb - 4))) - 1u)));
         }
-        table[k] = e;
+        table[g] = ent;
     }
 }
 
@@ -145,7 +164,7 @@ __device__ __forceinline__ float act_apply(int32_t fn, float x, float m, float n
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 conv_first_tc_kernel(const __grid_constant__ Params P)
 {
     constexpr bool kHalf = sizeof(T) == 2;
@@ -156,14 +175,14 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
     uint8_t* smem = smem_raw + (base - raw);
     const int b_bytes = P.ofm * P.cores * 16;
     uint8_t* sA = smem; uint8_t* sB = sA + kStages * kStageBytes;
-    int2* sTab = reinterpret_cast<int2*>(sB + b_bytes);
-    Aux* aux = reinterpret_cast<Aux*>(reinterpret_cast<uint8_t*>(sTab) + (size_t)P.cores * EPC * sizeof(int2));
+    int4* sTab = reinterpret_cast<int4*>(sB + b_bytes);
+    Aux* aux = reinterpret_cast<Aux*>(reinterpret_cast<uint8_t*>(sTab) + (size_t)P.cores * 2 * sizeof(int4));
     volatile uint32_t* s_abort = &aux->abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const EpiCfg& c = P.epi;
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&aux->a_full[i]), kBuildWarps); mbar_init(smem_u32(&aux->a_empty[i]), 1); }
+        for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&aux->a_full[i]), kBuildWarps / kStages); mbar_init(smem_u32(&aux->a_empty[i]), 1); }
         for (int i = 0; i < kAccBufs; ++i) { mbar_init(smem_u32(&aux->tmem_full[i]), 1); mbar_init(smem_u32(&aux->tmem_empty[i]), kEpiWarps); }
         aux->abort = 0u;
         mbar_fence_init();
@@ -171,7 +190,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
     if (warp == kMmaWarp) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
     // weights image, gather table and per-feature constants: once per CTA
     for (int i = tid; i < b_bytes / 16; i += kThreads) reinterpret_cast<uint4*>(sB)[i] = __ldg(reinterpret_cast<const uint4*>(P.wpacked) + i);
-    for (int i = tid; i < P.cores * EPC; i += kThreads) sTab[i] = __ldg(P.table + i);
+    for (int i = tid; i < P.cores * 2; i += kThreads) sTab[i] = __ldg(P.table + i);
     for (int j = tid; j < P.ofm; j += kThreads) {
         int32_t bi = 0; float bf = 0.f;
         if (kHalf) { if (P.bias_dtype != CLDNN_B200_NONE) bf = load_as_float(P.bias, P.bias_dtype, j); }
@@ -190,43 +209,129 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
 
     if (warp < kBuildWarps) {
         // ------------------------------ gather ------------------------------------
-        const int m = tid & 127, half = tid >> 7;
+        // Four groups of four warps; group g assembles every fourth operand stage (stage buffer g) on its own, all 128
+        // pixels of it, so four stages are under construction at once and each barrier round trip pays for a whole stage.
+        const int m = tid & 127, group = tid >> 7;
         const T* in = reinterpret_cast<const T*>(P.in) + P.in_off;
-        uint8_t* dst0 = sA + (m >> 3) * 1024 + (m & 7) * 16;
-        int stage = 0; uint32_t phase = 0; bool ok = true;
+        uint8_t* dst = sA + group * kStageBytes + (m >> 3) * 1024 + (m & 7) * 16;
+        uint32_t phase = 0; bool ok = true;
         PixelWalk px; px.init(blockIdx.x * 128u + (uint32_t)m, gridDim.x * 128u, P.Pn, P.Q);      // the host admits fewer than 2^31 pixels
-        for (int it = 0; it < my_tiles && ok; ++it, px.next()) {
+        int it = 0, ch = group;                                 // this group's next stage: chunk `ch` of the CTA's tile `it`
+        while (ch >= P.chunks) { ch -= P.chunks; ++it; px.next(); }
+        while (it < my_tiles && ok) {
             const bool valid = px.n < P.N;
-            const int n = px.n, p = px.p, q = px.q;
-            const int y0 = p * P.sy - P.pad_y, x0 = q * P.sx - P.pad_x;
-            const T* src = in + (int64_t)n * P.in_pb + (int64_t)y0 * P.in_py + (int64_t)x0 * P.in_px;   // dereferenced only at taps inside the image
-            const bool interior = valid && y0 >= 0 && y0 + P.ext_y < P.H && x0 >= 0 && x0 + P.ext_x < P.W;
-            for (int ch = 0; ch < P.chunks; ++ch) {
-                // one lane per warp polls the barrier, and one arrives for the warp: 256 threads on one shared-memory word serialise
-                if (lane == 0) ok = mbar_wait(smem_u32(&aux->a_empty[stage]), phase ^ 1u, s_abort, P.status, kErr + 1u);
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                __syncwarp();
-                if (!ok) break;
-                const int ncore = min(8, P.cores - ch * 8);
-                uint8_t* dst = dst0 + stage * kStageBytes;
-                for (int j = half; j < ncore; j += 2) {
-                    const int kb = (ch * 8 + j) * EPC;
-                    uint32_t e[EPC];
-                    if (FTC_DEBUG(P, 0)) {
+            const int y0 = px.p * P.sy - P.pad_y, x0 = px.q * P.sx - P.pad_x;
+            const T* src = in + (int64_t)px.n * P.in_pb + (int64_t)y0 * P.in_py + (int64_t)x0 * P.in_px;   // dereferenced only at taps inside the image
+            // one lane per warp polls the barrier, and one arrives for the warp: 128 threads on one shared-memory word serialise
+            if (lane == 0) ok = mbar_wait(smem_u32(&aux->a_empty[group]), phase ^ 1u, s_abort, P.status, kErr + 1u);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            if (!ok) break;
+            const int ncore = min(8, P.cores - ch * 8);
+            if (P.fast_ok && !FTC_DEBUG(P, 0)) {
+                // Every quantum is one run of QE consecutive input elements starting anywhere: the two aligned 8-byte words
+                // around it, shifted into place.  Elements [lo, hi) of the run are taps inside the image; only words holding
+                // one of them are read (an aligned word that holds a valid byte lies in the same page: the read cannot
+                // fault), everything else becomes zero (padding taps have zero weights, but 0 * Inf is not 0).  The loads
+                // of four cores are issued before the first of them is used.
+                // every tap of the pixel's window inside the image: no bounds to check, only the filter rows' padding taps to clear
+                const bool inside = valid && y0 >= 0 && y0 + P.ext_y < P.H && x0 >= 0 && x0 + P.ext_x < P.W;
+#pragma unroll 1
+                for (int jb = 0; jb < ncore; jb += 4) {
+                    uint2 w[8][2]; int meta[8];                              // per quantum: two aligned 8-byte words; byte offset | lo << 8 | hi << 16
+                    if (inside) {
 #pragma unroll
-                        for (int i = 0; i < EPC; ++i) e[i] = (uint32_t)(kb + i);
-                    } else if (interior && kb + EPC <= P.K) {
-#pragma unroll
-                        for (int i = 0; i < EPC; i += 2) {
-                            const int4 t = *reinterpret_cast<const int4*>(&sTab[kb + i]);
-                            e[i] = load_elem(src + t.x); e[i + 1] = load_elem(src + t.z);
+                        for (int u = 0; u < 8; ++u) {
+                            const int j = jb + (u >> 1);
+                            w[u][0] = w[u][1] = make_uint2(0u, 0u); meta[u] = 0;
+                            if (j < ncore) {
+                                const int2 t = *reinterpret_cast<const int2*>(&sTab[(ch * 8 + j) * 2 + (u & 1)]);
+                                const int nb = (t.y >> 24) * (int)sizeof(T);
+                                if (nb) {
+                                    const uintptr_t addr = reinterpret_cast<uintptr_t>(src + t.x);
+                                    const uint2* wp = reinterpret_cast<const uint2*>(addr & ~(uintptr_t)7);
+                                    const int o = (int)(addr & 7u);
+                                    w[u][0] = __ldg(wp);
+                                    if (o + nb > 8) w[u][1] = __ldg(wp + 1);       // the word holds a tap of the row: inside the tensor
+                                    meta[u] = o;
+                                }
+                            }
                         }
-                    } else {
 #pragma unroll
-                        for (int i = 0; i < EPC; ++i) {
-                            const int2 t = sTab[kb + i];
-                            const int iy = y0 + (t.y & 0xffff), ix = x0 + (t.y >> 16);
-                            e[i] = (valid && kb + i < P.K && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W) ? load_elem(src + t.x) : 0u;
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            const int j = jb + c4;
+                            if (j >= ncore) break;
+                            uint32_t d[4];
+#pragma unroll
+                            for (int h2 = 0; h2 < 2; ++h2) {
+                                const int u = 2 * c4 + h2;
+                                const int o = meta[u];
+                                const uint32_t sh = (uint32_t)(o & 3) * 8u;
+                                const int2 mk = *reinterpret_cast<const int2*>(&sTab[(ch * 8 + j) * 2 + h2].z);
+                                const uint32_t x0w = (o & 4) ? w[u][0].y : w[u][0].x, x1w = (o & 4) ? w[u][1].x : w[u][0].y, x2w = (o & 4) ? w[u][1].y : w[u][1].x;
+                                d[2 * h2] = __funnelshift_r(x0w, x1w, sh) & (uint32_t)mk.x;
+                                d[2 * h2 + 1] = __funnelshift_r(x1w, x2w, sh) & (uint32_t)mk.y;
+                            }
+                            *reinterpret_cast<uint4*>(dst + j * 128) = make_uint4(d[0], d[1], d[2], d[3]);
+                        }
+                        continue;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int j = jb + (u >> 1);
+                        w[u][0] = w[u][1] = make_uint2(0u, 0u); meta[u] = 0;
+                        if (j < ncore) {
+                            const int4 t = sTab[(ch * 8 + j) * 2 + (u & 1)];
+                            const int nv = t.y >> 24, iy = y0 + (t.y & 0xfff), ix0 = x0 + ((t.y >> 12) & 0xfff);
+                            const int lo = max(0, -ix0), hi = (valid && iy >= 0 && iy < P.H) ? min(nv, P.W - ix0) : 0;
+                            if (hi > lo) {
+                                const uintptr_t addr = reinterpret_cast<uintptr_t>(src + t.x);
+                                const uint2* wp = reinterpret_cast<const uint2*>(addr & ~(uintptr_t)7);
+                                const int o = (int)(addr & 7u);
+                                const int b0 = o + lo * (int)sizeof(T), b1 = o + hi * (int)sizeof(T);   // valid bytes, from the first word
+                                if (b0 < 8) w[u][0] = __ldg(wp);
+                                if (b1 > 8) w[u][1] = __ldg(wp + 1);
+                                meta[u] = o | (lo << 8) | (hi << 16);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        const int j = jb + c4;
+                        if (j >= ncore) break;
+                        uint32_t d[4];
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2) {
+                            const int u = 2 * c4 + h2;
+                            const int o = meta[u] & 0xff;
+                            const uint32_t sh = (uint32_t)(o & 3) * 8u;
+                            const int v0 = ((meta[u] >> 8) & 0xff) * (int)sizeof(T), v1 = (meta[u] >> 16) * (int)sizeof(T);   // valid bytes of the quantum
+                            // the run starts in the first or the second 32-bit half of the first word
+                            const uint32_t x0w = (o & 4) ? w[u][0].y : w[u][0].x, x1w = (o & 4) ? w[u][1].x : w[u][0].y, x2w = (o & 4) ? w[u][1].y : w[u][1].x;
+                            uint32_t q0 = __funnelshift_r(x0w, x1w, sh), q1 = __funnelshift_r(x1w, x2w, sh);
+                            if (v0 != 0 || v1 != 8) {
+                                const int a1 = min(v1, 4), c0 = max(v0 - 4, 0), c1 = v1 - 4;
+                                q0 = (a1 > v0) ? (q0 & ((a1 >= 4 ? 0xffffffffu : ((1u << (8 * a1)) - 1u)) & ~((1u << (8 * min(v0, 3))) - 1u))) : 0u;
+                                q1 = (c1 > c0) ? (q1 & ((c1 >= 4 ? 0xffffffffu : ((1u << (8 * c1)) - 1u)) & ~((1u << (8 * c0)) - 1u))) : 0u;
+                            }
+                            d[2 * h2] = q0; d[2 * h2 + 1] = q1;
+                        }
+                        *reinterpret_cast<uint4*>(dst + j * 128) = make_uint4(d[0], d[1], d[2], d[3]);
+                    }
+                }
+            } else {
+                for (int j = 0; j < ncore; ++j) {
+                    uint32_t e[EPC];
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int4 t = sTab[(ch * 8 + j) * 2 + h2];
+                        const int nv = t.y >> 24, iy = y0 + (t.y & 0xfff), ix0 = x0 + ((t.y >> 12) & 0xfff);
+                        const int64_t step = (int64_t)P.dil_x * P.in_px;
+#pragma unroll
+                        for (int i = 0; i < EPC / 2; ++i) {
+                            const int ix = ix0 + i * P.dil_x;
+                            const bool in_image = valid && !FTC_DEBUG(P, 0) && i < nv && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W;
+                            e[h2 * (EPC / 2) + i] = in_image ? load_elem(src + t.x + i * step) : 0u;
                         }
                     }
                     uint4 v;
@@ -240,11 +345,13 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
                     }
                     *reinterpret_cast<uint4*>(dst + j * 128) = v;
                 }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&aux->a_full[stage]));
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->a_full[group]));
+            phase ^= 1u;
+            ch += kStages;
+            while (ch >= P.chunks) { ch -= P.chunks; ++it; px.next(); }
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer --------------------------------
@@ -274,7 +381,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
-        const int quad = warp & 3;                              // warps 8..11 -> TMEM lanes 32*quad ..
+        const int quad = warp & 3;                              // warps 16..19 -> TMEM lanes 32*quad ..
         const int row = quad * 32 + lane;
         PixelWalk px; px.init(blockIdx.x * 128u + (uint32_t)row, gridDim.x * 128u, P.Pn, P.Q);
         for (int it = 0; it < my_tiles; ++it, px.next()) {
@@ -329,16 +436,16 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
 using firsttc::Params;
 
 static int ftc_esize(const cldnn_b200_conv_params& p) { return p.in.dtype == CLDNN_B200_F16 ? 2 : 1; }
+static int ftc_qpr(const cldnn_b200_conv_params& p) { const int qe = 8 / ftc_esize(p); return (p.kw + qe - 1) / qe; }   // 8-byte quanta per filter row
 static int ftc_cores(const cldnn_b200_conv_params& p)
 {
-    const int epc = 16 / ftc_esize(p);
-    const int cores = (p.ifm * p.kh * p.kw + epc - 1) / epc;
+    const int cores = (p.ifm * p.kh * ftc_qpr(p) + 1) / 2;             // two quanta per 16-byte core
     return (cores + 1) / 2 * 2;                                        // one instruction consumes two cores
 }
 static size_t ftc_smem(const cldnn_b200_conv_params& p)
 {
     const int cores = ftc_cores(p);
-    return 128 + (size_t)firsttc::kStages * firsttc::kStageBytes + (size_t)p.ofm * cores * 16 + (size_t)cores * (16 / ftc_esize(p)) * sizeof(int2) + sizeof(firsttc::Aux);
+    return 128 + (size_t)firsttc::kStages * firsttc::kStageBytes + (size_t)p.ofm * cores * 16 + (size_t)cores * 2 * sizeof(int4) + sizeof(firsttc::Aux);
 }
 
 static bool ftc_plan(const cldnn_b200_conv_params& p, std::string* why)
@@ -358,8 +465,8 @@ static bool ftc_plan(const cldnn_b200_conv_params& p, std::string* why)
     if (p.groups != 1 || p.fused_eltw) return no("plain convolution only");
     if (p.out.pf != 1) return no("output must be byxf");
     if (p.kh < 1 || p.kw < 1 || p.stride_x < 1 || p.stride_y < 1 || p.dil_x < 1 || p.dil_y < 1) return no("filter geometry");
-    if ((int64_t)p.ifm * p.kh * p.kw > firsttc::kMaxK) return no("C*kh*kw must not exceed 1024");
-    if ((p.kh - 1) * p.dil_y > 32767 || (p.kw - 1) * p.dil_x > 32767) return no("filter extent");
+    if ((int64_t)p.ifm * p.kh * ftc_qpr(p) > 2 * firsttc::kMaxCores) return no("too many filter rows (C * kh * 8-byte quanta per row above 512)");
+    if ((p.kh - 1) * p.dil_y > 4095 || (ftc_qpr(p) * (8 / ftc_esize(p))) * p.dil_x > 4095) return no("filter extent");
     if (p.ofm % 32 || p.ofm > firsttc::kMaxOfm || p.out.f != p.ofm || p.in.f != p.ifm) return no("output features: multiple of 32, at most 256");
     const int es = ftc_esize(p);
     if ((p.out.px * es) % 16 || (p.out.py * es) % 16 || (p.out.pb * es) % 16 || (p.out.offset * es) % 16) return no("output pitches must be 16-byte aligned");
@@ -379,7 +486,7 @@ static size_t ftc_table_offset(const cldnn_b200_conv_params& p) { return ((size_
 static size_t ftc_scratch(const void* vp)
 {
     const auto& p = *(const cldnn_b200_conv_params*)vp;
-    return ftc_table_offset(p) + (size_t)ftc_cores(p) * (16 / ftc_esize(p)) * sizeof(int2);
+    return ftc_table_offset(p) + (size_t)ftc_cores(p) * 2 * sizeof(int4);
 }
 
 static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
@@ -400,7 +507,10 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
 
     Params P{};
     P.N = p.in.b; P.H = p.in.y; P.W = p.in.x; P.Pn = p.out.y; P.Q = p.out.x; P.ofm = p.ofm;
-    P.K = p.ifm * p.kh * p.kw; P.cores = ftc_cores(p); P.chunks = (P.cores + 7) / 8;
+    P.runs = p.ifm * p.kh * ftc_qpr(p); P.cores = ftc_cores(p); P.chunks = (P.cores + 7) / 8;
+    P.run_len = ftc_qpr(p) * (8 / ftc_esize(p)); P.dil_x = p.dil_x;
+    // contiguous, undilated filter rows of elements aligned to their size: the shifted-word gather applies
+    P.fast_ok = (p.in.px == 1 && p.dil_x == 1) ? 1 : 0;
     P.sx = p.stride_x; P.sy = p.stride_y; P.pad_x = p.pad_x; P.pad_y = p.pad_y;
     P.ext_x = (p.kw - 1) * p.dil_x; P.ext_y = (p.kh - 1) * p.dil_y;
     P.M_total = (int64_t)P.N * P.Pn * P.Q;
@@ -413,7 +523,8 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     // inside half of the SM's 512 columns of tensor memory, else one CTA with up to four
     const size_t smem = ftc_smem(p);
     if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_first_tc: not enough shared memory");
-    int per_sm = (ctx->prop.sharedMemPerMultiprocessor / (smem + 1024) >= 2 && 256 / p.ofm >= 2) ? 2 : 1;
+    int per_sm = (ctx->prop.sharedMemPerMultiprocessor / (smem + 1024) >= 2 && 256 / p.ofm >= 2 &&
+                  2 * firsttc::kThreads <= ctx->prop.maxThreadsPerMultiProcessor) ? 2 : 1;
     P.nacc = std::min(firsttc::kAccBufs, (per_sm == 2 ? 256 : 512) / p.ofm);
     uint32_t cols = 32; while (cols < (uint32_t)(P.nacc * p.ofm)) cols <<= 1;
     P.tmem_cols = cols;
@@ -424,7 +535,7 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.lean = (!half && p.quantization && !P.mul_iqf && (!P.mul_oqf || !p.calibration) && !P.epi.dont_dequantize_bias &&
               (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU)) ? 1 : 0;
     P.in = a->input0; P.out = a->output; P.wpacked = (const uint8_t*)a->scratch;
-    P.table = (const int2*)((const uint8_t*)a->scratch + ftc_table_offset(p));
+    P.table = (const int4*)((const uint8_t*)a->scratch + ftc_table_offset(p));
     P.bias = a->bias; P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors;
     P.status = ctx->d_status;
 #ifdef CONV_TC_DEBUG
@@ -436,11 +547,11 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     if (half) {
         B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         firsttc::first_tc_pack<__half><<<pack_blocks, 256, 0, ctx->stream>>>((const __half*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset, p.ofm, p.ifm, p.kh, p.kw,
-                                                                              P.cores, (__half*)a->scratch, (int2*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
+                                                                              P.cores, (__half*)a->scratch, (int4*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     } else {
         B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<uint8_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         firsttc::first_tc_pack<uint8_t><<<pack_blocks, 256, 0, ctx->stream>>>((const uint8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset, p.ofm, p.ifm, p.kh, p.kw,
-                                                                               P.cores, (uint8_t*)a->scratch, (int2*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
+                                                                               P.cores, (uint8_t*)a->scratch, (int4*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     }
     B200_CUDA(cudaGetLastError());
     int grid = ctx->prop.multiProcessorCount * per_sm;

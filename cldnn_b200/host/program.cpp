@@ -512,9 +512,10 @@ void network_impl::select_layouts()
         if ((!i8 && !f16) || w.size.batch % 32 || w.size.batch > 256) return false;
         const bool simple_act = (n->act == CLDNN_B200_ACT_NONE || n->act == CLDNN_B200_ACT_RELU || n->act == CLDNN_B200_ACT_CLAMP) && !n->p.activation_negative_slope;
         if (i8 && w.size.x <= 8 && d->out.size.feature * w.size.y * 8 <= 256 && n->p.dilation.x == 1 && n->p.dilation.y == 1 && simple_act) return true;
-        const int64_t k = (int64_t)d->out.size.feature * w.size.y * w.size.x;
-        const int64_t image = w.size.batch * ((k + 31) / 32 * 32) * (f16 ? 2 : 1);       // resident weights in shared memory
-        return d->out.size.feature <= 4 && k <= 1024 && image <= 120 * 1024 && (f16 || simple_act);
+        const int64_t qe = f16 ? 4 : 8;                                                  // taps per 8-byte quantum of a padded filter row
+        const int64_t cores = ((int64_t)d->out.size.feature * w.size.y * ((w.size.x + qe - 1) / qe) + 3) / 4 * 2;
+        const int64_t image = w.size.batch * cores * 16;                                  // resident weights in shared memory
+        return d->out.size.feature <= 4 && cores <= 256 && image <= 120 * 1024 && (f16 || simple_act);
     };
     std::set<node*> chosen;
     for (node* n : order) {

@@ -1,5 +1,5 @@
-"""Parity of the general first-layer tensor-core convolution (conv_first_tc: few input features, dense K = C*kh*kw,
-planar input read in place) with the CPU oracle, through the C ABI: bit-exact for the 8-bit form, 1e-2 relative to the
+"""Parity of the general first-layer tensor-core convolution (conv_first_tc: few input features, K = C*kh filter rows padded to
+whole 16-byte core rows, planar input read in place) with the CPU oracle, through the C ABI: bit-exact for the 8-bit form, 1e-2 relative to the
 output scale for fp16 (the reference accumulates fp16 in half precision with device-defined rounding)."""
 import numpy as np
 import pytest
@@ -98,6 +98,6 @@ def test_conv_first_tc_reads_any_input_pitches(eng):
 
 def test_conv_first_tc_refusals(eng):
     k = eng.kernel("conv_first_tc")
-    assert not k.supports(_f16_case(56, N=1, C=128, K=64, H=8, W=8).p)              # K = 1152 > 1024
+    assert not k.supports(_f16_case(56, N=1, C=128, K=64, H=8, W=8).p)              # 384 filter rows: more cores than the gather table holds
     assert not k.supports(_f16_case(56, N=1, C=3, K=40, H=8, W=8).p)                # output features not a multiple of 32
     assert not k.supports(cases.make_conv_case(56, N=1, C=3, K=64, H=8, W=8, fmt="bfyx", f_align=1, out_dtype=np.uint8).p)   # planar output
