@@ -1,7 +1,7 @@
 """Per-layer convolution sweeps of the benchmark configurations, through the C ABI.
 
     python -m cldnn_b200.sweep vgg16_fp16 [--batch 32]
-    python -m cldnn_b200.sweep alexnet_fp16 | vgg16_fp16_net | mobilenet_v2_int8 | resnet50_int8 [--batch N]
+    python -m cldnn_b200.sweep alexnet_fp16 | alexnet_int8 | vgg16_fp16_net | mobilenet_v2_int8 | resnet50_int8 [--batch N]
 
 VGG16 fp16 (13 3x3 pad-1 layers, 64 -> 512 features, 224 -> 14 maps; weights N(0, sqrt(2 / fan_in)), inputs N(0, 1),
 fp32 accumulation): every layer is timed on the direct tensor-core kernel (conv_f16_tc, best tile shape of its tuning
@@ -138,6 +138,7 @@ def vgg16_fp16(batch=32, runs=20, out=sys.stdout):
 
 NETWORKS = {
     "alexnet_fp16": (lambda b: topologies.alexnet_fp16(b), 256),
+    "alexnet_int8": (lambda b: topologies.alexnet_int8(b), 256),
     "vgg16_fp16_net": (lambda b: topologies.vgg16_fp16(b), 32),
     "mobilenet_v2_int8": (lambda b: topologies.mobilenet_v2_int8(b), 128),
     "resnet50_int8": (lambda b: topologies.resnet50_int8(b), 256),

@@ -251,6 +251,48 @@ def alexnet_fp16(batch, seed=12, image=227, convs=ALEXNET_CONVS, classes=1000, f
     return s
 
 
+def alexnet_int8(batch, seed=13, image=227, convs=ALEXNET_CONVS, classes=1000, fc_width=4096):
+    """int8 AlexNet: the fp16 topology without its LRN layers (the reference's LRN kernels take fp16 / fp32 only): u8 image,
+    11x11 stride-4 first convolution, two-group conv2 / conv4 / conv5, 3x3 stride-2 max pooling, three quantised
+    fully_connected layers (f32 bias after the dequantisation, per-output calibration), softmax.  s8 weights uniform in
+    [-127, 127], i32 convolution biases, per-feature scales sized so the dequantised values spread over a few units, ReLU,
+    then a uniform requantisation onto u8."""
+    rng = np.random.default_rng(seed)
+    s = Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.u8, cl.format.bfyx, cl.tensor(batch, 3, image, image))
+    s.add(cl.input_layout("input", s.input_layout))
+    x, cin, size = "input", 3, image
+    in_sigma = 74.0                                                    # a u8 image; later layers see requantised ReLU outputs
+    for i, (w, k, stride, pad, groups, pool) in enumerate(convs):
+        name = "conv%d" % (i + 1)
+        fan = (cin // groups) * k * k
+        s.const(name + "_w", rng.integers(-127, 128, size=(w, cin // groups, k, k), dtype=np.int64).astype(np.int8))
+        s.const(name + "_b", rng.integers(-2048, 2049, size=w, dtype=np.int64).astype(np.int32))
+        s.const(name + "_q", (rng.uniform(1.0, 3.0, size=w) / (np.sqrt(fan) * 73.0 * in_sigma)).astype(np.float32))
+        s.add(cl.convolution(name, x, name + "_w", name + "_b", name + "_q", output_data_type=dt.u8, stride=(stride, stride), input_offset=(-pad, -pad),
+                             with_activation=True, groups=groups, output_quantization_factor=24.0))
+        x, cin, size, in_sigma = name, w, (size + 2 * pad - k) // stride + 1, 40.0
+        if pool or i == len(convs) - 1:
+            s.add(cl.pooling("pool%d" % (i + 1), x, cl.pooling_mode.max, size=(3, 3), stride=(2, 2)))
+            x, size = "pool%d" % (i + 1), (size - 3) // 2 + 1
+    fan = cin * size * size
+    for i, (wout, act) in enumerate(((fc_width, True), (fc_width, True), (classes, False))):
+        name = "fc%d" % (i + 6)
+        shape = (wout, cin, size, size) if i == 0 else (wout, fan, 1, 1)
+        s.const(name + "_w", rng.integers(-127, 128, size=shape, dtype=np.int64).astype(np.int8))
+        s.const(name + "_b", rng.uniform(-1.0, 1.0, size=wout).astype(np.float32))
+        s.const(name + "_q", (rng.uniform(1.0, 3.0, size=wout) / (np.sqrt(fan) * 73.0 * 40.0)).astype(np.float32))
+        s.const(name + "_c", rng.uniform(6.0, 12.0, size=wout).astype(np.float32))
+        s.add(cl.fully_connected(name, x, name + "_w", name + "_b", name + "_q", name + "_c", with_activation=act))
+        x, fan = name, wout
+    s.add(cl.reorder("fc8_f32", x, cl.format.bfyx, dt.f32))
+    s.add(cl.softmax("prob", "fc8_f32"))
+    s.outputs = ["prob", x]
+    return s
+
+
 def conv_ops(spec):
     """Multiply-add operations x2 of every convolution / fully_connected of a spec, per image (padding taps counted)."""
     shapes, total = {}, 0

@@ -210,6 +210,25 @@ def test_small_alexnet_fp16_network(eng, optimize):
 
 
 @pytest.mark.parametrize("optimize", [False, True])
+def test_small_alexnet_int8_network_bit_exact(eng, optimize):
+    """int8 AlexNet-style network (no LRN: the reference's LRN is floating-point only): 11x11 stride-4 first convolution read
+    from the planar image, two-group convolutions, quantised inner products (the first over a 2x2 map), unsigned outputs."""
+    spec = topologies.alexnet_int8(3, seed=6, image=99, convs=((32, 11, 4, 0, 1, True), (64, 5, 1, 2, 2, True), (96, 3, 1, 1, 1, False),
+                                                                (96, 3, 1, 1, 2, False), (64, 3, 1, 1, 2, False)), classes=10, fc_width=64)
+    x = _input(spec)
+    want = oracle_net.run(spec, {spec.input_id: x})
+    net, got = _run(eng, spec, x, optimize_data=optimize)
+    _compare(spec, want, got)
+    assert len(np.unique(got["fc8"])) > 3
+    info = net.primitives_info()
+    convs = [r for r in info if r["type"] == "convolution"]
+    fcs = [r for r in info if r["type"] == "fully_connected"]
+    if optimize:
+        assert [r["kernel"] for r in convs] == ["conv_first_tc"] + ["conv_i8_tc"] * 4, [r["kernel"] for r in convs]
+        assert all(r["kernel"] == "conv_i8_tc" for r in fcs), [r["kernel"] for r in fcs]
+
+
+@pytest.mark.parametrize("optimize", [False, True])
 def test_small_mobilenet_v2_int8_network_bit_exact(eng, optimize):
     """Inverted-residual blocks: 1x1 expansion and projection on the tensor cores, 3x3 depthwise on conv_i8_dw, ReLU6 as a
     clamp activation, quantised residual sums.  The optimising build folds each ReLU6 into its convolution, in front of
