@@ -292,8 +292,14 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     prof.miss(0, fp_); }
                     const uint32_t full = full0 + 8u * (uint32_t)stage;
                     const uint32_t dst = a_base + (uint32_t)stage * a_stage;
-                    mbar_expect_tx(full, tx);
                     const int c0 = cc * bk;
+                    if (TC_DEBUG(P, 5)) {                                                   // what-if: no operand loads, the stage is declared full at once
+                        mbar_arrive(full); ++issued;
+                        if (++cc == chunks) { cc = 0; ++tap; if (++sx == kw) { sx = 0; ++r; } }
+                        if (++stage == stages) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
+                    mbar_expect_tx(full, tx);
                     if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
                     if (patch) {                                                            // one patch per filter column
                         for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * P.patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
