@@ -69,9 +69,17 @@ static __device__ unsigned long long g_tc_prof[148 * 16];
 struct Prof {
     long long acc[3] = {0, 0, 0}; long long t_begin = 0;
     __device__ __forceinline__ void begin() { t_begin = clock64(); }
+#ifdef CONV_TC_CYCLES
+    // cycle mode: start / stop accumulate clocks per site (each read costs ~70 clocks: for shares, not absolutes)
+    long long t_s = 0;
+    __device__ __forceinline__ void start() { t_s = clock64(); }
+    __device__ __forceinline__ void stop(int i) { acc[i] += clock64() - t_s; }
+    __device__ __forceinline__ void miss(int, bool) {}
+#else
     __device__ __forceinline__ void start() {}
     __device__ __forceinline__ void stop(int) {}
     __device__ __forceinline__ void miss(int i, bool first_poll_ok) { acc[i] += first_poll_ok ? 0 : 1; }
+#endif
     __device__ __forceinline__ void flush(int slot, int n, long long extra = -1) {
         if (blockIdx.x >= 148) return;
         for (int i = 0; i < n; ++i) g_tc_prof[blockIdx.x * 16 + slot + i] = (unsigned long long)acc[i];

@@ -86,6 +86,20 @@ __device__ __forceinline__ void mma_chunk(uint32_t d_tmem, uint32_t a_lo, uint32
         mma_i8_ss(d_tmem, desc64(a_lo + 2u * k, hi), desc64(b_lo + 2u * k, hi), idesc, k ? 1u : acc_first);
 }
 
+// Patch mode, one channel chunk: KH x KW filter taps straight-line (a loop over run-time filter sizes costs the issuing
+// thread ~130 clocks per MMA in address arithmetic and branches, against the 48 an N = 64 instruction runs for).
+template <int KH, int KW, int KK>
+__device__ __forceinline__ void patch_issue(uint32_t d_tmem, uint32_t a_lo, uint32_t b_col, uint32_t patch_step, uint32_t b_tap_step,
+                                            uint32_t row_step, uint32_t b_row_step, uint32_t hi, uint32_t idesc, uint32_t accf)
+{
+#pragma unroll
+    for (int s = 0; s < KW; ++s)
+#pragma unroll
+        for (int r = 0; r < KH; ++r)
+            mma_chunk<KK>(d_tmem, a_lo + (uint32_t)s * patch_step + (uint32_t)r * row_step, b_col + (uint32_t)s * b_tap_step + (uint32_t)r * b_row_step,
+                          hi, idesc, (s | r) ? 1u : accf);
+}
+
 template <int BN>
 __device__ __forceinline__ void fast_chunk_ptrs(uint8_t* stg, int row, uint32_t sw, int c0, uint4*& p0, uint4*& p1)
 {
@@ -341,6 +355,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const int kh = P.kh, kw_ = P.kw;
             const uint32_t patch_step = (uint32_t)P.patch_alloc >> 4;                  //             the next filter column's patch
             const uint32_t b_tap_step = (uint32_t)P.chunks * b_step;                   //             the weights of the next filter column
+            const int patch_kind = (kh == 3 && kw_ == 3) ? (kk == 2 ? 1 : (kk == 4 ? 2 : 0)) : 0;   // 3x3 filters are issued straight-line
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
             Prof prof; prof.begin();
@@ -349,7 +364,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             for (; walk.valid() && ok; walk.next(), ++t) {
                 const int acc = t % NBUF;
                 { bool fp_ = true;
+                prof.start();
                 if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma, &fp_)) { ok = false; break; }
+                prof.stop(0);
                 prof.miss(0, fp_); }
                 if (!TC_DEBUG(P, 4)) tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
@@ -358,31 +375,38 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 if (patch) b_col = b_lo0 + (uint32_t)(walk.n_tile * kh) * b_row_step;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     { bool fp_ = true;
+                    prof.start();
                     if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u, &fp_)) { ok = false; break; }
+                    prof.stop(1);
                     prof.miss(1, fp_); }
                     prof.start();
                     if (TC_DEBUG(P, 0)) { }
-                    else if (patch) {
-                        // per filter column s one patch; rows r*bw .. r*bw+127 of it are the tile's 128 pixels under filter row r
-                        uint32_t as = a_lo, bs = b_col;
-                        for (int s = 0; s < kw_; ++s, as += patch_step, bs += b_tap_step) {
-                            uint32_t ar = as, br = bs;
-                            for (int r = 0; r < kh; ++r, ar += row_step, br += b_row_step) {
-                                if (kk == 4) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf);
-                                else if (kk == 2) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf);
-                                else mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf);
-                                accf = 1u;
-                            }
-                        }
-                        b_col += b_step;                                                     // next channel chunk
-                    } else {
+                    else if (!patch) {
                         if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         accf = 1u;
+                    } else {
+                        if (patch_kind == 1) patch_issue<3, 3, 2>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf);
+                        else if (patch_kind == 2) patch_issue<3, 3, 4>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf);
+                        else {
+                            // per filter column s one patch; rows r*bw .. r*bw+127 of it are the tile's 128 pixels under filter row r
+                            uint32_t as = a_lo, bs = b_col;
+                            for (int s = 0; s < kw_; ++s, as += patch_step, bs += b_tap_step) {
+                                uint32_t ar = as, br = bs;
+                                for (int r = 0; r < kh; ++r, ar += row_step, br += b_row_step) {
+                                    if (kk == 4) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf);
+                                    else if (kk == 2) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf);
+                                    else mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf);
+                                    accf = 1u;
+                                }
+                            }
+                        }
+                        accf = 1u;
+                        b_col += b_step;                                                     // next channel chunk
                     }
-                    prof.stop(2);
                     tc_commit(empty0 + 8u * (uint32_t)stage);                           // frees the stage once these MMAs have read it
+                    prof.stop(2);
                     if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
                     else { a_lo += a_step; b_lo += b_step; }
                 }
