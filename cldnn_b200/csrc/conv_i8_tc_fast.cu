@@ -294,12 +294,15 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const uint32_t full0 = smem_u32(&aux->full[0]), empty0 = smem_u32(&aux->empty[0]);
             Prof prof; prof.begin();
             TileWalk w; w.init(P, blockIdx.x, gridDim.x);
+            // Everything the loop needs sits in registers: this thread's scalar instructions are on the critical path of
+            // the layers whose stages hold little tensor-core work.
+            const int mode = P.a_mode, dil_x = P.dil_x, dil_y = P.dil_y, patch_alloc = P.patch_alloc;
             for (; w.valid() && ok; w.next()) {
                 int c_w = 0, c_h = 0, c_n = 0;
-                if (P.a_mode == A_IM2COL) { c_w = w.d0 * P.stride_x - P.pad_x; c_h = w.d1 * P.stride_y - P.pad_y; c_n = w.d2; }
-                else if (P.a_mode == A_TILED || patch) { c_w = w.d0 * P.bw - P.pad_x; c_h = w.d1 * P.bh - P.pad_y; c_n = w.d2 * P.bb; }
+                if (mode == A_IM2COL) { c_w = w.d0 * P.stride_x - P.pad_x; c_h = w.d1 * P.stride_y - P.pad_y; c_n = w.d2; }
+                else if (mode == A_TILED || patch) { c_w = w.d0 * P.bw - P.pad_x; c_h = w.d1 * P.bh - P.pad_y; c_n = w.d2 * P.bb; }
                 const int m0 = w.m_tile * kBM, n0 = w.n_tile * BN;
-                int tap = 0, cc = 0, r = 0, sx = 0;
+                int tap = 0, cc = 0, off_w = 0, off_h = 0, sx = 0;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     { bool fp_ = true;
                     if (!mbar_wait_lean(empty0 + 8u * (uint32_t)stage, phase ^ 1u, s_abort, P.status, kErrProducer, &fp_)) { ok = false; break; }
@@ -309,20 +312,20 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     const int c0 = cc * bk;
                     if (TC_DEBUG(P, 5)) {                                                   // what-if: no operand loads, the stage is declared full at once
                         mbar_arrive(full); ++issued;
-                        if (++cc == chunks) { cc = 0; ++tap; if (++sx == kw) { sx = 0; ++r; } }
+                        if (++cc == chunks) { cc = 0; ++tap; off_w += dil_x; if (++sx == kw) { sx = 0; off_w = 0; off_h += dil_y; } }
                         if (++stage == stages) { stage = 0; phase ^= 1u; }
                         continue;
                     }
                     mbar_expect_tx(full, tx);
                     if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
                     if (patch) {                                                            // one patch per filter column
-                        for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * P.patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
+                        for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
                     }
-                    else if (P.a_mode == A_FLAT) tma_load_2d(dst, &P.tmA, full, c0, m0);
-                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(sx * P.dil_x), (uint16_t)(r * P.dil_y));
-                    else tma_load_4d(dst, &P.tmA, full, c0, c_w + sx * P.dil_x, c_h + r * P.dil_y, c_n);
+                    else if (mode == A_FLAT) tma_load_2d(dst, &P.tmA, full, c0, m0);
+                    else if (mode == A_IM2COL) tma_load_im2col_4d(dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)off_w, (uint16_t)off_h);
+                    else tma_load_4d(dst, &P.tmA, full, c0, c_w + off_w, c_h + off_h, c_n);
                     ++issued;
-                    if (++cc == chunks) { cc = 0; ++tap; if (++sx == kw) { sx = 0; ++r; } }
+                    if (++cc == chunks) { cc = 0; ++tap; off_w += dil_x; if (++sx == kw) { sx = 0; off_w = 0; off_h += dil_y; } }
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
