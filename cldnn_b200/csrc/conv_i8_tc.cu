@@ -630,7 +630,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
     const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;     // operand signedness in the instruction descriptor
     P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(pl.bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-    P.nbuf = pl.bn >= 256 ? 2 : kMaxBufs;                      // accumulator and staging buffers in flight
+    P.nbuf = pl.bn >= 256 ? 2 : (pl.bn >= 128 ? 4 : 8);         // accumulator and staging buffers in flight: all of tensor memory
     P.tmem_cols = (uint32_t)(P.nbuf * pl.bn < 32 ? 32 : P.nbuf * pl.bn);
     P.ofm = p.ofm;
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;

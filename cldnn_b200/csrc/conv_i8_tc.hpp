@@ -17,7 +17,7 @@ constexpr int kStoreWarp = 2 + kEpiWarps;  // warp that issues the TMA stores of
 constexpr int kThreads = 64 + kEpiThreads + 32;
 constexpr int kMaxStages = 8;
 constexpr int kMaxBN = 256;
-constexpr int kMaxBufs = 4;               // accumulator / staging buffers in flight per CTA
+constexpr int kMaxBufs = 8;               // accumulator / staging buffers in flight per CTA (512 columns of tensor memory / feature tile)
 constexpr uint32_t kErrProducer = 0x10u, kErrMma = 0x20u, kErrEpilogue = 0x30u, kErrDrain = 0x40u;
 
 enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2, A_PATCH = 3 };
@@ -43,7 +43,7 @@ struct alignas(64) TcParams {
     int32_t cw, col_blocks, sw_shift, sw_mask, stage_rows;   // staging tile: column block width, 16-byte chunk swizzle
     int32_t mul_iqf, mul_oqf;
     int32_t lean;                        // epilogue configuration covered by the hoisted fast body
-    int32_t nbuf;                        // accumulator and staging buffers in flight (2 or 4)
+    int32_t nbuf;                        // accumulator and staging buffers in flight: 512 / feature tile, at most 8
     int32_t nstg;                        // conv_i8_tc_fast: staging tiles (>= nbuf when a fused residual is prefetched into them)
     // patch mode: all weights resident in shared memory, one activation patch per (filter column, channel chunk)
     int32_t ring_bytes, b_total_bytes;   // operand area: activation ring (+ weight ring or resident weights)

@@ -224,7 +224,7 @@ template <int BN, bool kFused>
 __global__ void __launch_bounds__(kFastThreads, 1)
 conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
 {
-    constexpr int NBUF = BN >= 256 ? 2 : 4;
+    constexpr int NBUF = BN >= 256 ? 2 : (BN >= 128 ? 4 : 8);         // all 512 columns of tensor memory
     constexpr int CW = BN < 128 ? BN : 128;
     constexpr int COLB = BN / CW;
     constexpr uint32_t kStagingBytes = (uint32_t)(kBM * BN);
