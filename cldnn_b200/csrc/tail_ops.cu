@@ -117,10 +117,11 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
     const int fv = p.in.f / 16;
     const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
     const bool fast_max = p.mode == CLDNN_B200_POOL_MAX && (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU);
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        const int f16 = (int)(idx % fv); int64_t t = idx / fv;
-        const int x = (int)(t % p.out.x); t /= p.out.x;
-        const int y = (int)(t % p.out.y); const int b = (int)(t / p.out.y);
+    // (32-bit index arithmetic: a 64-bit division costs more instructions than the pooling itself; the host admits < 2^31 items)
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x) {
+        const int f16 = (int)(idx % (uint32_t)fv); uint32_t t = idx / (uint32_t)fv;
+        const int x = (int)(t % (uint32_t)p.out.x); t /= (uint32_t)p.out.x;
+        const int y = (int)(t % (uint32_t)p.out.y); const int b = (int)(t / (uint32_t)p.out.y);
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
         if (fast_max) {
@@ -179,6 +180,7 @@ static bool pooling_i8_byxf_supports(const void* vp)
     if (p.in.pf != 1 || p.out.pf != 1 || p.in.f % 16) return false;
     const int64_t pitches[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
     for (int64_t v : pitches) if (v % 16) return false;
+    if ((int64_t)p.out.b * p.out.y * p.out.x * (p.in.f / 16) >= 0x7fffffffLL) return false;      // 32-bit item index
     return true;
 }
 
@@ -211,10 +213,10 @@ pooling_f16_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const 
     const int fv = p.in.f / 8;
     const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
     const bool is_max = p.mode == CLDNN_B200_POOL_MAX;
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        const int f8 = (int)(idx % fv); int64_t t = idx / fv;
-        const int x = (int)(t % p.out.x); t /= p.out.x;
-        const int y = (int)(t % p.out.y); const int b = (int)(t / p.out.y);
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x) {   // < 2^31 items (host check)
+        const int f8 = (int)(idx % (uint32_t)fv); uint32_t t = idx / (uint32_t)fv;
+        const int x = (int)(t % (uint32_t)p.out.x); t /= (uint32_t)p.out.x;
+        const int y = (int)(t % (uint32_t)p.out.y); const int b = (int)(t / (uint32_t)p.out.y);
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
         const int j0 = max(0, -oy), j1 = min(p.size_y, p.in.y - oy), i0 = max(0, -ox), i1 = min(p.size_x, p.in.x - ox);
@@ -262,6 +264,7 @@ static bool pooling_f16_byxf_supports(const void* vp)
     if (p.in.pf != 1 || p.out.pf != 1 || p.in.f % 8) return false;
     const int64_t pitches[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
     for (int64_t v : pitches) if (v % 8) return false;
+    if ((int64_t)p.out.b * p.out.y * p.out.x * (p.in.f / 8) >= 0x7fffffffLL) return false;       // 32-bit item index
     return true;
 }
 
@@ -588,10 +591,10 @@ lrn_f16_byxf_kernel(const __grid_constant__ cldnn_b200_lrn_params p, const __hal
     const int fv = p.in.f / 8;
     const int64_t total = (int64_t)p.in.b * p.in.y * p.in.x * fv;
     const float scale = __fdiv_rn(p.alpha, (float)p.size);
-    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
-        const int f8 = (int)(idx % fv); int64_t t = idx / fv;
-        const int x = (int)(t % p.in.x); t /= p.in.x;
-        const int y = (int)(t % p.in.y); const int b = (int)(t / p.in.y);
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x) {   // < 2^31 items (host check)
+        const int f8 = (int)(idx % (uint32_t)fv); uint32_t t = idx / (uint32_t)fv;
+        const int x = (int)(t % (uint32_t)p.in.x); t /= (uint32_t)p.in.x;
+        const int y = (int)(t % (uint32_t)p.in.y); const int b = (int)(t / (uint32_t)p.in.y);
         const int f0 = f8 * 8;
         const __half* src = in + tidx(p.in, b, f0, y, x);
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
@@ -626,6 +629,7 @@ static bool lrn_f16_byxf_supports(const void* vp)
     if (p.in.pf != 1 || p.out.pf != 1 || p.in.f % 8) return false;
     const int64_t pitches[] = {p.in.px, p.in.py, p.in.pb, p.in.offset, p.out.px, p.out.py, p.out.pb, p.out.offset};
     for (int64_t v : pitches) if (v % 8) return false;
+    if ((int64_t)p.in.b * p.in.y * p.in.x * (p.in.f / 8) >= 0x7fffffffLL) return false;         // 32-bit item index
     return true;
 }
 static int32_t lrn_f16_byxf_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
