@@ -89,7 +89,7 @@ class ClockSampler(threading.Thread):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of the 53 conv_i8_tc launches of one network execution at batch 256, per image
 # (one ncu capture on a B200; the algorithmic bytes of the same launches are 25.4 MB per image)
-NCU_DRAM_BYTES_PER_IMAGE_CONV_TC = 18.99e6
+NCU_DRAM_BYTES_PER_IMAGE_CONV_TC = 18.27e6
 NCU_TRAFFIC_BATCH = 256
 
 
