@@ -148,6 +148,31 @@ conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __gr
         for (int j = 0; j < p.kh; ++j) {
             const int iy = iy0 + j * p.dil_y; if (iy < 0 || iy >= p.in.y) continue;
             const uint8_t* rowp = src + (int64_t)iy * p.in.py;
+            if (p.kw == 3) {
+                // three-tap rows (the MobileNet case): the six loads of the row are issued before any arithmetic, so their
+                // latency is paid once per filter row instead of once per tap
+                uint4 xa3[3], xb3[3];
+#pragma unroll
+                for (int s = 0; s < 3; ++s) {
+                    const int xa = ix0 + s * p.dil_x, xb = ix1 + s * p.dil_x;
+                    xa3[s] = (xa >= 0 && xa < p.in.x) ? __ldg(reinterpret_cast<const uint4*>(rowp + (int64_t)xa * p.in.px)) : make_uint4(0, 0, 0, 0);
+                    xb3[s] = (second && xb >= 0 && xb < p.in.x) ? __ldg(reinterpret_cast<const uint4*>(rowp + (int64_t)xb * p.in.px)) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int s = 0; s < 3; ++s) {
+                    const uint32_t xw_a[4] = {xa3[s].x, xa3[s].y, xa3[s].z, xa3[s].w}, xw_b[4] = {xb3[s].x, xb3[s].y, xb3[s].z, xb3[s].w};
+                    const uint4* wt = s_w + (j * 3 + s) * c4n + g;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint4 wm = wt[k * a.c16n];
+                        acc0[4 * k + 0] = dp4a_in<kUnsignedIn>(xw_a[k], wm.x, acc0[4 * k + 0]); acc1[4 * k + 0] = dp4a_in<kUnsignedIn>(xw_b[k], wm.x, acc1[4 * k + 0]);
+                        acc0[4 * k + 1] = dp4a_in<kUnsignedIn>(xw_a[k], wm.y, acc0[4 * k + 1]); acc1[4 * k + 1] = dp4a_in<kUnsignedIn>(xw_b[k], wm.y, acc1[4 * k + 1]);
+                        acc0[4 * k + 2] = dp4a_in<kUnsignedIn>(xw_a[k], wm.z, acc0[4 * k + 2]); acc1[4 * k + 2] = dp4a_in<kUnsignedIn>(xw_b[k], wm.z, acc1[4 * k + 2]);
+                        acc0[4 * k + 3] = dp4a_in<kUnsignedIn>(xw_a[k], wm.w, acc0[4 * k + 3]); acc1[4 * k + 3] = dp4a_in<kUnsignedIn>(xw_b[k], wm.w, acc1[4 * k + 3]);
+                    }
+                }
+                continue;
+            }
             for (int s = 0; s < p.kw; ++s) {
                 const int xa = ix0 + s * p.dil_x, xb = ix1 + s * p.dil_x;
                 const bool va = xa >= 0 && xa < p.in.x, vb = second && xb >= 0 && xb < p.in.x;
