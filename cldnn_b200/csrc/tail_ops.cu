@@ -130,6 +130,23 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
             const int j0 = max(0, -oy), j1 = min(p.size_y, p.in.y - oy), i0 = max(0, -ox), i1 = min(p.size_x, p.in.x - ox);
             uint4 m = kUnsignedIn ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
             const uint8_t* src = in + tidx(p.in, b, f16 * 16, oy, ox);
+            if (p.size_x == 3 && p.size_y == 3 && j0 < j1 && i0 < i1) {
+                // 3x3 window: taps outside the input are replaced by the nearest valid tap (a repeated element does not
+                // change a maximum), so the nine loads carry no branches and are all in flight together
+                uint4 v[9];
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    const int64_t ro = (int64_t)min(max(j, j0), j1 - 1) * p.in.py;
+#pragma unroll
+                    for (int i = 0; i < 3; ++i)
+                        v[j * 3 + i] = __ldg((const uint4*)(src + ro + (int64_t)min(max(i, i0), i1 - 1) * p.in.px));
+                }
+#pragma unroll
+                for (int k = 0; k < 9; ++k) {
+                    if (kUnsignedIn) { m.x = __vmaxu4(m.x, v[k].x); m.y = __vmaxu4(m.y, v[k].y); m.z = __vmaxu4(m.z, v[k].z); m.w = __vmaxu4(m.w, v[k].w); }
+                    else { m.x = __vmaxs4(m.x, v[k].x); m.y = __vmaxs4(m.y, v[k].y); m.z = __vmaxs4(m.z, v[k].z); m.w = __vmaxs4(m.w, v[k].w); }
+                }
+            } else
             for (int j = j0; j < j1; ++j) {
 #pragma unroll 3
                 for (int i = i0; i < i1; ++i) {
@@ -207,6 +224,25 @@ const KernelDef kdef_pooling_i8_byxf = {"pooling_i8_byxf", sizeof(cldnn_b200_poo
 // packed halves, the average accumulated in fp32.  Same arithmetic as pooling_gpu_ref.cl
 // (its half accumulator for the average is replaced by a float one: tolerance parity).
 // ---------------------------------------------------------------------------------
+template <int S>
+__device__ __forceinline__ void pool_max_clamped(const __half* src, int64_t px, int64_t py, int i0, int i1, int j0, int j1, __half2 (&m)[4])
+{
+    uint4 v[S * S];
+#pragma unroll
+    for (int j = 0; j < S; ++j) {
+        const int64_t ro = (int64_t)min(max(j, j0), j1 - 1) * py;
+#pragma unroll
+        for (int i = 0; i < S; ++i)
+            v[j * S + i] = __ldg(reinterpret_cast<const uint4*>(src + ro + (int64_t)min(max(i, i0), i1 - 1) * px));
+    }
+#pragma unroll
+    for (int t = 0; t < S * S; ++t) {
+        const __half2* h = reinterpret_cast<const __half2*>(&v[t]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m[k] = __hmax2(m[k], h[k]);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 pooling_f16_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const __half* __restrict__ in, __half* __restrict__ out)
 {
@@ -225,6 +261,13 @@ pooling_f16_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const 
         __half2 m[4] = {lowest, lowest, lowest, lowest};
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         uint32_t n = 0;
+        const bool sq3 = p.size_x == 3 && p.size_y == 3, sq2 = p.size_x == 2 && p.size_y == 2;
+        if (is_max && (sq3 || sq2) && j0 < j1 && i0 < i1) {
+            // small square window: taps outside the input are replaced by the nearest valid tap (a repeated element
+            // does not change a maximum), so the loads carry no branches and are all in flight together
+            if (sq3) pool_max_clamped<3>(src, p.in.px, p.in.py, i0, i1, j0, j1, m);
+            else pool_max_clamped<2>(src, p.in.px, p.in.py, i0, i1, j0, j1, m);
+        } else
         for (int j = j0; j < j1; ++j) {
             for (int i = i0; i < i1; ++i) {
                 const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)j * p.in.py + (int64_t)i * p.in.px));
