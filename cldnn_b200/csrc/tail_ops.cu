@@ -110,6 +110,28 @@ __device__ __forceinline__ void unpack16(const uint4& v, int32_t (&e)[16])
     }
 }
 
+// Running maximum of four packed bytes kept as two words of 16-bit lanes, for the three-input 16-bit-pair maximum of
+// the hardware: the odd bytes are compared through the raw word (the upper byte of a lane decides, the lower byte is
+// ignored at the end), the even bytes are moved into the upper bytes of the lanes first.
+template <bool kUnsigned>
+struct ByteMax {
+    uint32_t odd = kUnsigned ? 0u : 0x80008000u, even = kUnsigned ? 0u : 0x80008000u;
+    static __device__ __forceinline__ uint32_t up(uint32_t w) { return __byte_perm(w, 0u, 0x2404); }    // bytes 0, 2 -> bytes 1, 3
+    static __device__ __forceinline__ uint32_t max3(uint32_t a, uint32_t b, uint32_t c) { return kUnsigned ? __vimax3_u16x2(a, b, c) : __vimax3_s16x2(a, b, c); }
+    __device__ __forceinline__ void add3(uint32_t a, uint32_t b, uint32_t c)
+    {
+        odd = max3(odd, max3(a, b, c), odd);
+        even = max3(even, max3(up(a), up(b), up(c)), even);
+    }
+    // relu: signed bytes, negative maxima become 0
+    __device__ __forceinline__ uint32_t result(bool relu) const
+    {
+        uint32_t o = odd, e = even;
+        if (!kUnsigned && relu) { o = __vimax3_s16x2_relu(o, o, o); e = __vimax3_s16x2_relu(e, e, e); }
+        return __byte_perm(o, e, 0x3715);                                                              // e.b1, o.b1, e.b3, o.b3
+    }
+};
+
 template <bool kUnsignedIn>
 __global__ void __launch_bounds__(256)
 pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const uint8_t* __restrict__ in, uint8_t* __restrict__ out)
@@ -125,11 +147,11 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
         if (fast_max) {
-            // maximum of the valid taps on packed bytes, no unpacking: the stored bits are the bits of the
+            // maximum of the valid taps on packed bytes, no unpacking to 32 bits: the stored bits are the bits of the
             // largest input (the conversion to the output type wraps), ReLU on a signed output is one more max
             const int j0 = max(0, -oy), j1 = min(p.size_y, p.in.y - oy), i0 = max(0, -ox), i1 = min(p.size_x, p.in.x - ox);
-            uint4 m = kUnsignedIn ? make_uint4(0u, 0u, 0u, 0u) : make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
             const uint8_t* src = in + tidx(p.in, b, f16 * 16, oy, ox);
+            ByteMax<kUnsignedIn> bm[4];
             if (p.size_x == 3 && p.size_y == 3 && j0 < j1 && i0 < i1) {
                 // 3x3 window: taps outside the input are replaced by the nearest valid tap (a repeated element does not
                 // change a maximum), so the nine loads carry no branches and are all in flight together
@@ -142,20 +164,20 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
                         v[j * 3 + i] = __ldg((const uint4*)(src + ro + (int64_t)min(max(i, i0), i1 - 1) * p.in.px));
                 }
 #pragma unroll
-                for (int k = 0; k < 9; ++k) {
-                    if (kUnsignedIn) { m.x = __vmaxu4(m.x, v[k].x); m.y = __vmaxu4(m.y, v[k].y); m.z = __vmaxu4(m.z, v[k].z); m.w = __vmaxu4(m.w, v[k].w); }
-                    else { m.x = __vmaxs4(m.x, v[k].x); m.y = __vmaxs4(m.y, v[k].y); m.z = __vmaxs4(m.z, v[k].z); m.w = __vmaxs4(m.w, v[k].w); }
+                for (int k = 0; k < 9; k += 3) {
+                    bm[0].add3(v[k].x, v[k + 1].x, v[k + 2].x); bm[1].add3(v[k].y, v[k + 1].y, v[k + 2].y);
+                    bm[2].add3(v[k].z, v[k + 1].z, v[k + 2].z); bm[3].add3(v[k].w, v[k + 1].w, v[k + 2].w);
                 }
             } else
             for (int j = j0; j < j1; ++j) {
 #pragma unroll 3
                 for (int i = i0; i < i1; ++i) {
                     const uint4 v = __ldg((const uint4*)(src + (int64_t)j * p.in.py + (int64_t)i * p.in.px));
-                    if (kUnsignedIn) { m.x = __vmaxu4(m.x, v.x); m.y = __vmaxu4(m.y, v.y); m.z = __vmaxu4(m.z, v.z); m.w = __vmaxu4(m.w, v.w); }
-                    else { m.x = __vmaxs4(m.x, v.x); m.y = __vmaxs4(m.y, v.y); m.z = __vmaxs4(m.z, v.z); m.w = __vmaxs4(m.w, v.w); }
+                    bm[0].add3(v.x, v.x, v.x); bm[1].add3(v.y, v.y, v.y); bm[2].add3(v.z, v.z, v.z); bm[3].add3(v.w, v.w, v.w);
                 }
             }
-            if (p.act == CLDNN_B200_ACT_RELU && p.out.dtype == CLDNN_B200_I8) { m.x = __vmaxs4(m.x, 0u); m.y = __vmaxs4(m.y, 0u); m.z = __vmaxs4(m.z, 0u); m.w = __vmaxs4(m.w, 0u); }
+            const bool relu = p.act == CLDNN_B200_ACT_RELU && p.out.dtype == CLDNN_B200_I8;
+            const uint4 m = make_uint4(bm[0].result(relu), bm[1].result(relu), bm[2].result(relu), bm[3].result(relu));
             *(uint4*)(out + tidx(p.out, b, f16 * 16, y, x)) = m;
             continue;
         }
@@ -163,6 +185,40 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
 #pragma unroll
         for (int i = 0; i < 16; ++i) r[i] = p.mode == CLDNN_B200_POOL_MAX ? -128 : 0;
         uint32_t n = 0;
+        const int taps = p.size_x * p.size_y;
+        if (p.mode == CLDNN_B200_POOL_AVG && ox >= 0 && oy >= 0 && ox + p.size_x <= p.in.x && oy + p.size_y <= p.in.y && taps <= 256) {
+            // whole window inside the input: sums of at most 256 bytes fit 16-bit lanes, so two masks and two additions
+            // take a word of four bytes (signed bytes are summed as byte + 128 and the 128s taken out at the end);
+            // eight taps are loaded per batch so that a long window (a global average) is not one load latency per tap
+            const uint8_t* src = in + tidx(p.in, b, f16 * 16, oy, ox);
+            uint32_t a[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+            int ti = 0, tj = 0;
+            for (int t0 = 0; t0 < taps; t0 += 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    v[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (t0 + u < taps) {
+                        v[u] = __ldg((const uint4*)(src + (int64_t)tj * p.in.py + (int64_t)ti * p.in.px));
+                        if (!kUnsignedIn) { v[u].x ^= 0x80808080u; v[u].y ^= 0x80808080u; v[u].z ^= 0x80808080u; v[u].w ^= 0x80808080u; }
+                    }
+                    if (++ti == p.size_x) { ti = 0; ++tj; }
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) { a[2 * k] += w[k] & 0x00ff00ffu; a[2 * k + 1] += (w[k] >> 8) & 0x00ff00ffu; }
+                }
+            }
+            n = (uint32_t)taps;
+            const int32_t off = kUnsignedIn ? 0 : 128 * taps;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                r[4 * k + 0] = (int32_t)(a[2 * k] & 0xffffu) - off;     r[4 * k + 1] = (int32_t)(a[2 * k + 1] & 0xffffu) - off;
+                r[4 * k + 2] = (int32_t)(a[2 * k] >> 16) - off;         r[4 * k + 3] = (int32_t)(a[2 * k + 1] >> 16) - off;
+            }
+        } else
         for (int j = 0; j < p.size_y; ++j) {
             const int iy = oy + j; if (iy < 0 || iy >= p.in.y) continue;
             for (int i = 0; i < p.size_x; ++i) {
