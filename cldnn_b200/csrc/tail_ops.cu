@@ -110,6 +110,28 @@ __device__ __forceinline__ void unpack16(const uint4& v, int32_t (&e)[16])
     }
 }
 
+// Item walk of the grid-stride loops over (batch, y, x, feature vector): the first item and the stride are
+// decomposed once, every later item follows by digit-wise addition with carries (a division by a run-time
+// divisor costs more instructions than the pooling of one item).
+struct ItemWalk {
+    int f, x, y, b, sf, sx, sy, sb, nf, nx, ny;
+    __device__ __forceinline__ void init(uint32_t first, uint32_t stride, int fv, int X, int Y)
+    {
+        nf = fv; nx = X; ny = Y;
+        f = (int)(first % (uint32_t)fv); uint32_t t = first / (uint32_t)fv;
+        x = (int)(t % (uint32_t)X); t /= (uint32_t)X; y = (int)(t % (uint32_t)Y); b = (int)(t / (uint32_t)Y);
+        sf = (int)(stride % (uint32_t)fv); t = stride / (uint32_t)fv;
+        sx = (int)(t % (uint32_t)X); t /= (uint32_t)X; sy = (int)(t % (uint32_t)Y); sb = (int)(t / (uint32_t)Y);
+    }
+    __device__ __forceinline__ void next()
+    {
+        f += sf; int c = f >= nf ? 1 : 0; f -= c ? nf : 0;
+        x += sx + c; c = x >= nx ? 1 : 0; x -= c ? nx : 0;
+        y += sy + c; c = y >= ny ? 1 : 0; y -= c ? ny : 0;
+        b += sb + c;
+    }
+};
+
 // Running maximum of four packed bytes kept as two words of 16-bit lanes, for the three-input 16-bit-pair maximum of
 // the hardware: the odd bytes are compared through the raw word (the upper byte of a lane decides, the lower byte is
 // ignored at the end), the even bytes are moved into the upper bytes of the lanes first.
@@ -140,10 +162,9 @@ pooling_i8_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const u
     const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
     const bool fast_max = p.mode == CLDNN_B200_POOL_MAX && (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU);
     // (32-bit index arithmetic: a 64-bit division costs more instructions than the pooling itself; the host admits < 2^31 items)
-    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x) {
-        const int f16 = (int)(idx % (uint32_t)fv); uint32_t t = idx / (uint32_t)fv;
-        const int x = (int)(t % (uint32_t)p.out.x); t /= (uint32_t)p.out.x;
-        const int y = (int)(t % (uint32_t)p.out.y); const int b = (int)(t / (uint32_t)p.out.y);
+    ItemWalk it; it.init(blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x, fv, p.out.x, p.out.y);
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x, it.next()) {
+        const int f16 = it.f, x = it.x, y = it.y, b = it.b;
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
         if (fast_max) {
@@ -305,10 +326,9 @@ pooling_f16_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const 
     const int fv = p.in.f / 8;
     const int64_t total = (int64_t)p.out.b * p.out.y * p.out.x * fv;
     const bool is_max = p.mode == CLDNN_B200_POOL_MAX;
-    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x) {   // < 2^31 items (host check)
-        const int f8 = (int)(idx % (uint32_t)fv); uint32_t t = idx / (uint32_t)fv;
-        const int x = (int)(t % (uint32_t)p.out.x); t /= (uint32_t)p.out.x;
-        const int y = (int)(t % (uint32_t)p.out.y); const int b = (int)(t / (uint32_t)p.out.y);
+    ItemWalk it; it.init(blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x, fv, p.out.x, p.out.y);
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x, it.next()) {   // < 2^31 items (host check)
+        const int f8 = it.f, x = it.x, y = it.y, b = it.b;
         const int ox = x * p.stride_x - p.pad_x, oy = y * p.stride_y - p.pad_y;
         if (ox + p.size_x < 0 || ox >= p.in.x || oy + p.size_y < 0 || oy >= p.in.y) continue;
         const int j0 = max(0, -oy), j1 = min(p.size_y, p.in.y - oy), i0 = max(0, -ox), i1 = min(p.size_x, p.in.x - ox);
@@ -337,6 +357,16 @@ pooling_f16_byxf_kernel(const __grid_constant__ cldnn_b200_pool_params p, const 
                 }
                 ++n;
             }
+        }
+        if (is_max && (p.act == CLDNN_B200_ACT_NONE || p.act == CLDNN_B200_ACT_RELU)) {
+            // the maximum is one of the inputs: stored as it is (ReLU: one more packed maximum), no trip through fp32
+            if (p.act == CLDNN_B200_ACT_RELU) {
+                const __half2 zero = __float2half2_rn(0.0f);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) m[k] = __hmax2(m[k], zero);
+            }
+            *reinterpret_cast<uint4*>(out + tidx(p.out, b, f8 * 8, y, x)) = *reinterpret_cast<const uint4*>(m);
+            continue;
         }
         float r[8];
         if (is_max) {

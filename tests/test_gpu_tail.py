@@ -53,6 +53,9 @@ POOLS = {
     "max2x2s2_s8_relu": dict(dtype=np.int8, N=1, C=48, H=8, W=8, size=2, stride=2, pad=0, mode=abi.POOL_MAX, act=abi.ACT_RELU),
     "global_avg_7x7_u8_to_s8": dict(dtype=np.uint8, N=3, C=64, H=7, W=7, size=7, stride=1, pad=0, mode=abi.POOL_AVG, out_dtype=np.int8),
     "avg3x3s1_pad1_s8_dynamic": dict(dtype=np.int8, N=1, C=16, H=6, W=7, size=3, stride=1, pad=1, mode=abi.POOL_AVG, div=abi.DIV_DYNAMIC),
+    # more items than one pass of the grid: every thread walks several (batch, y, x, feature vector) items
+    "max3x3s2_u8_many_items": dict(dtype=np.uint8, N=24, C=64, H=225, W=227, size=3, stride=2, pad=0, mode=abi.POOL_MAX),
+    "avg3x3s2_s8_many_items": dict(dtype=np.int8, N=40, C=48, H=113, W=225, size=3, stride=2, pad=1, mode=abi.POOL_AVG),
 }
 
 
@@ -107,6 +110,8 @@ F16_POOLS = {
     "max3x3s1_pad1_relu": dict(dtype=np.float16, N=1, C=40, H=9, W=7, size=3, stride=1, pad=1, mode=abi.POOL_MAX, act=abi.ACT_RELU, f_align=8),
     "global_avg_7x7": dict(dtype=np.float16, N=3, C=256, H=7, W=7, size=7, stride=1, pad=0, mode=abi.POOL_AVG, f_align=32),
     "avg3x3s2_pad1_dynamic": dict(dtype=np.float16, N=2, C=24, H=11, W=12, size=3, stride=2, pad=1, mode=abi.POOL_AVG, div=abi.DIV_DYNAMIC, f_align=8),
+    # more items than one pass of the grid: every thread walks several (batch, y, x, feature vector) items
+    "max2x2s2_many_items": dict(dtype=np.float16, N=40, C=72, H=113, W=115, size=2, stride=2, pad=0, mode=abi.POOL_MAX, f_align=8),
 }
 
 
