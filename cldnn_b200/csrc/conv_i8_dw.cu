@@ -85,6 +85,8 @@ struct Dw16Args {
     int32_t q2, c16n, lean, mul_oqf; // pixel pairs per row, 16-feature groups, conversion-free epilogue allowed, uniform O_QF present
     float acc_bound;                // taps * max|activation| * 128
     uint32_t items;
+    // column-walk kernel: every item is a strip of `strip_rows` output rows of one pixel pair and 4 features
+    int32_t strips, strip_rows; uint32_t col_items;
 };
 
 __global__ void dw_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t py, int64_t px, int64_t off, int C, int kh, int kw, uint32_t* __restrict__ dst)
@@ -103,6 +105,27 @@ __device__ __forceinline__ int32_t dp4a_in(uint32_t x, uint32_t w, int32_t c)
     if (kUnsignedIn) asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(c));
     else asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(w), "r"(c));
     return d;
+}
+
+// Four features of one pixel: accumulators -> requantised output word.  mode 0..2: conversion-free u8 / s8 / s8 after
+// ReLU (fast_quad), 3: every other configuration through the general epilogue.
+__device__ __forceinline__ uint32_t dw_epi_word(int mode, const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a,
+                                                const int32_t (&a4)[4], const int4 b4, const float4 q4, int f)
+{
+    if (mode == 0) return a.mul_oqf ? fast_quad<0, true>(a4, b4, q4, c.o_qf) : fast_quad<0, false>(a4, b4, q4, 1.0f);
+    if (mode == 1) return a.mul_oqf ? fast_quad<1, true>(a4, b4, q4, c.o_qf) : fast_quad<1, false>(a4, b4, q4, 1.0f);
+    if (mode == 2) return fast_quad<2, false>(a4, b4, q4, 1.0f);
+    uint32_t word = 0;
+    const int32_t bb[4] = {b4.x, b4.y, b4.z, b4.w}; const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float v = epi_quant(c, a4[e] + bb[e], qq[e], c.dont_dequantize_bias ? ((const float*)a.bias)[f + e] : 0.f,
+                                  p.calibration ? a.calib[f + e] : 1.f, 0.f, 1.f);
+        const int32_t r = __float2int_rz(v);
+        const int32_t sat = p.out.dtype == CLDNN_B200_U8 ? min(255, max(0, r)) : min(127, max(-128, r));
+        word |= ((uint32_t)sat & 0xffu) << (8 * e);
+    }
+    return word;
 }
 
 template <bool kUnsignedIn>
@@ -203,25 +226,105 @@ conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __gr
                 const int32_t a4[4] = {acc[4 * k], acc[4 * k + 1], acc[4 * k + 2], acc[4 * k + 3]};
                 const int4 b4 = *reinterpret_cast<const int4*>(s_bias + f0 + 4 * k);
                 const float4 q4 = *reinterpret_cast<const float4*>(s_quant + f0 + 4 * k);
-                if (mode == 0) ow[k] = a.mul_oqf ? fast_quad<0, true>(a4, b4, q4, c.o_qf) : fast_quad<0, false>(a4, b4, q4, 1.0f);
-                else if (mode == 1) ow[k] = a.mul_oqf ? fast_quad<1, true>(a4, b4, q4, c.o_qf) : fast_quad<1, false>(a4, b4, q4, 1.0f);
-                else if (mode == 2) ow[k] = fast_quad<2, false>(a4, b4, q4, 1.0f);
-                else {
-                    uint32_t word = 0;
-                    const int32_t bb[4] = {b4.x, b4.y, b4.z, b4.w}; const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int f = f0 + 4 * k + e;
-                        const float v = epi_quant(c, a4[e] + bb[e], qq[e], c.dont_dequantize_bias ? ((const float*)a.bias)[f] : 0.f,
-                                                  p.calibration ? a.calib[f] : 1.f, 0.f, 1.f);
-                        const int32_t r = __float2int_rz(v);
-                        const int32_t sat = p.out.dtype == CLDNN_B200_U8 ? min(255, max(0, r)) : min(127, max(-128, r));
-                        word |= ((uint32_t)sat & 0xffu) << (8 * e);
-                    }
-                    ow[k] = word;
-                }
+                ow[k] = dw_epi_word(mode, p, c, a, a4, b4, q4, f0 + 4 * k);
             }
             *reinterpret_cast<uint4*>(dst + (int64_t)px * p.out.px) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    }
+}
+
+// ---- 3x3 filters: 4 features x 2 pixels per thread, walking down a strip of output rows ----------
+// The nine masked weight words of each of the thread's 4 features, their bias and scale stay in registers for the
+// whole strip, and so do the three input rows under the current output row (kStride + 3 columns of one word each):
+// per output row a thread loads only the kStride new rows, one row ahead of their use.  No shared-memory traffic in
+// the loop; a warp reads and writes 128 consecutive bytes of a pixel.
+template <bool kUnsignedIn, int kStride>
+__global__ void __launch_bounds__(256, 2)
+conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid_constant__ EpiCfg c, const __grid_constant__ Dw16Args a)
+{
+    extern __shared__ uint4 s_dw[];
+    constexpr int kCols = kStride + 3;
+    const int C = p.out.f, c4n = C / 4;
+    uint4* s_w = s_dw;                                               // [tap][k][C / 16], as in the 16-feature kernel
+    int32_t* s_bias = reinterpret_cast<int32_t*>(s_dw + 9 * c4n);
+    float* s_quant = reinterpret_cast<float*>(s_bias + C);
+    __shared__ uint32_t s_wide;
+    if (threadIdx.x == 0) s_wide = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < 9 * c4n; i += blockDim.x) {
+        const int tap = i / c4n, r = i - tap * c4n;
+        s_w[(tap * 4 + (r & 3)) * a.c16n + (r >> 2)] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
+    }
+    bool wide = false;
+    for (int f = threadIdx.x; f < C; f += blockDim.x) {
+        const int32_t bi = (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? load_as_int(a.bias, p.bias_dtype, f) : 0;
+        const float q = p.quantization ? a.quant[f] : 1.0f;
+        s_bias[f] = bi; s_quant[f] = q;
+        wide = wide || !(__fmul_rn(__fmul_rn(__fadd_rn(a.acc_bound, fabsf((float)bi)), fabsf(q)), a.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f);
+    }
+    if (wide) atomicOr(&s_wide, 1u);
+    __syncthreads();
+    const int mode = (a.lean && !s_wide) ? (p.out.dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
+
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < a.col_items; idx += gridDim.x * blockDim.x) {
+        const uint32_t c4 = idx % (uint32_t)c4n; uint32_t t = idx / (uint32_t)c4n;
+        const uint32_t xq = t % (uint32_t)a.q2; t /= (uint32_t)a.q2;
+        const uint32_t strip = t % (uint32_t)a.strips; const uint32_t b = t / (uint32_t)a.strips;
+        const int f0 = (int)c4 * 4, x0 = (int)xq * 2;
+        const bool second = x0 + 1 < p.out.x;
+        uint32_t w[9][4];
+#pragma unroll
+        for (int tap = 0; tap < 9; ++tap) {
+            const uint4 wm = s_w[(tap * 4 + (int)(c4 & 3u)) * a.c16n + (int)(c4 >> 2)];
+            w[tap][0] = wm.x; w[tap][1] = wm.y; w[tap][2] = wm.z; w[tap][3] = wm.w;
+        }
+        const int4 b4 = *reinterpret_cast<const int4*>(s_bias + f0);
+        const float4 q4 = *reinterpret_cast<const float4*>(s_quant + f0);
+        // the kCols input columns under the pixel pair: byte offsets inside a row, -1 for a column outside the input
+        const int ix0 = x0 * kStride - p.pad_x;
+        int co[kCols];
+#pragma unroll
+        for (int s = 0; s < kCols; ++s) co[s] = (ix0 + s >= 0 && ix0 + s < p.in.x) ? (ix0 + s) * (int)p.in.px : -1;
+        const uint8_t* src = a.in + p.in.offset + (int64_t)b * p.in.pb + f0;
+        auto load_row = [&](int iy, uint32_t (&row)[kCols]) {
+            const bool in_y = iy >= 0 && iy < p.in.y;
+            const uint8_t* rowp = src + (int64_t)iy * p.in.py;
+#pragma unroll
+            for (int s = 0; s < kCols; ++s) row[s] = (in_y && co[s] >= 0) ? __ldg(reinterpret_cast<const uint32_t*>(rowp + co[s])) : 0u;
+        };
+        const int y0 = (int)strip * a.strip_rows, y1 = min(p.out.y, y0 + a.strip_rows);
+        int iy = y0 * kStride - p.pad_y;
+        uint32_t win[3][kCols];
+        load_row(iy, win[0]); load_row(iy + 1, win[1]); load_row(iy + 2, win[2]);
+        uint8_t* dst = a.out + p.out.offset + (int64_t)b * p.out.pb + (int64_t)y0 * p.out.py + (int64_t)x0 * p.out.px + f0;
+        for (int y = y0; y < y1; ++y, iy += kStride, dst += p.out.py) {
+            uint32_t nxt[kStride][kCols];
+            if (y + 1 < y1) {
+#pragma unroll
+                for (int r = 0; r < kStride; ++r) load_row(iy + 3 + r, nxt[r]);
+            } else {
+#pragma unroll
+                for (int r = 0; r < kStride; ++r)
+#pragma unroll
+                    for (int s = 0; s < kCols; ++s) nxt[r][s] = 0u;
+            }
+            int32_t acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+#pragma unroll
+                for (int s = 0; s < 3; ++s)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc0[e] = dp4a_in<kUnsignedIn>(win[j][s], w[j * 3 + s][e], acc0[e]);
+                        acc1[e] = dp4a_in<kUnsignedIn>(win[j][s + kStride], w[j * 3 + s][e], acc1[e]);
+                    }
+            *reinterpret_cast<uint32_t*>(dst) = dw_epi_word(mode, p, c, a, acc0, b4, q4, f0);
+            if (second) *reinterpret_cast<uint32_t*>(dst + p.out.px) = dw_epi_word(mode, p, c, a, acc1, b4, q4, f0);
+#pragma unroll
+            for (int s = 0; s < kCols; ++s) {
+                if (kStride == 1) { win[0][s] = win[1][s]; win[1][s] = win[2][s]; win[2][s] = nxt[0][s]; }
+                else { win[0][s] = win[2][s]; win[1][s] = nxt[0][s]; win[2][s] = nxt[kStride - 1][s]; }
+            }
         }
     }
 }
@@ -245,7 +348,6 @@ bool dw_plan(const cldnn_b200_conv_params& p, std::string* why)
     return true;
 }
 bool dw_supports(const void* vp) { return dw_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
-int dw_tune_count(const void*) { return 1; }
 
 // the 16-feature kernel: 16-byte aligned rows of features, its weight words and constants within shared memory
 bool dw16_ok(const cldnn_b200_conv_params& p)
@@ -257,6 +359,14 @@ bool dw16_ok(const cldnn_b200_conv_params& p)
     const int64_t items = (int64_t)p.out.b * p.out.y * ((p.out.x + 1) / 2) * (p.groups / 16);
     return items > 0 && items < 0x7fffffffLL;
 }
+// the column-walk kernel: 3x3 filters without dilation, stride 1 or 2 in both directions
+bool dwcol_ok(const cldnn_b200_conv_params& p)
+{
+    return dw16_ok(p) && p.kh == 3 && p.kw == 3 && p.dil_x == 1 && p.dil_y == 1 && p.stride_x == p.stride_y && (p.stride_x == 1 || p.stride_x == 2) &&
+           (int64_t)p.in.x * p.in.px < 0x7fffffffLL;
+}
+// tune 0: the column-walk kernel where it applies, 1: the 16-feature kernel
+int dw_tune_count(const void* vp) { return dwcol_ok(simplified_conv_params(*(const cldnn_b200_conv_params*)vp)) ? 2 : 1; }
 size_t dw_scratch(const void* vp)
 {
     const auto& p = *(const cldnn_b200_conv_params*)vp;
@@ -294,6 +404,30 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
         if (smem > 48 * 1024) {
             B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        }
+        if (dwcol_ok(p) && p.tune != 1) {
+            // strips of 14 output rows, shorter while the items would not fill the device
+            const int64_t per_row_strip = (int64_t)p.out.b * d.q2 * (p.groups / 4);
+            int rows = p.out.y < 14 ? p.out.y : 14;
+            while (rows > 4 && per_row_strip * ((p.out.y + rows - 1) / rows) < (int64_t)ctx->prop.multiProcessorCount * 1024) rows = (rows + 1) / 2;
+            d.strip_rows = rows; d.strips = (p.out.y + rows - 1) / rows;
+            const int64_t col_items = per_row_strip * d.strips;
+            if (col_items < 0x7fffffffLL) {
+                d.col_items = (uint32_t)col_items;
+                auto set_smem = [&](auto kern) { return smem > 48 * 1024 ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) : cudaSuccess; };
+                B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 2>));
+                B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 2>));
+                int64_t cblocks = (col_items + 255) / 256; const int64_t ccap = (int64_t)ctx->prop.multiProcessorCount * 8;
+                if (cblocks > ccap) cblocks = ccap;
+                const int cgrid = (int)cblocks; const int stride = p.stride_x;
+                out->fn = [p, c, d, cgrid, smem, uns_in, stride](cudaStream_t s) {
+                    if (uns_in) { if (stride == 1) conv_i8_dwcol_kernel<true, 1><<<cgrid, 256, smem, s>>>(p, c, d); else conv_i8_dwcol_kernel<true, 2><<<cgrid, 256, smem, s>>>(p, c, d); }
+                    else { if (stride == 1) conv_i8_dwcol_kernel<false, 1><<<cgrid, 256, smem, s>>>(p, c, d); else conv_i8_dwcol_kernel<false, 2><<<cgrid, 256, smem, s>>>(p, c, d); }
+                    return cudaGetLastError();
+                };
+                out->launches = 1;
+                return CLDNN_B200_SUCCESS;
+            }
         }
         int64_t blocks = ((int64_t)d.items + 255) / 256; const int64_t cap = (int64_t)ctx->prop.multiProcessorCount * 8;
         if (blocks > cap) blocks = cap;

@@ -300,6 +300,8 @@ DEPTHWISE = {
     "dw3x3_stride2_c96": dict(N=2, C=96, K=96, H=29, W=31, groups=96, stride=2),
     "dw5x5_dilated_c16": dict(N=1, C=16, K=16, H=13, W=12, groups=16, kh=5, kw=5, pad=4, dil=2),
     "dw3x3_c960_7x7": dict(N=3, C=960, K=960, H=7, W=7, groups=960),
+    # more strips of rows than one pass of the grid: the threads of the column-walk kernel take several items
+    "dw3x3_c144_many_items": dict(N=96, C=144, K=144, H=56, W=56, groups=144),
 }
 
 
@@ -312,9 +314,15 @@ def test_conv_i8_dw_matches_oracle(eng, name, variant):
     else:
         case = cases.make_conv_case(52, in_dtype=np.int8, out_dtype=np.int8, bias="f32", calib=True, act=abi.ACT_NONE,
                                     scale_lo=2.0 ** -11, scale_hi=2.0 ** -9, **kw)
-    assert eng.kernel("conv_i8_dw").supports(case.p)
-    want = _exact(eng, case, "conv_i8_dw")
-    assert len(np.unique(want)) > 4
+    k = eng.kernel("conv_i8_dw")
+    assert k.supports(case.p)
+    # tune 0: the column-walk kernel for 3x3 filters (the 16-feature kernel otherwise), tune 1: the 16-feature kernel
+    assert k.tune_count(case.p) == (2 if kw.get("kh", 3) == 3 else 1)
+    for tune in range(k.tune_count(case.p)):
+        case.p.tune = tune
+        want = _exact(eng, case, "conv_i8_dw")
+        assert len(np.unique(want)) > 4
+    case.p.tune = 0
     _exact(eng, case, "conv_ref")
 
 
@@ -337,8 +345,10 @@ def test_conv_i8_dw_conversion_free_variants(eng, name, wide):
         case = cases.make_conv_case(54, scale_lo=2.0 ** -11, scale_hi=2.0 ** -9, **geom, **DW_FAST[name])
         if wide:
             case.quant[5] = 700.0          # a feature whose values can exceed 2^22: the CTA takes the float-domain path
-        want = _exact(eng, case, "conv_i8_dw")
-        assert len(np.unique(want[:case.out_elems])) > 8
+        for tune in (0, 1):
+            case.p.tune = tune
+            want = _exact(eng, case, "conv_i8_dw")
+            assert len(np.unique(want[:case.out_elems])) > 8
 
 
 def test_conv_i8_dw_refuses_dense_and_grouped(eng):
