@@ -109,6 +109,10 @@ __device__ __forceinline__ int32_t dp4a_in(uint32_t x, uint32_t w, int32_t c)
 
 // Four features of one pixel: accumulators -> requantised output word.  mode 0..2: conversion-free u8 / s8 / s8 after
 // ReLU (fast_quad), 3: every other configuration through the general epilogue.
+template <int kMode, bool kOqf>
+__device__ __forceinline__ uint32_t dw_epi_word_t(const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a,
+                                                  const int32_t (&a4)[4], const int4 b4, const float4 q4, int f);
+
 __device__ __forceinline__ uint32_t dw_epi_word(int mode, const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a,
                                                 const int32_t (&a4)[4], const int4 b4, const float4 q4, int f)
 {
@@ -126,6 +130,14 @@ __device__ __forceinline__ uint32_t dw_epi_word(int mode, const cldnn_b200_conv_
         word |= ((uint32_t)sat & 0xffu) << (8 * e);
     }
     return word;
+}
+
+template <int kMode, bool kOqf>
+__device__ __forceinline__ uint32_t dw_epi_word_t(const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a,
+                                                  const int32_t (&a4)[4], const int4 b4, const float4 q4, int f)
+{
+    if (kMode < 3) return fast_quad<kMode, kOqf>(a4, b4, q4, kOqf ? c.o_qf : 1.0f);
+    return dw_epi_word(3, p, c, a, a4, b4, q4, f);
 }
 
 template <bool kUnsignedIn>
@@ -233,39 +245,13 @@ conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __gr
     }
 }
 
-// ---- 3x3 filters: 4 features x 2 pixels per thread, walking down a strip of output rows ----------
-// The nine masked weight words of each of the thread's 4 features, their bias and scale stay in registers for the
-// whole strip, and so do the three input rows under the current output row (kStride + 3 columns of one word each):
-// per output row a thread loads only the kStride new rows, one row ahead of their use.  No shared-memory traffic in
-// the loop; a warp reads and writes 128 consecutive bytes of a pixel.
-template <bool kUnsignedIn, int kStride>
-__global__ void __launch_bounds__(256, 2)
-conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid_constant__ EpiCfg c, const __grid_constant__ Dw16Args a)
+// Item loop of the column-walk kernel below for one epilogue variant (kMode as in dw_epi_word, kOqf: uniform O_QF).
+template <bool kUnsignedIn, int kStride, int kMode, bool kOqf>
+__device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a,
+                                            const uint4* s_w, const int32_t* s_bias, const float* s_quant)
 {
-    extern __shared__ uint4 s_dw[];
     constexpr int kCols = kStride + 3;
-    const int C = p.out.f, c4n = C / 4;
-    uint4* s_w = s_dw;                                               // [tap][k][C / 16], as in the 16-feature kernel
-    int32_t* s_bias = reinterpret_cast<int32_t*>(s_dw + 9 * c4n);
-    float* s_quant = reinterpret_cast<float*>(s_bias + C);
-    __shared__ uint32_t s_wide;
-    if (threadIdx.x == 0) s_wide = 0u;
-    __syncthreads();
-    for (int i = threadIdx.x; i < 9 * c4n; i += blockDim.x) {
-        const int tap = i / c4n, r = i - tap * c4n;
-        s_w[(tap * 4 + (r & 3)) * a.c16n + (r >> 2)] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
-    }
-    bool wide = false;
-    for (int f = threadIdx.x; f < C; f += blockDim.x) {
-        const int32_t bi = (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? load_as_int(a.bias, p.bias_dtype, f) : 0;
-        const float q = p.quantization ? a.quant[f] : 1.0f;
-        s_bias[f] = bi; s_quant[f] = q;
-        wide = wide || !(__fmul_rn(__fmul_rn(__fadd_rn(a.acc_bound, fabsf((float)bi)), fabsf(q)), a.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f);
-    }
-    if (wide) atomicOr(&s_wide, 1u);
-    __syncthreads();
-    const int mode = (a.lean && !s_wide) ? (p.out.dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
-
+    const int c4n = p.out.f / 4;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < a.col_items; idx += gridDim.x * blockDim.x) {
         const uint32_t c4 = idx % (uint32_t)c4n; uint32_t t = idx / (uint32_t)c4n;
         const uint32_t xq = t % (uint32_t)a.q2; t /= (uint32_t)a.q2;
@@ -318,8 +304,8 @@ conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __g
                         acc0[e] = dp4a_in<kUnsignedIn>(win[j][s], w[j * 3 + s][e], acc0[e]);
                         acc1[e] = dp4a_in<kUnsignedIn>(win[j][s + kStride], w[j * 3 + s][e], acc1[e]);
                     }
-            *reinterpret_cast<uint32_t*>(dst) = dw_epi_word(mode, p, c, a, acc0, b4, q4, f0);
-            if (second) *reinterpret_cast<uint32_t*>(dst + p.out.px) = dw_epi_word(mode, p, c, a, acc1, b4, q4, f0);
+            *reinterpret_cast<uint32_t*>(dst) = dw_epi_word_t<kMode, kOqf>(p, c, a, acc0, b4, q4, f0);
+            if (second) *reinterpret_cast<uint32_t*>(dst + p.out.px) = dw_epi_word_t<kMode, kOqf>(p, c, a, acc1, b4, q4, f0);
 #pragma unroll
             for (int s = 0; s < kCols; ++s) {
                 if (kStride == 1) { win[0][s] = win[1][s]; win[1][s] = win[2][s]; win[2][s] = nxt[0][s]; }
@@ -327,6 +313,45 @@ conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __g
             }
         }
     }
+}
+
+// ---- 3x3 filters: 4 features x 2 pixels per thread, walking down a strip of output rows ----------
+// The nine masked weight words of each of the thread's 4 features, their bias and scale stay in registers for the
+// whole strip, and so do the three input rows under the current output row (kStride + 3 columns of one word each):
+// per output row a thread loads only the kStride new rows, one row ahead of their use.  No shared-memory traffic in
+// the loop; a warp reads and writes 128 consecutive bytes of a pixel.
+template <bool kUnsignedIn, int kStride>
+__global__ void __launch_bounds__(256, 2)
+conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid_constant__ EpiCfg c, const __grid_constant__ Dw16Args a)
+{
+    extern __shared__ uint4 s_dw[];
+    constexpr int kCols = kStride + 3;
+    const int C = p.out.f, c4n = C / 4;
+    uint4* s_w = s_dw;                                               // [tap][k][C / 16], as in the 16-feature kernel
+    int32_t* s_bias = reinterpret_cast<int32_t*>(s_dw + 9 * c4n);
+    float* s_quant = reinterpret_cast<float*>(s_bias + C);
+    __shared__ uint32_t s_wide;
+    if (threadIdx.x == 0) s_wide = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < 9 * c4n; i += blockDim.x) {
+        const int tap = i / c4n, r = i - tap * c4n;
+        s_w[(tap * 4 + (r & 3)) * a.c16n + (r >> 2)] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
+    }
+    bool wide = false;
+    for (int f = threadIdx.x; f < C; f += blockDim.x) {
+        const int32_t bi = (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? load_as_int(a.bias, p.bias_dtype, f) : 0;
+        const float q = p.quantization ? a.quant[f] : 1.0f;
+        s_bias[f] = bi; s_quant[f] = q;
+        wide = wide || !(__fmul_rn(__fmul_rn(__fadd_rn(a.acc_bound, fabsf((float)bi)), fabsf(q)), a.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f);
+    }
+    if (wide) atomicOr(&s_wide, 1u);
+    __syncthreads();
+    // the epilogue variant is uniform over the CTA: chosen once, so that the row loop is straight-line code
+    const int mode = (a.lean && !s_wide) ? (p.out.dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
+    if (mode == 0) { if (a.mul_oqf) dwcol_items<kUnsignedIn, kStride, 0, true>(p, c, a, s_w, s_bias, s_quant); else dwcol_items<kUnsignedIn, kStride, 0, false>(p, c, a, s_w, s_bias, s_quant); }
+    else if (mode == 1) { if (a.mul_oqf) dwcol_items<kUnsignedIn, kStride, 1, true>(p, c, a, s_w, s_bias, s_quant); else dwcol_items<kUnsignedIn, kStride, 1, false>(p, c, a, s_w, s_bias, s_quant); }
+    else if (mode == 2) dwcol_items<kUnsignedIn, kStride, 2, false>(p, c, a, s_w, s_bias, s_quant);
+    else dwcol_items<kUnsignedIn, kStride, 3, false>(p, c, a, s_w, s_bias, s_quant);
 }
 
 bool dw_plan(const cldnn_b200_conv_params& p, std::string* why)
