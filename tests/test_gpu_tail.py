@@ -53,6 +53,9 @@ POOLS = {
     "max2x2s2_s8_relu": dict(dtype=np.int8, N=1, C=48, H=8, W=8, size=2, stride=2, pad=0, mode=abi.POOL_MAX, act=abi.ACT_RELU),
     "global_avg_7x7_u8_to_s8": dict(dtype=np.uint8, N=3, C=64, H=7, W=7, size=7, stride=1, pad=0, mode=abi.POOL_AVG, out_dtype=np.int8),
     "avg3x3s1_pad1_s8_dynamic": dict(dtype=np.int8, N=1, C=16, H=6, W=7, size=3, stride=1, pad=1, mode=abi.POOL_AVG, div=abi.DIV_DYNAMIC),
+    # windows inside the input: the average summed in 16-bit lanes
+    "global_avg_7x7_s8_relu": dict(dtype=np.int8, N=2, C=96, H=7, W=7, size=7, stride=1, pad=0, mode=abi.POOL_AVG, act=abi.ACT_RELU),
+    "avg4x4s2_u8": dict(dtype=np.uint8, N=2, C=32, H=10, W=12, size=4, stride=2, pad=0, mode=abi.POOL_AVG),
     # more items than one pass of the grid: every thread walks several (batch, y, x, feature vector) items
     "max3x3s2_u8_many_items": dict(dtype=np.uint8, N=24, C=64, H=225, W=227, size=3, stride=2, pad=0, mode=abi.POOL_MAX),
     "avg3x3s2_s8_many_items": dict(dtype=np.int8, N=40, C=48, H=113, W=225, size=3, stride=2, pad=1, mode=abi.POOL_AVG),
