@@ -264,6 +264,19 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
             const uint4 wm = s_w[(tap * 4 + (int)(c4 & 3u)) * a.c16n + (int)(c4 >> 2)];
             w[tap][0] = wm.x; w[tap][1] = wm.y; w[tap][2] = wm.z; w[tap][3] = wm.w;
         }
+        // stride 1: the four columns under the pixel pair are transposed into one word per feature (4 consecutive pixels
+        // of a row), so one dp4a takes a whole filter row: per feature and filter row the three weights in bytes 0..2
+        // for the left pixel and in bytes 1..3 for the right one
+        uint32_t wa[3][4], wb[3][4];
+        if (kStride == 1) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const uint32_t t0 = (w[j * 3 + 0][e] >> (8 * e)) & 0xffu, t1 = (w[j * 3 + 1][e] >> (8 * e)) & 0xffu, t2 = (w[j * 3 + 2][e] >> (8 * e)) & 0xffu;
+                    wa[j][e] = t0 | (t1 << 8) | (t2 << 16); wb[j][e] = wa[j][e] << 8;
+                }
+        }
         const int4 b4 = *reinterpret_cast<const int4*>(s_bias + f0);
         const float4 q4 = *reinterpret_cast<const float4*>(s_quant + f0);
         // the kCols input columns under the pixel pair: byte offsets inside a row, -1 for a column outside the input
@@ -278,16 +291,36 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
 #pragma unroll
             for (int s = 0; s < kCols; ++s) row[s] = (in_y && co[s] >= 0) ? __ldg(reinterpret_cast<const uint32_t*>(rowp + co[s])) : 0u;
         };
+        // stride 1, 4 x 4 byte transpose of a loaded row: (column, feature) -> (feature, column); done when the row enters
+        // the window, not when it is loaded, so that the loads stay ahead of their first use
+        auto transpose = [&](uint32_t (&row)[kCols]) {
+            if (kStride == 1) {
+                const uint32_t ta = __byte_perm(row[0], row[1], 0x5140), tb = __byte_perm(row[0], row[1], 0x7362);
+                const uint32_t tc = __byte_perm(row[2], row[3], 0x5140), td = __byte_perm(row[2], row[3], 0x7362);
+                row[0] = __byte_perm(ta, tc, 0x5410); row[1] = __byte_perm(ta, tc, 0x7632);
+                row[2] = __byte_perm(tb, td, 0x5410); row[3] = __byte_perm(tb, td, 0x7632);
+            }
+        };
         const int y0 = (int)strip * a.strip_rows, y1 = min(p.out.y, y0 + a.strip_rows);
         int iy = y0 * kStride - p.pad_y;
         uint32_t win[3][kCols];
         load_row(iy, win[0]); load_row(iy + 1, win[1]); load_row(iy + 2, win[2]);
+        // stride 1 keeps two rows in flight: `ahead` is the row of the next output row, loaded one iteration earlier
+        uint32_t ahead[kCols];
+        if (kStride == 1) {
+            if (y0 + 1 < y1) load_row(iy + 3, ahead);
+            else {
+#pragma unroll
+                for (int s = 0; s < kCols; ++s) ahead[s] = 0u;
+            }
+        }
+        transpose(win[0]); transpose(win[1]); transpose(win[2]);
         uint8_t* dst = a.out + p.out.offset + (int64_t)b * p.out.pb + (int64_t)y0 * p.out.py + (int64_t)x0 * p.out.px + f0;
         for (int y = y0; y < y1; ++y, iy += kStride, dst += p.out.py) {
             uint32_t nxt[kStride][kCols];
-            if (y + 1 < y1) {
+            if (kStride == 1 ? y + 2 < y1 : y + 1 < y1) {
 #pragma unroll
-                for (int r = 0; r < kStride; ++r) load_row(iy + 3 + r, nxt[r]);
+                for (int r = 0; r < kStride; ++r) load_row(iy + (kStride == 1 ? 4 : 3) + r, nxt[r]);
             } else {
 #pragma unroll
                 for (int r = 0; r < kStride; ++r)
@@ -295,20 +328,31 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
                     for (int s = 0; s < kCols; ++s) nxt[r][s] = 0u;
             }
             int32_t acc0[4] = {0, 0, 0, 0}, acc1[4] = {0, 0, 0, 0};
+            if (kStride == 1) {
 #pragma unroll
-            for (int j = 0; j < 3; ++j)
-#pragma unroll
-                for (int s = 0; s < 3; ++s)
+                for (int j = 0; j < 3; ++j)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        acc0[e] = dp4a_in<kUnsignedIn>(win[j][s], w[j * 3 + s][e], acc0[e]);
-                        acc1[e] = dp4a_in<kUnsignedIn>(win[j][s + kStride], w[j * 3 + s][e], acc1[e]);
+                        acc0[e] = dp4a_in<kUnsignedIn>(win[j][e], wa[j][e], acc0[e]);
+                        acc1[e] = dp4a_in<kUnsignedIn>(win[j][e], wb[j][e], acc1[e]);
                     }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 3; ++j)
+#pragma unroll
+                    for (int s = 0; s < 3; ++s)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            acc0[e] = dp4a_in<kUnsignedIn>(win[j][s], w[j * 3 + s][e], acc0[e]);
+                            acc1[e] = dp4a_in<kUnsignedIn>(win[j][s + kStride], w[j * 3 + s][e], acc1[e]);
+                        }
+            }
             *reinterpret_cast<uint32_t*>(dst) = dw_epi_word_t<kMode, kOqf>(p, c, a, acc0, b4, q4, f0);
             if (second) *reinterpret_cast<uint32_t*>(dst + p.out.px) = dw_epi_word_t<kMode, kOqf>(p, c, a, acc1, b4, q4, f0);
+            if (kStride == 1) transpose(ahead);
 #pragma unroll
             for (int s = 0; s < kCols; ++s) {
-                if (kStride == 1) { win[0][s] = win[1][s]; win[1][s] = win[2][s]; win[2][s] = nxt[0][s]; }
+                if (kStride == 1) { win[0][s] = win[1][s]; win[1][s] = win[2][s]; win[2][s] = ahead[s]; ahead[s] = nxt[0][s]; }
                 else { win[0][s] = win[2][s]; win[1][s] = nxt[0][s]; win[2][s] = nxt[kStride - 1][s]; }
             }
         }
@@ -316,8 +360,9 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
 }
 
 // ---- 3x3 filters: 4 features x 2 pixels per thread, walking down a strip of output rows ----------
-// The nine masked weight words of each of the thread's 4 features, their bias and scale stay in registers for the
-// whole strip, and so do the three input rows under the current output row (kStride + 3 columns of one word each):
+// The weight words of the thread's 4 features (stride 2: nine masked words per feature, one dp4a per multiply-add;
+// stride 1: the input words transposed to 4 pixels of one feature, one dp4a per filter row), their bias and scale stay
+// in registers for the whole strip, and so do the three input rows under the current output row (kStride + 3 columns of one word each):
 // per output row a thread loads only the kStride new rows, one row ahead of their use.  No shared-memory traffic in
 // the loop; a warp reads and writes 128 consecutive bytes of a pixel.
 template <bool kUnsignedIn, int kStride>
