@@ -305,22 +305,23 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
         int iy = y0 * kStride - p.pad_y;
         uint32_t win[3][kCols];
         load_row(iy, win[0]); load_row(iy + 1, win[1]); load_row(iy + 2, win[2]);
-        // stride 1 keeps two rows in flight: `ahead` is the row of the next output row, loaded one iteration earlier
-        uint32_t ahead[kCols];
-        if (kStride == 1) {
-            if (y0 + 1 < y1) load_row(iy + 3, ahead);
+        // two output rows of loads in flight: `ahead` holds the new rows of the next output row, loaded one iteration earlier
+        uint32_t ahead[kStride][kCols];
+#pragma unroll
+        for (int r = 0; r < kStride; ++r) {
+            if (y0 + 1 < y1) load_row(iy + 3 + r, ahead[r]);
             else {
 #pragma unroll
-                for (int s = 0; s < kCols; ++s) ahead[s] = 0u;
+                for (int s = 0; s < kCols; ++s) ahead[r][s] = 0u;
             }
         }
         transpose(win[0]); transpose(win[1]); transpose(win[2]);
         uint8_t* dst = a.out + p.out.offset + (int64_t)b * p.out.pb + (int64_t)y0 * p.out.py + (int64_t)x0 * p.out.px + f0;
         for (int y = y0; y < y1; ++y, iy += kStride, dst += p.out.py) {
             uint32_t nxt[kStride][kCols];
-            if (kStride == 1 ? y + 2 < y1 : y + 1 < y1) {
+            if (y + 2 < y1) {
 #pragma unroll
-                for (int r = 0; r < kStride; ++r) load_row(iy + (kStride == 1 ? 4 : 3) + r, nxt[r]);
+                for (int r = 0; r < kStride; ++r) load_row(iy + 3 + kStride + r, nxt[r]);
             } else {
 #pragma unroll
                 for (int r = 0; r < kStride; ++r)
@@ -349,11 +350,13 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
             }
             *reinterpret_cast<uint32_t*>(dst) = dw_epi_word_t<kMode, kOqf>(p, c, a, acc0, b4, q4, f0);
             if (second) *reinterpret_cast<uint32_t*>(dst + p.out.px) = dw_epi_word_t<kMode, kOqf>(p, c, a, acc1, b4, q4, f0);
-            if (kStride == 1) transpose(ahead);
+            if (kStride == 1) transpose(ahead[0]);
 #pragma unroll
             for (int s = 0; s < kCols; ++s) {
-                if (kStride == 1) { win[0][s] = win[1][s]; win[1][s] = win[2][s]; win[2][s] = ahead[s]; ahead[s] = nxt[0][s]; }
-                else { win[0][s] = win[2][s]; win[1][s] = nxt[0][s]; win[2][s] = nxt[kStride - 1][s]; }
+                if (kStride == 1) { win[0][s] = win[1][s]; win[1][s] = win[2][s]; win[2][s] = ahead[0][s]; }
+                else { win[0][s] = win[2][s]; win[1][s] = ahead[0][s]; win[2][s] = ahead[kStride - 1][s]; }
+#pragma unroll
+                for (int r = 0; r < kStride; ++r) ahead[r][s] = nxt[r][s];
             }
         }
     }
