@@ -369,7 +369,7 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
 // per output row a thread loads only the kStride new rows, one row ahead of their use.  No shared-memory traffic in
 // the loop; a warp reads and writes 128 consecutive bytes of a pixel.
 template <bool kUnsignedIn, int kStride>
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(256, kStride == 1 ? 3 : 2)
 conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid_constant__ EpiCfg c, const __grid_constant__ Dw16Args a)
 {
     extern __shared__ uint4 s_dw[];
