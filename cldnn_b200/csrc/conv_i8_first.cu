@@ -383,8 +383,9 @@ static bool first_plan(const cldnn_b200_conv_params& p, std::string* why)
     return true;
 }
 static bool first_supports(const void* vp) { return first_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
-// tune 0 / 2: as many CTAs per SM as fit (at most two), 1: one CTA per SM with the double-buffered epilogue
-static int first_tune_count(const void*) { return 3; }
+// tune 0 / 2: as many CTAs per SM as fit (at most two), 1: one CTA per SM with the double-buffered epilogue,
+// 3: up to three CTAs per SM (72 registers per thread: more warps against the latency of the patch loads)
+static int first_tune_count(const void*) { return 4; }
 static int first_kp(const cldnn_b200_conv_params& p) { return (p.ifm * p.kh * 8 + 31) / 32 * 32; }
 static size_t first_scratch(const void* vp) { const auto& p = *(const cldnn_b200_conv_params*)vp; return (size_t)p.ofm * first_kp(p); }
 
@@ -434,9 +435,10 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory");
     B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // CTAs per SM: bounded by shared memory and by tensor memory (512 columns per SM)
     int per_sm = (int)(ctx->prop.sharedMemPerMultiprocessor / (smem + 1024));
-    per_sm = std::min(per_sm, std::min(2, (int)(512 / P.tmem_cols)));
+    per_sm = std::min(per_sm, std::min(p.tune == 3 ? 3 : 2, (int)(512 / P.tmem_cols)));
     if (per_sm < 1) per_sm = 1;
     if (p.tune == 1) per_sm = 1;
     P.ctas_per_sm = per_sm;
@@ -447,7 +449,8 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
 
 static cudaError_t first_launch(const FirstParams& P, int grid, size_t smem, cudaStream_t s)
 {
-    if (P.ctas_per_sm >= 2) conv_i8_first_kernel<2><<<grid, kFThreads, smem, s>>>(P);
+    if (P.ctas_per_sm >= 3) conv_i8_first_kernel<3><<<grid, kFThreads, smem, s>>>(P);
+    else if (P.ctas_per_sm == 2) conv_i8_first_kernel<2><<<grid, kFThreads, smem, s>>>(P);
     else conv_i8_first_kernel<1><<<grid, kFThreads, smem, s>>>(P);
     return cudaGetLastError();
 }
