@@ -720,10 +720,9 @@ lrn_f16_byxf_kernel(const __grid_constant__ cldnn_b200_lrn_params p, const __hal
     const int fv = p.in.f / 8;
     const int64_t total = (int64_t)p.in.b * p.in.y * p.in.x * fv;
     const float scale = __fdiv_rn(p.alpha, (float)p.size);
-    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x) {   // < 2^31 items (host check)
-        const int f8 = (int)(idx % (uint32_t)fv); uint32_t t = idx / (uint32_t)fv;
-        const int x = (int)(t % (uint32_t)p.in.x); t /= (uint32_t)p.in.x;
-        const int y = (int)(t % (uint32_t)p.in.y); const int b = (int)(t / (uint32_t)p.in.y);
+    ItemWalk it; it.init(blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x, fv, p.in.x, p.in.y);
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < (uint32_t)total; idx += gridDim.x * blockDim.x, it.next()) {   // < 2^31 items (host check)
+        const int f8 = it.f, x = it.x, y = it.y, b = it.b;
         const int f0 = f8 * 8;
         const __half* src = in + tidx(p.in, b, f0, y, x);
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));

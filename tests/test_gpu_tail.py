@@ -135,7 +135,7 @@ def test_pooling_fp16_matches_oracle(eng, name, kernel):
 
 
 @pytest.mark.parametrize("kernel", ["lrn_f16_byxf", "lrn_ref"])
-@pytest.mark.parametrize("shape", [(2, 96, 13, 14), (1, 256, 5, 6), (3, 8, 4, 4)])
+@pytest.mark.parametrize("shape", [(2, 96, 13, 14), (1, 256, 5, 6), (3, 8, 4, 4), (24, 96, 55, 54)])   # the last: several items per thread
 def test_lrn_fp16_across_channels_matches_oracle(eng, kernel, shape):
     """AlexNet's local response normalisation (window 5, k = 1, alpha = 1e-4, beta = 0.75; and a strong alpha so the
     neighbours matter) in the feature-innermost layout; 2e-3 relative to the output scale (fp16 output, device pow)."""
