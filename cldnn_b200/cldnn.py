@@ -21,8 +21,8 @@ class data_types:
 
 
 class format:
-    yxfb, byxf, bfyx, byxf_af32 = 0, 1, 2, 24
-    names = {0: "yxfb", 1: "byxf", 2: "bfyx", 24: "byxf_af32"}
+    yxfb, byxf, bfyx, byxf_af32 = 0, 1, 2, 21
+    names = {0: "yxfb", 1: "byxf", 2: "bfyx", 21: "byxf_af32"}
 
 
 class eltwise_mode:

@@ -461,25 +461,33 @@ static CUresult f16_pixel_map(CUtensorMap* tm, const F16Plan& pl, void* ptr, con
 }
 
 template <int BN, bool kFused>
-static cudaError_t f16_launch_inst(const Params& P, int grid, size_t smem, int max_smem, cudaStream_t s)
+static cudaError_t f16_launch_inst(const Params& P, int grid, size_t smem, cudaStream_t s)
 {
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(f16tc::conv_f16_tc_kernel<BN, kFused>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
     f16tc::conv_f16_tc_kernel<BN, kFused><<<grid, f16tc::kThreads, smem, s>>>(P);
     return cudaGetLastError();
 }
-static cudaError_t f16_launch(const Params& P, int grid, size_t smem, int max_smem, cudaStream_t s)
+static cudaError_t f16_launch(const Params& P, int grid, size_t smem, cudaStream_t s)
 {
     const bool f = P.fused != 0;
     switch (P.bn) {
-    case 64:  return f ? f16_launch_inst<64, true>(P, grid, smem, max_smem, s) : f16_launch_inst<64, false>(P, grid, smem, max_smem, s);
-    case 128: return f ? f16_launch_inst<128, true>(P, grid, smem, max_smem, s) : f16_launch_inst<128, false>(P, grid, smem, max_smem, s);
-    default:  return f ? f16_launch_inst<256, true>(P, grid, smem, max_smem, s) : f16_launch_inst<256, false>(P, grid, smem, max_smem, s);
+    case 64:  return f ? f16_launch_inst<64, true>(P, grid, smem, s) : f16_launch_inst<64, false>(P, grid, smem, s);
+    case 128: return f ? f16_launch_inst<128, true>(P, grid, smem, s) : f16_launch_inst<128, false>(P, grid, smem, s);
+    default:  return f ? f16_launch_inst<256, true>(P, grid, smem, s) : f16_launch_inst<256, false>(P, grid, smem, s);
     }
+}
+// The dynamic shared-memory limit belongs to (function, device): it is raised to the device maximum every time a launch
+// is prepared, with the context's device current, so that each GPU of a process gets it and nothing is kept in a
+// process-wide flag.
+static cudaError_t f16_configure(const Params& P, int max_smem)
+{
+    const bool f = P.fused != 0;
+    const void* fn;
+    switch (P.bn) {
+    case 64:  fn = f ? (const void*)f16tc::conv_f16_tc_kernel<64, true> : (const void*)f16tc::conv_f16_tc_kernel<64, false>; break;
+    case 128: fn = f ? (const void*)f16tc::conv_f16_tc_kernel<128, true> : (const void*)f16tc::conv_f16_tc_kernel<128, false>; break;
+    default:  fn = f ? (const void*)f16tc::conv_f16_tc_kernel<256, true> : (const void*)f16tc::conv_f16_tc_kernel<256, false>; break;
+    }
+    return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
 }
 
 static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
@@ -586,8 +594,9 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     int grid = ctx->prop.multiProcessorCount;
     if (grid > P.total_tiles) grid = P.total_tiles;
     if (grid < 1) return fail(CLDNN_B200_INVALID_ARG, "conv_f16_tc: empty output");
-    const size_t smem = smem_bytes; const int ms = (int)max_smem;
-    out->fn = [P, grid, smem, ms](cudaStream_t s) { return f16_launch(P, grid, smem, ms, s); };
+    const size_t smem = smem_bytes;
+    B200_CUDA(f16_configure(P, (int)max_smem));
+    out->fn = [P, grid, smem](cudaStream_t s) { return f16_launch(P, grid, smem, s); };
     out->launches = 1;
     return CLDNN_B200_SUCCESS;
 }
@@ -656,8 +665,9 @@ int32_t f16_batched_gemm_prepare(cldnn_b200_ctx_impl* ctx, const void* A, const 
     if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_DEVICE_ERROR, "f16 batched gemm: tensor map rejected by the driver (CUresult " + std::to_string((int)cr) + ")");
     int grid = ctx->prop.multiProcessorCount;
     if (grid > P.total_tiles) grid = P.total_tiles;
-    const size_t smem = smem_bytes; const int ms = (int)max_smem;
-    fn = [P, grid, smem, ms](cudaStream_t s) { return f16_launch(P, grid, smem, ms, s); };
+    const size_t smem = smem_bytes;
+    B200_CUDA(f16_configure(P, (int)max_smem));
+    fn = [P, grid, smem](cudaStream_t s) { return f16_launch(P, grid, smem, s); };
     return CLDNN_B200_SUCCESS;
 }
 

@@ -64,18 +64,12 @@ struct Params {
     uint32_t idesc, tmem_cols, sbo_b;
     int32_t bias_dtype, act; float act_m, act_n;     // fp16 epilogue
     int32_t nacc;                                    // accumulator buffers in tensor memory: up to kAccBufs of ofm columns each
-    int32_t debug;                                   // diagnostic builds (-DCONV_TC_DEBUG): what-if switches, 0 otherwise
     int32_t mul_iqf, mul_oqf, lean;                  // 8-bit epilogue (lean: per-feature scale, optional uniform O_QF, NONE / ReLU, integer bias)
     const void* in; void* out; const uint8_t* wpacked; const int4* table; const void* bias; const float* quant; const float* calib;
     uint32_t* status;
     EpiCfg epi;
 };
 
-#ifdef CONV_TC_DEBUG
-#define FTC_DEBUG(P, bit) (((P).debug >> (bit)) & 1)
-#else
-#define FTC_DEBUG(P, bit) 0
-#endif
 
 struct Aux {
     uint64_t a_full[kStages], a_empty[kStages], tmem_full[kAccBufs], tmem_empty[kAccBufs];
@@ -228,7 +222,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
             __syncwarp();
             if (!ok) break;
             const int ncore = min(8, P.cores - ch * 8);
-            if (P.fast_ok && !FTC_DEBUG(P, 0)) {
+            if (P.fast_ok) {
                 // Every quantum is one run of QE consecutive input elements starting anywhere: the two aligned 8-byte words
                 // around it, shifted into place.  Elements [lo, hi) of the run are taps inside the image; only words holding
                 // one of them are read (an aligned word that holds a valid byte lies in the same page: the read cannot
@@ -330,7 +324,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
 #pragma unroll
                         for (int i = 0; i < EPC / 2; ++i) {
                             const int ix = ix0 + i * P.dil_x;
-                            const bool in_image = valid && !FTC_DEBUG(P, 0) && i < nv && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W;
+                            const bool in_image = valid && i < nv && iy >= 0 && iy < P.H && ix >= 0 && ix < P.W;
                             e[h2 * (EPC / 2) + i] = in_image ? load_elem(src + t.x + i * step) : 0u;
                         }
                     }
@@ -369,7 +363,6 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
                     const uint64_t adesc = desc_interleaved(smem_u32(sA + stage * kStageBytes), 128u, 1024u);
                     const uint64_t bdesc = desc_interleaved(smem_u32(sB + ch * 8 * 128), 128u, P.sbo_b);
                     for (int i = 0; i < nm; ++i) {
-                        if (FTC_DEBUG(P, 2)) break;
                         if (kHalf) mma_f16_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
                         else mma_i8_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
                     }
@@ -398,7 +391,7 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
                 tmem_ld_32x32(t_row + (uint32_t)c0, r);
                 tmem_ld_wait();
                 if (c0 + 32 >= P.ofm) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[buf])); }
-                if (!valid || FTC_DEBUG(P, 1)) continue;
+                if (!valid) continue;
                 if (kHalf) {
                     uint4* op = reinterpret_cast<uint4*>(out_row + c0);
 #pragma unroll
@@ -538,18 +531,15 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.table = (const int4*)((const uint8_t*)a->scratch + ftc_table_offset(p));
     P.bias = a->bias; P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors;
     P.status = ctx->d_status;
-#ifdef CONV_TC_DEBUG
-    if (const char* e = getenv("CLDNN_B200_TC_DEBUG")) P.debug = atoi(e);
-#endif
 
     // pack the weights and build the table once, on the context's stream, before anything that is prepared here can run
     const int pack_blocks = (p.ofm * P.cores * (16 / es) + 255) / 256;
     if (half) {
-        B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin));
         firsttc::first_tc_pack<__half><<<pack_blocks, 256, 0, ctx->stream>>>((const __half*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset, p.ofm, p.ifm, p.kh, p.kw,
                                                                               P.cores, (__half*)a->scratch, (int4*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     } else {
-        B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<uint8_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<uint8_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin));
         firsttc::first_tc_pack<uint8_t><<<pack_blocks, 256, 0, ctx->stream>>>((const uint8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset, p.ofm, p.ifm, p.kh, p.kw,
                                                                                P.cores, (uint8_t*)a->scratch, (int4*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     }

@@ -475,8 +475,10 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
         B200_CUDA(cudaGetLastError());
         const size_t smem = (size_t)taps_c * 4 + (size_t)p.groups * 8;
         if (smem > 48 * 1024) {
-            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            // the device maximum (less the kernels' few static bytes), never this shape's own size: the limit is shared by
+            // every prepared launch of the function
+            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin - 1024));
+            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin - 1024));
         }
         if (dwcol_ok(p) && p.tune != 1) {
             // strips of 14 output rows, shorter while the items would not fill the device
@@ -487,7 +489,7 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
             const int64_t col_items = per_row_strip * d.strips;
             if (col_items < 0x7fffffffLL) {
                 d.col_items = (uint32_t)col_items;
-                auto set_smem = [&](auto kern) { return smem > 48 * 1024 ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) : cudaSuccess; };
+                auto set_smem = [&](auto kern) { return smem > 48 * 1024 ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin - 1024) : cudaSuccess; };
                 B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 2>));
                 B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 2>));
                 int64_t cblocks = (col_items + 255) / 256; const int64_t ccap = (int64_t)ctx->prop.multiProcessorCount * 8;

@@ -368,7 +368,7 @@ static bool first_plan(const cldnn_b200_conv_params& p, std::string* why)
     if (p.out.pf != 1 || !is_int8(p.out.dtype)) return no("output must be 8-bit byxf");
     if (p.kw > 8 || p.kh < 1 || p.kw < 1) return no("filter width up to 8");
     if (p.dil_x != 1 || p.dil_y != 1) return no("no dilation");
-    if (p.ifm * p.kh * 8 > kFMaxK) return no("C*kh*8 must not exceed 256");
+    if (p.ifm < 1 || (int64_t)p.ifm * p.kh * 8 > kFMaxK) return no("C*kh*8 must not exceed 256");
     if (p.ofm % 32 || p.ofm > kFMaxOfm || p.out.f != p.ofm || p.in.f != p.ifm) return no("output features: multiple of 32, at most 256");
     if (p.out.px % 16 || p.out.py % 16 || p.out.pb % 16 || p.out.offset % 16) return no("output pitches must be 16-byte aligned");
     if (p.stride_x < 1 || p.stride_y < 1 || p.stride_x > 4 || p.stride_y > 4) return no("stride 1..4");
@@ -433,9 +433,12 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     if (patch_bytes / 4 > kBuilders * kMaxPre) return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_i8_first: the input patch of one tile is too large");
     smem = 128 + (size_t)2 * 128 * P.Kp + (size_t)P.ofm * P.Kp + ((patch_bytes + 15) & ~15) + sizeof(FirstAux);
     if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory");
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // the limit is a property of the function on this device, shared by every prepared launch: always the device maximum,
+    // so that a later, smaller shape never lowers it under an earlier launch that is still alive
+    const int max_smem = (int)ctx->prop.sharedMemPerBlockOptin;
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
     // CTAs per SM: bounded by shared memory and by tensor memory (512 columns per SM)
     int per_sm = (int)(ctx->prop.sharedMemPerMultiprocessor / (smem + 1024));
     per_sm = std::min(per_sm, std::min(p.tune == 3 ? 3 : 2, (int)(512 / P.tmem_cols)));
@@ -516,10 +519,18 @@ extern "C" int32_t cldnn_b200_conv_first_noalloc(cldnn_b200_ctx ctx, const cldnn
 {
     using namespace b200;
     if (!ctx || !params || !args) return fail(CLDNN_B200_INVALID_ARG, "conv_first_noalloc: null argument");
-    const size_t need = (params->ofm > 0 && params->ifm > 0 && params->kh > 0) ? first_scratch(params) : 0;
-    if (need > kNoAllocScratchBytes)
-        return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_first_noalloc: the packed weights need " + std::to_string(need) + " bytes, the built-in scratch holds " +
-                                                 std::to_string(kNoAllocScratchBytes) + "; use conv_i8_first with caller-provided scratch");
+    {
+        // shapes the kernel cannot run are refused first, with the same code conv_i8_first gives them; only then the size
+        // of the packed weights (64-bit: the counts come from the caller) is held against the built-in array
+        const cldnn_b200_conv_params sp = simplified_conv_params(*params);
+        std::string why;
+        if (!first_plan(sp, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_first_noalloc: " + why);
+        const uint64_t kp = ((uint64_t)sp.ifm * (uint64_t)sp.kh * 8u + 31u) / 32u * 32u;
+        const uint64_t need = (uint64_t)sp.ofm * kp;
+        if (need > kNoAllocScratchBytes)
+            return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_first_noalloc: the packed weights need " + std::to_string(need) + " bytes, the built-in scratch holds " +
+                                                     std::to_string(kNoAllocScratchBytes) + "; use conv_i8_first with caller-provided scratch");
+    }
     int prev = -1;
     if (cudaGetDevice(&prev) != cudaSuccess) { (void)cudaGetLastError(); prev = -1; }
     if (prev != ctx->device) B200_CUDA(cudaSetDevice(ctx->device));

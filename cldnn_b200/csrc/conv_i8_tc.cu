@@ -114,9 +114,6 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool fused_staged = P.staged && P.epi.fused_eltw;
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 0) atomicMin(&g_tc_time[0], globaltimer());
-#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
@@ -136,15 +133,11 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 0) atomicMax(&g_tc_time[2], globaltimer());
-#endif
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true; int t = 0;
-            Prof prof; prof.begin();
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
                 // base coordinates of the tile's first pixel
@@ -160,9 +153,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (fused_staged) {
                     // second input of the fused eltwise: same pixels and features as the output tile
                     const int a = t % P.nbuf;
-                    prof.start();
                     if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) { ok = false; break; }
-                    prof.stop(1);
                     const uint32_t rf = smem_u32(&aux->res_full[a]);
                     mbar_expect_tx(rf, (uint32_t)(P.stage_rows * P.cw * P.col_blocks));
                     for (int cb = 0; cb < P.col_blocks; ++cb) {
@@ -174,9 +165,7 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
-                    prof.start();
                     if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
-                    prof.stop(0);
                     const uint32_t full = smem_u32(&aux->full[stage]);
                     mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
                     const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
@@ -191,7 +180,6 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                     if (++stage == P.stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            prof.flush(0, 2);
             if (!ok) {
                 // unwind: let the copies already in flight land before the CTA's shared memory goes away
                 int st = stage; uint32_t ph = phase;
@@ -207,18 +195,13 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
-            Prof prof; prof.begin();
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t % P.nbuf;
-                prof.start();
                 if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
-                prof.stop(0);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.bn);
                 for (int ks = 0; ks < P.k_steps; ++ks) {
-                    prof.start();
                     if (!mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
-                    prof.stop(1);
                     tc_fence_after();
                     const uint64_t adesc = make_smem_desc(a_base + (uint32_t)(stage * P.a_stage_bytes), P.sbo, P.layout_type);
                     const uint64_t bdesc = make_smem_desc(b_base + (uint32_t)(stage * P.b_stage_bytes), P.sbo, P.layout_type);
@@ -230,7 +213,6 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
-            prof.flush(3, 2);
             // drain: every issued MMA must have retired before TMEM is released
             tc_commit(smem_u32(&aux->drain));
             const uint64_t t0 = globaltimer();
@@ -242,13 +224,10 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         // ------------------------------ TMA store issuer --------------------------
         if (lane == 0 && P.staged) {
             int t = 0;
-            Prof prof; prof.begin();
             for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
                 const int a = t % P.nbuf;
-                prof.start();
                 if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
-                prof.stop(0);
                 int tw = 0, th = 0, tb = 0;
                 if (P.a_mode == A_TILED) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
                 const int n0 = n_tile * P.bn;
@@ -260,12 +239,9 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                     else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
                 }
                 bulk_commit();
-                prof.start();
                 bulk_wait_read0();                                  // the buffer may be refilled once TMA has read it
-                prof.stop(1);
                 mbar_arrive(smem_u32(&aux->stage_free[a]));
             }
-            prof.flush(6, 2);
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
@@ -278,13 +254,11 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         const EpiCfg& c = P.epi;
         const uint32_t sw = (uint32_t)((row >> P.sw_shift) & P.sw_mask);
         int t = 0; bool ok = true; int cur_n_tile = -1;
-        Prof prof; prof.begin();
         for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
             int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
             const int acc = t % P.nbuf;
             const int n0 = n_tile * P.bn;
             if (n_tile != cur_n_tile) {
-                prof.start();
                 // per-channel constants of this feature range; every warp has left the previous range
                 named_bar_sync(1, kEpiThreads);
                 for (int j = et; j < P.bn; j += kEpiThreads) {
@@ -301,19 +275,14 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 named_bar_sync(1, kEpiThreads);
                 cur_n_tile = n_tile;
-                prof.stop(2);
             }
-            prof.start();
             if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue)) { ok = false; break; }
-            prof.stop(0);
-            prof.start();
             if (P.staged) {
                 // the staging buffer is ours once its residual tile has landed (fused) or its previous store has read it out
                 const bool got = fused_staged ? mbar_wait(smem_u32(&aux->res_full[acc]), ((uint32_t)(t / P.nbuf) & 1u), s_abort, P.status, kErrEpilogue + 1u)
                                               : mbar_wait(smem_u32(&aux->stage_free[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
                 if (!got) { ok = false; break; }
             }
-            prof.stop(1);
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * P.bn);
 
@@ -374,18 +343,11 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc]));
             }
         }
-        if (warp == 2 && lane == 0) prof.flush(9, 3, t);
     }
 
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 64) atomicMin(&g_tc_time[3], globaltimer());
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 0) atomicMax(&g_tc_time[1], globaltimer());
-#endif
 }
 
 // ------------------------------------------------------------------------------------
@@ -668,9 +630,6 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     const int out_kind = out_u8 ? 0 : ((p.fused_eltw ? p.eltw_act : p.act) == CLDNN_B200_ACT_RELU ? 2 : 1);
     P.fast_variant = (out_kind << 1) | ((p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) ? 1 : 0) | (P.mul_oqf ? 8 : 0);
     P.acc_bound = (float)p.kh * (float)p.kw * (float)p.ifm * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
-#ifdef CONV_TC_DEBUG
-    if (const char* e = getenv("CLDNN_B200_TC_DEBUG")) P.debug = atoi(e);
-#endif
     const bool use_fast = (p.tune <= 12 || p.tune > 24) && tc_fast_eligible(P);
 
     const size_t aux_bytes = use_fast ? tc_fast_aux_bytes() : sizeof(TcSmemAux);

@@ -1,6 +1,5 @@
 // Shared declarations of the tensor-core 8-bit convolution kernels: the launch
-// parameter block the host fills once per prepared launch, and the optional
-// per-role wait-cycle counters of diagnostic builds.
+// parameter block the host fills once per prepared launch.
 #pragma once
 #include <cuda.h>
 #include "engine.hpp"
@@ -48,7 +47,6 @@ struct alignas(64) TcParams {
     // patch mode: all weights resident in shared memory, one activation patch per (filter column, channel chunk)
     int32_t ring_bytes, b_total_bytes;   // operand area: activation ring (+ weight ring or resident weights)
     int32_t patch_alloc;                 // bytes reserved per filter column's patch inside a stage (a stage holds the kw patches of one channel chunk)
-    int32_t debug;                       // diagnostic builds (-DCONV_TC_DEBUG): what-if switches, 0 otherwise
     int32_t fast_variant;                // conv_i8_tc_fast: (output kind << 1) | ReLU before the residual sum
     float acc_bound;                     // K * max|activation| * 128: no accumulator can exceed it in magnitude
     // output / residual addressing for the direct path, in elements
@@ -59,45 +57,6 @@ struct alignas(64) TcParams {
     uint32_t* status;
     EpiCfg epi;
 };
-
-// Optional per-role wait-cycle counters (diagnostic builds only, -DCONV_TC_PROFILE).
-#ifdef CONV_TC_PROFILE
-// one copy per translation unit; the debug readers below see the copy of the file that defines them
-static __device__ unsigned long long g_tc_prof[148 * 16];
-// counts, per wait site, how often the barrier was not yet complete at the first poll (reading the clock costs ~70 clocks
-// per read, too much inside the loops); the role's total loop time is taken from two clock reads
-struct Prof {
-    long long acc[3] = {0, 0, 0}; long long t_begin = 0;
-    __device__ __forceinline__ void begin() { t_begin = clock64(); }
-#ifdef CONV_TC_CYCLES
-    // cycle mode: start / stop accumulate clocks per site (each read costs ~70 clocks: for shares, not absolutes)
-    long long t_s = 0;
-    __device__ __forceinline__ void start() { t_s = clock64(); }
-    __device__ __forceinline__ void stop(int i) { acc[i] += clock64() - t_s; }
-    __device__ __forceinline__ void miss(int, bool) {}
-#else
-    __device__ __forceinline__ void start() {}
-    __device__ __forceinline__ void stop(int) {}
-    __device__ __forceinline__ void miss(int i, bool first_poll_ok) { acc[i] += first_poll_ok ? 0 : 1; }
-#endif
-    __device__ __forceinline__ void flush(int slot, int n, long long extra = -1) {
-        if (blockIdx.x >= 148) return;
-        for (int i = 0; i < n; ++i) g_tc_prof[blockIdx.x * 16 + slot + i] = (unsigned long long)acc[i];
-        g_tc_prof[blockIdx.x * 16 + slot + n] = (unsigned long long)(clock64() - t_begin);
-        if (extra >= 0) g_tc_prof[blockIdx.x * 16 + slot + n + 1] = (unsigned long long)extra;
-    }
-};
-static __device__ unsigned long long g_tc_time[4];      // first CTA entry, last CTA exit, last loop begin, first loop end (globaltimer ns)
-#else
-struct Prof {
-    __device__ __forceinline__ void begin() {}
-    __device__ __forceinline__ void start() {}
-    __device__ __forceinline__ void stop(int) {}
-    __device__ __forceinline__ void miss(int, bool) {}
-    __device__ __forceinline__ void flush(int, int, long long = -1) {}
-};
-#endif
-
 
 // conv_i8_tc_fast.cu: the specialised kernels for the common network configuration.
 bool tc_fast_eligible(const TcParams& P);

@@ -73,11 +73,6 @@ __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi)
     uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi)); return d;
 }
 // KK tensor-core instructions over one channel chunk, 32 bytes of K each
-#ifdef CONV_TC_DEBUG
-#define TC_DEBUG(P, bit) (((P).debug >> (bit)) & 1)
-#else
-#define TC_DEBUG(P, bit) 0
-#endif
 template <int KK>
 __device__ __forceinline__ void mma_chunk(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t acc_first)
 {
@@ -244,9 +239,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     volatile uint32_t* s_abort = &aux->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 0) atomicMin(&g_tc_time[0], globaltimer());
-#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
@@ -269,9 +261,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     const uint32_t tmem_base = aux->tmem_base;
     griddep_launch_dependents();
     griddep_wait();                                   // everything below may touch memory the previous kernel wrote or read
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 0) atomicMax(&g_tc_time[2], globaltimer());
-#endif
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -292,7 +281,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const uint32_t tx = (uint32_t)(patch ? P.a_tx_bytes : P.a_tx_bytes + P.b_tx_bytes);
             const uint32_t a_stage = (uint32_t)P.a_stage_bytes, b_stage = (uint32_t)P.b_stage_bytes;
             const uint32_t full0 = smem_u32(&aux->full[0]), empty0 = smem_u32(&aux->empty[0]);
-            Prof prof; prof.begin();
             TileWalk w; w.init(P, blockIdx.x, gridDim.x);
             // Everything the loop needs sits in registers: this thread's scalar instructions are on the critical path of
             // the layers whose stages hold little tensor-core work.
@@ -304,18 +292,10 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 const int m0 = w.m_tile * kBM, n0 = w.n_tile * BN;
                 int tap = 0, cc = 0, off_w = 0, off_h = 0, sx = 0;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    { bool fp_ = true;
-                    if (!mbar_wait_lean(empty0 + 8u * (uint32_t)stage, phase ^ 1u, s_abort, P.status, kErrProducer, &fp_)) { ok = false; break; }
-                    prof.miss(0, fp_); }
+                    if (!mbar_wait_lean(empty0 + 8u * (uint32_t)stage, phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
                     const uint32_t full = full0 + 8u * (uint32_t)stage;
                     const uint32_t dst = a_base + (uint32_t)stage * a_stage;
                     const int c0 = cc * bk;
-                    if (TC_DEBUG(P, 5)) {                                                   // what-if: no operand loads, the stage is declared full at once
-                        mbar_arrive(full); ++issued;
-                        if (++cc == chunks) { cc = 0; ++tap; off_w += dil_x; if (++sx == kw) { sx = 0; off_w = 0; off_h += dil_y; } }
-                        if (++stage == stages) { stage = 0; phase ^= 1u; }
-                        continue;
-                    }
                     mbar_expect_tx(full, tx);
                     if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
                     if (patch) {                                                            // one patch per filter column
@@ -329,7 +309,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
                 }
             }
-            prof.flush(0, 1);
             if (!ok) {
                 // unwind: let the copies already in flight land before the CTA's shared memory goes away
                 int st = stage; uint32_t ph = phase;
@@ -361,30 +340,19 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const int patch_kind = (kh == 3 && kw_ == 3) ? (kk == 2 ? 1 : (kk == 4 ? 2 : 0)) : 0;   // 3x3 filters are issued straight-line
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
-            Prof prof; prof.begin();
             if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u);
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             for (; walk.valid() && ok; walk.next(), ++t) {
                 const int acc = t % NBUF;
-                { bool fp_ = true;
-                prof.start();
-                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma, &fp_)) { ok = false; break; }
-                prof.stop(0);
-                prof.miss(0, fp_); }
-                if (!TC_DEBUG(P, 4)) tc_fence_after();
+                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 uint32_t accf = 0u;
                 uint32_t b_col = 0u;                                                   // patch mode: weights of (filter column, channel chunk)
                 if (patch) b_col = b_lo0 + (uint32_t)(walk.n_tile * kh) * b_row_step;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    { bool fp_ = true;
-                    prof.start();
-                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u, &fp_)) { ok = false; break; }
-                    prof.stop(1);
-                    prof.miss(1, fp_); }
-                    prof.start();
-                    if (TC_DEBUG(P, 0)) { }
-                    else if (!patch) {
+                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    if (!patch) {
                         if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
@@ -409,13 +377,11 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                         b_col += b_step;                                                     // next channel chunk
                     }
                     tc_commit(empty0 + 8u * (uint32_t)stage);                           // frees the stage once these MMAs have read it
-                    prof.stop(2);
                     if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
                     else { a_lo += a_step; b_lo += b_step; }
                 }
                 if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
-            prof.flush(2, 3);
             // drain: every issued MMA must have retired before TMEM is released
             tc_commit(smem_u32(&aux->drain));
             const uint64_t t0 = globaltimer();
@@ -427,20 +393,16 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // ------------------------------ TMA store issuer --------------------------
         if (lane == 0) {
             int t = 0;
-            Prof prof; prof.begin();
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;            // the output of an im2col tile is addressed by its first pixel index
             for (; walk.valid(); walk.next(), ++t) {
                 const int n_tile = walk.n_tile, m_tile = walk.m_tile;
                 const int a = t % NSTG;
-                prof.start();
                 if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
-                prof.stop(0);
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
                 const int tw = walk.d0, th = walk.d1, tb = walk.d2;
 #pragma unroll
                 for (int cb = 0; cb < COLB; ++cb) {
-                    if (TC_DEBUG(P, 3)) break;
                     const int f0 = n_tile * BN + cb * CW;
                     if (f0 >= P.ofm) break;                         // ragged feature count: nothing of the tensor in this block
                     const uint32_t src = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * CW);
@@ -448,12 +410,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
                 }
                 bulk_commit();
-                prof.start();
                 bulk_wait_read0();                                  // the buffer may be refilled once TMA has read it
-                prof.stop(1);
                 mbar_arrive(smem_u32(&aux->stage_free[a]));
             }
-            prof.flush(6, 2);
         }
     } else if (warp == 3) {
         // ------------------------------ residual loader ---------------------------
@@ -462,7 +421,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // never holds back the operand loads of later tiles.
         if (kFused && lane == 0) {
             int t = 0;
-            Prof prof; prof.begin();
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;
             for (; walk.valid(); walk.next(), ++t) {
@@ -470,9 +428,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
                 const int o_w = walk.d0 * P.bw, o_h = walk.d1 * P.bh, c_n = walk.d2 * P.bb;
                 const int a = t % NSTG;
-                prof.start();
                 if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
-                prof.stop(1);
                 const uint32_t rf = smem_u32(&aux->res_full[a]);
                 int cbs = 0;                                        // column blocks that hold features of the tensor
 #pragma unroll
@@ -505,7 +461,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         const bool with_oqf = (P.fast_variant & 8) != 0;            // uniform O_QF after the dequantisation
         const float oqf = c.o_qf, oqf_abs = with_oqf ? fabsf(c.o_qf) : 1.0f;
         int cur_n_tile = -1; bool ok = true; bool wide = false;
-        Prof prof; prof.begin();
         int t = group;
         TileWalk walk; walk.init(P, blockIdx.x + group * gridDim.x, kGroups * gridDim.x);
         walk.mode = A_FLAT;                                         // only the feature tile is needed here
@@ -514,7 +469,6 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const int acc = t % NBUF;
             const uint32_t par = (uint32_t)(t / NBUF) & 1u;
             if (n_tile != cur_n_tile) {
-                prof.start();
                 named_bar_sync(1 + group, 128);                     // every warp of the group has left the previous feature range
                 bool w = false;
                 for (int j = gt; j < BN; j += 128) {
@@ -532,24 +486,18 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 named_bar_sync(1 + group, 128);
                 wide = (aux->wide[group][0] | aux->wide[group][1] | aux->wide[group][2] | aux->wide[group][3]) != 0u;
                 cur_n_tile = n_tile;
-                prof.stop(2);
             }
-            prof.start();
             if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), par, s_abort, P.status, kErrEpilogue)) { ok = false; break; }
-            prof.stop(0);
-            prof.start();
             // the staging buffer is ours once its residual tile has landed (fused) or its previous store has been read out
             const int sb = t % NSTG; const uint32_t spar = (uint32_t)(t / NSTG) & 1u;
             const bool got = kFused ? mbar_wait(smem_u32(&aux->res_full[sb]), spar, s_abort, P.status, kErrEpilogue + 1u)
                                     : mbar_wait(smem_u32(&aux->stage_free[sb]), spar ^ 1u, s_abort, P.status, kErrEpilogue + 1u);
             if (!got) { ok = false; break; }
-            prof.stop(1);
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
             uint8_t* stg = staging + (size_t)sb * kStagingBytes;
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
-            if (TC_DEBUG(P, 1)) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(te); }
-            else if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
+            if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
             else if (with_oqf) {
                 // u8 or plain s8 output, no ReLU between convolution and residual sum (the host admits nothing else here)
                 if (kFused) {
@@ -580,34 +528,13 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->out_ready[sb]));
         }
-        if (ew == 0 && lane == 0) prof.flush(9, 3, (t - group) / kGroups);
     }
 
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == kFastEpiWarp0 * 32) atomicMin(&g_tc_time[3], globaltimer());
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
-#ifdef CONV_TC_PROFILE
-    if (threadIdx.x == 0) atomicMax(&g_tc_time[1], globaltimer());
-#endif
 }
 
-#ifdef CONV_TC_PROFILE
-extern "C" __attribute__((visibility("default"))) int cldnn_b200_debug_tc_prof(unsigned long long* host_out)
-{
-    return (int)cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(g_tc_prof));
-}
-extern "C" __attribute__((visibility("default"))) int cldnn_b200_debug_tc_time(unsigned long long* host_out)
-{
-    cudaDeviceSynchronize();
-    int rc = (int)cudaMemcpyFromSymbol(host_out, g_tc_time, sizeof(g_tc_time));
-    const unsigned long long init[4] = {~0ull, 0ull, 0ull, ~0ull};
-    cudaMemcpyToSymbol(g_tc_time, init, sizeof(init));
-    return rc;
-}
-#endif
 
 // ------------------------------------------------------------------------------------
 // host side

@@ -48,6 +48,17 @@ extern "C" {
 
 const char* cldnn_b200_last_error(void) { return g_last_error.c_str(); }
 
+int32_t cldnn_b200_device_count(int32_t* count)
+{
+    B200_TRY
+    if (!count) return fail(CLDNN_B200_INVALID_ARG, "device_count: null out");
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    *count = n;
+    return CLDNN_B200_SUCCESS;
+    B200_CATCH
+}
+
 int32_t cldnn_b200_ctx_create(int32_t device, uint32_t enable_profiling, cldnn_b200_ctx* out)
 {
     B200_TRY

@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libcldnn_b200.so")
 # every symbol include/cldnn_b200.h declares, with its argument types
 _SIGNATURES = {
     "cldnn_b200_last_error": (C.c_char_p, []),
+    "cldnn_b200_device_count": (C.c_int32, [C.POINTER(C.c_int32)]),
     "cldnn_b200_ctx_create": (C.c_int32, [C.c_int32, C.c_uint32, C.POINTER(C.c_void_p)]),
     "cldnn_b200_ctx_destroy": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_ctx_info": (C.c_int32, [C.c_void_p, C.POINTER(abi.EngineInfo)]),
@@ -57,6 +58,7 @@ _SIGNATURES = {
     "cldnn_b200_prepared_destroy": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_time": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_uint64)]),
     "cldnn_b200_conv_first_noalloc": (C.c_int32, [C.c_void_p, C.POINTER(abi.ConvParams), C.POINTER(abi.Args)]),
+    "cldnn_b200_tensor_peak": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_double)]),
     "cldnn_b200_graph_begin": (C.c_int32, [C.c_void_p]),
     "cldnn_b200_graph_end": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "cldnn_b200_graph_launch": (C.c_int32, [C.c_void_p]),
@@ -230,6 +232,12 @@ class Engine:
         n = C.c_uint64()
         _check(self.lib.cldnn_b200_ctx_launch_count(self.handle, C.byref(n)))
         return n.value
+
+    def tensor_peak(self, dtype=abi.I8, n=256):
+        """Measured tensor-core peak of this device in tera-operations per second (cldnn_b200_tensor_peak)."""
+        v = C.c_double()
+        _check(self.lib.cldnn_b200_tensor_peak(self.handle, dtype, n, C.byref(v)))
+        return v.value
 
     def device_status(self):
         s = C.c_uint32()

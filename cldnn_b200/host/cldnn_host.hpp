@@ -27,7 +27,7 @@ enum class data_types : int32_t { none = CLDNN_B200_NONE, i8 = CLDNN_B200_I8, u8
 
 // activation / weights memory formats (values of cldnn_format_type, api/C/cldnn.h:271-317)
 struct format {
-    enum type : int32_t { yxfb = 0, byxf = 1, bfyx = 2, byxf_af32 = 24, any = -1 };
+    enum type : int32_t { yxfb = 0, byxf = 1, bfyx = 2, byxf_af32 = 21, any = -1 };
     static const char* name(int32_t f);
 };
 
@@ -68,6 +68,8 @@ public:
     explicit engine(int32_t device = 0, bool enable_profiling = false);
     cldnn_b200_engine_info get_info() const;
     void* stream() const;                       // cudaStream_t of the engine's queue
+    void sync() const;                          // waits for everything enqueued on the engine's queue
+    uint32_t device_status() const;             // non-zero after a kernel gave up a bounded wait
     bool profiling() const;
     std::shared_ptr<engine_impl> impl;
 };
@@ -190,6 +192,7 @@ public:
     void set_input_data(const std::string& id, const memory& m);
     void execute();                             // enqueue; returns immediately
     memory get_output(const std::string& id);   // waits for completion, returns the primitive's memory
+    memory output_memory(const std::string& id) const;   // the same memory object without waiting (the caller waits on the event)
     std::vector<std::string> get_output_ids() const;
     std::vector<primitive_info> get_primitives_info() const;   // executed order, with chosen kernels
     uint64_t launches_per_execute() const;

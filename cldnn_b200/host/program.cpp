@@ -99,6 +99,8 @@ engine::engine(int32_t device, bool enable_profiling) : impl(std::make_shared<en
 }
 void* engine::stream() const { void* s = nullptr; check(cldnn_b200_ctx_stream(impl->ctx, &s), "engine stream"); return s; }
 bool engine::profiling() const { return impl->profiling; }
+void engine::sync() const { check(cldnn_b200_ctx_sync(impl->ctx), "engine sync"); }
+uint32_t engine::device_status() const { uint32_t st = 0; check(cldnn_b200_ctx_device_status(impl->ctx, &st), "device status"); return st; }
 cldnn_b200_engine_info engine::get_info() const { return impl->info; }
 
 // one device allocation; several memory objects may view it over disjoint lifetimes (memory pool)
@@ -1010,6 +1012,10 @@ memory network::get_output(const std::string& id)
     wait();
     uint32_t st = 0; check(cldnn_b200_ctx_device_status(impl->eng->ctx, &st), "device status");
     if (st) throw error("a kernel gave up waiting (device status 0x" + std::to_string(st) + ")", CLDNN_B200_DEVICE_ERROR);
+    return output_memory(id);
+}
+memory network::output_memory(const std::string& id) const
+{
     for (node* n : impl->order) if (n->is_output && (n->answers_for == id || n->p.id == id)) return n->mem;
     node* n = impl->get(id);
     if (!n->mem) throw error("primitive '" + id + "' has no memory (fused away); request it as an output", CLDNN_B200_INVALID_ARG);

@@ -331,3 +331,27 @@ def conv_ops(spec):
         else:
             shapes[p.id] = (c, h, w)
     return total, per_layer
+
+
+def primitive_inputs(spec):
+    """{primitive id: [ids of its activation inputs]} of a spec, in the spec's own (unfused) terms."""
+    out = {}
+    for p in spec.prims:
+        if p.kind in ("data", "input_layout"):
+            continue
+        out[p.id] = [p.args[k] for k in ("input", "input2") if k in p.args and p.args[k]]
+    return out
+
+
+def weight_bytes(spec):
+    """{primitive id: bytes of its constants (weights, bias, scales)} as the caller provides them."""
+    out = {}
+    for p in spec.prims:
+        if p.kind in ("data", "input_layout"):
+            continue
+        n = 0
+        for k, v in p.args.items():
+            if isinstance(v, str) and v in spec.consts and k not in ("input", "input2"):
+                n += spec.consts[v].nbytes
+        out[p.id] = n
+    return out

@@ -246,6 +246,8 @@ CLDNN_B200_API const char* cldnn_b200_last_error(void);
 
 /* ---- context: replaces gpu_toolkit::create and the queue it owns
  *      (src/gpu/ocl_toolkit.cpp:75-151) -------------------------------------- */
+/* number of CUDA devices visible to the process (0 without a driver): cldnn_get_engine_count, src/cldnn.cpp:179-190 */
+CLDNN_B200_API int32_t cldnn_b200_device_count(int32_t* count);
 CLDNN_B200_API int32_t cldnn_b200_ctx_create(int32_t device, uint32_t enable_profiling, cldnn_b200_ctx* out);
 CLDNN_B200_API int32_t cldnn_b200_ctx_destroy(cldnn_b200_ctx ctx);
 CLDNN_B200_API int32_t cldnn_b200_ctx_info(cldnn_b200_ctx ctx, cldnn_b200_engine_info* info);
@@ -333,8 +335,16 @@ CLDNN_B200_API int32_t cldnn_b200_graph_destroy(cldnn_b200_graph g);
  *     before starting any stream capture on the device.
  *   - All calls on a device share the one array and it keeps the previous call's contents.  Each call rewrites every
  *     byte it later reads, so sequential calls are independent; calls whose kernels may overlap on the GPU (other
- *     streams, other contexts or processes' threads on the same device using this entry point) race on it.        */
+ *     streams or contexts of the same process on the same device using this entry point) race on it.  Another
+ *     process loads its own copy of the library image and therefore its own array.                               */
 CLDNN_B200_API int32_t cldnn_b200_conv_first_noalloc(cldnn_b200_ctx ctx, const cldnn_b200_conv_params* params, const cldnn_b200_args* args);
+/* Measured tensor-core peak of the context's device, in tera-operations per second (2 per multiply-add): one CTA per
+ * SM issues tcgen05.mma (M = 128, N = n in {64, 128, 256}, 32 bytes of K) on operands resident in shared memory, the
+ * accumulator in tensor memory, a few milliseconds per call.  dtype: CLDNN_B200_I8 (s8 x s8 -> s32) or CLDNN_B200_F16
+ * (f16 x f16 -> f32).  It is the denominator roofline fractions of the convolution kernels are quoted against; it plays
+ * the part of the reference's device capability query (engine_info_internal, src/gpu/engine_info.cpp:190-231), which
+ * reports core counts and clock only.                                                                              */
+CLDNN_B200_API int32_t cldnn_b200_tensor_peak(cldnn_b200_ctx ctx, int32_t dtype, int32_t n, double* tera_ops_per_second);
 /* device-side status word: 0 when the last launches completed normally,
  * otherwise a code written by a kernel whose bounded wait gave up           */
 CLDNN_B200_API int32_t cldnn_b200_ctx_device_status(cldnn_b200_ctx ctx, uint32_t* status);

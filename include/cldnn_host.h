@@ -35,7 +35,7 @@ typedef struct cldnn_host_network_impl*  cldnn_host_network;
 #define CLDNN_HOST_FORMAT_YXFB 0
 #define CLDNN_HOST_FORMAT_BYXF 1
 #define CLDNN_HOST_FORMAT_BFYX 2
-#define CLDNN_HOST_FORMAT_BYXF_AF32 24
+#define CLDNN_HOST_FORMAT_BYXF_AF32 21
 
 /* cldnn_get_last_error_message, src/cldnn.cpp:746 */
 CLDNN_B200_API const char* cldnn_host_last_error(void);

@@ -355,3 +355,43 @@ def test_conv_i8_dw_refuses_dense_and_grouped(eng):
     k = eng.kernel("conv_i8_dw")
     assert not k.supports(cases.make_conv_case(53, N=1, C=32, K=32, H=8, W=8).p)
     assert not k.supports(cases.make_conv_case(53, N=1, C=32, K=32, H=8, W=8, groups=4).p)
+
+
+def _prepare_on_gpu(eng, case, kernel, tune=0):
+    """Prepared launch + its buffers for `case`; the caller runs it and reads `out`."""
+    import ctypes as C
+    from cldnn_b200 import engine as E
+    p = cases.copy_params(case.p)
+    p.tune = tune
+    k = eng.kernel(kernel)
+    mems = [eng.upload(v) if v is not None else None for v in (case.inp, case.w, case.bias, case.quant, case.calib)]
+    out_dt = abi.np_dtype_of(p.out.dtype)
+    out = eng.alloc(case.out_elems * out_dt.itemsize)
+    sb = C.c_size_t()
+    eng.lib.cldnn_b200_kernel_scratch_bytes(k.handle, C.byref(p), C.sizeof(p), C.byref(sb))
+    scratch = eng.alloc(sb.value) if sb.value else None
+    args = E.make_args(input0=mems[0], weights=mems[1], bias=mems[2], quant=mems[3], calib=mems[4], output=out, scratch=scratch)
+    return k.prepare(p, args), out, out_dt, mems + [scratch]
+
+
+@pytest.mark.parametrize("kernel", ["conv_i8_first", "conv_first_tc"])
+def test_two_prepared_launches_with_different_shared_memory_needs(eng, kernel):
+    """The dynamic shared-memory limit is a property of the kernel function, not of one prepared launch: preparing a
+    small shape after a large one must leave the large one runnable (both stay alive, as two networks of a process do)."""
+    big = cases.make_conv_case(71, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, **FIRST_LAYER["resnet_conv1"])
+    small = cases.make_conv_case(72, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, **FIRST_LAYER["one_feature_3x3"])
+    for c in (big, small):
+        assert eng.kernel(kernel).supports(c.p)
+    pa, out_a, dt_a, keep_a = _prepare_on_gpu(eng, big, kernel)
+    pb, out_b, dt_b, keep_b = _prepare_on_gpu(eng, small, kernel)
+    pa.run()
+    pb.run()
+    pa.run()
+    eng.sync()
+    assert eng.device_status() == 0
+    for case, out, dt in ((big, out_a, dt_a), (small, out_b, dt_b)):
+        want = cases.run_oracle(case)
+        got = out.read(dt, case.out_elems)
+        assert np.array_equal(want[:case.out_elems], got[:case.out_elems])
+    pa.destroy()
+    pb.destroy()

@@ -47,6 +47,8 @@ def test_no_alloc_entry_point_matches_regular_one_twice_in_a_row():
             n = case.out_elems
             assert np.array_equal(want[:n], got[:n]), "%d outputs differ" % int((want[:n] != got[:n]).sum())
             assert (want[:n] != 0).any()
+            # and both equal the CPU oracle (bit-exact: integer outputs)
+            assert np.array_equal(cases.run_oracle(case)[:n], got[:n])
         # a weights image beyond the built-in 32 KiB is refused before anything is launched
         big = cases.make_conv_case(33, N=1, C=4, K=256, H=16, W=16, kh=8, kw=8, stride=1, pad=0, fmt="bfyx", f_align=1,
                                    out_fmt="byxf", out_dtype=np.uint8)
@@ -56,5 +58,9 @@ def test_no_alloc_entry_point_matches_regular_one_twice_in_a_row():
         args = E.make_args(input0=src[0], weights=src[1], bias=src[2], quant=src[3], output=dummy)
         assert eng.lib.cldnn_b200_conv_first_noalloc(eng.handle, C.byref(p), C.byref(args)) == abi.UNSUPPORTED_SIZE
         assert b"32768" in eng.lib.cldnn_b200_last_error()
+        # a shape the kernel itself cannot run comes back with the code the regular entry point gives it, whatever its size
+        p.ofm = 512
+        p.out.f = 512
+        assert eng.lib.cldnn_b200_conv_first_noalloc(eng.handle, C.byref(p), C.byref(args)) == abi.UNSUPPORTED_FORMAT
     finally:
         eng.close()
