@@ -20,6 +20,7 @@ DIMENSION_MISMATCH = -7
 I8, U8, I32, F16, F32, NONE = 0x01, 0x41, 0x04, 0x82, 0x84, 0x00
 
 ACT_NONE, ACT_RELU, ACT_RELU_NEGATIVE_SLOPE, ACT_CLAMP = 0, 1, 2, 3
+EPILOGUE_REF, EPILOGUE_MMAD, EPILOGUE_IMAD = 0, 1, 2       # cldnn_b200_conv_params.epilogue_order
 ACT_LOGISTIC, ACT_TANH, ACT_ABS, ACT_LINEAR, ACT_SQUARE, ACT_SQRT, ACT_ELU = 4, 5, 6, 7, 8, 9, 10
 
 POOL_MAX, POOL_AVG = 0, 1
@@ -72,7 +73,7 @@ class ConvParams(C.Structure):
                 ("eltw_calibration", C.c_int32),
                 ("eltw_stride_x", C.c_int32), ("eltw_stride_y", C.c_int32),
                 ("in_out_opt", C.c_int32),
-                ("tune", C.c_int32), ("reserved", C.c_int32 * 7)]
+                ("tune", C.c_int32), ("epilogue_order", C.c_int32), ("reserved", C.c_int32 * 6)]
 
 
 class Args(C.Structure):

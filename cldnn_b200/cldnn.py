@@ -78,6 +78,8 @@ _SIGNATURES = {
     "cldnn_host_add_softmax": (_i, [_vp, _cp, _cp]),
     "cldnn_host_add_softmax_dim": (_i, [_vp, _cp, _cp, C.c_int32]),
     "cldnn_host_add_lrn": (_i, [_vp, _cp, _cp, _u, _f, _f, _f]),
+    "cldnn_host_add_concatenation": (_i, [_vp, _cp, _cp, _i]),
+    "cldnn_host_tuning_cache_check": (_i, [_cp, _u, C.POINTER(C.c_size_t)]),
     "cldnn_host_network_build": (_i, [_vp, _vp, C.POINTER(_BuildOptions), C.POINTER(_vp)]),
     "cldnn_host_network_release": (_i, [_vp]),
     "cldnn_host_network_set_input": (_i, [_vp, _cp, _vp]),
@@ -340,6 +342,16 @@ def lrn(id, input, size=5, k=1.0, alpha=1e-4, beta=0.75):
     return primitive("lrn", id, input=input, size=size, k=k, alpha=alpha, beta=beta)
 
 
+class concatenation_axis:
+    """concatenation::concatenation_axis (api/CPP/concatenation.hpp:44-52): the index into the tensor's sizes."""
+    along_b, along_f, along_x, along_y = 0, 1, 2, 3
+
+
+def concatenation(id, inputs, axis=concatenation_axis.along_f):
+    inputs = list(inputs)
+    return primitive("concatenation", id, input=inputs[0], inputs=inputs, axis=axis)
+
+
 class topology:
     def __init__(self, *prims):
         self.prims = []
@@ -396,6 +408,8 @@ class topology:
                     st = lib.cldnn_host_add_softmax_dim(h, _b(p.id), _b(a["input"]), int(a.get("dimension", 3)))
                 elif k == "lrn":
                     st = lib.cldnn_host_add_lrn(h, _b(p.id), _b(a["input"]), a["size"], a["k"], a["alpha"], a["beta"])
+                elif k == "concatenation":
+                    st = lib.cldnn_host_add_concatenation(h, _b(p.id), _b(",".join(a["inputs"])), a["axis"])
                 else:
                     raise error(abi.UNSUPPORTED_FORMAT, "primitive type '%s' is outside the supported path" % k)
                 _check(st)
@@ -453,9 +467,10 @@ class network:
         _check(self.lib.cldnn_host_network_info(self.handle, buf, need.value, None))
         rows = []
         for line in buf.value.decode().splitlines():
-            pid, kind, kernel, tune, fmt, dt, dims, fused, is_out = line.split("|")
+            pid, kind, kernel, tune, fmt, dt, dims, fused, is_out, in_place = line.split("|")
             rows.append(dict(id=pid, type=kind, kernel=kernel, tune=int(tune), format=fmt, data_type=int(dt),
-                             dims=tuple(int(v) for v in dims.split(",")), fused=[f for f in fused.split(",") if f], is_output=is_out == "1"))
+                             dims=tuple(int(v) for v in dims.split(",")), fused=[f for f in fused.split(",") if f], is_output=is_out == "1",
+                             in_place=in_place == "1"))
         return rows
 
     def profiling_info(self):

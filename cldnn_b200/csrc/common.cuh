@@ -123,6 +123,7 @@ struct EpiCfg {
     int32_t bias_dtype, dont_dequantize_bias;
     int32_t act, fused_eltw, has_non_conv_scale, eltw_act, eltw_calibration;
     int32_t out_dtype, out_is_fp, eltw_dtype;
+    int32_t order;               // CLDNN_B200_EPILOGUE_*
     float i_qf, o_qf, act_m, act_n, non_conv_scale, eltw_m, eltw_n;
 };
 
@@ -138,9 +139,22 @@ inline EpiCfg make_epi_cfg(const cldnn_b200_conv_params& p)
     e.eltw_act = p.eltw_act; e.eltw_calibration = p.eltw_calibration;
     e.out_dtype = p.out.dtype; e.out_is_fp = is_fp(p.out.dtype) ? 1 : 0;
     e.eltw_dtype = p.in_out_opt ? p.out.dtype : p.eltw.dtype;
+    e.order = p.epilogue_order;
     e.i_qf = p.i_qf; e.o_qf = p.o_qf; e.act_m = p.act_m; e.act_n = p.act_n;
     e.non_conv_scale = p.non_conv_scale; e.eltw_m = p.eltw_m; e.eltw_n = p.eltw_n;
     return e;
+}
+
+// The MMAD / IMAD epilogue orders exist for quantised signed 8-bit outputs with a float bias; IMAD's fused form needs eltwise
+// calibration factors, MMAD has no fused form; neither knows a non-convolution scale.
+inline bool epilogue_order_ok(const cldnn_b200_conv_params& p)
+{
+    if (p.epilogue_order == CLDNN_B200_EPILOGUE_REF) return true;
+    if (p.epilogue_order != CLDNN_B200_EPILOGUE_MMAD && p.epilogue_order != CLDNN_B200_EPILOGUE_IMAD) return false;
+    if (!p.quantization || p.bias_dtype != CLDNN_B200_F32 || p.out.dtype != CLDNN_B200_I8) return false;      // the kernels' unit type is char
+    if (p.fused_eltw && (p.epilogue_order == CLDNN_B200_EPILOGUE_MMAD || !p.eltw_calibration || p.has_non_conv_scale)) return false;
+    if (p.fused_eltw && !is_int8(p.in_out_opt ? p.out.dtype : p.eltw.dtype)) return false;
+    return true;
 }
 
 // A clamp that the unsigned saturating store performs anyway is dropped: with an 8-bit unsigned output, a uniform O_QF > 0,
@@ -150,7 +164,7 @@ inline EpiCfg make_epi_cfg(const cldnn_b200_conv_params& p)
 inline cldnn_b200_conv_params simplified_conv_params(const cldnn_b200_conv_params& p0)
 {
     cldnn_b200_conv_params p = p0;
-    if (p.act == CLDNN_B200_ACT_CLAMP && !p.fused_eltw && p.out.dtype == CLDNN_B200_U8 && !p.calibration && p.has_o_qf && p.o_qf > 0.0f &&
+    if (p.epilogue_order == CLDNN_B200_EPILOGUE_REF && p.act == CLDNN_B200_ACT_CLAMP && !p.fused_eltw && p.out.dtype == CLDNN_B200_U8 && !p.calibration && p.has_o_qf && p.o_qf > 0.0f &&
         p.act_m <= 0.0f && p.act_n * p.o_qf >= 255.0f) {
         p.act = CLDNN_B200_ACT_NONE; p.act_m = 0.0f; p.act_n = 0.0f;
     }
@@ -163,9 +177,28 @@ inline cldnn_b200_conv_params simplified_conv_params(const cldnn_b200_conv_param
 // round -> [+ scaled residual -> activation -> * eltw_calib[f] -> round].
 // `acc` already holds the i32 bias when the bias is integer.  Returns the float
 // value to hand to the saturating store.
+// The MMAD / IMAD orders (convolution_gpu_mmad.cl:106-132, fused_conv_eltwise_gpu_imad.cl:171-207): everything up to the
+// first rounding in float, then the value lives in the 8-bit output type (low 8 bits of the rounded integer), where the
+// activation is applied; IMAD adds the residual as integers and requantises the sum.
+static __device__ __noinline__ float epi_quant_alt(const EpiCfg& c, int32_t acc, float q, float bias_f, float calib, float eltw_elem, float eltw_calib)
+{
+    float v = __int2float_rn(acc);
+    v = __fmul_rn(__fmul_rn(v, q), c.i_qf);
+    v = __fadd_rn(v, bias_f);
+    v = round_half_away(__fmul_rn(v, c.calibration ? calib : c.o_qf));
+    const int32_t r = __float2int_rz(v);
+    int32_t a8 = c.out_dtype == CLDNN_B200_U8 ? (int32_t)(uint8_t)r : (int32_t)(int8_t)r;
+    a8 = act_int(c.act, a8, c.act_m, c.act_n);
+    if (c.order == CLDNN_B200_EPILOGUE_MMAD || !c.fused_eltw) return (float)a8;
+    const float s = round_half_away(__fmul_rn((float)(a8 + (int32_t)eltw_elem), eltw_calib));
+    const int32_t lo = c.out_dtype == CLDNN_B200_U8 ? 0 : -128, hi = c.out_dtype == CLDNN_B200_U8 ? 255 : 127;
+    return (float)act_int(c.eltw_act, sat_i32_from_float(s, lo, hi), c.eltw_m, c.eltw_n);
+}
+
 __device__ __forceinline__ float epi_quant(const EpiCfg& c, int32_t acc, float q, float bias_f, float calib,
                                            float eltw_elem, float eltw_calib)
 {
+    if (c.order != CLDNN_B200_EPILOGUE_REF) return epi_quant_alt(c, acc, q, bias_f, calib, eltw_elem, eltw_calib);
     float v = __int2float_rn(acc);
     if (c.quantization) { v = __fmul_rn(v, q); v = __fmul_rn(v, c.i_qf); }
     if (c.dont_dequantize_bias) v = __fadd_rn(v, bias_f);

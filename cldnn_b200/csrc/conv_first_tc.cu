@@ -444,6 +444,7 @@ static size_t ftc_smem(const cldnn_b200_conv_params& p)
 static bool ftc_plan(const cldnn_b200_conv_params& p, std::string* why)
 {
     auto no = [&](const char* m) { if (why) *why = m; return false; };
+    if (p.epilogue_order != CLDNN_B200_EPILOGUE_REF) return no("reference epilogue order only");
     const bool half = p.in.dtype == CLDNN_B200_F16;
     if (half) {
         if (p.w_dtype != CLDNN_B200_F16 || p.out.dtype != CLDNN_B200_F16) return no("fp16 weights and output with fp16 input");

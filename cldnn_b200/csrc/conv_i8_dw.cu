@@ -405,6 +405,7 @@ conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __g
 bool dw_plan(const cldnn_b200_conv_params& p, std::string* why)
 {
     auto no = [&](const char* m) { if (why) *why = m; return false; };
+    if (p.epilogue_order != CLDNN_B200_EPILOGUE_REF) return no("reference epilogue order only");
     if (!is_int8(p.in.dtype) || p.w_dtype != CLDNN_B200_I8 || !is_int8(p.out.dtype)) return no("8-bit activations, weights and output only");
     if (p.groups < 2 || p.ofm != 1 || p.ifm != 1 || p.in.f != p.groups || p.out.f != p.groups) return no("depthwise only: one input and one output feature per group");
     if (p.fused_eltw) return no("no fused eltwise");

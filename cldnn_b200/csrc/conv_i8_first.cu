@@ -364,6 +364,7 @@ static bool first_plan(const cldnn_b200_conv_params& p, std::string* why)
     auto no = [&](const char* m) { if (why) *why = m; return false; };
     if (!is_int8(p.in.dtype) || p.w_dtype != CLDNN_B200_I8) return no("8-bit activations and weights only");
     if (p.groups != 1 || p.fused_eltw) return no("plain convolution only");
+    if (p.epilogue_order != CLDNN_B200_EPILOGUE_REF) return no("reference epilogue order only");
     if (p.in.px != 1) return no("input must be planar (bfyx)");
     if (p.out.pf != 1 || !is_int8(p.out.dtype)) return no("output must be 8-bit byxf");
     if (p.kw > 8 || p.kh < 1 || p.kw < 1) return no("filter width up to 8");

@@ -413,7 +413,7 @@ static void choose_box(int Q, int Pn, int N, int& bw, int& bh, int& bb)
 static bool lean_params(const cldnn_b200_conv_params& p)
 {
     auto none_or_relu = [](int32_t fn) { return fn == CLDNN_B200_ACT_NONE || fn == CLDNN_B200_ACT_RELU; };
-    if (!p.quantization || p.i_qf != 1.0f || p.calibration) return false;
+    if (!p.quantization || p.i_qf != 1.0f || p.calibration || p.epilogue_order != CLDNN_B200_EPILOGUE_REF) return false;
     if (!is_int8(p.out.dtype) || !none_or_relu(p.act)) return false;
     if (p.o_qf != 1.0f) {
         // a uniform O_QF: positive, in front of an unsigned or a plain signed saturation, no ReLU in front of a residual sum
@@ -451,6 +451,7 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
     if (!is_int8(p.in.dtype)) return no("activations must be u8 or i8");
     if (p.w_dtype != CLDNN_B200_I8) return no("weights must be i8");
     if (p.groups != 1) return no("grouped convolution is handled by other kernels");
+    if (!epilogue_order_ok(p)) return no("the MMAD / IMAD epilogue orders need quantisation, an f32 bias and an 8-bit output (IMAD fused: eltwise calibration)");
     if (p.kh < 1 || p.kw < 1 || p.kh * p.kw > 255) return no("filter size");
     if (p.stride_x < 1 || p.stride_y < 1 || p.dil_x < 1 || p.dil_y < 1) return no("stride/dilation");
     if (p.out.f != p.ofm || p.in.f != p.ifm) return no("feature counts");
@@ -606,7 +607,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.quant = a->weights_quantization_factors; P.calib = a->output_calibration_factors; P.ecal = a->eltw_output_calibration_factors;
     P.status = ctx->d_status;
     P.epi = make_epi_cfg(p);
-    P.fast_epi = (P.epi.quant_path && is_int8(p.out.dtype) && act_is_simple(p.act, p.act_m) &&
+    P.fast_epi = (p.epilogue_order == CLDNN_B200_EPILOGUE_REF && P.epi.quant_path && is_int8(p.out.dtype) && act_is_simple(p.act, p.act_m) &&
                   (!p.fused_eltw || (is_int8(P.epi.eltw_dtype) && act_is_simple(p.eltw_act, p.eltw_m)))) ? 1 : 0;
     P.mul_iqf = p.i_qf != 1.0f ? 1 : 0;
     P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;

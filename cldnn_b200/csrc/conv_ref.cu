@@ -98,6 +98,7 @@ static bool conv_ref_supports(const void* vp)
     if (p.groups < 1 || p.ofm < 1 || p.ifm < 1 || p.kh < 1 || p.kw < 1) return false;
     if (p.stride_x < 1 || p.stride_y < 1 || p.dil_x < 1 || p.dil_y < 1) return false;
     if (p.out.f != p.ofm * p.groups) return false;
+    if (!epilogue_order_ok(p)) return false;
     return true;
 }
 static int conv_ref_tune_count(const void*) { return 1; }

@@ -2,6 +2,7 @@
 // are turned into status codes with a thread-local message, as exception_handler
 // does for the reference's C API (src/include/api_impl.h:61-140).
 #include <cstring>
+#include <fstream>
 #include <sstream>
 #include "../../include/cldnn_host.h"
 #include "cldnn_host.hpp"
@@ -169,6 +170,29 @@ int32_t cldnn_host_add_lrn(cldnn_host_topology t, const char* id, const char* in
     return guarded([&] { need(t, "add_lrn"); t->t.add(lrn(str(id), str(input), size, k, alpha, beta)); });
 }
 
+int32_t cldnn_host_tuning_cache_check(const char* path, uint32_t compute_units, size_t* entries)
+{
+    return guarded([&] {
+        need(path, "tuning_cache_check"); need(entries, "tuning_cache_check");
+        std::ifstream f(path);
+        if (!f) throw error(std::string("cannot read '") + path + "'", CLDNN_B200_INVALID_ARG);
+        std::stringstream ss; ss << f.rdbuf();
+        const auto all = parse_tuning_cache(ss.str());
+        auto it = all.find(std::to_string(compute_units));
+        *entries = it == all.end() ? 0 : it->second.size();
+    });
+}
+
+int32_t cldnn_host_add_concatenation(cldnn_host_topology t, const char* id, const char* inputs, int32_t axis)
+{
+    return guarded([&] {
+        need(t, "add_concatenation");
+        std::vector<std::string> ins; std::stringstream ss(str(inputs)); std::string item;
+        while (std::getline(ss, item, ',')) if (!item.empty()) ins.push_back(item);
+        t->t.add(concatenation(str(id), ins, axis));
+    });
+}
+
 int32_t cldnn_host_network_build(cldnn_host_engine e, cldnn_host_topology t, const cldnn_host_build_options* o, cldnn_host_network* out)
 {
     return guarded([&] {
@@ -203,7 +227,7 @@ int32_t cldnn_host_network_info(cldnn_host_network n, char* buffer, size_t buffe
         for (auto& i : n->n.get_primitives_info())
             ss << i.id << "|" << i.type << "|" << i.kernel << "|" << i.tune << "|" << format::name(i.output.fmt) << "|" << (int)i.output.data_type << "|"
                << i.output.size.batch << "," << i.output.size.feature << "," << i.output.size.y << "," << i.output.size.x << "|" << i.original_ids << "|"
-               << (i.is_output ? 1 : 0) << "\n";
+               << (i.is_output ? 1 : 0) << "|" << (i.in_place ? 1 : 0) << "\n";
         const std::string s = ss.str();
         if (needed) *needed = s.size() + 1;
         if (buffer && buffer_bytes) { const size_t k = std::min(buffer_bytes - 1, s.size()); std::memcpy(buffer, s.data(), k); buffer[k] = 0; }

@@ -103,7 +103,7 @@ enum class tuning_mode : int32_t { tuning_disabled = 0, tuning_use_cache = 1, tu
 //   activation           api/CPP/activation.hpp
 //   pooling              api/CPP/pooling.hpp
 //   fully_connected      api/CPP/fully_connected.hpp
-//   softmax, lrn, reorder, data, input_layout
+//   softmax, lrn, reorder, concatenation (api/CPP/concatenation.hpp), data, input_layout
 struct primitive {
     std::string type, id;
     std::vector<std::string> input;
@@ -122,6 +122,7 @@ struct primitive {
     int32_t activation_func = CLDNN_B200_ACT_NONE; float act_a = 0.0f, act_b = 0.0f;
     pooling_mode pool_mode = pooling_mode::max; tensor size{1, 1, 1, 1}; bool global_pooling = false;
     uint32_t lrn_size = 5; float lrn_k = 1.0f, lrn_alpha = 1e-4f, lrn_beta = 0.75f;
+    int32_t concat_axis = 1;                                        // concatenation: index into tensor sizes (0 batch, 1 feature, 2 x, 3 y), api/C/concatenation.h:33-40
     int32_t softmax_dimension = 3;                                  // softmax::dimension_t: normalize_f 0, _x 1, _y 2, _fyx 3 (the default, api/CPP/softmax.hpp:59)
     layout target;                                        // reorder output layout / input_layout layout
     std::vector<float> subtract_per_feature;              // reorder mean values
@@ -157,6 +158,8 @@ primitive fully_connected(const std::string& id, const std::string& input, const
 enum softmax_dimension : int32_t { normalize_f = 0, normalize_x = 1, normalize_y = 2, normalize_fyx = 3 };   // api/CPP/softmax.hpp:44-50
 primitive softmax(const std::string& id, const std::string& input, int32_t dimension = normalize_fyx);
 primitive lrn(const std::string& id, const std::string& input, uint32_t size, float k, float alpha, float beta);
+enum concatenation_axis : int32_t { along_b = 0, along_f = 1, along_x = 2, along_y = 3 };
+primitive concatenation(const std::string& id, const std::vector<std::string>& inputs, int32_t axis);
 
 // cldnn::topology -- api/CPP/topology.hpp
 class topology {
@@ -173,6 +176,7 @@ private:
 struct build_options {
     bool optimize_data = false;                 // fusing + layout optimisation + weights pre-packing
     bool fuse_any_conv_eltwise = true;          // lift the reference's 1x1 / stride-1 restriction on conv+eltwise fusing
+    bool conv_eltw_read_write_opt = true;       // a fused_conv_eltwise writes its result over its second input where that is safe
     tuning_mode tuning = tuning_mode::tuning_disabled;
     std::string tuning_cache_path;              // JSON: { "<SM count>": { "<params hash>": ["kernel", tune_index] } }
     std::vector<std::string> outputs;           // empty: every primitive without users
@@ -182,6 +186,7 @@ struct build_options {
 
 struct primitive_info {
     std::string id, type, original_ids, kernel; int32_t tune = 0; layout output; bool is_output = false;
+    bool in_place = false;                      // fused_conv_eltwise: the result overwrites the second input's buffer
 };
 
 // cldnn::network -- api/CPP/network.hpp
@@ -203,6 +208,10 @@ public:
     void wait();
     std::shared_ptr<network_impl> impl;
 };
+
+// The tuning cache file as text -> { "<compute units>": { "<hash>": (kernel, tuning index) } }; throws `error` on malformed JSON
+// or on entries that are not ["kernel", index] (the schema of the reference's cache.json, auto_tuner.cpp:72-118).
+std::map<std::string, std::map<std::string, std::pair<std::string, int>>> parse_tuning_cache(const std::string& text);
 
 // output spatial size of a sliding window; convolution: src/include/sliding_window_utils.h:87-124 (range mode `all`),
 // pooling: :126-230 + src/pooling.cpp:91-92 (range mode `exceed_once_data`)

@@ -219,6 +219,11 @@ primitive lrn(const std::string& id, const std::string& input, uint32_t size, fl
     primitive p; p.type = "lrn"; p.id = id; p.input = {input}; p.lrn_size = size; p.lrn_k = k; p.lrn_alpha = alpha; p.lrn_beta = beta; return p;
 }
 
+primitive concatenation(const std::string& id, const std::vector<std::string>& inputs, int32_t axis)
+{
+    primitive p; p.type = "concatenation"; p.id = id; p.input = inputs; p.concat_axis = axis; return p;
+}
+
 void topology::add(const primitive& p)
 {
     if (p.id.empty()) throw error("topology: primitive without id", CLDNN_B200_INVALID_ARG);
@@ -238,6 +243,7 @@ struct node {
     layout out;
     bool is_output = false;
     bool removed = false;
+    bool in_place = false;              // fused_conv_eltwise: output written over the second input (second_input_in_output)
     std::string answers_for;            // user-visible id this node's output stands for (after fusing / reorder insertion)
     std::string fused_ids;              // ids of primitives folded into this one
     // fused activations (prepare_primitive_fusing)
@@ -249,6 +255,7 @@ struct node {
     std::shared_ptr<struct block> scratch; // kernel workspace (kernel_scratch_bytes)
     std::string kernel; int32_t tune = 0;
     cldnn_b200_prepared prepared = nullptr;
+    std::vector<cldnn_b200_prepared> more_prepared;   // further launches of the same primitive (concatenation: one copy per input)
     int order = -1;
     bool constant() const { return p.type == "data"; }
 };
@@ -274,6 +281,7 @@ public:
     uint64_t launches = 0;
     size_t pool_bytes = 0;
     std::map<std::string, std::pair<std::string, int>> tuning_cache;   // hash -> (kernel, tune)
+    std::map<std::string, std::map<std::string, std::pair<std::string, int>>> other_devices;   // sections of the cache file for other SM counts, written back untouched
     std::vector<std::pair<cldnn_b200_event, cldnn_b200_event>> prof_events;   // per node of `order`, profiling only
     bool cache_dirty = false;
 
@@ -281,7 +289,7 @@ public:
     {
         if (eng && eng->ctx) cldnn_b200_ctx_sync(eng->ctx);
         if (graph) cldnn_b200_graph_destroy(graph);
-        for (auto& n : nodes) if (n->prepared) cldnn_b200_prepared_destroy(n->prepared);
+        for (auto& n : nodes) { if (n->prepared) cldnn_b200_prepared_destroy(n->prepared); for (auto pr : n->more_prepared) cldnn_b200_prepared_destroy(pr); }
         for (auto& pe : prof_events) { cldnn_b200_event_destroy(pe.first); cldnn_b200_event_destroy(pe.second); }
     }
 
@@ -305,6 +313,7 @@ public:
     void fuse_activations();
     void fuse_conv_eltwise();
     void select_layouts();
+    void conv_eltw_read_write_opt();
     void replace_dep(node* consumer, node* from, node* to) { for (auto& id : consumer->p.input) if (id == from->p.id) id = to->p.id; }
     void allocate_and_prepare();
     void prepare_kernel(node* n);
@@ -313,7 +322,11 @@ public:
     memory pack_conv_weights(node* n, int32_t stored_ifm, int32_t groups = 1);
     void load_cache(); void save_cache();
     void execute();
-    void run_prepared(node* n) { if (n->prepared) check(cldnn_b200_run(n->prepared), "run " + n->p.id); }
+    void run_prepared(node* n)
+    {
+        if (n->prepared) check(cldnn_b200_run(n->prepared), "run " + n->p.id);
+        for (auto pr : n->more_prepared) check(cldnn_b200_run(pr), "run " + n->p.id);
+    }
 };
 
 void network_impl::link()
@@ -388,6 +401,19 @@ void network_impl::calc_layout(node* n)
         const layout& b = n->deps.at(1)->out;
         o.size.x = std::max(in.size.x, b.size.x); o.size.y = std::max(in.size.y, b.size.y);
         o.size.feature = std::max(in.size.feature, b.size.feature); o.size.batch = std::max(in.size.batch, b.size.batch);
+    } else if (p.type == "concatenation") {
+        // concatenation_inst::calc_output_layout (src/concatenation.cpp:34-63): the first input's layout with the sizes along the axis summed
+        if (p.concat_axis < 0 || p.concat_axis > 3) throw error(p.id + ": concatenation axis must be b, f, x or y", CLDNN_B200_INVALID_ARG);
+        auto dim = [&](tensor& t) -> int32_t& { return p.concat_axis == 0 ? t.batch : (p.concat_axis == 1 ? t.feature : (p.concat_axis == 2 ? t.x : t.y)); };
+        int32_t total = 0;
+        for (node* d : n->deps) {
+            tensor a = d->out.size, b = in.size;
+            total += dim(a);
+            dim(a) = 0; dim(b) = 0;
+            if (!(a == b)) throw error(p.id + ": inputs differ outside the concatenation axis", CLDNN_B200_DIMENSION_MISMATCH);
+            if (d->out.data_type != in.data_type) throw error(p.id + ": inputs differ in data type", CLDNN_B200_INVALID_ARG);
+        }
+        dim(o.size) = total;
     } else if (p.type == "activation" || p.type == "softmax" || p.type == "lrn") {
         // same shape and type
     } else throw error("primitive type '" + p.type + "' is outside the supported path", CLDNN_B200_UNSUPPORTED_FORMAT);
@@ -523,7 +549,7 @@ void network_impl::select_layouts()
     for (node* n : order) {
         if (n->removed || n->constant() || n->p.type == "input_layout" || n->deps.empty()) continue;
         if (conv_like(n)) chosen.insert(n);
-        else if ((n->p.type == "pooling" || n->p.type == "eltwise" || n->p.type == "activation" || n->p.type == "lrn") &&
+        else if ((n->p.type == "pooling" || n->p.type == "eltwise" || n->p.type == "activation" || n->p.type == "lrn" || n->p.type == "concatenation") &&
                  (is_int8(n->deps[0]->out.data_type) || n->deps[0]->out.data_type == data_types::f16)) {
             bool all = true; for (node* d : n->deps) all &= chosen.count(d) > 0;
             if (all) chosen.insert(n);
@@ -553,6 +579,25 @@ void network_impl::select_layouts()
     for (node* n : order) { calc_layout(n); if (chosen.count(n)) n->out.fmt = format::byxf_af32; }
 }
 
+// prepare_conv_eltw_read_write_opt (src/graph_optimizer/prepare_primitive_fusing.cpp:468-555): when the result of a
+// fused_conv_eltwise has exactly the layout of its second input, the two share one buffer and the kernel reads the residual
+// from the place it then writes (second_input_in_output).  The reference re-points every other reader of the second input at
+// the shared buffer whatever its place in the execution order; here the buffer is shared only when every other reader runs
+// before the fused primitive, so nobody can see the overwritten values.
+void network_impl::conv_eltw_read_write_opt()
+{
+    for (node* n : order) {
+        if (n->removed || n->p.type != "fused_conv_eltwise" || n->deps.size() != 2) continue;
+        node* r = n->deps[1];
+        if (r == n->deps[0] || r->constant() || r->p.type == "input_layout" || r->is_output) continue;
+        if (!(r->out == n->out) || n->p.eltw_stride.x != 1 || n->p.eltw_stride.y != 1) continue;
+        bool safe = true;
+        for (node* u : r->users) safe &= u == n || u->order < n->order;
+        if (!safe) continue;
+        n->in_place = true;
+    }
+}
+
 // --------------------------------------------------------------------------------------
 // tuning cache: same schema as the reference's cache.json (kernel_selector/core/auto_tuner.cpp:72-118), keyed by the
 // number of compute units (SMs) and a hash of the launch constants.
@@ -565,29 +610,123 @@ static std::string fnv1a_hex(const void* data, size_t n, const std::string& salt
     char buf[32]; snprintf(buf, sizeof(buf), "%016llx", (unsigned long long)h); return buf;
 }
 
+// A small JSON reader for the cache file (the reference parses cache.json with rapidjson, auto_tuner.cpp:72-104): values
+// are objects, arrays, strings, numbers, true / false / null; anything malformed makes the whole file unusable (and says so)
+// instead of silently dropping entries.
+namespace {
+struct json_value {
+    enum kind_t { null_v, bool_v, number_v, string_v, array_v, object_v } kind = null_v;
+    double number = 0.0; bool boolean = false; std::string text;
+    std::vector<json_value> items;                              // array
+    std::vector<std::pair<std::string, json_value>> members;    // object, in file order
+    const json_value* find(const std::string& key) const { for (auto& m : members) if (m.first == key) return &m.second; return nullptr; }
+};
+struct json_reader {
+    const std::string& s; size_t i = 0;
+    explicit json_reader(const std::string& text) : s(text) {}
+    [[noreturn]] void bad(const char* what) const { throw error(std::string("tuning cache: ") + what + " at offset " + std::to_string(i), CLDNN_B200_INVALID_ARG); }
+    void ws() { while (i < s.size() && (s[i] == ' ' || s[i] == '\n' || s[i] == '\t' || s[i] == '\r')) ++i; }
+    bool eat(char c) { ws(); if (i < s.size() && s[i] == c) { ++i; return true; } return false; }
+    std::string string_body()
+    {
+        std::string out;
+        while (true) {
+            if (i >= s.size()) bad("unterminated string");
+            const char c = s[i++];
+            if (c == '"') return out;
+            if (c != '\\') { out.push_back(c); continue; }
+            if (i >= s.size()) bad("unterminated escape");
+            const char e = s[i++];
+            switch (e) {
+            case '"': out.push_back('"'); break; case '\\': out.push_back('\\'); break; case '/': out.push_back('/'); break;
+            case 'b': out.push_back('\b'); break; case 'f': out.push_back('\f'); break; case 'n': out.push_back('\n'); break;
+            case 'r': out.push_back('\r'); break; case 't': out.push_back('\t'); break;
+            case 'u': {
+                if (i + 4 > s.size()) bad("short \\u escape");
+                const unsigned cp = (unsigned)std::strtoul(s.substr(i, 4).c_str(), nullptr, 16); i += 4;
+                if (cp < 0x80) out.push_back((char)cp);
+                else if (cp < 0x800) { out.push_back((char)(0xc0 | (cp >> 6))); out.push_back((char)(0x80 | (cp & 0x3f))); }
+                else { out.push_back((char)(0xe0 | (cp >> 12))); out.push_back((char)(0x80 | ((cp >> 6) & 0x3f))); out.push_back((char)(0x80 | (cp & 0x3f))); }
+                break;
+            }
+            default: bad("unknown escape");
+            }
+        }
+    }
+    json_value value(int depth = 0)
+    {
+        if (depth > 32) bad("nesting too deep");
+        ws();
+        if (i >= s.size()) bad("unexpected end");
+        json_value v;
+        const char c = s[i];
+        if (c == '{') {
+            ++i; v.kind = json_value::object_v;
+            if (eat('}')) return v;
+            do {
+                ws();
+                if (i >= s.size() || s[i] != '"') bad("object key expected");
+                ++i;
+                std::string key = string_body();
+                if (!eat(':')) bad("':' expected");
+                v.members.push_back({key, value(depth + 1)});
+            } while (eat(','));
+            if (!eat('}')) bad("'}' expected");
+            return v;
+        }
+        if (c == '[') {
+            ++i; v.kind = json_value::array_v;
+            if (eat(']')) return v;
+            do v.items.push_back(value(depth + 1)); while (eat(','));
+            if (!eat(']')) bad("']' expected");
+            return v;
+        }
+        if (c == '"') { ++i; v.kind = json_value::string_v; v.text = string_body(); return v; }
+        if (s.compare(i, 4, "true") == 0) { i += 4; v.kind = json_value::bool_v; v.boolean = true; return v; }
+        if (s.compare(i, 5, "false") == 0) { i += 5; v.kind = json_value::bool_v; return v; }
+        if (s.compare(i, 4, "null") == 0) { i += 4; return v; }
+        char* end = nullptr;
+        v.number = std::strtod(s.c_str() + i, &end);
+        if (end == s.c_str() + i) bad("value expected");
+        i = (size_t)(end - s.c_str()); v.kind = json_value::number_v;
+        return v;
+    }
+    json_value document() { json_value v = value(); ws(); if (i != s.size()) bad("trailing characters"); return v; }
+};
+}  // namespace
+
+// { "<compute units>": { "<hash of the launch constants>": ["<kernel>", <tuning index>], ... }, ... }: the entries under this
+// device's SM count are taken, other devices' sections are kept out.
+std::map<std::string, std::map<std::string, std::pair<std::string, int>>> parse_tuning_cache(const std::string& text)
+{
+    std::map<std::string, std::map<std::string, std::pair<std::string, int>>> out;
+    if (text.find_first_not_of(" \n\t\r") == std::string::npos) return out;   // an empty file is an empty cache
+    const json_value doc = json_reader(text).document();
+    if (doc.kind != json_value::object_v) throw error("tuning cache: the top level must be an object keyed by compute-unit count", CLDNN_B200_INVALID_ARG);
+    for (auto& dev : doc.members) {
+        if (dev.second.kind != json_value::object_v) throw error("tuning cache: device section '" + dev.first + "' must be an object", CLDNN_B200_INVALID_ARG);
+        auto& section = out[dev.first];
+        for (auto& m : dev.second.members) {
+            const json_value& e = m.second;
+            if (e.kind != json_value::array_v || e.items.size() != 2 || e.items[0].kind != json_value::string_v || e.items[1].kind != json_value::number_v)
+                throw error("tuning cache: entry '" + m.first + "' must be [\"kernel\", index]", CLDNN_B200_INVALID_ARG);
+            section[m.first] = {e.items[0].text, (int)e.items[1].number};
+        }
+    }
+    return out;
+}
+
 void network_impl::load_cache()
 {
-    tuning_cache.clear();
+    tuning_cache.clear(); other_devices.clear();
     if (opts.tuning_cache_path.empty()) return;
     std::ifstream f(opts.tuning_cache_path);
     if (!f) return;
-    std::stringstream ss; ss << f.rdbuf(); const std::string s = ss.str();
-    const std::string key = "\"" + std::to_string(eng->info.cores_count) + "\"";
-    size_t pos = s.find(key);
-    if (pos == std::string::npos) return;
-    size_t open = s.find('{', pos); if (open == std::string::npos) return;
-    size_t close = s.find('}', open); if (close == std::string::npos) return;
-    size_t i = open;
-    while (true) {                                                  // entries: "hash": ["kernel", tune]
-        size_t q1 = s.find('"', i + 1); if (q1 == std::string::npos || q1 > close) break;
-        size_t q2 = s.find('"', q1 + 1); if (q2 == std::string::npos) break;
-        size_t q3 = s.find('"', q2 + 1); if (q3 == std::string::npos) break;
-        size_t q4 = s.find('"', q3 + 1); if (q4 == std::string::npos) break;
-        size_t comma = s.find(',', q4); size_t rb = s.find(']', q4);
-        if (comma == std::string::npos || rb == std::string::npos || rb > close) break;
-        tuning_cache[s.substr(q1 + 1, q2 - q1 - 1)] = {s.substr(q3 + 1, q4 - q3 - 1), std::atoi(s.substr(comma + 1, rb - comma - 1).c_str())};
-        i = rb;
-    }
+    std::stringstream ss; ss << f.rdbuf();
+    other_devices = parse_tuning_cache(ss.str());
+    const std::string mine = std::to_string(eng->info.cores_count);
+    auto it = other_devices.find(mine);
+    if (it != other_devices.end()) { tuning_cache = it->second; other_devices.erase(it); }
 }
 
 void network_impl::save_cache()
@@ -595,11 +734,17 @@ void network_impl::save_cache()
     if (opts.tuning_cache_path.empty() || !cache_dirty) return;
     std::ofstream f(opts.tuning_cache_path);
     if (!f) throw error("cannot write tuning cache '" + opts.tuning_cache_path + "'", CLDNN_B200_ERROR);
-    f << "{\n  \"" << eng->info.cores_count << "\": {\n";
-    size_t k = 0;
-    for (auto& e : tuning_cache)
-        f << "    \"" << e.first << "\": [\"" << e.second.first << "\", " << e.second.second << "]" << (++k < tuning_cache.size() ? "," : "") << "\n";
-    f << "  }\n}\n";
+    auto section = [&](const std::string& key, const std::map<std::string, std::pair<std::string, int>>& entries, bool last) {
+        f << "  \"" << key << "\": {\n";
+        size_t k = 0;
+        for (auto& e : entries)
+            f << "    \"" << e.first << "\": [\"" << e.second.first << "\", " << e.second.second << "]" << (++k < entries.size() ? "," : "") << "\n";
+        f << "  }" << (last ? "" : ",") << "\n";
+    };
+    f << "{\n";
+    for (auto& o : other_devices) section(o.first, o.second, false);
+    section(std::to_string(eng->info.cores_count), tuning_cache, true);
+    f << "}\n";
     cache_dirty = false;
 }
 
@@ -754,7 +899,8 @@ void network_impl::prepare_kernel(node* n)
             if (n->eltw_act != CLDNN_B200_ACT_NONE) { cp.eltw_m = n->eltw_m; cp.eltw_n = n->eltw_n; }
             cp.eltw_calibration = n->ec ? 1 : 0;
             cp.eltw_stride_x = p.eltw_stride.x; cp.eltw_stride_y = p.eltw_stride.y;
-            cp.in_out_opt = 0;
+            cp.in_out_opt = n->in_place ? 1 : 0;
+            if (n->in_place) a.input1 = nullptr;
         }
         std::function<void()> fc_fallback;
         if (fc) {
@@ -886,6 +1032,27 @@ void network_impl::prepare_kernel(node* n)
         finish({"reorder_ref"}, &rp, sizeof(rp), [](int) {});
         return;
     }
+    if (t == "concatenation") {
+        // concatenation_gpu (src/gpu/concatenation_gpu.cpp): one copy launch per input, each writing its slice of the output;
+        // the copy kernel addresses both sides through pitches, so any of the supported layouts works on either side
+        const cldnn_b200_tensor od = n->out.desc();
+        int64_t at = 0;
+        n->kernel = "reorder_ref"; n->tune = 0;
+        for (node* d : n->deps) {
+            cldnn_b200_reorder_params rp{};
+            rp.in = d->out.desc(); rp.out = od;
+            rp.out.b = rp.in.b; rp.out.f = rp.in.f; rp.out.y = rp.in.y; rp.out.x = rp.in.x;
+            const int64_t pitch = p.concat_axis == 0 ? od.pb : (p.concat_axis == 1 ? od.pf : (p.concat_axis == 2 ? od.px : od.py));
+            const int64_t len = p.concat_axis == 0 ? rp.in.b : (p.concat_axis == 1 ? rp.in.f : (p.concat_axis == 2 ? rp.in.x : rp.in.y));
+            rp.out.offset += at * pitch;
+            at += len;
+            cldnn_b200_args ca{}; ca.input0 = d->mem.device_ptr(); ca.output = n->mem.device_ptr();
+            cldnn_b200_prepared pr = nullptr;
+            check(cldnn_b200_prepare(eng->kernel("reorder_ref"), &rp, sizeof(rp), &ca, &pr), p.id + " (concatenation copy)");
+            if (!n->prepared) n->prepared = pr; else n->more_prepared.push_back(pr);
+        }
+        return;
+    }
     if (t == "lrn") {
         cldnn_b200_lrn_params lp{}; lp.in = n->deps[0]->out.desc(); lp.out = n->out.desc();
         lp.size = (int32_t)p.lrn_size; lp.k = p.lrn_k; lp.alpha = p.lrn_alpha; lp.beta = p.lrn_beta;
@@ -916,18 +1083,29 @@ void network_impl::allocate_and_prepare()
     for (node* n : order) {
         if (n->p.type == "data") { n->mem = n->p.mem; continue; }
         if (n->p.type == "input_layout") continue;                  // bound by set_input_data
+        if (n->in_place) {
+            // the second input's buffer becomes the output: it now lives until this node's last reader
+            node* r = n->deps[1];
+            n->mem = memory(); n->mem.impl = std::make_shared<memory_impl>(); n->mem.impl->l = n->out; n->mem.impl->blk = r->mem.impl->blk;
+            for (auto& lv : live) if (lv.second == r->mem.impl->blk) lv.first = std::max(lv.first, last_use[n->order]);
+            continue;
+        }
         for (auto it = live.begin(); it != live.end();) {
             if (it->first < n->order) { free_blocks.insert({it->second->bytes, it->second}); it = live.erase(it); } else ++it;
         }
         const size_t need = std::max<size_t>(n->out.bytes_count(), 16);
         std::shared_ptr<block> blk;
-        if (!n->is_output) {
+        // fp16 tensors whose stored feature count exceeds the real one: the kernels write the real features only and the
+        // consumer multiplies the padded lanes by zero weights, which is only safe while those lanes hold zeros (a previous
+        // tenant's Inf or NaN times zero is NaN).  Such a tensor keeps a zero-filled block of its own for the network's life.
+        const bool private_block = n->out.data_type == data_types::f16 && n->out.stored_features() != n->out.size.feature;
+        if (!n->is_output && !private_block) {
             auto it = free_blocks.lower_bound(need);
             if (it != free_blocks.end() && it->first <= 2 * need + 65536) { blk = it->second; free_blocks.erase(it); }
         }
         if (!blk) { blk = new_block(eng, need); if (!n->is_output) pool_bytes += blk->bytes; }
         n->mem = memory(); n->mem.impl = std::make_shared<memory_impl>(); n->mem.impl->l = n->out; n->mem.impl->blk = blk;
-        if (!n->is_output) live.push_back({last_use[n->order], blk});
+        if (!n->is_output && !private_block) live.push_back({last_use[n->order], blk});
     }
 }
 
@@ -949,6 +1127,7 @@ void network_impl::build(const topology& topo)
         fuse_conv_eltwise();
         fuse_activations();                                         // relu behind a freshly fused conv+eltwise
         select_layouts();
+        if (opts.conv_eltw_read_write_opt) conv_eltw_read_write_opt();
     }
     load_cache();
     allocate_and_prepare();
@@ -960,11 +1139,15 @@ void network_impl::execute()
     if (inputs_changed) {
         // (re)build the launches: pointers of the inputs are baked into the prepared kernels
         if (graph) { cldnn_b200_graph_destroy(graph); graph = nullptr; }
-        for (node* n : order) if (n->prepared) { cldnn_b200_prepared_destroy(n->prepared); n->prepared = nullptr; }
+        for (node* n : order) {
+            if (n->prepared) { cldnn_b200_prepared_destroy(n->prepared); n->prepared = nullptr; }
+            for (auto pr : n->more_prepared) cldnn_b200_prepared_destroy(pr);
+            n->more_prepared.clear();
+        }
         for (node* n : order) if (n->p.type != "data" && n->p.type != "input_layout") prepare_kernel(n);
         save_cache();
         check(cldnn_b200_ctx_sync(eng->ctx), "sync");
-        launches = 0; for (node* n : order) if (n->prepared) ++launches;
+        launches = 0; for (node* n : order) if (n->prepared) launches += 1 + n->more_prepared.size();
         if (opts.use_graph && !eng->profiling) {
             check(cldnn_b200_graph_begin(eng->ctx), "graph begin");
             try { for (node* n : order) run_prepared(n); }
@@ -1026,7 +1209,7 @@ std::vector<primitive_info> network::get_primitives_info() const
 {
     std::vector<primitive_info> v;
     for (node* n : impl->order) {
-        primitive_info i; i.id = n->p.id; i.type = n->p.type; i.original_ids = n->fused_ids; i.kernel = n->kernel; i.tune = n->tune; i.output = n->out; i.is_output = n->is_output;
+        primitive_info i; i.id = n->p.id; i.type = n->p.type; i.original_ids = n->fused_ids; i.kernel = n->kernel; i.tune = n->tune; i.output = n->out; i.is_output = n->is_output; i.in_place = n->in_place;
         v.push_back(i);
     }
     return v;

@@ -70,6 +70,23 @@ extern "C" {
 #define CLDNN_B200_ACT_SQRT                 9
 #define CLDNN_B200_ACT_ELU                 10
 
+/* Operation order of the quantised epilogue.  The reference's kernels do not agree on it; the parity target is the
+ * reference-order kernel, the other two are offered for callers whose models were calibrated against the optimised kernels:
+ *   REF   fused_conv_eltwise_gpu_ref.cl:148-232  (i32 bias | dequantise, f32 bias) -> activation -> * calib|O_QF -> round
+ *                                                 [-> + residual * scale -> activation -> * eltw_calib -> round] -> saturate
+ *   MMAD  convolution_gpu_mmad.cl:106-132        round(((float)acc * q * I_QF + bias_f32) * calib|O_QF) -> convert to the 8-bit
+ *                                                 type -> activation on the 8-bit value.  No residual.  Needs an f32 bias.
+ *   IMAD  fused_conv_eltwise_gpu_imad.cl:171-207 round(((float)acc * q * I_QF + bias_f32) * calib|O_QF) -> 8-bit -> activation
+ *                                                 [-> saturate(round(((int)a + (int)residual) * eltw_calib)) -> activation].
+ *                                                 Needs an f32 bias and, when fused, eltwise calibration factors.
+ * The conversion "to the 8-bit type" of MMAD / IMAD does not saturate in the reference (convert_char / TO_UNIT_TYPE on a value
+ * that may be out of range, which OpenCL leaves to the implementation); here it keeps the low 8 bits of the rounded integer.
+ * Both take a signed 8-bit output (the kernels' unit type is char).  For values inside the 8-bit range, ReLU or no
+ * activation and positive factors all three orders give the same result.                                                   */
+#define CLDNN_B200_EPILOGUE_REF  0
+#define CLDNN_B200_EPILOGUE_MMAD 1
+#define CLDNN_B200_EPILOGUE_IMAD 2
+
 /* A 4-D activation tensor as the reference kernels see it: logical sizes plus
  * element pitches and the offset of element (0,0,0,0) -- the INPUT0_* /
  * OUTPUT_* macro family of jitter.cpp:229-262 and GET_DATA_INDEX of
@@ -117,7 +134,8 @@ typedef struct cldnn_b200_conv_params {
     int32_t in_out_opt;          /* second input lives in the output       */
     /* implementation choice (tuning index of the selected kernel)          */
     int32_t tune;
-    int32_t reserved[7];
+    int32_t epilogue_order;      /* CLDNN_B200_EPILOGUE_*: whose operation order the quantised epilogue follows */
+    int32_t reserved[6];
 } cldnn_b200_conv_params;
 
 /* Arguments by role, in the order of kernel_selector's ArgumentDescriptor

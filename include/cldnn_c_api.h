@@ -1,6 +1,6 @@
 /* The public C boundary of clDNN for the convolution hot path, as libclDNN64.so of this repository exports it.
  *
- * clDNN's applications (its header-only C++ API api/CPP/*.hpp, its tests, the Inference-Engine plugin) reach the library
+ * clDNN's applications (its header-only C++ API under api/CPP, its tests, the Inference-Engine plugin) reach the library
  * through the C entry points and plain-data descriptors of api/C/cldnn.h and api/C/<primitive>.h.  This header declares
  * the same symbols with the same binary layout, so that code compiled against the reference's own headers links against
  * this library unchanged; it exists so that the library itself can be built without the reference tree.  Each block
@@ -128,7 +128,8 @@ typedef struct { cldnn_data_type data_type; char enabled; } cldnn_optional_data_
 
 /* api/C/cldnn.h:445-475: the activation functions this library implements keep the reference's values */
 typedef enum {
-    activation_none = 0, activation_relu = 3, activation_relu_negative_slope = 4, activation_clamp = 5
+    activation_none = 0, activation_logistic = 1, activation_hyperbolic_tan = 2, activation_relu = 3, activation_relu_negative_slope = 4,
+    activation_clamp = 5, activation_abs = 7, activation_linear = 8, activation_square = 9, activation_sqrt = 10, activation_elu = 11
 } cldnn_activation_func;
 typedef struct { float a, b; } cldnn_activation_additional_params;
 typedef enum { mean_none, mean_subtract, mean_mul, mean_div } cldnn_reorder_mean_mode;

@@ -97,6 +97,12 @@ CLDNN_B200_API int32_t cldnn_host_add_softmax(cldnn_host_topology t, const char*
 /* dimension: cldnn_softmax_dimension (api/C/softmax.h:34-40): 0 normalize_f, 1 normalize_x, 2 normalize_y, 3 normalize_fyx */
 CLDNN_B200_API int32_t cldnn_host_add_softmax_dim(cldnn_host_topology t, const char* id, const char* input, int32_t dimension);
 CLDNN_B200_API int32_t cldnn_host_add_lrn(cldnn_host_topology t, const char* id, const char* input, uint32_t size, float k, float alpha, float beta);
+/* Checks a tuning cache file (the reference's cache.json schema, kernel_selector/core/auto_tuner.cpp:72-118): *entries receives
+ * the number of entries stored for `compute_units` streaming multiprocessors (0 when the file has no such section); malformed
+ * JSON or a malformed entry gives CLDNN_B200_INVALID_ARG with the position in the last-error text.  Needs no device.      */
+CLDNN_B200_API int32_t cldnn_host_tuning_cache_check(const char* path, uint32_t compute_units, size_t* entries);
+/* cldnn::concatenation (api/CPP/concatenation.hpp:40-78): `inputs` is a comma-separated list of ids, axis 0 batch, 1 feature, 2 x, 3 y */
+CLDNN_B200_API int32_t cldnn_host_add_concatenation(cldnn_host_topology t, const char* id, const char* inputs, int32_t axis);
 
 /* build options, api/C/cldnn.h:207-232 */
 typedef struct cldnn_host_build_options {

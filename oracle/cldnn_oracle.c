@@ -218,6 +218,28 @@ static void conv_one(const cldnn_b200_conv_params* p, const cldnn_b200_args* a,
             acc_i += (int32_t)load_elem(a->bias, p->bias_dtype, fg);
     }
 
+    if (quant_path && p->epilogue_order != CLDNN_B200_EPILOGUE_REF) {
+        /* The optimised int8 kernels' own orders: convolution_gpu_mmad.cl:106-132 (MMAD) and
+         * fused_conv_eltwise_gpu_imad.cl:171-207 (IMAD).  Both need QUANTIZATION_TERM with a float bias. */
+        float t = (float)acc_i * a->weights_quantization_factors[fg];                      /* mmad :110-113, imad :180 */
+        t = t * p->i_qf;
+        t = t + ((const float*)a->bias)[fg];
+        t = roundf(t * (p->calibration ? a->output_calibration_factors[fg] : p->o_qf));   /* mmad :111/:113, imad :191-194 */
+        /* (UNIT_TYPE) / convert_char / TO_UNIT_TYPE of the rounded value: not saturating; the low 8 bits are kept */
+        const int32_t r = (int32_t)t;
+        int32_t a8 = p->out.dtype == CLDNN_B200_U8 ? (int32_t)(uint8_t)r : (int32_t)(int8_t)r;
+        a8 = act_int(p->act, a8, p->act_m, p->act_n);                                      /* mmad :126, imad :199 */
+        if (p->epilogue_order == CLDNN_B200_EPILOGUE_MMAD || !p->fused_eltw) { store_sat_int(a->output, p->out.dtype, dst, a8); return; }
+        const void* esrc = p->in_out_opt ? a->output : a->input1;
+        const int32_t edt = p->in_out_opt ? p->out.dtype : p->eltw.dtype;
+        const int64_t ei = p->in_out_opt ? dst : tidx(&p->eltw, b, fg, (int64_t)y * p->eltw_stride_y, (int64_t)x * p->eltw_stride_x);
+        const float s = roundf((float)(a8 + load_int(esrc, edt, ei)) * a->eltw_output_calibration_factors[fg]);   /* imad :201-203 */
+        int32_t o = p->out.dtype == CLDNN_B200_U8 ? (s < 0.0f ? 0 : (s > 255.0f ? 255 : (int32_t)s)) : (s < -128.0f ? -128 : (s > 127.0f ? 127 : (int32_t)s));
+        o = act_int(p->eltw_act, o, p->eltw_m, p->eltw_n);
+        store_sat_int(a->output, p->out.dtype, dst, o);
+        return;
+    }
+
     if (quant_path) {
         float deq = (float)acc_i;                                                          /* :165-171 */
         if (p->quantization) { deq = deq * a->weights_quantization_factors[fg]; deq = deq * p->i_qf; }
@@ -308,6 +330,12 @@ int32_t oracle_conv_range(const cldnn_b200_conv_params* p, const cldnn_b200_args
 {
     const int F = p->ofm * p->groups;
     if (F != p->out.f) return CLDNN_B200_DIMENSION_MISMATCH;
+    if (p->epilogue_order != CLDNN_B200_EPILOGUE_REF) {
+        /* the MMAD / IMAD orders: quantised, f32 bias, char output; IMAD's fused form needs eltwise calibration factors */
+        if ((p->epilogue_order != CLDNN_B200_EPILOGUE_MMAD && p->epilogue_order != CLDNN_B200_EPILOGUE_IMAD) || !p->quantization ||
+            p->bias_dtype != CLDNN_B200_F32 || p->out.dtype != CLDNN_B200_I8) return CLDNN_B200_UNSUPPORTED_FORMAT;
+        if (p->fused_eltw && (p->epilogue_order == CLDNN_B200_EPILOGUE_MMAD || !p->eltw_calibration || p->has_non_conv_scale)) return CLDNN_B200_UNSUPPORTED_FORMAT;
+    }
     if (bf_begin < 0) bf_begin = 0;
     if (bf_end > (int64_t)p->out.b * F) bf_end = (int64_t)p->out.b * F;
 #ifdef _OPENMP

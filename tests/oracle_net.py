@@ -200,6 +200,9 @@ def run(spec, inputs, threads=0, stats=None, keep=None, conv_impl="oracle", fuse
             lp.in_, lp.out = _tensor(x), _tensor(x)
             lp.size, lp.k, lp.alpha, lp.beta = a["size"], a["k"], a["alpha"], a["beta"]
             res = oracle_lib.lrn(lp, x.reshape(-1)).reshape(x.shape)
+        elif k == "concatenation":
+            # concatenation_gpu_ref.cl: every input copied to its offset along the axis (tensor sizes are b, f, x, y; arrays are [b, f, y, x])
+            res = np.concatenate([vals[i] for i in a["inputs"]], axis={0: 0, 1: 1, 2: 3, 3: 2}[a["axis"]])
         else:
             raise ValueError("oracle_net: primitive kind " + k)
         vals[p.id] = res

@@ -11,7 +11,15 @@ from cldnn_b200 import abi
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF_DIR = os.path.join(ROOT, "oracle", "_ref")
-REFERENCE_ROOT = os.environ.get("CLDNN_REFERENCE_ROOT", "/root/reference")
+def _reference_root():
+    """The clDNN source tree: CLDNN_REFERENCE_ROOT, else a directory named `reference` beside this repository."""
+    env = os.environ.get("CLDNN_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(ROOT), "reference")
+
+
+REFERENCE_ROOT = _reference_root()
 _T = {abi.I8: "c", abi.U8: "uc", abi.F32: "f"}
 _libs = {}
 

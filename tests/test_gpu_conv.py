@@ -395,3 +395,26 @@ def test_two_prepared_launches_with_different_shared_memory_needs(eng, kernel):
         assert np.array_equal(want[:case.out_elems], got[:case.out_elems])
     pa.destroy()
     pb.destroy()
+
+
+@pytest.mark.parametrize("order", ["mmad", "imad", "imad_fused"])
+@pytest.mark.parametrize("kernel", ["conv_ref", "conv_i8_tc"])
+def test_alternative_epilogue_orders_match_oracle(eng, order, kernel):
+    """The operation orders of the reference's optimised int8 kernels (convolution_gpu_mmad.cl:105-128,
+    fused_conv_eltwise_gpu_imad.cl:171-205) as selectable epilogue modes, on the generic kernel and on the tensor cores;
+    scales chosen so that part of the values leaves the 8-bit range, where those orders wrap instead of saturating."""
+    fused = order == "imad_fused"
+    for calib, act in ((False, abi.ACT_RELU), (True, abi.ACT_NONE), (True, abi.ACT_CLAMP)):
+        case = cases.make_conv_case(81, N=3, C=64, K=96, H=9, W=11, in_dtype=np.int8, out_dtype=np.int8, bias="f32", calib=calib, act=act,
+                                    fused=fused, eltw_dtype=np.int8, eltw_calib=fused, eltw_act=act, scale_lo=2.0 ** -12, scale_hi=2.0 ** -9,
+                                    o_qf=1.0 if calib else 0.75)
+        case.p.act_m, case.p.act_n, case.p.eltw_m, case.p.eltw_n = -20.0, 90.0, -20.0, 90.0
+        case.p.epilogue_order = abi.EPILOGUE_MMAD if order == "mmad" else abi.EPILOGUE_IMAD
+        assert eng.kernel(kernel).supports(case.p)
+        want = _exact(eng, case, kernel)
+        assert len(np.unique(want[:case.out_elems])) > 64
+    # the orders exist for a float bias and a signed 8-bit output only
+    bad = cases.make_conv_case(82, N=1, C=32, K=32, H=6, W=6)
+    bad.p.epilogue_order = abi.EPILOGUE_IMAD
+    assert not eng.kernel(kernel).supports(bad.p)
+    assert not eng.kernel("conv_i8_dw").supports(bad.p)

@@ -52,6 +52,9 @@ def test_small_residual_network_bit_exact(eng, optimize):
         assert all(r["kernel"] in ("conv_i8_tc", "conv_i8_first") and r["format"] == "byxf_af32" for r in convs)
         assert convs[0]["kernel"] == "conv_i8_first"          # the image is consumed in its planar layout, no input reorder
         assert any(r["kernel"] == "pooling_i8_byxf" for r in info)
+        # prepare_conv_eltw_read_write_opt: an identity-shortcut block writes its result over the shortcut's buffer; a projection
+        # shortcut (s8 against the u8 result) or the last block (s8 result over a u8 shortcut) cannot
+        assert {r["id"] for r in info if r["in_place"]} == {"s2_b1_c"}
     else:
         # optimize_data(false): reference-order kernels in the caller's layout, like the reference's own tests
         assert all(r["kernel"] in ("conv_ref", "fc_ref") and r["format"] == "bfyx" for r in convs)
@@ -280,3 +283,37 @@ def test_grouped_convolutions_run_dense_on_block_diagonal_weights(eng):
         if optimize:
             assert all(r["kernel"] == "conv_i8_tc" for r in convs), [(r["id"], r["kernel"]) for r in convs]
     assert len(np.unique(want["c5"])) > 8
+
+
+@pytest.mark.parametrize("optimize", [False, True])
+@pytest.mark.parametrize("axis", ["f", "y", "b"])
+def test_concatenation_of_convolution_branches(eng, optimize, axis):
+    """Two quantised branches of different width joined by `concatenation` (src/gpu/concatenation_gpu.cpp: one copy per
+    input at its offset) and consumed by a further convolution; along features the joined tensor has 48 + 80 features,
+    so in the feature-innermost padded layout the second slice starts inside a 32-feature group."""
+    rng = np.random.default_rng(21)
+    s = topologies.Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.u8, cl.format.bfyx, cl.tensor(2, 32, 10, 9))
+    s.add(cl.input_layout("input", s.input_layout))
+
+    def conv(name, x, cin, cout, k, out_dt=dt.u8):
+        s.const(name + "_w", rng.integers(-127, 128, size=(cout, cin, k, k), dtype=np.int64).astype(np.int8))
+        s.const(name + "_b", rng.integers(-4096, 4097, size=cout, dtype=np.int64).astype(np.int32))
+        s.const(name + "_q", (rng.uniform(1.0, 3.0, size=cout) / (np.sqrt(cin * k * k) * 73.0 * 2.0)).astype(np.float32))
+        s.add(cl.convolution(name, x, name + "_w", name + "_b", name + "_q", output_data_type=out_dt, input_offset=(-(k // 2), -(k // 2)), with_activation=True))
+        return name
+    same = axis != "f"
+    a = conv("left", "input", 32, 48, 1)
+    b = conv("right", "input", 32, 48 if same else 80, 3)
+    ax = {"b": cl.concatenation_axis.along_b, "f": cl.concatenation_axis.along_f, "y": cl.concatenation_axis.along_y}[axis]
+    s.add(cl.concatenation("joined", [a, b], ax))
+    conv("head", "joined", 48 if same else 128, 64, 1, dt.i8)
+    s.outputs = ["joined", "head"]
+    x = _input(s)
+    want = oracle_net.run(s, {s.input_id: x})
+    net, got = _run(eng, s, x, optimize_data=optimize)
+    _compare(s, want, got)
+    assert want["joined"].shape[{"b": 0, "f": 1, "y": 2}[axis]] == (4 if axis == "b" else (128 if axis == "f" else 18))
+    assert len(np.unique(want["head"])) > 16

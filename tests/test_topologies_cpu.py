@@ -46,3 +46,32 @@ def test_mobilenet_v2_operation_count():
     spec = topologies.mobilenet_v2_int8(1)
     dw = [p for p in spec.prims if p.kind == "convolution" and p.args.get("groups", 1) > 4]
     assert len(dw) == 17 and all(spec.consts[p.args["weights"]].shape[1] == 1 for p in dw)
+
+
+def test_tuning_cache_reader_is_a_real_json_reader(tmp_path):
+    """The cache file has the reference's schema ({ "<compute units>": { "<hash>": ["kernel", index] } },
+    kernel_selector/core/auto_tuner.cpp:72-118).  Reformatting, other devices' sections in front of the wanted one, braces
+    inside strings and escapes must not lose entries; malformed input is an error, not an empty cache."""
+    import ctypes as C
+    from cldnn_b200 import abi
+    from cldnn_b200 import cldnn as cl
+    lib = cl.load_library()
+    lib.cldnn_host_last_error.restype = C.c_char_p if hasattr(lib, "cldnn_host_last_error") else None
+    n = C.c_size_t()
+
+    def check(text, units=148):
+        p = tmp_path / "cache.json"
+        p.write_text(text)
+        return lib.cldnn_host_tuning_cache_check(str(p).encode(), units, C.byref(n)), n.value
+
+    shipped = open(__import__("os").path.join(__import__("os").path.dirname(cl.__file__), "cache", "tuning_cache.json")).read()
+    st, count = check(shipped)
+    assert st == 0 and count > 100
+    tricky = '{"72":{"aa":["conv_ref",0]},\n\t"148" : { "k}1" : [ "conv_{i8}_tc" , 7 ],"k\\"2":["a\\u0041b",\n 3 ] } , "200": {}}'
+    assert check(tricky) == (0, 2)
+    assert check(tricky, 72) == (0, 1)
+    assert check(tricky, 5) == (0, 0)
+    assert check("") == (0, 0)
+    for bad in ('{"148": {"h": ["k", 1]', '{"148": {"h": ["k"]}}', '{"148": {"h": "k"}}', '[1, 2]', '{"148": {"h": ["k", 1]}} x', '{"148": {h: ["k", 1]}}'):
+        st, _ = check(bad)
+        assert st == abi.INVALID_ARG, bad
