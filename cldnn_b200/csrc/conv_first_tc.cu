@@ -536,11 +536,11 @@ static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     // pack the weights and build the table once, on the context's stream, before anything that is prepared here can run
     const int pack_blocks = (p.ofm * P.cores * (16 / es) + 255) / 256;
     if (half) {
-        B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin));
+        B200_CUDA(raise_smem_limit((const void*)firsttc::conv_first_tc_kernel<__half>, ctx->device, smem));
         firsttc::first_tc_pack<__half><<<pack_blocks, 256, 0, ctx->stream>>>((const __half*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset, p.ofm, p.ifm, p.kh, p.kw,
                                                                               P.cores, (__half*)a->scratch, (int4*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     } else {
-        B200_CUDA(cudaFuncSetAttribute(firsttc::conv_first_tc_kernel<uint8_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin));
+        B200_CUDA(raise_smem_limit((const void*)firsttc::conv_first_tc_kernel<uint8_t>, ctx->device, smem));
         firsttc::first_tc_pack<uint8_t><<<pack_blocks, 256, 0, ctx->stream>>>((const uint8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset, p.ofm, p.ifm, p.kh, p.kw,
                                                                                P.cores, (uint8_t*)a->scratch, (int4*)P.table, p.in.pf, p.in.py, p.in.px, p.dil_x, p.dil_y);
     }

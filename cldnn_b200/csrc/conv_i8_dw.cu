@@ -440,7 +440,9 @@ bool dwcol_ok(const cldnn_b200_conv_params& p)
            (int64_t)p.in.x * p.in.px < 0x7fffffffLL;
 }
 // tune 0: the column-walk kernel where it applies, 1: the 16-feature kernel
-int dw_tune_count(const void* vp) { return dwcol_ok(simplified_conv_params(*(const cldnn_b200_conv_params*)vp)) ? 2 : 1; }
+// 0 = automatic (the column-walk kernel where it applies, the 16-feature kernel otherwise), 1 = the 16-feature kernel,
+// 2 = the column-walk kernel by name: the tuner times the indices from 1 up, index 0 being the untuned default everywhere.
+int dw_tune_count(const void* vp) { return dwcol_ok(simplified_conv_params(*(const cldnn_b200_conv_params*)vp)) ? 3 : 1; }
 size_t dw_scratch(const void* vp)
 {
     const auto& p = *(const cldnn_b200_conv_params*)vp;
@@ -476,10 +478,9 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
         B200_CUDA(cudaGetLastError());
         const size_t smem = (size_t)taps_c * 4 + (size_t)p.groups * 8;
         if (smem > 48 * 1024) {
-            // the device maximum (less the kernels' few static bytes), never this shape's own size: the limit is shared by
-            // every prepared launch of the function
-            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin - 1024));
-            B200_CUDA(cudaFuncSetAttribute(conv_i8_dw16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin - 1024));
+            // the limit is shared by every prepared launch of the function on this device: it only ever grows
+            B200_CUDA(raise_smem_limit((const void*)conv_i8_dw16_kernel<true>, ctx->device, smem));
+            B200_CUDA(raise_smem_limit((const void*)conv_i8_dw16_kernel<false>, ctx->device, smem));
         }
         if (dwcol_ok(p) && p.tune != 1) {
             // strips of 14 output rows, shorter while the items would not fill the device
@@ -490,7 +491,7 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
             const int64_t col_items = per_row_strip * d.strips;
             if (col_items < 0x7fffffffLL) {
                 d.col_items = (uint32_t)col_items;
-                auto set_smem = [&](auto kern) { return smem > 48 * 1024 ? cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->prop.sharedMemPerBlockOptin - 1024) : cudaSuccess; };
+                auto set_smem = [&](auto kern) { return raise_smem_limit((const void*)kern, ctx->device, smem); };
                 B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 2>));
                 B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 2>));
                 int64_t cblocks = (col_items + 255) / 256; const int64_t ccap = (int64_t)ctx->prop.multiProcessorCount * 8;

@@ -434,12 +434,10 @@ static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     if (patch_bytes / 4 > kBuilders * kMaxPre) return fail(CLDNN_B200_UNSUPPORTED_SIZE, "conv_i8_first: the input patch of one tile is too large");
     smem = 128 + (size_t)2 * 128 * P.Kp + (size_t)P.ofm * P.Kp + ((patch_bytes + 15) & ~15) + sizeof(FirstAux);
     if (smem > (size_t)ctx->prop.sharedMemPerBlockOptin) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory");
-    // the limit is a property of the function on this device, shared by every prepared launch: always the device maximum,
-    // so that a later, smaller shape never lowers it under an earlier launch that is still alive
-    const int max_smem = (int)ctx->prop.sharedMemPerBlockOptin;
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
-    B200_CUDA(cudaFuncSetAttribute(conv_i8_first_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem));
+    // the limit is shared by every prepared launch of the function on this device: it only ever grows
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_kernel<1>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_kernel<2>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_kernel<3>, ctx->device, smem));
     // CTAs per SM: bounded by shared memory and by tensor memory (512 columns per SM)
     int per_sm = (int)(ctx->prop.sharedMemPerMultiprocessor / (smem + 1024));
     per_sm = std::min(per_sm, std::min(p.tune == 3 ? 3 : 2, (int)(512 / P.tmem_cols)));

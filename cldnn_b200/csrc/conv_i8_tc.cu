@@ -377,13 +377,16 @@ static bool load_driver_entry_points()
     return g_encode_tiled && g_encode_im2col;
 }
 
-struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; };
+struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; int epi_groups; };
 
 // tune index -> (addressing mode, feature tile).  0 = automatic choice.
 static const int kTuneBN[4] = {32, 64, 128, 256};
 // Indices 13..24 repeat 1..12 on the general kernel where the specialised one (conv_i8_tc_fast.cu) would be used;
-// 25..28 are the patch mode (resident weights, one activation patch per filter column) of the specialised kernel.
-static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4 + 4; }
+// 25..28 are the patch mode (resident weights, one activation patch per filter column) of the specialised kernel;
+// 29..40 and 41..44 repeat 1..12 and 25..28 on the specialised kernel with four epilogue warp groups instead of two
+// (16 epilogue warps per SM: for the layers whose time is the epilogue's instruction issue).
+constexpr int kTuneFourGroups = 28;
+static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4 + 4 + 3 * 4 + 4; }
 constexpr size_t kPatchWeightBytes = 72 * 1024;       // largest weight tensor the patch mode keeps resident
 
 static bool dense_byxf(const cldnn_b200_tensor& t)
@@ -482,6 +485,16 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
                            (int64_t)p.in.b * p.in.pb >= 131072;     // small tensors take the tiled path
     int tune = p.tune;
     int mode = -1, bn = 0;
+    pl.epi_groups = 2;
+    if (tune > kTuneFourGroups) {
+        pl.epi_groups = 4;
+        tune -= kTuneFourGroups;                                   // 1..12 as they are, 13..16 are the patch modes 25..28
+        if (tune > 12) tune += 12;
+        if (!lean_params(p)) return no("four epilogue groups exist on the specialised kernel only");
+    }
+    // every ring a group waits on (accumulators, staging tiles) must hold a multiple of the group count: a group then meets
+    // every phase of the barriers it waits on, which is what a parity wait needs.  256-feature tiles have two accumulators.
+    auto groups_fit = [&](int fbn) { return pl.epi_groups == 2 || fbn == 64 || fbn == 128; };
     if (tune > 24) { mode = A_PATCH; bn = kTuneBN[(tune - 25) % 4]; }
     else {
         if (tune > 12) tune -= 12;
@@ -507,6 +520,7 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
     if (mode == A_TILED && !tiled_ok) return no("tiled addressing needs stride 1 or a pointwise filter");
     if (mode == A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded (or tensor below 128 KiB)");
     if (bn == 0) bn = p.ofm > 128 ? 256 : (p.ofm > 64 ? 128 : (p.ofm > 32 ? 64 : 32));
+    if (!groups_fit(bn)) return no("four epilogue groups need feature tiles of 64 or 128 (eight or four accumulators)");
     if (mode == A_PATCH) { if (const char* m = patch_why(bn)) return no(m); }
     // 256-feature tiles with a fused residual: three 32 KiB staging tiles + three operand stages need 24 KiB stages;
     // worth it unless the reduction is long (>= 4 chunks of 128 channels), where fewer, larger stages win
@@ -631,7 +645,9 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     const int out_kind = out_u8 ? 0 : ((p.fused_eltw ? p.eltw_act : p.act) == CLDNN_B200_ACT_RELU ? 2 : 1);
     P.fast_variant = (out_kind << 1) | ((p.fused_eltw && p.act == CLDNN_B200_ACT_RELU) ? 1 : 0) | (P.mul_oqf ? 8 : 0);
     P.acc_bound = (float)p.kh * (float)p.kw * (float)p.ifm * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
+    P.epi_groups = pl.epi_groups;
     const bool use_fast = (p.tune <= 12 || p.tune > 24) && tc_fast_eligible(P);
+    if (pl.epi_groups > 2 && !use_fast) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: four epilogue groups exist on the specialised kernel only");
 
     const size_t aux_bytes = use_fast ? tc_fast_aux_bytes() : sizeof(TcSmemAux);
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
@@ -649,6 +665,14 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
         // the store of tile t has drained (measured: 108 -> 97 us on the 64 -> 256 layer of ResNet-50's first stage)
         P.nstg = 3;
         staging_total = (size_t)P.nstg * kBM * pl.bn;
+    }
+    // Few, large operand stages (the patch mode's three patches per stage) leave the loads of a tile in flight for only one
+    // tile's worth of tensor-core work; with fewer staging tiles than accumulators another stage fits, and the producer runs a
+    // tile further ahead of the load latency.  Four staging tiles keep both group counts a divisor of the ring.
+    if (use_fast && P.staged && P.nstg == P.nbuf && P.nbuf > 4) {
+        auto stages_with = [&](size_t staging) { return max_smem > 1024 + aux_bytes + staging + resident ? (max_smem - 1024 - aux_bytes - staging - resident) / stage_bytes : 0; };
+        const size_t fewer = (size_t)4 * kBM * pl.bn;
+        if (stages_with(staging_total) < 4 && stages_with(fewer) > stages_with(staging_total)) { P.nstg = 4; staging_total = fewer; }
     }
     if (max_smem < 1024 + aux_bytes + staging_total + resident + 2 * stage_bytes) {
         if (patch) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_tc: not enough shared memory for the patch mode");

@@ -48,6 +48,7 @@ struct alignas(64) TcParams {
     int32_t ring_bytes, b_total_bytes;   // operand area: activation ring (+ weight ring or resident weights)
     int32_t patch_alloc;                 // bytes reserved per filter column's patch inside a stage (a stage holds the kw patches of one channel chunk)
     int32_t fast_variant;                // conv_i8_tc_fast: (output kind << 1) | ReLU before the residual sum
+    int32_t epi_groups;                  // conv_i8_tc_fast: epilogue warp groups per CTA, 2 or 4
     float acc_bound;                     // K * max|activation| * 128: no accumulator can exceed it in magnitude
     // output / residual addressing for the direct path, in elements
     int64_t out_px, out_py, out_pb, out_off;

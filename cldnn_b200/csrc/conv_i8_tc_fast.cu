@@ -34,9 +34,9 @@
 
 namespace b200 {
 
-constexpr int kFastThreads = 384;          // warp 0 operand loads, 1 MMA issue, 2 TMA stores, 3 residual loads, 4..11 epilogue
-constexpr int kFastEpiWarp0 = 4;
-constexpr int kGroups = 2;                 // epilogue warp groups, alternate tiles
+constexpr int kFastEpiWarp0 = 4;            // warp 0 operand loads, 1 MMA issue, 2 TMA stores, 3 residual loads, 4.. epilogue
+constexpr int kMaxGroups = 4;               // epilogue warp groups of four warps each: two or four per CTA (template parameter)
+constexpr int fast_threads(int groups) { return 128 + 128 * groups; }
 constexpr int kMaxStg = 8;                 // staging tiles
 
 struct FastAux {
@@ -51,9 +51,9 @@ struct FastAux {
     uint64_t b_full;                       // patch mode: the resident weights have landed
     uint32_t tmem_base;
     uint32_t abort;
-    uint32_t wide[kGroups][4];             // per epilogue warp: a feature of the current tile may leave the integer-safe range
-    alignas(16) int32_t bias_i[kGroups][kMaxBN];
-    alignas(16) float quant[kGroups][kMaxBN];
+    uint32_t wide[kMaxGroups][4];          // per epilogue warp: a feature of the current tile may leave the integer-safe range
+    alignas(16) int32_t bias_i[kMaxGroups][kMaxBN];
+    alignas(16) float quant[kMaxGroups][kMaxBN];
 };
 
 size_t tc_fast_aux_bytes() { return sizeof(FastAux); }
@@ -136,12 +136,46 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
     }
 }
 
+// The same quadrant with one register buffer: used by the four-group variant, where 16 epilogue warps per SM hide the
+// latency of the tensor-memory load between them and the register budget is 102 per thread.
+template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
+__device__ __forceinline__ void fast_tile_single(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
+                                                 uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f)
+{
+    const int32_t* bias = aux->bias_i[group];
+    const float* quant = aux->quant[group];
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        uint4 *p0, *p1;
+        tmem_ld_32x32(t_row + (uint32_t)c0, r);
+        fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
+        tmem_ld_wait();
+        if (c0 + 32 >= BN) {
+            // the accumulator has been read out: the MMA issuer may reuse it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty_bar);
+        }
+        fast_chunk32<kFused, kRelu1, kOut, kOqf>(r, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg, oqf);
+    }
+}
+
 // The variants with a uniform O_QF stay out of line, so that the common ones keep their registers and code layout.
-template <int BN, bool kFused, int kOut>
+template <int BN, bool kFused, int kOut, int G>
 __device__ __noinline__ void fast_tile_oqf(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
                                            uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf)
 {
-    fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf);
+    if (G > 2) fast_tile_single<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf);
+    else fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf);
+}
+// two register buffers with two groups, one with four
+template <int BN, bool kFused, bool kRelu1, int kOut, int G>
+__device__ __forceinline__ void fast_tile_any(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
+                                              uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+{
+    if (G > 2) fast_tile_single<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg);
+    else fast_tile<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg);
 }
 
 // The same tile in float arithmetic, element by element (fused residual only):
@@ -215,10 +249,11 @@ struct TileWalk {
     }
 };
 
-template <int BN, bool kFused>
-__global__ void __launch_bounds__(kFastThreads, 1)
+template <int BN, bool kFused, int G>
+__global__ void __launch_bounds__(fast_threads(G), 1)
 conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
 {
+    constexpr int kGroups = G;                                          // epilogue warp groups, taking tiles in turn
     constexpr int NBUF = BN >= 256 ? 2 : (BN >= 128 ? 4 : 8);         // all 512 columns of tensor memory
     constexpr int CW = BN < 128 ? BN : 128;
     constexpr int COLB = BN / CW;
@@ -501,27 +536,27 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             else if (with_oqf) {
                 // u8 or plain s8 output, no ReLU between convolution and residual sum (the host admits nothing else here)
                 if (kFused) {
-                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
-                    else fast_tile_oqf<BN, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    else fast_tile_oqf<BN, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
                 } else {
-                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
-                    else fast_tile_oqf<BN, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    else fast_tile_oqf<BN, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
                 }
             }
             else if (kFused) {
                 switch (variant) {
-                    case 0: fast_tile<BN, true, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 1: fast_tile<BN, true, true, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 2: fast_tile<BN, true, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 3: fast_tile<BN, true, true, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 4: fast_tile<BN, true, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    default: fast_tile<BN, true, true, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 0: fast_tile_any<BN, true, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 1: fast_tile_any<BN, true, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 2: fast_tile_any<BN, true, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 3: fast_tile_any<BN, true, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 4: fast_tile_any<BN, true, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    default: fast_tile_any<BN, true, true, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
                 }
             } else {
                 switch (variant >> 1) {
-                    case 0: fast_tile<BN, false, false, 0>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 1: fast_tile<BN, false, false, 1>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    default: fast_tile<BN, false, false, 2>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 0: fast_tile_any<BN, false, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 1: fast_tile_any<BN, false, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    default: fast_tile_any<BN, false, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
                 }
             }
             fence_async_smem();
@@ -552,15 +587,17 @@ bool tc_fast_eligible(const TcParams& P)
     return true;
 }
 
-static const void* fast_kernel_of(const TcParams& P)
+template <int G>
+static const void* fast_kernel_of_g(const TcParams& P)
 {
     const bool f = P.epi.fused_eltw != 0;
     switch (P.bn) {
-    case 64:  return f ? (const void*)conv_i8_tc_fast_kernel<64, true> : (const void*)conv_i8_tc_fast_kernel<64, false>;
-    case 128: return f ? (const void*)conv_i8_tc_fast_kernel<128, true> : (const void*)conv_i8_tc_fast_kernel<128, false>;
-    default:  return f ? (const void*)conv_i8_tc_fast_kernel<256, true> : (const void*)conv_i8_tc_fast_kernel<256, false>;
+    case 64:  return f ? (const void*)conv_i8_tc_fast_kernel<64, true, G> : (const void*)conv_i8_tc_fast_kernel<64, false, G>;
+    case 128: return f ? (const void*)conv_i8_tc_fast_kernel<128, true, G> : (const void*)conv_i8_tc_fast_kernel<128, false, G>;
+    default:  return f ? (const void*)conv_i8_tc_fast_kernel<256, true, G> : (const void*)conv_i8_tc_fast_kernel<256, false, G>;
     }
 }
+static const void* fast_kernel_of(const TcParams& P) { return P.epi_groups > 2 ? fast_kernel_of_g<4>(P) : fast_kernel_of_g<2>(P); }
 
 cudaError_t tc_fast_configure(const TcParams& P, int max_smem)
 {
@@ -570,7 +607,7 @@ cudaError_t tc_fast_configure(const TcParams& P, int max_smem)
 cudaError_t tc_fast_launch(const TcParams& P, int grid, size_t smem_bytes, cudaStream_t stream)
 {
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(kFastThreads); cfg.dynamicSmemBytes = smem_bytes; cfg.stream = stream;
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((unsigned)fast_threads(P.epi_groups > 2 ? 4 : 2)); cfg.dynamicSmemBytes = smem_bytes; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;

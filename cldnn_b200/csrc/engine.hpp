@@ -48,6 +48,11 @@ struct cldnn_b200_graph_impl {
 
 namespace b200 {
 
+// Raises the dynamic shared-memory limit of kernel `fn` on `device` (which must be current) to at least `bytes`.  The limit
+// is a property of (function, device) shared by every prepared launch, so it only ever grows: a later, smaller shape must
+// not lower it under an earlier launch that is still alive.
+cudaError_t raise_smem_limit(const void* fn, int device, size_t bytes);
+
 struct KernelDef {
     const char* name;
     size_t params_size;
@@ -73,6 +78,7 @@ extern const KernelDef kdef_lrn_f16_byxf;
 extern const KernelDef kdef_fc_ref;
 extern const KernelDef kdef_softmax;
 extern const KernelDef kdef_eltwise_ref;
+extern const KernelDef kdef_eltwise_byxf;
 extern const KernelDef kdef_reorder_ref;
 extern const KernelDef kdef_lrn_ref;
 extern const KernelDef kdef_activation_ref;

@@ -654,6 +654,107 @@ static int32_t eltwise_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const c
 const KernelDef kdef_eltwise_ref = {"eltwise_ref", sizeof(cldnn_b200_eltwise_params), eltwise_supports, one_tune, nullptr, eltwise_prepare};
 
 // ---------------------------------------------------------------------------------
+// eltwise over equal dense layouts, 16 bytes per thread (the role of eltwise_simple_vload8.cl among the reference's kernels):
+// both inputs and the output have the same sizes, pitches and element size, so the tensors are walked as flat arrays.
+// 8-bit: the requantising form of generic_eltwise_ref.cl (integer operation, * O_QF or calibrations[f], round, saturate to
+// char, activation, saturating store); fp16: the floating form.  Activations none / ReLU; features innermost when the
+// factors are per feature.  Same results as eltwise_ref, element for element.
+// ---------------------------------------------------------------------------------
+template <bool kHalf>
+__global__ void __launch_bounds__(256)
+eltwise_vec_kernel(const __grid_constant__ cldnn_b200_eltwise_params p, const uint4* __restrict__ in0, const uint4* __restrict__ in1,
+                   const float* __restrict__ calib, uint4* __restrict__ out, int64_t vectors, int32_t stored_f)
+{
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < vectors; v += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 a = in0[v], c = in1[v];
+        uint4 r;
+        if (kHalf) {
+            const __half2* ah = reinterpret_cast<const __half2*>(&a); const __half2* ch = reinterpret_cast<const __half2*>(&c);
+            __half2* rh = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 x = __half22float2(ah[i]), y = __half22float2(ch[i]);
+                float2 z;
+                switch (p.mode) {
+                case CLDNN_B200_ELTW_SUB: z = make_float2(__fsub_rn(x.x, y.x), __fsub_rn(x.y, y.y)); break;
+                case CLDNN_B200_ELTW_MAX: z = make_float2(fmaxf(x.x, y.x), fmaxf(x.y, y.y)); break;
+                case CLDNN_B200_ELTW_MIN: z = make_float2(fminf(x.x, y.x), fminf(x.y, y.y)); break;
+                case CLDNN_B200_ELTW_PROD: z = make_float2(__fmul_rn(x.x, y.x), __fmul_rn(x.y, y.y)); break;
+                default: z = make_float2(__fadd_rn(x.x, y.x), __fadd_rn(x.y, y.y)); break;
+                }
+                if (p.act == CLDNN_B200_ACT_RELU) { z.x = fmaxf(0.0f, z.x); z.y = fmaxf(0.0f, z.y); }
+                rh[i] = __floats2half2_rn(z.x, z.y);
+            }
+        } else {
+            const uint8_t* ab = reinterpret_cast<const uint8_t*>(&a); const uint8_t* cb = reinterpret_cast<const uint8_t*>(&c);
+            uint8_t* rb = reinterpret_cast<uint8_t*>(&r);
+            const int f0 = p.calibration ? (int)((v * 16) % stored_f) : 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int32_t x = p.in0.dtype == CLDNN_B200_U8 ? (int32_t)ab[i] : (int32_t)(int8_t)ab[i];
+                const int32_t y = p.in1.dtype == CLDNN_B200_U8 ? (int32_t)cb[i] : (int32_t)(int8_t)cb[i];
+                int32_t z;
+                switch (p.mode) {
+                case CLDNN_B200_ELTW_SUB: z = x - y; break;
+                case CLDNN_B200_ELTW_MAX: z = max(x, y); break;
+                case CLDNN_B200_ELTW_MIN: z = min(x, y); break;
+                case CLDNN_B200_ELTW_PROD: z = x * y; break;
+                default: z = x + y; break;
+                }
+                // a feature lane beyond the tensor's feature count (padding of the layout) has no factor: it stays what the operation gives on zeros
+                const float factor = p.calibration ? (f0 + i < p.out.f ? calib[f0 + i] : 1.0f) : p.o_qf;
+                z = sat_i32_from_float(round_half_away(__fmul_rn((float)z, factor)), -128, 127);
+                if (p.act == CLDNN_B200_ACT_RELU) z = max(z, 0);
+                rb[i] = p.out.dtype == CLDNN_B200_U8 ? (uint8_t)max(z, 0) : (uint8_t)(int8_t)z;
+            }
+        }
+        out[v] = r;
+    }
+}
+static bool same_dense(const cldnn_b200_tensor& a, const cldnn_b200_tensor& b)
+{
+    return a.b == b.b && a.f == b.f && a.y == b.y && a.x == b.x && a.pb == b.pb && a.pf == b.pf && a.py == b.py && a.px == b.px && a.offset == 0 && b.offset == 0;
+}
+// bytes of the tensor when it is one dense block (no padding between rows, images): 0 otherwise
+static int64_t dense_elems(const cldnn_b200_tensor& t)
+{
+    if (t.pf == 1) return (t.py == t.px * t.x && t.pb == t.py * t.y && t.px >= t.f) ? t.pb * t.b : 0;        // byxf, features possibly padded
+    if (t.px == 1) return (t.py == t.x && t.pf == t.py * t.y && t.pb == t.pf * t.f) ? t.pb * t.b : 0;          // bfyx
+    return 0;
+}
+static bool eltwise_vec_supports(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_eltwise_params*)vp;
+    if (p.stride_x0 != 1 || p.stride_y0 != 1 || p.stride_x1 != 1 || p.stride_y1 != 1) return false;
+    if (!same_dense(p.in0, p.out) || !same_dense(p.in1, p.out)) return false;
+    if (p.act != CLDNN_B200_ACT_NONE && p.act != CLDNN_B200_ACT_RELU) return false;
+    const bool half = p.in0.dtype == CLDNN_B200_F16 && p.in1.dtype == CLDNN_B200_F16 && p.out.dtype == CLDNN_B200_F16 && !p.quantization;
+    const bool bytes = is_int8(p.in0.dtype) && is_int8(p.in1.dtype) && is_int8(p.out.dtype) && p.quantization;
+    if (!half && !bytes) return false;
+    const int64_t n = dense_elems(p.out);
+    if (n <= 0 || (n * (half ? 2 : 1)) % 16) return false;
+    if (bytes && p.calibration && (p.out.pf != 1 || p.out.px % 16)) return false;          // per-feature factors: 16 consecutive features per vector
+    return true;
+}
+static int32_t eltwise_vec_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_eltwise_params p = *(const cldnn_b200_eltwise_params*)vp;
+    if (!eltwise_vec_supports(vp)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "eltwise_byxf: equal dense layouts, strides 1, 8-bit requantising or fp16 form, NONE / ReLU only");
+    if (!a->input0 || !a->input1 || !a->output) return fail(CLDNN_B200_INVALID_ARG, "eltwise_byxf: two inputs and an output are required");
+    if (p.quantization && p.calibration && !a->output_calibration_factors) return fail(CLDNN_B200_INVALID_ARG, "eltwise_byxf: calibration factors missing");
+    if (((uintptr_t)a->input0 | (uintptr_t)a->input1 | (uintptr_t)a->output) & 15) return fail(CLDNN_B200_INVALID_ARG, "eltwise_byxf: buffers must be 16-byte aligned");
+    const bool half = p.in0.dtype == CLDNN_B200_F16;
+    const int64_t vectors = dense_elems(p.out) * (half ? 2 : 1) / 16;
+    const uint4* i0 = (const uint4*)a->input0; const uint4* i1 = (const uint4*)a->input1; uint4* o = (uint4*)a->output; const float* c = a->output_calibration_factors;
+    const int32_t sf = (int32_t)(p.out.pf == 1 ? p.out.px : 1);
+    const int grid = grid_for(vectors, 256, ctx);
+    if (half) out->fn = [=](cudaStream_t s) { eltwise_vec_kernel<true><<<grid, 256, 0, s>>>(p, i0, i1, c, o, vectors, sf); return cudaGetLastError(); };
+    else out->fn = [=](cudaStream_t s) { eltwise_vec_kernel<false><<<grid, 256, 0, s>>>(p, i0, i1, c, o, vectors, sf); return cudaGetLastError(); };
+    return CLDNN_B200_SUCCESS;
+}
+const KernelDef kdef_eltwise_byxf = {"eltwise_byxf", sizeof(cldnn_b200_eltwise_params), eltwise_vec_supports, one_tune, nullptr, eltwise_vec_prepare};
+
+// ---------------------------------------------------------------------------------
 // reorder (cl_kernels/reorder_data.cl:72-128).  Threads walk the destination in
 // its own memory order so writes coalesce; a destination feature beyond the
 // source's feature count is written as zero (feature padding of the new layout).

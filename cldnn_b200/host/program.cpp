@@ -318,7 +318,7 @@ public:
     void allocate_and_prepare();
     void prepare_kernel(node* n);
     void pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t params_size,
-                     const cldnn_b200_args& args, const std::function<void(int)>& set_tune);
+                     const cldnn_b200_args& args, const std::function<void(int)>& set_tune, bool time_all = false);
     memory pack_conv_weights(node* n, int32_t stored_ifm, int32_t groups = 1);
     void load_cache(); void save_cache();
     void execute();
@@ -751,8 +751,10 @@ void network_impl::save_cache()
 // kernel_selector_base::GetNaiveBestKernel / GetAutoTuneBestKernel (kernel_selector/core/kernel_selector.cpp:80-280):
 // candidates are tried in priority order and the first whose Validate() accepts the constants wins, unless tuning is on,
 // in which case every (kernel, tuning variant) is timed on the device and the fastest is kept and cached.
+// `time_all`: the candidates are alternatives of equal standing (direct and Winograd convolution), all of them are timed;
+// otherwise later candidates are fallbacks that are only reached when the earlier ones refuse the constants.
 void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t psize,
-                               const cldnn_b200_args& args, const std::function<void(int)>& set_tune)
+                               const cldnn_b200_args& args, const std::function<void(int)>& set_tune, bool time_all)
 {
     if (!opts.force_kernel.empty()) {                               // "<primitive id>=<kernel>[:tune],..."
         std::stringstream ss(opts.force_kernel); std::string item;
@@ -767,7 +769,7 @@ void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidat
     }
     set_tune(0);
     // the key carries the generation of the kernel set: timings taken on older kernels must not be reused
-    const std::string hash = fnv1a_hex(params, psize, n->p.type + "#g2");
+    const std::string hash = fnv1a_hex(params, psize, n->p.type + "#g3");
     if (opts.tuning != tuning_mode::tuning_disabled) {
         auto it = tuning_cache.find(hash);
         if (it != tuning_cache.end()) {
@@ -800,7 +802,7 @@ void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidat
                 cldnn_b200_prepared_destroy(pr);
                 if (st == CLDNN_B200_SUCCESS && ns < best_ns) { best_ns = ns; best_k = cand; best_t = t; }
             }
-            if (!best_k.empty()) break;                              // a preferred kernel took the job: the fallback is not timed
+            if (!best_k.empty() && !time_all) break;                 // a preferred kernel took the job: the fallback is not timed
         }
         if (!best_k.empty()) {
             n->kernel = best_k; n->tune = best_t; set_tune(best_t);
@@ -860,8 +862,8 @@ void network_impl::prepare_kernel(node* n)
     if (n->ec) a.eltw_output_calibration_factors = (const float*)n->ec->mem.device_ptr();
     for (node* f : {n->wq, n->oc, n->ec}) if (f && f->out.data_type != data_types::f32) throw error(p.id + ": quantization / calibration factors must be f32", CLDNN_B200_INVALID_ARG);
 
-    auto finish = [&](const std::vector<std::string>& cands, void* params, size_t size, const std::function<void(int)>& set_tune) {
-        pick_kernel(n, cands, params, size, a, set_tune);
+    auto finish = [&](const std::vector<std::string>& cands, void* params, size_t size, const std::function<void(int)>& set_tune, bool time_all = false) {
+        pick_kernel(n, cands, params, size, a, set_tune, time_all);
         check(cldnn_b200_prepare(eng->kernel(n->kernel), params, size, &a, &n->prepared), p.id + " (" + n->kernel + ")");
     };
 
@@ -968,7 +970,30 @@ void network_impl::prepare_kernel(node* n)
             int32_t yes = 0;
             if (cldnn_b200_kernel_supports(eng->kernel(tc_kernel), &tp, sizeof(tp), &yes) == CLDNN_B200_SUCCESS && yes) {
                 a = ta; cp = tp;
-                finish({tc_kernel}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
+                // Winograd F(2x2, 3x3) beside the direct form, behind a gate modelled on should_use_winograd_2x3_s1
+                // (src/layout_optimizer.cpp:34-53): 3x3 stride-1 undilated ungrouped fp16 convolutions whose feature counts are
+                // multiples of 64, maps of at least 8x8, an input that is neither tiny nor so large that the transformed
+                // operands (16/4 x input + 16/4 x output, in a workspace) get out of hand.  Where the reference rewrites the graph
+                // (reorder_inputs.cpp:179-277) the two forms are alternatives of one primitive here: with tuning on both are timed
+                // and the faster one is kept; without tuning the direct form runs.
+                std::vector<std::string> cands = {tc_kernel};
+                int32_t wino_yes = 0; size_t wino_bytes = 0;
+                const int64_t in_count = (int64_t)in.size.batch * in.size.feature * in.size.x * in.size.y;
+                const bool gate = half_tc && !fc && t == "convolution" && cp.groups == 1 && w.size.x == 3 && w.size.y == 3 && cp.stride_x == 1 && cp.stride_y == 1 &&
+                                  cp.dil_x == 1 && cp.dil_y == 1 && in.size.feature % 64 == 0 && w.size.batch % 64 == 0 && in.size.x >= 8 && in.size.y >= 8 &&
+                                  in_count >= 50000;
+                if (gate && cldnn_b200_kernel_supports(eng->kernel("conv_f16_winograd"), &cp, sizeof(cp), &wino_yes) == CLDNN_B200_SUCCESS && wino_yes &&
+                    cldnn_b200_kernel_scratch_bytes(eng->kernel("conv_f16_winograd"), &cp, sizeof(cp), &wino_bytes) == CLDNN_B200_SUCCESS &&
+                    wino_bytes && wino_bytes <= ((size_t)1 << 31)) {
+                    n->scratch = new_block(eng, wino_bytes);
+                    a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
+                    cands.push_back("conv_f16_winograd");
+                }
+                finish(cands, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; }, cands.size() > 1);
+                if (n->kernel != "conv_f16_winograd" && n->scratch) {      // the direct form won: the workspace goes back
+                    // (the prepared launch of the direct kernel never looks at the scratch pointer)
+                    n->scratch.reset();
+                }
                 return;
             }
             n->packed_weights = memory();
@@ -1018,7 +1043,7 @@ void network_impl::prepare_kernel(node* n)
         ep.quantization = p.eltw_quantized ? 1 : 0; ep.calibration = n->oc ? 1 : 0; ep.o_qf = p.output_quantization_factor;
         ep.act = n->act != CLDNN_B200_ACT_NONE ? n->act : act_from_slope(p.with_activation, p.activation_negative_slope, ep.act_m);
         if (n->act != CLDNN_B200_ACT_NONE) { ep.act_m = n->act_m; ep.act_n = n->act_n; }
-        finish({"eltwise_ref"}, &ep, sizeof(ep), [](int) {});
+        finish({"eltwise_byxf", "eltwise_ref"}, &ep, sizeof(ep), [](int) {});
         return;
     }
     if (t == "reorder") {

@@ -140,7 +140,8 @@ def test_conv_i8_tc_fast_variants(eng, name, wide):
     want = cases.run_oracle(case)
     n = case.out_elems
     assert len(np.unique(want[:n])) > 64
-    for tune in (0, 10, 11, 12, 7):   # automatic, tiled box with 64 / 128 / 256 features per tile, TMA im2col with 128
+    # automatic, tiled box with 64 / 128 / 256 features per tile, TMA im2col with 128, then the same with four epilogue groups
+    for tune in (0, 10, 11, 12, 7, 38, 39, 35):
         p = cases.copy_params(case.p)
         p.tune = tune
         assert k.supports(p)
@@ -170,7 +171,8 @@ def test_conv_i8_tc_requantised_ragged_features(eng, name, features):
     n = case.out_elems
     assert len(np.unique(want[:n])) > 32
     ran = 0
-    for tune in (0, 2, 3, 4, 10, 11, 7, 15):     # automatic; flat with 64 / 128 / 256 features per tile; tiled 64 / 128; im2col 128; general kernel
+    # automatic; flat with 64 / 128 / 256 features per tile; tiled 64 / 128; im2col 128; general kernel; four epilogue groups
+    for tune in (0, 2, 3, 4, 10, 11, 7, 15, 30, 31, 39):
         p = cases.copy_params(case.p)
         p.tune = tune
         if not k.supports(p):
@@ -191,7 +193,7 @@ def test_conv_i8_tc_requantised_3x3_and_wide(eng):
                 case.quant[70] = 0.5
             want = cases.run_oracle(case)
             n = case.out_elems
-            for tune in (0, 10, 11, 6, 26):
+            for tune in (0, 10, 11, 6, 26, 38, 42):
                 p = cases.copy_params(case.p)
                 p.tune = tune
                 if not k.supports(p):
@@ -223,6 +225,8 @@ def test_conv_i8_first_matches_oracle(eng, name, variant):
     want = _exact(eng, case, "conv_i8_first")
     assert (want != 0).any()
     _exact(eng, case, "conv_i8_first", tune=1)       # one CTA per SM, double-buffered epilogue
+    _exact(eng, case, "conv_i8_first", tune=2)       # as many CTAs per SM as fit, at most two
+    _exact(eng, case, "conv_i8_first", tune=3)       # up to three CTAs per SM
 
 
 def test_conv_i8_first_requantised(eng):
@@ -236,7 +240,8 @@ def test_conv_i8_first_requantised(eng):
             want = _exact(eng, case, kernel)
             assert len(np.unique(want[:case.out_elems])) > 16
             if kernel == "conv_i8_first":
-                _exact(eng, case, kernel, tune=1)
+                for tune in (1, 2, 3):
+                    _exact(eng, case, kernel, tune=tune)
 
 
 def test_conv_i8_first_plain_variants(eng):
@@ -249,7 +254,7 @@ def test_conv_i8_first_plain_variants(eng):
                                         scale_lo=2.0 ** -12, scale_hi=2.0 ** -10, **geom)
             if wide:
                 case.quant[5] = 900.0
-            for tune in (0, 1):
+            for tune in (0, 1, 3):
                 _exact(eng, case, "conv_i8_first", tune=tune)
 
 
@@ -316,8 +321,8 @@ def test_conv_i8_dw_matches_oracle(eng, name, variant):
                                     scale_lo=2.0 ** -11, scale_hi=2.0 ** -9, **kw)
     k = eng.kernel("conv_i8_dw")
     assert k.supports(case.p)
-    # tune 0: the column-walk kernel for 3x3 filters (the 16-feature kernel otherwise), tune 1: the 16-feature kernel
-    assert k.tune_count(case.p) == (2 if kw.get("kh", 3) == 3 else 1)
+    # tune 0 (and 2): the column-walk kernel for 3x3 filters (the 16-feature kernel otherwise), tune 1: the 16-feature kernel
+    assert k.tune_count(case.p) == (3 if kw.get("kh", 3) == 3 else 1)
     for tune in range(k.tune_count(case.p)):
         case.p.tune = tune
         want = _exact(eng, case, "conv_i8_dw")

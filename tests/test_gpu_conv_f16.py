@@ -112,20 +112,22 @@ WINOGRAD = {
 
 @pytest.mark.parametrize("name", sorted(WINOGRAD))
 def test_conv_f16_winograd_matches_oracle(eng, name):
-    """Winograd F(2x2, 3x3) against the direct-form oracle: 1e-2 relative, judged absolutely below a quarter of the output
-    scale -- the transformed operands live in fp16 (as in the reference), so small outputs that are differences of large
-    terms carry an absolute error of about 1e-3 of the scale whatever their own size."""
+    """Winograd F(2x2, 3x3) against the direct-form oracle.  The reference pins nothing here (it has no Winograd test), so the
+    bar is this repository's own: 1e-2 relative to each value, and for values below a tenth of the output scale an absolute
+    1e-3 of the scale.  Measured on these geometries the largest absolute error is 5.4e-4 .. 6.7e-4 of the scale -- the final
+    rounding to fp16 at the top of the range, as for the direct kernel; the fp16 transforms add nothing visible beyond it --
+    and 1.9e-3 relative among values above a quarter of the scale."""
     case = cases.make_conv_case(41, **WINOGRAD[name], **F16)
     k = eng.kernel("conv_f16_winograd")
     assert k.supports(case.p)
-    _close(eng, case, "conv_f16_winograd", floor=0.25)
+    _close(eng, case, "conv_f16_winograd", floor=0.1)
 
 
 def test_conv_f16_winograd_epilogue_and_refusals(eng):
     k = eng.kernel("conv_f16_winograd")
     for extra in (dict(bias="none"), dict(act=abi.ACT_NONE), dict(act=abi.ACT_CLAMP)):
         kw = dict(F16); kw.update(extra)
-        _close(eng, cases.make_conv_case(42, N=2, C=32, K=64, H=14, W=14, **kw), "conv_f16_winograd", floor=0.25)
+        _close(eng, cases.make_conv_case(42, N=2, C=32, K=64, H=14, W=14, **kw), "conv_f16_winograd", floor=0.1)
     assert not k.supports(cases.make_conv_case(43, N=1, C=32, K=32, H=8, W=8, stride=2, **F16).p)
     assert not k.supports(cases.make_conv_case(43, N=1, C=32, K=32, H=8, W=8, kh=1, kw=1, pad=0, **F16).p)
     assert not k.supports(cases.make_conv_case(43, N=1, C=32, K=32, H=8, W=8).p)            # 8-bit

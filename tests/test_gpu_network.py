@@ -317,3 +317,60 @@ def test_concatenation_of_convolution_branches(eng, optimize, axis):
     _compare(s, want, got)
     assert want["joined"].shape[{"b": 0, "f": 1, "y": 2}[axis]] == (4 if axis == "b" else (128 if axis == "f" else 18))
     assert len(np.unique(want["head"])) > 16
+
+
+def _single_fp16_conv(batch, cin, cout, size, seed=31):
+    rng = np.random.default_rng(seed)
+    s = topologies.Spec()
+    dt = cl.data_types
+    s.input_id = "input"
+    s.input_layout = cl.layout(dt.f16, cl.format.bfyx, cl.tensor(batch, cin, size, size))
+    s.add(cl.input_layout("input", s.input_layout))
+    s.const("w", (rng.standard_normal((cout, cin, 3, 3)) * np.sqrt(2.0 / (cin * 9))).astype(np.float16))
+    s.const("b", (rng.standard_normal(cout) * 0.05).astype(np.float16))
+    s.add(cl.convolution("conv", "input", "w", "b", input_offset=(-1, -1), with_activation=True))
+    s.outputs = ["conv"]
+    x = rng.standard_normal((batch, cin, size, size)).astype(np.float16)
+    return s, x
+
+
+def _winograd_close(got, want):
+    """Winograd F(2x2, 3x3) against the direct-form oracle: 1e-2 relative to each value, an absolute 1e-3 of the output scale
+    for the small ones (measured: at most 6.7e-4 of the scale, the final rounding to fp16 at the top of the range)."""
+    w, g = want.astype(np.float32), got.astype(np.float32)
+    scale = float(np.abs(w).max())
+    err = np.abs(g - w)
+    bad = err > np.maximum(1e-2 * np.abs(w), 1e-3 * scale)
+    assert not bad.any(), "%d of %d values; worst %.4g on scale %.4g" % (int(bad.sum()), w.size, float(err.max()), scale)
+    return float(err.max() / scale)
+
+
+def test_winograd_is_a_selectable_alternative_of_the_fp16_convolution(eng):
+    """The gate modelled on should_use_winograd_2x3_s1 (src/layout_optimizer.cpp:34-53) admits this layer, so
+    conv_f16_winograd is a candidate of the primitive: forced, it runs inside a network and agrees with the oracle; a layer the
+    gate refuses (48 features) never gets it."""
+    s, x = _single_fp16_conv(4, 64, 64, 16)
+    want = oracle_net.run(s, {s.input_id: x})
+    net, got = _run(eng, s, x, optimize_data=True, force_kernel="conv=conv_f16_winograd")
+    info = {r["id"]: r for r in net.primitives_info()}
+    assert info["conv"]["kernel"] == "conv_f16_winograd"
+    _winograd_close(got["conv"], want["conv"])
+    s2, x2 = _single_fp16_conv(4, 48, 64, 16)
+    with pytest.raises(cl.error):
+        _run(eng, s2, x2, optimize_data=True, force_kernel="conv=conv_f16_winograd")
+
+
+def test_tuner_times_winograd_against_the_direct_form_on_a_vgg_layer(eng):
+    """VGG16's 512 -> 512 layer on a 14x14 map at batch 32, tile shapes and form chosen by on-device timing: whichever of the
+    two wins is recorded as the primitive's kernel, and the result agrees with the oracle (first and last image)."""
+    s, x = _single_fp16_conv(32, 512, 512, 14)
+    net, got = _run(eng, s, x, optimize_data=True, tuning=cl.tuning_mode.tuning_tune_and_cache)
+    info = {r["id"]: r for r in net.primitives_info()}
+    assert info["conv"]["kernel"] in ("conv_f16_tc", "conv_f16_winograd")
+    small, _ = _single_fp16_conv(2, 512, 512, 14)
+    want = oracle_net.run(small, {small.input_id: x[[0, 31]]})
+    if info["conv"]["kernel"] == "conv_f16_winograd":
+        _winograd_close(got["conv"][[0, 31]], want["conv"])
+    else:
+        w, g = want["conv"].astype(np.float32), got["conv"][[0, 31]].astype(np.float32)
+        assert np.abs(g - w).max() <= 1e-2 * float(np.abs(w).max())

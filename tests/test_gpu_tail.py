@@ -169,3 +169,50 @@ def test_softmax_whole_image_scope_matches_oracle(eng):
     got = _run(eng, "softmax", sp, 3 * 21 * 9 * 7, np.float32, input0=x)
     assert np.allclose(got, want[:got.size], rtol=1e-4, atol=1e-8)
     assert np.allclose(got.reshape(3, -1).sum(axis=1), 1.0, atol=1e-4)
+
+
+def _eltwise_params(dtype0, dtype1, out_dtype, shape, fmt, f_align, mode, quant, calib, o_qf, act):
+    N, C, H, W = shape
+    ep = abi.EltwiseParams()
+    ep.in0, n = abi.tensor(abi.dtype_of(np.dtype(dtype0)), N, C, H, W, fmt, f_align)
+    ep.in1, _ = abi.tensor(abi.dtype_of(np.dtype(dtype1)), N, C, H, W, fmt, f_align)
+    ep.out, _ = abi.tensor(abi.dtype_of(np.dtype(out_dtype)), N, C, H, W, fmt, f_align)
+    ep.mode = mode
+    ep.stride_x0 = ep.stride_y0 = ep.stride_x1 = ep.stride_y1 = 1
+    ep.quantization, ep.calibration, ep.o_qf, ep.act = int(quant), int(calib), o_qf, act
+    return ep, n
+
+
+ELTWISE = {
+    # the requantising 8-bit form (generic_eltwise_ref.cl with QUANTIZATION_TERM) and the floating form, on padded byxf and on bfyx
+    "sum_s8_s8_oqf_byxf": dict(d0=np.int8, d1=np.int8, out=np.int8, fmt="byxf", f_align=32, mode=abi.ELTW_SUM, quant=True, calib=False, o_qf=0.5, act=abi.ACT_NONE),
+    "sum_u8_s8_to_u8_relu_byxf": dict(d0=np.uint8, d1=np.int8, out=np.uint8, fmt="byxf", f_align=32, mode=abi.ELTW_SUM, quant=True, calib=False, o_qf=1.0, act=abi.ACT_RELU),
+    "max_s8_calibrated_byxf": dict(d0=np.int8, d1=np.int8, out=np.int8, fmt="byxf", f_align=32, mode=abi.ELTW_MAX, quant=True, calib=True, o_qf=1.0, act=abi.ACT_NONE),
+    "prod_s8_oqf_bfyx": dict(d0=np.int8, d1=np.int8, out=np.int8, fmt="bfyx", f_align=1, mode=abi.ELTW_PROD, quant=True, calib=False, o_qf=0.01, act=abi.ACT_RELU),
+    "sum_f16_relu_byxf": dict(d0=np.float16, d1=np.float16, out=np.float16, fmt="byxf", f_align=32, mode=abi.ELTW_SUM, quant=False, calib=False, o_qf=1.0, act=abi.ACT_RELU),
+    "sub_f16_bfyx": dict(d0=np.float16, d1=np.float16, out=np.float16, fmt="bfyx", f_align=1, mode=abi.ELTW_SUB, quant=False, calib=False, o_qf=1.0, act=abi.ACT_NONE),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ELTWISE))
+@pytest.mark.parametrize("kernel", ["eltwise_byxf", "eltwise_ref"])
+@pytest.mark.parametrize("shape", [(3, 48, 9, 16), (40, 96, 57, 56)])          # the second: several vectors per thread
+def test_eltwise_matches_oracle(eng, name, kernel, shape):
+    c = ELTWISE[name]
+    ep, n = _eltwise_params(c["d0"], c["d1"], c["out"], shape, c["fmt"], c["f_align"], c["mode"], c["quant"], c["calib"], c["o_qf"], c["act"])
+    rng = np.random.default_rng(5)
+
+    def values(dt):
+        dt = np.dtype(dt)
+        logical = rng.standard_normal(shape).astype(dt) if dt.kind == "f" else rng.integers(np.iinfo(dt).min, np.iinfo(dt).max + 1, size=shape).astype(dt)
+        return abi.to_layout(logical, c["fmt"], c["f_align"])
+    a, b = values(c["d0"]), values(c["d1"])
+    calib = rng.uniform(0.25, 1.5, size=shape[1]).astype(np.float32) if c["calib"] else None
+    want = oracle_lib.eltwise(ep, a, b, calib)
+    got = _run(eng, kernel, ep, n, c["out"], input0=a, input1=b, calib=calib)
+    real = abi.from_layout(want[:n], shape, c["fmt"], c["f_align"]), abi.from_layout(got[:n], shape, c["fmt"], c["f_align"])
+    if np.dtype(c["out"]).kind == "f":
+        np.testing.assert_array_equal(real[0].view(np.uint16), real[1].view(np.uint16))
+    else:
+        assert np.array_equal(real[0], real[1])
+    assert len(np.unique(real[0])) > 8
