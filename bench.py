@@ -278,7 +278,7 @@ def table_markdown(title, rows, peaks_note):
 
 
 def run_vgg_layers(args, peaks):
-    """BASELINE configs[1]: the 13 3x3 layers of VGG16 at batch 32, fp16, direct tensor-core kernel against the Winograd
+    """The layer benchmark of the reference's Winograd kernels: the 13 3x3 layers of VGG16 at batch 32, fp16, direct tensor-core kernel against the Winograd
     F(2x2, 3x3) path, each on its best tile shape; TFLOP/s on the direct form's operation count for both."""
     import ctypes as C
     import numpy as np

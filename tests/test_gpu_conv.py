@@ -30,7 +30,7 @@ def _exact(eng, case, kernel, tune=0):
 
 
 GEOMS = {
-    # BASELINE config 1: N=1, C=128 -> K=128, 28x28, 3x3 stride 1 pad 1, u8 in, s8 out, ReLU
+    # the reference's own CPU-runnable int8 layer case: N=1, C=128 -> K=128, 28x28, 3x3 stride 1 pad 1, u8 in, s8 out, ReLU
     "config1": dict(N=1, C=128, K=128, H=28, W=28),
     "1x1": dict(N=2, C=64, K=256, H=56, W=56, kh=1, kw=1, pad=0),
     "1x1_stride2": dict(N=2, C=256, K=128, H=28, W=28, kh=1, kw=1, pad=0, stride=2),

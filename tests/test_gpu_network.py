@@ -64,7 +64,7 @@ def test_small_residual_network_bit_exact(eng, optimize):
 
 
 def test_resnet50_int8_batch2_bit_exact(eng):
-    """BASELINE configuration: ResNet-50 v1 int8, full size (224x224), here at batch 2 so the CPU oracle finishes in seconds."""
+    """The headline workload: ResNet-50 v1 int8, full size (224x224), here at batch 2 so the CPU oracle finishes in seconds."""
     spec = topologies.resnet50_int8(2)
     x = _input(spec, seed=7)
     stats = {}
