@@ -173,7 +173,10 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
+        // The whole warp walks the tiles and waits on the barriers, one elected lane issues the copies: a warp-uniform loop
+        // lets the compiler keep its state on the uniform datapath, which a loop inside a one-lane branch cannot use.
+        {
+            const bool leader = elect_one();
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
             const int bke = P.bk >> 1;                               // channels per chunk
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
@@ -189,16 +192,18 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
                 }
                 int tap = P.batch_tiles ? m_tile / P.batch_tiles : 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
-                    if (!mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErr)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait_lean(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErr))) { ok = false; break; }
                     const uint32_t full = smem_u32(&aux->full[stage]);
-                    mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
                     const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
                     const uint32_t b_dst = b_base + (uint32_t)(stage * P.b_stage_bytes);
                     const int c0 = cc * bke;
-                    if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
-                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
-                    else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
-                    tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * BN);
+                    if (leader) {
+                        mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
+                        if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
+                        else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
+                        else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
+                        tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * BN);
+                    }
                     ++issued;
                     if (++cc == P.chunks) { cc = 0; ++tap; if (++s == P.kw) { s = 0; ++r; } }
                     if (++stage == P.stages) { stage = 0; phase ^= 1u; }
@@ -217,7 +222,8 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();
             const uint32_t hi = desc_hi(P.sbo, P.layout_type);
             const uint32_t a_lo0 = desc_lo(a_base), b_lo0 = desc_lo(b_base);
             const uint32_t a_step = (uint32_t)P.a_stage_bytes >> 4, b_step = (uint32_t)P.b_stage_bytes >> 4;
@@ -228,31 +234,35 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t % NBUF;
-                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErr + 1u)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErr + 1u))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 uint32_t accf = 0u;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErr + 2u)) { ok = false; break; }
-                    if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
-                    else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
-                    else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                    if (!__all_sync(0xffffffffu, mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErr + 2u))) { ok = false; break; }
+                    if (leader) {
+                        if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        tc_commit(empty0 + 8u * (uint32_t)stage);
+                    }
                     accf = 1u;
-                    tc_commit(empty0 + 8u * (uint32_t)stage);
                     if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
                     else { a_lo += a_step; b_lo += b_step; }
                 }
-                if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
+                if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
         }
     } else if (warp == 2) {
         // ------------------------------ TMA store issuer --------------------------
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();                           // issues, commits and waits for the stores: bulk groups are per thread
             int t = 0;
             for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
                 const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
                 const int a = t % NSTG;
-                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErr + 3u)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErr + 3u))) break;
+                if (!leader) continue;
                 int tw = 0, th = 0, tb = 0;
                 if (boxed) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
 #pragma unroll
@@ -270,14 +280,16 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
         }
     } else if (warp == 3) {
         // ------------------------------ residual loader ---------------------------
-        if (kFused && lane == 0) {
+        if (kFused) {
+            const bool leader = elect_one();
             int t = 0;
             for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
                 const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
                 int o_w = 0, o_h = 0, c_n = 0;
                 if (boxed) { const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb; }
                 const int a = t % NSTG;
-                if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErr + 4u)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErr + 4u))) break;
+                if (!leader) continue;
                 const uint32_t rf = smem_u32(&aux->res_full[a]);
                 int cbs = 0;
                 for (int cb = 0; cb < COLB; ++cb) if (n_tile * BN + cb * 64 < P.ofm) ++cbs;

@@ -136,7 +136,10 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
+        // The whole warp walks the tiles and waits on the barriers, one elected lane issues the copies: a warp-uniform loop
+        // lets the compiler keep its state on the uniform datapath, which a loop inside a one-lane branch cannot use.
+        {
+            const bool leader = ptx::elect_one();
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true; int t = 0;
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 int m_tile, n_tile; tile_coords(P, tile, m_tile, n_tile);
@@ -153,10 +156,10 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 if (fused_staged) {
                     // second input of the fused eltwise: same pixels and features as the output tile
                     const int a = t % P.nbuf;
-                    if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u))) { ok = false; break; }
                     const uint32_t rf = smem_u32(&aux->res_full[a]);
-                    mbar_expect_tx(rf, (uint32_t)(P.stage_rows * P.cw * P.col_blocks));
-                    for (int cb = 0; cb < P.col_blocks; ++cb) {
+                    if (leader) mbar_expect_tx(rf, (uint32_t)(P.stage_rows * P.cw * P.col_blocks));
+                    for (int cb = 0; cb < P.col_blocks && leader; ++cb) {
                         const uint32_t dst = smem_u32(staging) + (uint32_t)a * staging_bytes + (uint32_t)(cb * kBM * P.cw);
                         const int f0 = n_tile * P.bn + cb * P.cw;
                         if (P.a_mode == A_TILED) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
@@ -165,16 +168,18 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
                 }
                 int tap = 0, cc = 0, r = 0, s = 0;
                 for (int ks = 0; ks < P.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrProducer))) { ok = false; break; }
                     const uint32_t full = smem_u32(&aux->full[stage]);
-                    mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
                     const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
                     const uint32_t b_dst = b_base + (uint32_t)(stage * P.b_stage_bytes);
                     const int c0 = cc * P.bk;
-                    if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
-                    else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
-                    else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
-                    tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * P.bn);
+                    if (leader) {
+                        mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
+                        if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
+                        else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
+                        else tma_load_4d(a_dst, &P.tmA, full, c0, c_w + s * P.dil_x, c_h + r * P.dil_y, c_n);
+                        tma_load_3d(b_dst, &P.tmB, full, c0, tap, n_tile * P.bn);
+                    }
                     ++issued;
                     if (++cc == P.chunks) { cc = 0; ++tap; if (++s == P.kw) { s = 0; ++r; } }
                     if (++stage == P.stages) { stage = 0; phase ^= 1u; }
@@ -193,28 +198,31 @@ conv_i8_tc_kernel(const __grid_constant__ TcParams P)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        {
+            const bool leader = ptx::elect_one();
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t % P.nbuf;
-                if (!mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / P.nbuf) & 1u)) ^ 1u, s_abort, P.status, kErrMma))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * P.bn);
                 for (int ks = 0; ks < P.k_steps; ++ks) {
-                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrMma + 1u))) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t adesc = make_smem_desc(a_base + (uint32_t)(stage * P.a_stage_bytes), P.sbo, P.layout_type);
                     const uint64_t bdesc = make_smem_desc(b_base + (uint32_t)(stage * P.b_stage_bytes), P.sbo, P.layout_type);
                     const int kk = P.bk >> 5;                       // one instruction consumes K = 32 bytes
-                    for (int k = 0; k < kk; ++k)
-                        mma_i8_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P.idesc, (ks | k) ? 1u : 0u);
-                    tc_commit(smem_u32(&aux->empty[stage]));        // frees the stage once these MMAs have read it
+                    if (leader) {
+                        for (int k = 0; k < kk; ++k)
+                            mma_i8_ss(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), P.idesc, (ks | k) ? 1u : 0u);
+                        tc_commit(smem_u32(&aux->empty[stage]));    // frees the stage once these MMAs have read it
+                    }
                     if (++stage == P.stages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
+                if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
             // drain: every issued MMA must have retired before TMEM is released
-            tc_commit(smem_u32(&aux->drain));
+            if (leader) tc_commit(smem_u32(&aux->drain));
             const uint64_t t0 = globaltimer();
             while (!mbar_try_wait(smem_u32(&aux->drain), 0u)) {
                 if (globaltimer() - t0 > kWaitLimitNs) { atomicCAS(P.status, 0u, kErrDrain); break; }

@@ -300,8 +300,12 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         const bool patch = P.a_mode == A_PATCH;
-        if (lane == 0) {
-            if (patch && blockIdx.x < (unsigned)P.total_tiles) {
+        // The whole warp walks the tiles and waits on the barriers; one elected lane issues the copies.  With the loop
+        // warp-uniform the compiler keeps the loop state and the copies' operands on the uniform datapath, which a loop
+        // inside a one-lane branch cannot use: the role's instruction count per stage is what bounds small-tile layers.
+        {
+            const bool leader = ptx::elect_one();
+            if (leader && patch && blockIdx.x < (unsigned)P.total_tiles) {
                 // patch mode: every filter tap of every feature tile, once per CTA
                 const uint32_t bf = smem_u32(&aux->b_full);
                 mbar_expect_tx(bf, (uint32_t)P.b_total_bytes);
@@ -327,18 +331,20 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 const int m0 = w.m_tile * kBM, n0 = w.n_tile * BN;
                 int tap = 0, cc = 0, off_w = 0, off_h = 0, sx = 0;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!mbar_wait_lean(empty0 + 8u * (uint32_t)stage, phase ^ 1u, s_abort, P.status, kErrProducer)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait_lean(empty0 + 8u * (uint32_t)stage, phase ^ 1u, s_abort, P.status, kErrProducer))) { ok = false; break; }
                     const uint32_t full = full0 + 8u * (uint32_t)stage;
                     const uint32_t dst = a_base + (uint32_t)stage * a_stage;
                     const int c0 = cc * bk;
-                    mbar_expect_tx(full, tx);
-                    if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
-                    if (patch) {                                                            // one patch per filter column
-                        for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
+                    if (leader) {
+                        mbar_expect_tx(full, tx);
+                        if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
+                        if (patch) {                                                            // one patch per filter column
+                            for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
+                        }
+                        else if (mode == A_FLAT) tma_load_2d(dst, &P.tmA, full, c0, m0);
+                        else if (mode == A_IM2COL) tma_load_im2col_4d(dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)off_w, (uint16_t)off_h);
+                        else tma_load_4d(dst, &P.tmA, full, c0, c_w + off_w, c_h + off_h, c_n);
                     }
-                    else if (mode == A_FLAT) tma_load_2d(dst, &P.tmA, full, c0, m0);
-                    else if (mode == A_IM2COL) tma_load_im2col_4d(dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)off_w, (uint16_t)off_h);
-                    else tma_load_4d(dst, &P.tmA, full, c0, c_w + off_w, c_h + off_h, c_n);
                     ++issued;
                     if (++cc == chunks) { cc = 0; ++tap; off_w += dil_x; if (++sx == kw) { sx = 0; off_w = 0; off_h += dil_y; } }
                     if (++stage == stages) { stage = 0; phase ^= 1u; }
@@ -357,9 +363,11 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        // One thread feeds the tensor core; everything it can precompute is precomputed, because at small
-        // feature tiles an MMA runs for only 48-64 clocks and a dependent scalar instruction costs ~4.
-        if (lane == 0) {
+        // One elected lane feeds the tensor core while the whole warp runs the loop (see the producer); everything that can be
+        // precomputed is precomputed, because at small feature tiles an MMA runs for only 48-64 clocks and a dependent
+        // scalar instruction costs ~4.
+        {
+            const bool leader = ptx::elect_one();
             const uint32_t hi = desc_hi(P.sbo, P.layout_type);
             const uint32_t a_lo0 = desc_lo(a_base), b_lo0 = desc_lo(b_base);
             const uint32_t a_step = (uint32_t)P.a_stage_bytes >> 4, b_step = (uint32_t)P.b_stage_bytes >> 4;
@@ -375,35 +383,35 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const int patch_kind = (kh == 3 && kw_ == 3) ? (kk == 2 ? 1 : (kk == 4 ? 2 : 0)) : 0;   // 3x3 filters are issued straight-line
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
-            if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u);
+            if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u));
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             for (; walk.valid() && ok; walk.next(), ++t) {
                 const int acc = t % NBUF;
-                if (!mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma)) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErrMma))) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 uint32_t accf = 0u;
                 uint32_t b_col = 0u;                                                   // patch mode: weights of (filter column, channel chunk)
                 if (patch) b_col = b_lo0 + (uint32_t)(walk.n_tile * kh) * b_row_step;
                 for (int ks = 0; ks < k_steps; ++ks) {
-                    if (!mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u))) { ok = false; break; }
                     if (!patch) {
-                        if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
-                        else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
-                        else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
+                        if (kk == 4) { if (leader) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
+                        else if (kk == 2) { if (leader) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
+                        else { if (leader) mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
                         accf = 1u;
                     } else {
-                        if (patch_kind == 1) patch_issue<3, 3, 2>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf);
-                        else if (patch_kind == 2) patch_issue<3, 3, 4>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf);
+                        if (patch_kind == 1) { if (leader) patch_issue<3, 3, 2>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf); }
+                        else if (patch_kind == 2) { if (leader) patch_issue<3, 3, 4>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf); }
                         else {
                             // per filter column s one patch; rows r*bw .. r*bw+127 of it are the tile's 128 pixels under filter row r
                             uint32_t as = a_lo, bs = b_col;
                             for (int s = 0; s < kw_; ++s, as += patch_step, bs += b_tap_step) {
                                 uint32_t ar = as, br = bs;
                                 for (int r = 0; r < kh; ++r, ar += row_step, br += b_row_step) {
-                                    if (kk == 4) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf);
-                                    else if (kk == 2) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf);
-                                    else mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf);
+                                    if (kk == 4) { if (leader) mma_chunk<4>(d_tmem, ar, br, hi, idesc, accf); }
+                                    else if (kk == 2) { if (leader) mma_chunk<2>(d_tmem, ar, br, hi, idesc, accf); }
+                                    else { if (leader) mma_chunk<1>(d_tmem, ar, br, hi, idesc, accf); }
                                     accf = 1u;
                                 }
                             }
@@ -411,14 +419,14 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                         accf = 1u;
                         b_col += b_step;                                                     // next channel chunk
                     }
-                    tc_commit(empty0 + 8u * (uint32_t)stage);                           // frees the stage once these MMAs have read it
+                    if (leader) tc_commit(empty0 + 8u * (uint32_t)stage);                           // frees the stage once these MMAs have read it
                     if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
                     else { a_lo += a_step; b_lo += b_step; }
                 }
-                if (ok) tc_commit(smem_u32(&aux->tmem_full[acc]));
+                if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[acc]));
             }
             // drain: every issued MMA must have retired before TMEM is released
-            tc_commit(smem_u32(&aux->drain));
+            if (leader) tc_commit(smem_u32(&aux->drain));
             const uint64_t t0 = globaltimer();
             while (!mbar_try_wait(smem_u32(&aux->drain), 0u)) {
                 if (globaltimer() - t0 > kWaitLimitNs) { atomicCAS(P.status, 0u, kErrDrain); break; }
@@ -426,14 +434,16 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         }
     } else if (warp == 2) {
         // ------------------------------ TMA store issuer --------------------------
-        if (lane == 0) {
+        {
+            const bool leader = ptx::elect_one();                    // issues, commits and waits for the stores: bulk groups are per thread
             int t = 0;
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;            // the output of an im2col tile is addressed by its first pixel index
             for (; walk.valid(); walk.next(), ++t) {
                 const int n_tile = walk.n_tile, m_tile = walk.m_tile;
                 const int a = t % NSTG;
-                if (!mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErrEpilogue + 2u)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErrEpilogue + 2u))) break;
+                if (!leader) continue;
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
                 const int tw = walk.d0, th = walk.d1, tb = walk.d2;
 #pragma unroll
@@ -454,7 +464,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // Second input of the fused sum: same pixels and features as the output tile, brought into the
         // staging buffer the epilogue will overwrite.  Its own warp, so that waiting for a staging buffer
         // never holds back the operand loads of later tiles.
-        if (kFused && lane == 0) {
+        if (kFused) {
+            const bool leader = ptx::elect_one();
             int t = 0;
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;
@@ -463,7 +474,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 const bool boxed = P.a_mode == A_TILED || P.a_mode == A_PATCH;
                 const int o_w = walk.d0 * P.bw, o_h = walk.d1 * P.bh, c_n = walk.d2 * P.bb;
                 const int a = t % NSTG;
-                if (!mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErrProducer + 1u))) break;
+                if (!leader) continue;
                 const uint32_t rf = smem_u32(&aux->res_full[a]);
                 int cbs = 0;                                        // column blocks that hold features of the tensor
 #pragma unroll

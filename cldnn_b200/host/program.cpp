@@ -317,7 +317,7 @@ public:
     void replace_dep(node* consumer, node* from, node* to) { for (auto& id : consumer->p.input) if (id == from->p.id) id = to->p.id; }
     void allocate_and_prepare();
     void prepare_kernel(node* n);
-    void pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t params_size,
+    void pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t params_size, const void* key_params,
                      const cldnn_b200_args& args, const std::function<void(int)>& set_tune, bool time_all = false);
     memory pack_conv_weights(node* n, int32_t stored_ifm, int32_t groups = 1);
     void load_cache(); void save_cache();
@@ -753,7 +753,7 @@ void network_impl::save_cache()
 // in which case every (kernel, tuning variant) is timed on the device and the fastest is kept and cached.
 // `time_all`: the candidates are alternatives of equal standing (direct and Winograd convolution), all of them are timed;
 // otherwise later candidates are fallbacks that are only reached when the earlier ones refuse the constants.
-void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t psize,
+void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidates, void* params, size_t psize, const void* key_params,
                                const cldnn_b200_args& args, const std::function<void(int)>& set_tune, bool time_all)
 {
     if (!opts.force_kernel.empty()) {                               // "<primitive id>=<kernel>[:tune],..."
@@ -768,8 +768,9 @@ void network_impl::pick_kernel(node* n, const std::vector<std::string>& candidat
         }
     }
     set_tune(0);
-    // the key carries the generation of the kernel set: timings taken on older kernels must not be reused
-    const std::string hash = fnv1a_hex(params, psize, n->p.type + "#g3");
+    // the key carries the generation of the kernel set: timings taken on older kernels must not be reused.  `key_params`:
+    // the constants with the fields that do not bear on the choice cleared (same size as `params`)
+    const std::string hash = fnv1a_hex(key_params ? key_params : params, psize, n->p.type + "#g3");
     if (opts.tuning != tuning_mode::tuning_disabled) {
         auto it = tuning_cache.find(hash);
         if (it != tuning_cache.end()) {
@@ -862,8 +863,9 @@ void network_impl::prepare_kernel(node* n)
     if (n->ec) a.eltw_output_calibration_factors = (const float*)n->ec->mem.device_ptr();
     for (node* f : {n->wq, n->oc, n->ec}) if (f && f->out.data_type != data_types::f32) throw error(p.id + ": quantization / calibration factors must be f32", CLDNN_B200_INVALID_ARG);
 
-    auto finish = [&](const std::vector<std::string>& cands, void* params, size_t size, const std::function<void(int)>& set_tune, bool time_all = false) {
-        pick_kernel(n, cands, params, size, a, set_tune, time_all);
+    auto finish = [&](const std::vector<std::string>& cands, void* params, size_t size, const std::function<void(int)>& set_tune, bool time_all = false,
+                      const void* key_params = nullptr) {
+        pick_kernel(n, cands, params, size, key_params, a, set_tune, time_all);
         check(cldnn_b200_prepare(eng->kernel(n->kernel), params, size, &a, &n->prepared), p.id + " (" + n->kernel + ")");
     };
 
@@ -989,7 +991,9 @@ void network_impl::prepare_kernel(node* n)
                     a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
                     cands.push_back("conv_f16_winograd");
                 }
-                finish(cands, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; }, cands.size() > 1);
+                // the tile shape does not depend on whether the residual is read from the output buffer: one cache entry for both
+                cldnn_b200_conv_params key = cp; key.in_out_opt = 0; key.tune = 0;
+                finish(cands, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; }, cands.size() > 1, &key);
                 if (n->kernel != "conv_f16_winograd" && n->scratch) {      // the direct form won: the workspace goes back
                     // (the prepared launch of the direct kernel never looks at the scratch pointer)
                     n->scratch.reset();
