@@ -385,7 +385,7 @@ static bool load_driver_entry_points()
     return g_encode_tiled && g_encode_im2col;
 }
 
-struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; int epi_groups; };
+struct TcPlan { int a_mode; int bn; int bk; int bw, bh, bb; int epi_groups; int pair; };
 
 // tune index -> (addressing mode, feature tile).  0 = automatic choice.
 static const int kTuneBN[4] = {32, 64, 128, 256};
@@ -393,8 +393,10 @@ static const int kTuneBN[4] = {32, 64, 128, 256};
 // 25..28 are the patch mode (resident weights, one activation patch per filter column) of the specialised kernel;
 // 29..40 and 41..44 repeat 1..12 and 25..28 on the specialised kernel with four epilogue warp groups instead of two
 // (16 epilogue warps per SM: for the layers whose time is the epilogue's instruction issue).
+// 45..50: CTA pairs on the specialised kernel (two epilogue groups): 45 + 2 * mode + {128, 256}[i], mode flat / im2col / tiled
 constexpr int kTuneFourGroups = 28;
-static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4 + 4 + 3 * 4 + 4; }
+constexpr int kTunePair = 44;
+static int tc_tune_count(const void*) { return 1 + 2 * 3 * 4 + 4 + 3 * 4 + 4 + 6; }
 constexpr size_t kPatchWeightBytes = 72 * 1024;       // largest weight tensor the patch mode keeps resident
 
 static bool dense_byxf(const cldnn_b200_tensor& t)
@@ -493,8 +495,15 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
                            (int64_t)p.in.b * p.in.pb >= 131072;     // small tensors take the tiled path
     int tune = p.tune;
     int mode = -1, bn = 0;
-    pl.epi_groups = 2;
-    if (tune > kTuneFourGroups) {
+    pl.epi_groups = 2; pl.pair = 0;
+    if (tune > kTunePair) {
+        if (tune > kTunePair + 6) return no("unknown tuning index");
+        if (!lean_params(p)) return no("CTA pairs exist on the specialised kernel only");
+        pl.pair = 1;
+        const int t6 = tune - kTunePair - 1;
+        tune = 1 + 4 * (t6 / 2) + 2 + (t6 & 1);                   // the same addressing mode with a 128- or 256-feature tile
+    }
+    else if (tune > kTuneFourGroups) {
         pl.epi_groups = 4;
         tune -= kTuneFourGroups;                                   // 1..12 as they are, 13..16 are the patch modes 25..28
         if (tune > 12) tune += 12;
@@ -530,6 +539,7 @@ static bool tc_plan(const cldnn_b200_conv_params& p, TcPlan& pl, std::string* wh
     if (bn == 0) bn = p.ofm > 128 ? 256 : (p.ofm > 64 ? 128 : (p.ofm > 32 ? 64 : 32));
     if (!groups_fit(bn)) return no("four epilogue groups need feature tiles of 64 or 128 (eight or four accumulators)");
     if (mode == A_PATCH) { if (const char* m = patch_why(bn)) return no(m); }
+    if (pl.pair && (p.ofm % bn || (int64_t)p.out.b * p.out.y * p.out.x < 2 * kBM)) return no("CTA pairs need whole feature tiles and at least two pixel tiles");
     // 256-feature tiles with a fused residual: three 32 KiB staging tiles + three operand stages need 24 KiB stages;
     // worth it unless the reduction is long (>= 4 chunks of 128 channels), where fewer, larger stages win
     if (bn == 256 && p.fused_eltw && pl.bk == 128 && cs < 512 && lean_params(p)) pl.bk = 64;
@@ -596,11 +606,16 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
         P.tiles_w = P.tiles_h = 1;
         P.m_tiles = (int)((P.M_total + kBM - 1) / kBM);
     }
+    P.pair = pl.pair;
+    // CTA pairs take pixel tiles two at a time: an odd count gets one phantom tile past the tensor (its loads read the
+    // out-of-range fill, its stores are clipped away); each CTA loads half of the feature tile's weight rows
+    if (pl.pair) P.m_tiles = (P.m_tiles + 1) & ~1;
+    const int b_rows = pl.pair ? pl.bn / 2 : pl.bn;
     P.total_tiles = P.m_tiles * P.n_tiles;
     P.stage_rows = boxed ? pl.bw * pl.bh * pl.bb : kBM;
-    P.a_stage_bytes = kBM * pl.bk; P.b_stage_bytes = pl.bn * pl.bk;
+    P.a_stage_bytes = kBM * pl.bk; P.b_stage_bytes = b_rows * pl.bk;
     P.a_tx_bytes = P.stage_rows * pl.bk;
-    P.b_tx_bytes = pl.bn * pl.bk;
+    P.b_tx_bytes = b_rows * pl.bk;
     if (pl.a_mode == A_PATCH) {
         // a stage holds the patch; the tensor core reads 128 rows from row r * bw, r < kh, so the stage spans that far
         const int patch_rows = (pl.bh + p.kh - 1) * pl.bw, read_rows = (p.kh - 1) * pl.bw + kBM;
@@ -614,7 +629,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.sbo = 8u * (uint32_t)pl.bk;
     P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
     const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;     // operand signedness in the instruction descriptor
-    P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(pl.bn >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+    P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(pl.bn >> 3) << 17) | ((uint32_t)((pl.pair ? 2 * kBM : kBM) >> 4) << 24);
     P.nbuf = pl.bn >= 256 ? 2 : (pl.bn >= 128 ? 4 : 8);         // accumulator and staging buffers in flight: all of tensor memory
     P.tmem_cols = (uint32_t)(P.nbuf * pl.bn < 32 ? 32 : P.nbuf * pl.bn);
     P.ofm = p.ofm;
@@ -655,6 +670,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     P.acc_bound = (float)p.kh * (float)p.kw * (float)p.ifm * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
     P.epi_groups = pl.epi_groups;
     const bool use_fast = (p.tune <= 12 || p.tune > 24) && tc_fast_eligible(P);
+    if (pl.pair && !use_fast) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: CTA pairs exist on the specialised kernel only");
     if (pl.epi_groups > 2 && !use_fast) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: four epilogue groups exist on the specialised kernel only");
 
     const size_t aux_bytes = use_fast ? tc_fast_aux_bytes() : sizeof(TcSmemAux);
@@ -739,7 +755,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     {
         cuuint64_t dims[3] = {(cuuint64_t)cs, (cuuint64_t)(p.kh * p.kw), (cuuint64_t)p.ofm};
         cuuint64_t strides[2] = {(cuuint64_t)p.w_px, (cuuint64_t)p.w_po};
-        cuuint32_t box[3] = {(cuuint32_t)pl.bk, 1, (cuuint32_t)pl.bn};
+        cuuint32_t box[3] = {(cuuint32_t)pl.bk, 1, (cuuint32_t)b_rows};
         cuuint32_t es[3] = {1, 1, 1};
         void* w_ptr = (char*)const_cast<void*>(a->weights) + p.w_offset;
         cr = g_encode_tiled(&P.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
@@ -761,6 +777,7 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
 
     int grid = ctx->prop.multiProcessorCount;
     if (grid > P.total_tiles) grid = P.total_tiles;
+    if (pl.pair) grid &= ~1;                                           // whole clusters of two (total_tiles is even)
     if (grid < 1) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_tc: empty output");
     const size_t smem = smem_bytes;
     if (use_fast) {

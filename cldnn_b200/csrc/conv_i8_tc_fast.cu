@@ -73,12 +73,14 @@ __device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi)
     uint64_t d; asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi)); return d;
 }
 // KK tensor-core instructions over one channel chunk, 32 bytes of K each
-template <int KK>
+template <int KK, bool kPair = false>
 __device__ __forceinline__ void mma_chunk(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t acc_first)
 {
 #pragma unroll
-    for (int k = 0; k < KK; ++k)
-        mma_i8_ss(d_tmem, desc64(a_lo + 2u * k, hi), desc64(b_lo + 2u * k, hi), idesc, k ? 1u : acc_first);
+    for (int k = 0; k < KK; ++k) {
+        if (kPair) mma_i8_ss_pair(d_tmem, desc64(a_lo + 2u * k, hi), desc64(b_lo + 2u * k, hi), idesc, k ? 1u : acc_first);
+        else mma_i8_ss(d_tmem, desc64(a_lo + 2u * k, hi), desc64(b_lo + 2u * k, hi), idesc, k ? 1u : acc_first);
+    }
 }
 
 // Patch mode, one channel chunk: KH x KW filter taps straight-line (a loop over run-time filter sizes costs the issuing
@@ -93,6 +95,13 @@ __device__ __forceinline__ void patch_issue(uint32_t d_tmem, uint32_t a_lo, uint
         for (int r = 0; r < KH; ++r)
             mma_chunk<KK>(d_tmem, a_lo + (uint32_t)s * patch_step + (uint32_t)r * row_step, b_col + (uint32_t)s * b_tap_step + (uint32_t)r * b_row_step,
                           hi, idesc, (s | r) ? 1u : accf);
+}
+
+// The accumulator has been read out: tell the MMA issuer (in a CTA pair it sits in the CTA of rank 0, and `bar` is then
+// that CTA's barrier as a cluster address).
+__device__ __forceinline__ void release_acc(uint32_t bar, bool pair)
+{
+    if (pair) mbar_arrive_cluster(bar); else mbar_arrive(bar);
 }
 
 template <int BN>
@@ -110,7 +119,8 @@ __device__ __forceinline__ void fast_chunk_ptrs(uint8_t* stg, int row, uint32_t 
 // neutral constants, and the store clips them.)
 template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f)
+                                          uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f,
+                                          bool pair = false)
 {
     const int32_t* bias = aux->bias_i[group];
     const float* quant = aux->quant[group];
@@ -129,7 +139,7 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
             // the accumulator has been read out: the MMA issuer may reuse it
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar);
+            if (lane == 0) release_acc(tmem_empty_bar, pair);
         }
         fast_chunk_ptrs<BN>(stg, row, sw, c0 + 32, p0, p1);
         fast_chunk32<kFused, kRelu1, kOut, kOqf>(rb, bias + c0 + 32, quant + c0 + 32, p0, p1, e_xor, k_pos, k_neg, oqf);
@@ -140,7 +150,8 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
 // latency of the tensor-memory load between them and the register budget is 102 per thread.
 template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_tile_single(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                                 uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f)
+                                                 uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f,
+                                                 bool pair = false)
 {
     const int32_t* bias = aux->bias_i[group];
     const float* quant = aux->quant[group];
@@ -155,7 +166,7 @@ __device__ __forceinline__ void fast_tile_single(const FastAux* aux, int group, 
             // the accumulator has been read out: the MMA issuer may reuse it
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty_bar);
+            if (lane == 0) release_acc(tmem_empty_bar, pair);
         }
         fast_chunk32<kFused, kRelu1, kOut, kOqf>(r, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg, oqf);
     }
@@ -164,25 +175,25 @@ __device__ __forceinline__ void fast_tile_single(const FastAux* aux, int group, 
 // The variants with a uniform O_QF stay out of line, so that the common ones keep their registers and code layout.
 template <int BN, bool kFused, int kOut, int G>
 __device__ __noinline__ void fast_tile_oqf(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                           uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf)
+                                           uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf, bool pair)
 {
-    if (G > 2) fast_tile_single<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf);
-    else fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf);
+    if (G > 2) fast_tile_single<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf, pair);
+    else fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf, pair);
 }
 // two register buffers with two groups, one with four
 template <int BN, bool kFused, bool kRelu1, int kOut, int G>
 __device__ __forceinline__ void fast_tile_any(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                              uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg)
+                                              uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, bool pair)
 {
-    if (G > 2) fast_tile_single<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg);
-    else fast_tile<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg);
+    if (G > 2) fast_tile_single<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, 1.0f, pair);
+    else fast_tile<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, 1.0f, pair);
 }
 
 // The same tile in float arithmetic, element by element (fused residual only):
 // taken when a feature's value range could leave the integer-safe range.
 template <int BN>
 __device__ __noinline__ void fast_tile_wide(const TcParams& P, const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row,
-                                            uint32_t sw, uint32_t tmem_empty_bar, int lane)
+                                            uint32_t sw, uint32_t tmem_empty_bar, int lane, bool pair)
 {
     const EpiCfg& c = P.epi;
 #pragma unroll 1
@@ -205,7 +216,7 @@ __device__ __noinline__ void fast_tile_wide(const TcParams& P, const FastAux* au
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(tmem_empty_bar);
+    if (lane == 0) release_acc(tmem_empty_bar, pair);
 }
 
 // The tiles a role visits: tile = first + i * step.  Integer division costs a single thread ~120 clocks, so the
@@ -249,7 +260,10 @@ struct TileWalk {
     }
 };
 
-template <int BN, bool kFused, int G>
+// kPair: the CTAs of a cluster of two work on two vertically adjacent pixel tiles with one tensor-core instruction stream
+// (tcgen05 cta_group::2, M = 256): each CTA loads its own 128 pixel rows and HALF of the feature tile's weight rows, so a
+// stage costs an SM (128 + BN / 2) x BK bytes of L2 traffic instead of (128 + BN) x BK for the same tensor-core work.
+template <int BN, bool kFused, int G, bool kPair = false>
 __global__ void __launch_bounds__(fast_threads(G), 1)
 conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
 {
@@ -274,10 +288,12 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     volatile uint32_t* s_abort = &aux->abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = kPair ? cluster_ctarank() : 0u;              // 0 issues the tensor-core instructions of the pair
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
-        for (int a = 0; a < kMaxBufs; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4); }
+        // in a pair the accumulators of both CTAs are released to rank 0's barrier: four warps from each
+        for (int a = 0; a < kMaxBufs; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), kPair ? 8 : 4); }
         for (int a = 0; a < kMaxStg; ++a) {
             mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
             mbar_init(smem_u32(&aux->out_ready[a]), 4);
@@ -289,9 +305,13 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         prefetch_tensormap(&P.tmA); prefetch_tensormap(&P.tmB); prefetch_tensormap(&P.tmO);
         if (kFused) prefetch_tensormap(&P.tmE);
     }
-    if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    if (warp == 1) {
+        if (kPair) { tmem_alloc_pair(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish_pair(); }
+        else { tmem_alloc(smem_u32(&aux->tmem_base), P.tmem_cols); tmem_relinquish(); }
+    }
     tc_fence_before();
-    __syncthreads();
+    if (kPair) cluster_sync_all();                     // the peer's barriers exist before anything arrives on them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
     griddep_launch_dependents();
@@ -335,7 +355,15 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     const uint32_t full = full0 + 8u * (uint32_t)stage;
                     const uint32_t dst = a_base + (uint32_t)stage * a_stage;
                     const int c0 = cc * bk;
-                    if (leader) {
+                    if (leader && kPair) {
+                        // both CTAs' copies report to rank 0's barrier, which expects the bytes of both
+                        const uint32_t full_r0 = mapa_rank(full, 0u);
+                        if (rank == 0u) mbar_expect_tx(full, 2u * tx);
+                        tma_load_3d_pair(b_base + (uint32_t)stage * b_stage, &P.tmB, full_r0, c0, tap, n0 + (int)rank * (BN / 2));
+                        if (mode == A_FLAT) tma_load_2d_pair(dst, &P.tmA, full_r0, c0, m0);
+                        else if (mode == A_IM2COL) tma_load_im2col_4d_pair(dst, &P.tmA, full_r0, c0, c_w, c_h, c_n, (uint16_t)off_w, (uint16_t)off_h);
+                        else tma_load_4d_pair(dst, &P.tmA, full_r0, c0, c_w + off_w, c_h + off_h, c_n);
+                    } else if (leader) {
                         mbar_expect_tx(full, tx);
                         if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
                         if (patch) {                                                            // one patch per filter column
@@ -366,7 +394,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // One elected lane feeds the tensor core while the whole warp runs the loop (see the producer); everything that can be
         // precomputed is precomputed, because at small feature tiles an MMA runs for only 48-64 clocks and a dependent
         // scalar instruction costs ~4.
-        {
+        // In a pair only the CTA of rank 0 issues; its instructions and commits act on both CTAs.
+        if (!kPair || rank == 0u) {
             const bool leader = ptx::elect_one();
             const uint32_t hi = desc_hi(P.sbo, P.layout_type);
             const uint32_t a_lo0 = desc_lo(a_base), b_lo0 = desc_lo(b_base);
@@ -396,9 +425,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!__all_sync(0xffffffffu, mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u))) { ok = false; break; }
                     if (!patch) {
-                        if (kk == 4) { if (leader) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
-                        else if (kk == 2) { if (leader) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
-                        else { if (leader) mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
+                        if (kk == 4) { if (leader) mma_chunk<4, kPair>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
+                        else if (kk == 2) { if (leader) mma_chunk<2, kPair>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
+                        else { if (leader) mma_chunk<1, kPair>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
                         accf = 1u;
                     } else {
                         if (patch_kind == 1) { if (leader) patch_issue<3, 3, 2>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf); }
@@ -419,11 +448,11 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                         accf = 1u;
                         b_col += b_step;                                                     // next channel chunk
                     }
-                    if (leader) tc_commit(empty0 + 8u * (uint32_t)stage);                           // frees the stage once these MMAs have read it
+                    if (leader) { if (kPair) tc_commit_pair(empty0 + 8u * (uint32_t)stage); else tc_commit(empty0 + 8u * (uint32_t)stage); }                           // frees the stage once these MMAs have read it
                     if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
                     else { a_lo += a_step; b_lo += b_step; }
                 }
-                if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[acc]));
+                if (ok && leader) { if (kPair) tc_commit_pair(smem_u32(&aux->tmem_full[acc])); else tc_commit(smem_u32(&aux->tmem_full[acc])); }
             }
             // drain: every issued MMA must have retired before TMEM is released
             if (leader) tc_commit(smem_u32(&aux->drain));
@@ -543,32 +572,32 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
             uint8_t* stg = staging + (size_t)sb * kStagingBytes;
-            const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
-            if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane);
+            const uint32_t te = kPair ? mapa_rank(smem_u32(&aux->tmem_empty[acc]), 0u) : smem_u32(&aux->tmem_empty[acc]);
+            if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane, kPair);
             else if (with_oqf) {
                 // u8 or plain s8 output, no ReLU between convolution and residual sum (the host admits nothing else here)
                 if (kFused) {
-                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
-                    else fast_tile_oqf<BN, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
+                    else fast_tile_oqf<BN, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
                 } else {
-                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
-                    else fast_tile_oqf<BN, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
+                    else fast_tile_oqf<BN, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
                 }
             }
             else if (kFused) {
                 switch (variant) {
-                    case 0: fast_tile_any<BN, true, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 1: fast_tile_any<BN, true, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 2: fast_tile_any<BN, true, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 3: fast_tile_any<BN, true, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 4: fast_tile_any<BN, true, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    default: fast_tile_any<BN, true, true, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 0: fast_tile_any<BN, true, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 1: fast_tile_any<BN, true, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 2: fast_tile_any<BN, true, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 3: fast_tile_any<BN, true, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 4: fast_tile_any<BN, true, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    default: fast_tile_any<BN, true, true, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
                 }
             } else {
                 switch (variant >> 1) {
-                    case 0: fast_tile_any<BN, false, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    case 1: fast_tile_any<BN, false, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
-                    default: fast_tile_any<BN, false, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg); break;
+                    case 0: fast_tile_any<BN, false, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 1: fast_tile_any<BN, false, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    default: fast_tile_any<BN, false, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
                 }
             }
             fence_async_smem();
@@ -578,8 +607,10 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     }
 
     tc_fence_before();
-    __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, P.tmem_cols); }
+    // a pair leaves together: rank 0's tensor-core instructions read the peer's shared memory and the peer arrives on rank 0's barriers
+    if (kPair) cluster_sync_all();
+    else __syncthreads();
+    if (warp == 1) { tc_fence_after(); if (kPair) tmem_dealloc_pair(tmem_base, P.tmem_cols); else tmem_dealloc(tmem_base, P.tmem_cols); }
 }
 
 
@@ -590,6 +621,7 @@ bool tc_fast_eligible(const TcParams& P)
 {
     if (!P.lean || !P.staged) return false;
     if (P.bn != 64 && P.bn != 128 && P.bn != 256) return false;
+    if (P.pair && (P.bn < 128 || P.a_mode == A_PATCH || P.epi_groups != 2)) return false;
     // a uniform O_QF: positive, and only in front of an unsigned or plain signed saturation
     if (P.mul_oqf) {
         if (P.epi.calibration || !(P.epi.o_qf > 0.0f)) return false;
@@ -599,6 +631,12 @@ bool tc_fast_eligible(const TcParams& P)
     return true;
 }
 
+static const void* fast_kernel_pair(const TcParams& P)
+{
+    const bool f = P.epi.fused_eltw != 0;
+    if (P.bn == 128) return f ? (const void*)conv_i8_tc_fast_kernel<128, true, 2, true> : (const void*)conv_i8_tc_fast_kernel<128, false, 2, true>;
+    return f ? (const void*)conv_i8_tc_fast_kernel<256, true, 2, true> : (const void*)conv_i8_tc_fast_kernel<256, false, 2, true>;
+}
 template <int G>
 static const void* fast_kernel_of_g(const TcParams& P)
 {
@@ -609,7 +647,11 @@ static const void* fast_kernel_of_g(const TcParams& P)
     default:  return f ? (const void*)conv_i8_tc_fast_kernel<256, true, G> : (const void*)conv_i8_tc_fast_kernel<256, false, G>;
     }
 }
-static const void* fast_kernel_of(const TcParams& P) { return P.epi_groups > 2 ? fast_kernel_of_g<4>(P) : fast_kernel_of_g<2>(P); }
+static const void* fast_kernel_of(const TcParams& P)
+{
+    if (P.pair) return fast_kernel_pair(P);
+    return P.epi_groups > 2 ? fast_kernel_of_g<4>(P) : fast_kernel_of_g<2>(P);
+}
 
 cudaError_t tc_fast_configure(const TcParams& P, int max_smem)
 {
@@ -620,10 +662,15 @@ cudaError_t tc_fast_launch(const TcParams& P, int grid, size_t smem_bytes, cudaS
 {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3((unsigned)fast_threads(P.epi_groups > 2 ? 4 : 2)); cfg.dynamicSmemBytes = smem_bytes; cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
+    if (P.pair) {                                                       // clusters of two CTAs (the grid is even)
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     void* args[1] = {const_cast<TcParams*>(&P)};
     return cudaLaunchKernelExC(&cfg, fast_kernel_of(P), args);
 }

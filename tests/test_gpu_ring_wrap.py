@@ -41,20 +41,22 @@ SUM = dict(fused=True, out_dtype=np.uint8, act=abi.ACT_NONE)      # the ResNet b
 
 # tune index of conv_i8_tc: 1 + 4 * mode + {32, 64, 128, 256}[i] with mode flat / im2col / tiled; +12 = the general kernel;
 # 25..28 patch mode; +28 (29..40, and 41..44 for the patch mode) = the specialised kernel with four epilogue warp groups
-# (feature tiles of 64 and 128 only: the rings must hold a multiple of the group count)
+# (feature tiles of 64 and 128 only: the rings must hold a multiple of the group count);
+# 45..50 = CTA pairs (cta_group::2): 45 + 2 * mode + {128, 256}[i]
 I8_CASES = {
     # name: (geometry, epilogue, [(tune, feature tile)])
     "3x3_k64_plain": (dict(N=200, C=32, K=64, H=56, W=56), dict(),
                       [(6, 64), (10, 64), (26, 64), (18, 64), (22, 64), (34, 64), (38, 64), (42, 64)]),
     "3x3_k256_sum": (dict(N=50, C=32, K=256, H=56, W=56), SUM,
-                     [(7, 128), (11, 128), (27, 128), (8, 256), (12, 256), (28, 256), (19, 128), (24, 256), (35, 128), (39, 128), (43, 128)]),
+                     [(7, 128), (11, 128), (27, 128), (8, 256), (12, 256), (28, 256), (19, 128), (24, 256), (35, 128), (39, 128), (43, 128),
+                      (47, 128), (48, 256), (49, 128), (50, 256)]),
     "1x1_k128_sum": (dict(N=200, C=32, K=128, H=56, W=56, kh=1, kw=1, pad=0), SUM,
-                     [(2, 64), (3, 128), (14, 64), (15, 128), (30, 64), (31, 128)]),
+                     [(2, 64), (3, 128), (14, 64), (15, 128), (30, 64), (31, 128), (45, 128)]),
     "1x1_k512_sum_s8res": (dict(N=256, C=64, K=512, H=28, W=28, kh=1, kw=1, pad=0),
                            dict(fused=True, out_dtype=np.int8, act=abi.ACT_NONE, eltw_dtype=np.int8),
-                           [(3, 128), (4, 256), (16, 256), (31, 128)]),
+                           [(3, 128), (4, 256), (16, 256), (31, 128), (45, 128), (46, 256)]),
     "1x1_k256_plain_u8": (dict(N=100, C=64, K=256, H=56, W=56, kh=1, kw=1, pad=0), dict(out_dtype=np.uint8),
-                          [(2, 64), (4, 256), (12, 256), (30, 64), (39, 128)]),
+                          [(2, 64), (4, 256), (12, 256), (30, 64), (39, 128), (46, 256), (50, 256)]),
 }
 
 
