@@ -349,27 +349,31 @@ conv_first_tc_kernel(const __grid_constant__ Params P)
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        // the whole warp runs the loop, one elected lane issues (loop state stays on the uniform datapath)
+        {
+            const bool leader = elect_one();
             int stage = 0; uint32_t phase = 0; bool ok = true;
             for (int it = 0; it < my_tiles && ok; ++it) {
                 const int buf = it % P.nacc; const uint32_t par = (uint32_t)(it / P.nacc) & 1u;
-                if (!mbar_wait(smem_u32(&aux->tmem_empty[buf]), par ^ 1u, s_abort, P.status, kErr + 2u)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tmem_empty[buf]), par ^ 1u, s_abort, P.status, kErr + 2u))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.ofm);
                 for (int ch = 0; ch < P.chunks; ++ch) {
-                    if (!mbar_wait(smem_u32(&aux->a_full[stage]), phase, s_abort, P.status, kErr + 3u)) { ok = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->a_full[stage]), phase, s_abort, P.status, kErr + 3u))) { ok = false; break; }
                     tc_fence_after();
                     const int nm = min(8, P.cores - ch * 8) >> 1;           // one instruction consumes two cores along K
                     const uint64_t adesc = desc_interleaved(smem_u32(sA + stage * kStageBytes), 128u, 1024u);
                     const uint64_t bdesc = desc_interleaved(smem_u32(sB + ch * 8 * 128), 128u, P.sbo_b);
-                    for (int i = 0; i < nm; ++i) {
-                        if (kHalf) mma_f16_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
-                        else mma_i8_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
+                    if (leader) {
+                        for (int i = 0; i < nm; ++i) {
+                            if (kHalf) mma_f16_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
+                            else mma_i8_ss(d_tmem, adesc + (uint64_t)(i * 16), bdesc + (uint64_t)(i * 16), P.idesc, (ch | i) ? 1u : 0u);
+                        }
+                        tc_commit(smem_u32(&aux->a_empty[stage]));
                     }
-                    tc_commit(smem_u32(&aux->a_empty[stage]));
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
-                if (ok) tc_commit(smem_u32(&aux->tmem_full[buf]));
+                if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[buf]));
             }
         }
     } else {

@@ -298,20 +298,24 @@ conv_i8_first_kernel(const __grid_constant__ FirstParams P)
         }
     } else if (warp == 8) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        // the whole warp runs the loop, one elected lane issues (loop state stays on the uniform datapath)
+        {
+            const bool leader = elect_one();
             const int kk = P.Kp >> 5;
             const uint64_t bdesc = make_desc_interleaved(smem_u32(sB), 128u, sbo);
             for (int it = 0; it < my_tiles; ++it) {
                 const int buf = it & 1; const uint32_t par = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(smem_u32(&aux->tmem_empty[buf]), par ^ 1u, s_abort, P.status, kErrFirst + 2u)) break;
-                if (!mbar_wait(smem_u32(&aux->a_full[buf]), par, s_abort, P.status, kErrFirst + 3u)) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tmem_empty[buf]), par ^ 1u, s_abort, P.status, kErrFirst + 2u))) break;
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->a_full[buf]), par, s_abort, P.status, kErrFirst + 3u))) break;
                 tc_fence_after();
                 const uint64_t adesc = make_desc_interleaved(smem_u32(sA + buf * a_bytes), 128u, sbo);
                 const uint32_t d_tmem = tmem_base + (uint32_t)(buf * P.ofm);
-                for (int k = 0; k < kk; ++k)                    // one instruction consumes two core matrices along K: 2 * 128 bytes
-                    mma_i8_ss(d_tmem, adesc + (uint64_t)(k * 16), bdesc + (uint64_t)(k * 16), P.idesc, k ? 1u : 0u);
-                tc_commit(smem_u32(&aux->a_empty[buf]));
-                tc_commit(smem_u32(&aux->tmem_full[buf]));
+                if (leader) {
+                    for (int k = 0; k < kk; ++k)                // one instruction consumes two core matrices along K: 2 * 128 bytes
+                        mma_i8_ss(d_tmem, adesc + (uint64_t)(k * 16), bdesc + (uint64_t)(k * 16), P.idesc, k ? 1u : 0u);
+                    tc_commit(smem_u32(&aux->a_empty[buf]));
+                    tc_commit(smem_u32(&aux->tmem_full[buf]));
+                }
             }
         }
     } else {
