@@ -87,6 +87,7 @@ struct Dw16Args {
     uint32_t items;
     // column-walk kernel: every item is a strip of `strip_rows` output rows of one pixel pair and 4 features
     int32_t strips, strip_rows; uint32_t col_items;
+    const uint32_t* wide_flag;      // column-walk kernel: non-zero when some feature's values may leave the range the conversion-free epilogue is exact in
 };
 
 __global__ void dw_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t py, int64_t px, int64_t off, int C, int kh, int kw, uint32_t* __restrict__ dst)
@@ -95,6 +96,18 @@ __global__ void dw_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int f = i % C, t = i / C; const int j = t / kw, s = t - j * kw;
         dst[i] = ((uint32_t)(uint8_t)w[off + (int64_t)f * po + j * py + s * px]) << (8 * (f & 3));
+    }
+}
+
+// Whether any feature's dequantised values could reach 2^22 (where the conversion-free epilogue stops being exact): evaluated
+// once when the launch is prepared, so that the column-walk kernel needs no pass over the per-feature constants per CTA.
+__global__ void dw_wide_flag(const void* __restrict__ bias, int bias_dtype, int use_bias, const float* __restrict__ quant, int quantization,
+                             float acc_bound, float oqf_abs, int C, uint32_t* __restrict__ flag)
+{
+    for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < C; f += gridDim.x * blockDim.x) {
+        const int32_t bi = use_bias ? load_as_int(bias, bias_dtype, f) : 0;
+        const float q = quantization ? quant[f] : 1.0f;
+        if (!(__fmul_rn(__fmul_rn(__fadd_rn(acc_bound, fabsf((float)bi)), fabsf(q)), oqf_abs) < 4.0e6f)) atomicOr(flag, 1u);
     }
 }
 
@@ -247,9 +260,13 @@ conv_i8_dw16_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __gr
 
 // Item loop of the column-walk kernel below for one epilogue variant (kMode as in dw_epi_word, kOqf: uniform O_QF).
 template <bool kUnsignedIn, int kStride, int kMode, bool kOqf>
-__device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a,
-                                            const uint4* s_w, const int32_t* s_bias, const float* s_quant)
+__device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, const EpiCfg& c, const Dw16Args& a)
 {
+    // The weight words, bias and scale of a thread's 4 features come straight from global memory (a warp reads 512
+    // consecutive bytes per tap; the few KB involved stay in L1 / L2): a CTA that first stages all features' constants in
+    // shared memory spends, on the small maps of a network's last stages, more time and L2 traffic on that than on its items.
+    const uint4* g_w = reinterpret_cast<const uint4*>(a.wmask);
+    const bool use_bias = p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias;
     constexpr int kCols = kStride + 3;
     const int c4n = p.out.f / 4;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < a.col_items; idx += gridDim.x * blockDim.x) {
@@ -261,7 +278,7 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
         uint32_t w[9][4];
 #pragma unroll
         for (int tap = 0; tap < 9; ++tap) {
-            const uint4 wm = s_w[(tap * 4 + (int)(c4 & 3u)) * a.c16n + (int)(c4 >> 2)];
+            const uint4 wm = __ldg(g_w + tap * c4n + (int)c4);
             w[tap][0] = wm.x; w[tap][1] = wm.y; w[tap][2] = wm.z; w[tap][3] = wm.w;
         }
         // stride 1: the four columns under the pixel pair are transposed into one word per feature (4 consecutive pixels
@@ -277,8 +294,12 @@ __device__ __forceinline__ void dwcol_items(const cldnn_b200_conv_params& p, con
                     wa[j][e] = t0 | (t1 << 8) | (t2 << 16); wb[j][e] = wa[j][e] << 8;
                 }
         }
-        const int4 b4 = *reinterpret_cast<const int4*>(s_bias + f0);
-        const float4 q4 = *reinterpret_cast<const float4*>(s_quant + f0);
+        int4 b4 = make_int4(0, 0, 0, 0);
+        if (use_bias) {
+            if (p.bias_dtype == CLDNN_B200_I32) b4 = __ldg(reinterpret_cast<const int4*>(a.bias) + c4);
+            else b4 = make_int4(load_as_int(a.bias, p.bias_dtype, f0), load_as_int(a.bias, p.bias_dtype, f0 + 1), load_as_int(a.bias, p.bias_dtype, f0 + 2), load_as_int(a.bias, p.bias_dtype, f0 + 3));
+        }
+        const float4 q4 = p.quantization ? __ldg(reinterpret_cast<const float4*>(a.quant) + c4) : make_float4(1.0f, 1.0f, 1.0f, 1.0f);
         // the kCols input columns under the pixel pair: byte offsets inside a row, -1 for a column outside the input
         const int ix0 = x0 * kStride - p.pad_x;
         int co[kCols];
@@ -372,34 +393,13 @@ template <bool kUnsignedIn, int kStride>
 __global__ void __launch_bounds__(256, kStride == 1 ? 3 : 2)
 conv_i8_dwcol_kernel(const __grid_constant__ cldnn_b200_conv_params p, const __grid_constant__ EpiCfg c, const __grid_constant__ Dw16Args a)
 {
-    extern __shared__ uint4 s_dw[];
-    constexpr int kCols = kStride + 3;
-    const int C = p.out.f, c4n = C / 4;
-    uint4* s_w = s_dw;                                               // [tap][k][C / 16], as in the 16-feature kernel
-    int32_t* s_bias = reinterpret_cast<int32_t*>(s_dw + 9 * c4n);
-    float* s_quant = reinterpret_cast<float*>(s_bias + C);
-    __shared__ uint32_t s_wide;
-    if (threadIdx.x == 0) s_wide = 0u;
-    __syncthreads();
-    for (int i = threadIdx.x; i < 9 * c4n; i += blockDim.x) {
-        const int tap = i / c4n, r = i - tap * c4n;
-        s_w[(tap * 4 + (r & 3)) * a.c16n + (r >> 2)] = __ldg(reinterpret_cast<const uint4*>(a.wmask) + i);
-    }
-    bool wide = false;
-    for (int f = threadIdx.x; f < C; f += blockDim.x) {
-        const int32_t bi = (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? load_as_int(a.bias, p.bias_dtype, f) : 0;
-        const float q = p.quantization ? a.quant[f] : 1.0f;
-        s_bias[f] = bi; s_quant[f] = q;
-        wide = wide || !(__fmul_rn(__fmul_rn(__fadd_rn(a.acc_bound, fabsf((float)bi)), fabsf(q)), a.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f);
-    }
-    if (wide) atomicOr(&s_wide, 1u);
-    __syncthreads();
-    // the epilogue variant is uniform over the CTA: chosen once, so that the row loop is straight-line code
-    const int mode = (a.lean && !s_wide) ? (p.out.dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
-    if (mode == 0) { if (a.mul_oqf) dwcol_items<kUnsignedIn, kStride, 0, true>(p, c, a, s_w, s_bias, s_quant); else dwcol_items<kUnsignedIn, kStride, 0, false>(p, c, a, s_w, s_bias, s_quant); }
-    else if (mode == 1) { if (a.mul_oqf) dwcol_items<kUnsignedIn, kStride, 1, true>(p, c, a, s_w, s_bias, s_quant); else dwcol_items<kUnsignedIn, kStride, 1, false>(p, c, a, s_w, s_bias, s_quant); }
-    else if (mode == 2) dwcol_items<kUnsignedIn, kStride, 2, false>(p, c, a, s_w, s_bias, s_quant);
-    else dwcol_items<kUnsignedIn, kStride, 3, false>(p, c, a, s_w, s_bias, s_quant);
+    // the epilogue variant is uniform over the launch: chosen once, so that the row loop is straight-line code
+    const bool wide = __ldg(a.wide_flag) != 0u;
+    const int mode = (a.lean && !wide) ? (p.out.dtype == CLDNN_B200_U8 ? 0 : (c.act == CLDNN_B200_ACT_RELU ? 2 : 1)) : 3;
+    if (mode == 0) { if (a.mul_oqf) dwcol_items<kUnsignedIn, kStride, 0, true>(p, c, a); else dwcol_items<kUnsignedIn, kStride, 0, false>(p, c, a); }
+    else if (mode == 1) { if (a.mul_oqf) dwcol_items<kUnsignedIn, kStride, 1, true>(p, c, a); else dwcol_items<kUnsignedIn, kStride, 1, false>(p, c, a); }
+    else if (mode == 2) dwcol_items<kUnsignedIn, kStride, 2, false>(p, c, a);
+    else dwcol_items<kUnsignedIn, kStride, 3, false>(p, c, a);
 }
 
 bool dw_plan(const cldnn_b200_conv_params& p, std::string* why)
@@ -446,7 +446,7 @@ int dw_tune_count(const void* vp) { return dwcol_ok(simplified_conv_params(*(con
 size_t dw_scratch(const void* vp)
 {
     const auto& p = *(const cldnn_b200_conv_params*)vp;
-    return dw16_ok(p) ? (size_t)p.kh * p.kw * p.groups * 4 : 0;
+    return dw16_ok(p) ? (size_t)p.kh * p.kw * p.groups * 4 + 16 : 0;     // the weight words, then the range flag of the column-walk kernel
 }
 
 int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
@@ -476,6 +476,13 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
         const int taps_c = p.kh * p.kw * p.groups;
         dw_pack_weights<<<(taps_c + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_py, p.w_px, p.w_offset, p.groups, p.kh, p.kw, (uint32_t*)a->scratch);
         B200_CUDA(cudaGetLastError());
+        uint32_t* flag = reinterpret_cast<uint32_t*>((char*)a->scratch + (size_t)taps_c * 4);
+        B200_CUDA(cudaMemsetAsync(flag, 0, 16, ctx->stream));
+        dw_wide_flag<<<(p.groups + 255) / 256, 256, 0, ctx->stream>>>(a->bias, p.bias_dtype, (p.bias_dtype != CLDNN_B200_NONE && !c.dont_dequantize_bias) ? 1 : 0,
+                                                                   a->weights_quantization_factors, p.quantization, d.acc_bound,
+                                                                   d.mul_oqf ? fabsf(p.o_qf) : 1.0f, p.groups, flag);
+        B200_CUDA(cudaGetLastError());
+        d.wide_flag = flag;
         const size_t smem = (size_t)taps_c * 4 + (size_t)p.groups * 8;
         if (smem > 48 * 1024) {
             // the limit is shared by every prepared launch of the function on this device: it only ever grows
@@ -491,15 +498,12 @@ int32_t dw_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_ar
             const int64_t col_items = per_row_strip * d.strips;
             if (col_items < 0x7fffffffLL) {
                 d.col_items = (uint32_t)col_items;
-                auto set_smem = [&](auto kern) { return raise_smem_limit((const void*)kern, ctx->device, smem); };
-                B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<true, 2>));
-                B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 1>)); B200_CUDA(set_smem(conv_i8_dwcol_kernel<false, 2>));
                 int64_t cblocks = (col_items + 255) / 256; const int64_t ccap = (int64_t)ctx->prop.multiProcessorCount * 8;
                 if (cblocks > ccap) cblocks = ccap;
                 const int cgrid = (int)cblocks; const int stride = p.stride_x;
-                out->fn = [p, c, d, cgrid, smem, uns_in, stride](cudaStream_t s) {
-                    if (uns_in) { if (stride == 1) conv_i8_dwcol_kernel<true, 1><<<cgrid, 256, smem, s>>>(p, c, d); else conv_i8_dwcol_kernel<true, 2><<<cgrid, 256, smem, s>>>(p, c, d); }
-                    else { if (stride == 1) conv_i8_dwcol_kernel<false, 1><<<cgrid, 256, smem, s>>>(p, c, d); else conv_i8_dwcol_kernel<false, 2><<<cgrid, 256, smem, s>>>(p, c, d); }
+                out->fn = [p, c, d, cgrid, uns_in, stride](cudaStream_t s) {
+                    if (uns_in) { if (stride == 1) conv_i8_dwcol_kernel<true, 1><<<cgrid, 256, 0, s>>>(p, c, d); else conv_i8_dwcol_kernel<true, 2><<<cgrid, 256, 0, s>>>(p, c, d); }
+                    else { if (stride == 1) conv_i8_dwcol_kernel<false, 1><<<cgrid, 256, 0, s>>>(p, c, d); else conv_i8_dwcol_kernel<false, 2><<<cgrid, 256, 0, s>>>(p, c, d); }
                     return cudaGetLastError();
                 };
                 out->launches = 1;
