@@ -137,9 +137,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 conv_f16_tc_kernel(const __grid_constant__ Params P)
 {
     constexpr int NBUF = BN >= 256 ? 2 : 4;                          // fp32 accumulators: BN columns each, 512 in all
-    constexpr int NSTG = 2;                                          // staging tiles of 128 x BN halves
-    constexpr int COLB = BN / 64;
-    constexpr uint32_t kStagingBytes = (uint32_t)(kBM * BN * 2);
+    // Staging goes by units of up to 128 features (32 KiB): a 256-feature tile is converted and stored in two halves through
+    // the same two unit buffers, which leaves 64 KiB more of shared memory to the operand ring than whole-tile staging would
+    // (the deep layers are bound by the bytes the ring keeps in flight, not by the epilogue).  Each epilogue group owns one unit
+    // buffer and fills it for the halves of its tiles in turn (use n = (local tile / 2) * UNITS + half, barrier parity n & 1):
+    // every use of a buffer waits for the use directly before it, by the same group, so a parity wait can never be two
+    // phases ahead of its barrier.  The store and residual warps serve the units in the order
+    // (tile i, half 0), (tile i + 1, half 0), (tile i, half 1), (tile i + 1, half 1), i even, which keeps each buffer's order.
+    constexpr int NSTG = 2;                                          // unit buffers = epilogue groups
+    constexpr int UNITS = BN > 128 ? BN / 128 : 1;                   // units per tile
+    constexpr int UW = BN / UNITS;                                   // features per unit
+    constexpr int COLB = UW / 64;                                    // 64-half column blocks per unit
+    constexpr uint32_t kStagingBytes = (uint32_t)(kBM * UW * 2);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -257,48 +266,62 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
         // ------------------------------ TMA store issuer --------------------------
         {
             const bool leader = elect_one();                           // issues, commits and waits for the stores: bulk groups are per thread
-            int t = 0;
-            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
-                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
-                const int a = t % NSTG;
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->out_ready[a]), ((uint32_t)(t / NSTG) & 1u), s_abort, P.status, kErr + 3u))) break;
-                if (!leader) continue;
-                int tw = 0, th = 0, tb = 0;
-                if (boxed) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
+            bool alive = true;
+            for (int i0 = 0; alive && (int64_t)blockIdx.x + (int64_t)i0 * gridDim.x < P.total_tiles; i0 += 2) {
+                for (int h = 0; h < UNITS && alive; ++h) {
+                    for (int g = 0; g < 2 && alive; ++g) {
+                        const int64_t tile64 = (int64_t)blockIdx.x + (int64_t)(i0 + g) * gridDim.x;
+                        if (tile64 >= P.total_tiles) break;
+                        const int tile = (int)tile64;
+                        const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
+                        const int n = (i0 >> 1) * UNITS + h;               // this buffer's use count
+                        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->out_ready[g]), (uint32_t)n & 1u, s_abort, P.status, kErr + 3u))) { alive = false; break; }
+                        if (!leader) continue;
+                        int tw = 0, th = 0, tb = 0;
+                        if (boxed) { tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; th = t2 % P.tiles_h; tb = t2 / P.tiles_h; }
 #pragma unroll
-                for (int cb = 0; cb < COLB; ++cb) {
-                    const int f0 = n_tile * BN + cb * 64;
-                    if (f0 >= P.ofm) break;
-                    const uint32_t src = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * 128);
-                    if (boxed) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
-                    else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
+                        for (int cb = 0; cb < COLB; ++cb) {
+                            const int f0 = n_tile * BN + h * UW + cb * 64;
+                            if (f0 >= P.ofm) break;
+                            const uint32_t src = smem_u32(staging) + (uint32_t)g * kStagingBytes + (uint32_t)(cb * kBM * 128);
+                            if (boxed) tma_store_4d(&P.tmO, src, f0, tw * P.bw, th * P.bh, tb * P.bb);
+                            else tma_store_2d(&P.tmO, src, f0, m_tile * kBM);
+                        }
+                        bulk_commit();
+                        bulk_wait_read0();
+                        mbar_arrive(smem_u32(&aux->stage_free[g]));
+                    }
                 }
-                bulk_commit();
-                bulk_wait_read0();
-                mbar_arrive(smem_u32(&aux->stage_free[a]));
             }
         }
     } else if (warp == 3) {
         // ------------------------------ residual loader ---------------------------
         if (kFused) {
             const bool leader = elect_one();
-            int t = 0;
-            for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x, ++t) {
-                const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
-                int o_w = 0, o_h = 0, c_n = 0;
-                if (boxed) { const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb; }
-                const int a = t % NSTG;
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->stage_free[a]), (((uint32_t)(t / NSTG) & 1u)) ^ 1u, s_abort, P.status, kErr + 4u))) break;
-                if (!leader) continue;
-                const uint32_t rf = smem_u32(&aux->res_full[a]);
-                int cbs = 0;
-                for (int cb = 0; cb < COLB; ++cb) if (n_tile * BN + cb * 64 < P.ofm) ++cbs;
-                mbar_expect_tx(rf, (uint32_t)(P.stage_rows * 128 * cbs));
-                for (int cb = 0; cb < cbs; ++cb) {
-                    const uint32_t dst = smem_u32(staging) + (uint32_t)a * kStagingBytes + (uint32_t)(cb * kBM * 128);
-                    const int f0 = n_tile * BN + cb * 64;
-                    if (boxed) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
-                    else tma_load_2d(dst, &P.tmE, rf, f0, m_tile * kBM);
+            bool alive = true;
+            for (int i0 = 0; alive && (int64_t)blockIdx.x + (int64_t)i0 * gridDim.x < P.total_tiles; i0 += 2) {
+                for (int h = 0; h < UNITS && alive; ++h) {
+                    for (int g = 0; g < 2 && alive; ++g) {
+                        const int64_t tile64 = (int64_t)blockIdx.x + (int64_t)(i0 + g) * gridDim.x;
+                        if (tile64 >= P.total_tiles) break;
+                        const int tile = (int)tile64;
+                        const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
+                        int o_w = 0, o_h = 0, c_n = 0;
+                        if (boxed) { const int tw = m_tile % P.tiles_w; const int t2 = m_tile / P.tiles_w; o_w = tw * P.bw; o_h = (t2 % P.tiles_h) * P.bh; c_n = (t2 / P.tiles_h) * P.bb; }
+                        const int n = (i0 >> 1) * UNITS + h;
+                        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->stage_free[g]), ((uint32_t)n & 1u) ^ 1u, s_abort, P.status, kErr + 4u))) { alive = false; break; }
+                        if (!leader) continue;
+                        const uint32_t rf = smem_u32(&aux->res_full[g]);
+                        int cbs = 0;
+                        for (int cb = 0; cb < COLB; ++cb) if (n_tile * BN + h * UW + cb * 64 < P.ofm) ++cbs;
+                        mbar_expect_tx(rf, (uint32_t)(P.stage_rows * 128 * cbs));
+                        for (int cb = 0; cb < cbs; ++cb) {
+                            const uint32_t dst = smem_u32(staging) + (uint32_t)g * kStagingBytes + (uint32_t)(cb * kBM * 128);
+                            const int f0 = n_tile * BN + h * UW + cb * 64;
+                            if (boxed) tma_load_4d(dst, &P.tmE, rf, f0, o_w, o_h, c_n);
+                            else tma_load_2d(dst, &P.tmE, rf, f0, m_tile * kBM);
+                        }
+                    }
                 }
             }
         }
@@ -313,7 +336,7 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
         int t = group;
         for (int tile = blockIdx.x + group * gridDim.x; tile < P.total_tiles && ok; tile += kGroups * gridDim.x, t += kGroups) {
             const int n_tile = tile / P.m_tiles;
-            const int acc = t % NBUF, sb = t % NSTG;
+            const int acc = t % NBUF;
             if (n_tile != cur_n_tile) {
                 named_bar_sync(1 + group, 128);
                 for (int j = gt; j < BN; j += 128) {
@@ -326,27 +349,30 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
                 cur_n_tile = n_tile;
             }
             if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), (uint32_t)(t / NBUF) & 1u, s_abort, P.status, kErr + 5u)) { ok = false; break; }
-            const bool got = kFused ? mbar_wait(smem_u32(&aux->res_full[sb]), (uint32_t)(t / NSTG) & 1u, s_abort, P.status, kErr + 6u)
-                                    : mbar_wait(smem_u32(&aux->stage_free[sb]), ((uint32_t)(t / NSTG) & 1u) ^ 1u, s_abort, P.status, kErr + 6u);
-            if (!got) { ok = false; break; }
-            tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
-            uint8_t* stg = staging + (size_t)sb * kStagingBytes;
             const float* bias = aux->bias[group];
+            for (int h = 0; h < UNITS && ok; ++h) {
+                const int n = (t >> 1) * UNITS + h, sb = group;       // this group's buffer, its use count
+                const bool got = kFused ? mbar_wait(smem_u32(&aux->res_full[sb]), (uint32_t)n & 1u, s_abort, P.status, kErr + 6u)
+                                        : mbar_wait(smem_u32(&aux->stage_free[sb]), ((uint32_t)n & 1u) ^ 1u, s_abort, P.status, kErr + 6u);
+                if (!got) { ok = false; break; }
+                tc_fence_after();
+                uint8_t* stg = staging + (size_t)sb * kStagingBytes;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32(t_row + (uint32_t)c0, r);
-                tmem_ld_wait();
-                if (c0 + 32 >= BN) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc])); }
-                if (n_tile * BN + c0 >= P.ofm) continue;
-                uint4* p[4];
-                chunk_ptrs(stg, row, sw, c0, p);
-                chunk32<kFused>(P, r, bias + c0, p);
+                for (int c0 = h * UW; c0 < (h + 1) * UW; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(t_row + (uint32_t)c0, r);
+                    tmem_ld_wait();
+                    if (c0 + 32 >= BN) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(smem_u32(&aux->tmem_empty[acc])); }
+                    if (n_tile * BN + c0 >= P.ofm) continue;
+                    uint4* p[4];
+                    chunk_ptrs(stg, row, sw, c0 - h * UW, p);
+                    chunk32<kFused>(P, r, bias + c0, p);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->out_ready[sb]));
             }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&aux->out_ready[sb]));
         }
     }
     tc_fence_before();
@@ -441,8 +467,6 @@ static bool f16_plan(const cldnn_b200_conv_params& p, F16Plan& pl, std::string* 
     if (mode == f16tc::A_TILED && !tiled_ok) return no("tiled addressing needs stride 1 or a pointwise filter");
     if (mode == f16tc::A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded (or tensor below 128 KiB)");
     if (bn == 0) bn = p.ofm > 128 ? 256 : (p.ofm > 64 ? 128 : 64);
-    // two staging tiles of 128 x 256 halves leave room for 24 KiB stages only: halve the channel chunk there
-    if (bn == 256 && pl.bk == 128) pl.bk = 64;
     pl.a_mode = mode; pl.bn = bn; pl.bw = pl.bh = pl.bb = 1;
     if (mode == f16tc::A_TILED) f16_choose_box(p.out.x, p.out.y, p.out.b, pl.bw, pl.bh, pl.bb);
     // TMA needs the flat output / residual views pixel-dense; the tiled mode takes pitches
@@ -545,7 +569,7 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
 
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
-    const size_t staging_total = (size_t)2 * f16tc::kBM * pl.bn * 2;
+    const size_t staging_total = (size_t)2 * f16tc::kBM * (pl.bn > 128 ? 128 : pl.bn) * 2;   // two unit buffers of up to 128 features
     const size_t aux_bytes = sizeof(f16tc::Aux);
     if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_f16_tc: not enough shared memory");
     int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);
@@ -623,7 +647,6 @@ int32_t f16_batched_gemm_prepare(cldnn_b200_ctx_impl* ctx, const void* A, const 
     F16Plan pl{}; pl.a_mode = f16tc::A_FLAT; pl.bw = pl.bh = pl.bb = 1;
     pl.bn = ofm > 128 ? 256 : (ofm > 64 ? 128 : 64);
     pl.bk = cs % 64 == 0 ? 128 : (cs % 32 == 0 ? 64 : 32);
-    if (pl.bn == 256 && pl.bk == 128) pl.bk = 64;
     Params P{};
     P.a_mode = f16tc::A_FLAT; P.N = 1; P.P = 1; P.Q = batches * rows;
     P.kh = P.kw = 1; P.stride_x = P.stride_y = P.dil_x = P.dil_y = 1;
@@ -645,7 +668,7 @@ int32_t f16_batched_gemm_prepare(cldnn_b200_ctx_impl* ctx, const void* A, const 
     P.status = ctx->d_status;
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
-    const size_t staging_total = (size_t)2 * f16tc::kBM * pl.bn * 2;
+    const size_t staging_total = (size_t)2 * f16tc::kBM * (pl.bn > 128 ? 128 : pl.bn) * 2;   // two unit buffers of up to 128 features
     const size_t aux_bytes = sizeof(f16tc::Aux);
     if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_f16_tc: not enough shared memory");
     int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);
