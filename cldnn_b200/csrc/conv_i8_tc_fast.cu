@@ -555,7 +555,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                     const int32_t bi = (real && c.bias_dtype != CLDNN_B200_NONE) ? ((const int32_t*)P.bias)[f] : 0;
                     const float q = real ? P.quant[f] : 1.0f;
                     aux->bias_i[group][j] = bi; aux->quant[group][j] = q;
-                    w = w || !(__fmul_rn(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)), oqf_abs) < 4.0e6f);
+                    // (columns past the last feature hold zero accumulators: they cannot leave the range, whatever O_QF is)
+                    w = w || (real && !(__fmul_rn(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)), oqf_abs) < 4.0e6f));
                 }
                 w = __any_sync(0xffffffffu, w);
                 if (lane == 0) aux->wide[group][quad] = w ? 1u : 0u;
