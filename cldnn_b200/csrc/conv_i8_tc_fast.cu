@@ -114,27 +114,27 @@ __device__ __forceinline__ void fast_chunk_ptrs(uint8_t* stg, int row, uint32_t 
     p1 = reinterpret_cast<uint4*>(rowp + (((((uint32_t)o >> 4) + 1u) ^ sw) << 4));
 }
 
-// One 32-row quadrant of a tile, all BN feature columns.
-// (The last feature tile of a ragged feature count is converted in full: its surplus columns hold zero accumulators and
-// neutral constants, and the store clips them.)
+// One 32-row quadrant of a tile, feature columns 0 .. c_hi - 1 (c_hi: BN, or for the last feature tile of a ragged feature
+// count the real columns rounded up to the loop's granularity: the surplus columns inside that hold zero accumulators and
+// neutral constants, the columns beyond it are not converted at all, and the store clips both).
 template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
                                           uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f,
-                                          bool pair = false)
+                                          bool pair = false, int c_hi = BN)
 {
     const int32_t* bias = aux->bias_i[group];
     const float* quant = aux->quant[group];
     uint32_t ra[32], rb[32];
     tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 64) {
+    for (int c0 = 0; c0 < c_hi; c0 += 64) {
         uint4 *p0, *p1;
         tmem_ld_wait();
         tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);             // in flight while `ra` is converted
         fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
         fast_chunk32<kFused, kRelu1, kOut, kOqf>(ra, bias + c0, quant + c0, p0, p1, e_xor, k_pos, k_neg, oqf);
         tmem_ld_wait();
-        if (c0 + 64 < BN) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
+        if (c0 + 64 < c_hi) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
         else {
             // the accumulator has been read out: the MMA issuer may reuse it
             tc_fence_before();
@@ -151,18 +151,18 @@ __device__ __forceinline__ void fast_tile(const FastAux* aux, int group, uint32_
 template <int BN, bool kFused, bool kRelu1, int kOut, bool kOqf = false>
 __device__ __forceinline__ void fast_tile_single(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
                                                  uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf = 1.0f,
-                                                 bool pair = false)
+                                                 bool pair = false, int c_hi = BN)
 {
     const int32_t* bias = aux->bias_i[group];
     const float* quant = aux->quant[group];
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
+    for (int c0 = 0; c0 < c_hi; c0 += 32) {
         uint32_t r[32];
         uint4 *p0, *p1;
         tmem_ld_32x32(t_row + (uint32_t)c0, r);
         fast_chunk_ptrs<BN>(stg, row, sw, c0, p0, p1);
         tmem_ld_wait();
-        if (c0 + 32 >= BN) {
+        if (c0 + 32 >= c_hi) {
             // the accumulator has been read out: the MMA issuer may reuse it
             tc_fence_before();
             __syncwarp();
@@ -175,18 +175,18 @@ __device__ __forceinline__ void fast_tile_single(const FastAux* aux, int group, 
 // The variants with a uniform O_QF stay out of line, so that the common ones keep their registers and code layout.
 template <int BN, bool kFused, int kOut, int G>
 __device__ __noinline__ void fast_tile_oqf(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                           uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf, bool pair)
+                                           uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, float oqf, bool pair, int c_hi)
 {
-    if (G > 2) fast_tile_single<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf, pair);
-    else fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf, pair);
+    if (G > 2) fast_tile_single<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf, pair, c_hi);
+    else fast_tile<BN, kFused, false, kOut, true>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, oqf, pair, c_hi);
 }
 // two register buffers with two groups, one with four
 template <int BN, bool kFused, bool kRelu1, int kOut, int G>
 __device__ __forceinline__ void fast_tile_any(const FastAux* aux, int group, uint32_t t_row, uint8_t* stg, int row, uint32_t sw,
-                                              uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, bool pair)
+                                              uint32_t tmem_empty_bar, int lane, uint32_t e_xor, int32_t k_pos, int32_t k_neg, bool pair, int c_hi)
 {
-    if (G > 2) fast_tile_single<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, 1.0f, pair);
-    else fast_tile<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, 1.0f, pair);
+    if (G > 2) fast_tile_single<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, 1.0f, pair, c_hi);
+    else fast_tile<BN, kFused, kRelu1, kOut>(aux, group, t_row, stg, row, sw, tmem_empty_bar, lane, e_xor, k_pos, k_neg, 1.0f, pair, c_hi);
 }
 
 // The same tile in float arithmetic, element by element (fused residual only):
@@ -574,31 +574,34 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
             uint8_t* stg = staging + (size_t)sb * kStagingBytes;
             const uint32_t te = kPair ? mapa_rank(smem_u32(&aux->tmem_empty[acc]), 0u) : smem_u32(&aux->tmem_empty[acc]);
+            // columns to convert: all of the tile, or the real ones of a ragged last feature tile in whole loop trips
+            const int real_cols = P.ofm - n_tile * BN;
+            const int c_hi = real_cols >= BN ? BN : ((real_cols + (G > 2 ? 31 : 63)) & ~(G > 2 ? 31 : 63));
             if (wide) fast_tile_wide<BN>(P, aux, group, t_row, stg, row, sw, te, lane, kPair);
             else if (with_oqf) {
                 // u8 or plain s8 output, no ReLU between convolution and residual sum (the host admits nothing else here)
                 if (kFused) {
-                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
-                    else fast_tile_oqf<BN, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair, c_hi);
+                    else fast_tile_oqf<BN, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair, c_hi);
                 } else {
-                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
-                    else fast_tile_oqf<BN, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair);
+                    if ((variant >> 1) == 0) fast_tile_oqf<BN, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair, c_hi);
+                    else fast_tile_oqf<BN, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, oqf, kPair, c_hi);
                 }
             }
             else if (kFused) {
                 switch (variant) {
-                    case 0: fast_tile_any<BN, true, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    case 1: fast_tile_any<BN, true, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    case 2: fast_tile_any<BN, true, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    case 3: fast_tile_any<BN, true, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    case 4: fast_tile_any<BN, true, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    default: fast_tile_any<BN, true, true, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 0: fast_tile_any<BN, true, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    case 1: fast_tile_any<BN, true, true, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    case 2: fast_tile_any<BN, true, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    case 3: fast_tile_any<BN, true, true, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    case 4: fast_tile_any<BN, true, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    default: fast_tile_any<BN, true, true, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
                 }
             } else {
                 switch (variant >> 1) {
-                    case 0: fast_tile_any<BN, false, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    case 1: fast_tile_any<BN, false, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
-                    default: fast_tile_any<BN, false, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair); break;
+                    case 0: fast_tile_any<BN, false, false, 0, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    case 1: fast_tile_any<BN, false, false, 1, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
+                    default: fast_tile_any<BN, false, false, 2, G>(aux, group, t_row, stg, row, sw, te, lane, e_xor, k_pos, k_neg, kPair, c_hi); break;
                 }
             }
             fence_async_smem();
