@@ -50,6 +50,9 @@ I8_CASES = {
     "3x3_k256_sum": (dict(N=50, C=32, K=256, H=56, W=56), SUM,
                      [(7, 128), (11, 128), (27, 128), (8, 256), (12, 256), (28, 256), (19, 128), (24, 256), (35, 128), (39, 128), (43, 128),
                       (47, 128), (48, 256), (49, 128), (50, 256)]),
+    # long reduction into 256-feature tiles without a residual: the output goes out by 128-feature units through one buffer
+    "3x3_k256_plain_u8": (dict(N=50, C=32, K=256, H=56, W=56), dict(out_dtype=np.uint8),
+                          [(8, 256), (12, 256), (48, 256), (50, 256), (7, 128)]),
     "1x1_k128_sum": (dict(N=200, C=32, K=128, H=56, W=56, kh=1, kw=1, pad=0), SUM,
                      [(2, 64), (3, 128), (14, 64), (15, 128), (30, 64), (31, 128), (45, 128)]),
     "1x1_k512_sum_s8res": (dict(N=256, C=64, K=512, H=28, W=28, kh=1, kw=1, pad=0),
