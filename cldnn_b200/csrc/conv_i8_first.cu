@@ -22,6 +22,7 @@
 #include "engine.hpp"
 #include "sm100_ptx.cuh"
 #include "conv_epilogue.cuh"
+#include "conv_i8_first_rows.hpp"
 
 namespace b200 {
 
@@ -387,12 +388,24 @@ static bool first_plan(const cldnn_b200_conv_params& p, std::string* why)
     if (p.ifm * patch_h * patch_wp / 4 > 128 * 9) return no("the input patch of one tile is too large");
     return true;
 }
-static bool first_supports(const void* vp) { return first_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
+constexpr int kTuneRows = 4;
+static bool first_supports(const void* vp)
+{
+    const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
+    if (p.tune == kTuneRows) return first_rows_plan(simplified_conv_params(p), nullptr);
+    return first_plan(p, nullptr);
+}
 // tune 0 / 2: as many CTAs per SM as fit (at most two), 1: one CTA per SM with the double-buffered epilogue,
-// 3: up to three CTAs per SM (72 registers per thread: more warps against the latency of the patch loads)
-static int first_tune_count(const void*) { return 4; }
+// 3: up to three CTAs per SM (72 registers per thread: more warps against the latency of the patch loads),
+// 4: the row form (conv_i8_first_rows.cu: output rows as GEMM rows, the raw image as the TMA-loaded operand)
+static int first_tune_count(const void*) { return 5; }
 static int first_kp(const cldnn_b200_conv_params& p) { return (p.ifm * p.kh * 8 + 31) / 32 * 32; }
-static size_t first_scratch(const void* vp) { const auto& p = *(const cldnn_b200_conv_params*)vp; return (size_t)p.ofm * first_kp(p); }
+static size_t first_scratch(const void* vp)
+{
+    const auto& p = *(const cldnn_b200_conv_params*)vp;
+    if (p.tune == kTuneRows) return first_rows_scratch(p);
+    return (size_t)p.ofm * first_kp(p);
+}
 
 // Validates the arguments and fills the launch constants; `wpacked` is where the packed weights will live.
 static int32_t first_setup(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p_in, const cldnn_b200_args* a, void* wpacked, size_t wpacked_bytes,
@@ -471,6 +484,7 @@ static cudaError_t first_pack(const cldnn_b200_conv_params& p, const cldnn_b200_
 static int32_t first_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
     const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
+    if (p.tune == kTuneRows) return first_rows_prepare(ctx, p, a, out);
     FirstParams P; int grid = 0; size_t smem = 0;
     const int32_t st = first_setup(ctx, p, a, a->scratch, a->scratch_bytes, P, grid, smem);
     if (st != CLDNN_B200_SUCCESS) return st;

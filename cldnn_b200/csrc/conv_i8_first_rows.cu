@@ -1,0 +1,419 @@
+// conv_i8_first, row form: the first convolution of an 8-bit image network (few planar input features, stride 2,
+// 64 output features) as a GEMM whose rows are OUTPUT ROWS and whose operand is the raw image, so that no thread
+// ever assembles an im2col operand:
+//
+//   D[y, (i, f)] = sum over (ky, c)  A_(ky,c)[y, 0..31] . T_(ky,c)[(i, f), 0..31]
+//
+// for the four output columns x = 4j + i of one "x-block" j.  A_(ky,c)[y, :] are 32 consecutive bytes of input row
+// 2y + ky - pad_y of feature c, starting at a 16-byte aligned column u(j) -- exactly what one TMA box of 32 bytes x
+// 128 rows x C features delivers (every second row through the row pitch, zero fill outside the image = the padding).
+// T_(ky,c) is the filter row (ky, c) laid out as a banded (Toeplitz) matrix: T[(i, f), k] = w[f][c][ky][k - off - 2i].
+// The window of 32 columns holds the 13 + (kw - 7) the four outputs need at offset `off`, which depends only on the
+// parity of j (13 and 5 for a 7-wide filter with padding 3): two variants of T, and a CTA works on x-blocks of one
+// parity only, so it keeps one variant resident in shared memory (C * kh * 8 KB; 168 KB for 7x7x3).
+// The tensor core multiplies ~4.6 x the taps that exist (32-column window for a 7-tap filter); in exchange the
+// per-tile work of the general first-layer kernel's four builder warps disappears, and what remains per tile of
+// 128 rows x 4 columns is C * kh MMAs (M 128, N 256, K 32), kh TMA copies and the requantising epilogue.
+//
+// Roles: warp 0 issues the copies, warp 1 the MMAs, warps 4..11 are two epilogue groups taking tiles in turn (one
+// accumulator of 256 columns each).  The operation order of the epilogue is the reference's
+// (kernel_selector/core/cl_kernels/fused_conv_eltwise_gpu_ref.cl:65-234); it is the conversion-free form of
+// conv_epilogue.cuh, with the float-domain form per value where a feature's range demands it.
+#include <cuda.h>
+#include <mutex>
+#include <string>
+#include "engine.hpp"
+#include "sm100_ptx.cuh"
+#include "conv_epilogue.cuh"
+#include "conv_i8_first_rows.hpp"
+
+namespace b200 {
+
+using namespace ptx;
+
+constexpr int kRThreads = 384;
+constexpr int kRMaxStages = 4;
+constexpr int kRCols = 256;                     // four output columns x 64 features
+constexpr int kROfm = 64;
+constexpr uint32_t kErrRows = 0x58u;
+
+struct RowsParams {
+    alignas(64) CUtensorMap tmA[2];             // input rows of even / odd index
+    alignas(64) CUtensorMap tmB;                // banded filter rows, both variants
+    int32_t N, C, P, Q, kh, ofm;
+    int32_t tiles_y, jcount[2], total[2];       // x-blocks of even / odd index per row of tiles, tiles per variant
+    int32_t u0[2];                              // window start of the first x-block of each parity
+    int32_t row_q[16], row_r[16];               // filter row ky reads input rows 2 (y + row_q) + row_r
+    int32_t stages, a_chan_bytes, a_stage_bytes, b_bytes;   // one feature's rows of a stage (box rows x 32), C of them, the filter image
+    int32_t st32;                                       // output rows are 32-byte aligned: one 32-byte store per 32 features
+    uint32_t idesc;
+    int64_t out_px, out_py, out_pb, out_off;
+    int32_t mul_oqf, mode;                      // mode: 0 u8, 1 s8, 2 s8 after ReLU; +4 with a uniform O_QF
+    float acc_bound;
+    uint8_t* out; const void* bias; const float* quant;
+    uint32_t* status;
+    EpiCfg epi;
+};
+
+struct RowsAux {
+    uint64_t full[kRMaxStages], empty[kRMaxStages], tmem_full[2], tmem_empty[2], b_full, drain;
+    uint32_t tmem_base, abort, wide;
+    alignas(16) int32_t bias_i[kROfm];
+    alignas(16) float quant[kROfm];
+};
+
+// filter [ofm][C][kh][kw] (any pitches) -> [variant][ky * C + c][n = i * 64 + f][k = 0..31], zero outside the band
+__global__ void rows_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t pi, int64_t py, int64_t px, int64_t off,
+                                  int C, int kh, int kw, int off0, int off1, uint8_t* __restrict__ dst)
+{
+    const int chunks = C * kh;
+    const int total = 2 * chunks * kRCols * 32;
+    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const int k = idx & 31; int r = idx >> 5;
+        const int n = r % kRCols; r /= kRCols;
+        const int g = r % chunks; const int v = r / chunks;
+        const int ky = g / C, c = g - ky * C;
+        const int i = n / kROfm, f = n - i * kROfm;
+        const int kx = k - (v ? off1 : off0) - 2 * i;
+        int8_t val = 0;
+        if (kx >= 0 && kx < kw) val = w[off + f * po + c * pi + ky * py + kx * px];
+        dst[idx] = (uint8_t)val;
+    }
+}
+
+struct RowsTile { int n, ty, j, jv; };
+__device__ __forceinline__ RowsTile rows_tile(const RowsParams& P, int v, int t)
+{
+    RowsTile r;
+    r.jv = t % P.jcount[v]; const int rest = t / P.jcount[v];
+    r.ty = rest % P.tiles_y; r.n = rest / P.tiles_y;
+    r.j = 2 * r.jv + v;
+    return r;
+}
+
+// 32 accumulator columns of one row, float-domain form (features whose values may leave the exact range of the other)
+__device__ __noinline__ void rows_chunk_wide(const EpiCfg& c, const RowsAux* aux, const uint32_t (&r)[32], int f0, uint8_t* dst)
+{
+    alignas(16) uint8_t b[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const float v = epi_quant(c, (int32_t)r[j] + aux->bias_i[f0 + j], aux->quant[f0 + j], 0.0f, 1.0f, 0.0f, 1.0f);
+        const int32_t i = __float2int_rz(v);
+        b[j] = c.out_dtype == CLDNN_B200_U8 ? (uint8_t)min(255, max(0, i)) : (uint8_t)(int8_t)min(127, max(-128, i));
+    }
+    reinterpret_cast<uint4*>(dst)[0] = reinterpret_cast<const uint4*>(b)[0];
+    reinterpret_cast<uint4*>(dst)[1] = reinterpret_cast<const uint4*>(b)[1];
+}
+
+// 32 output bytes of one pixel: one 32-byte store (a whole sector) where the address allows it
+__device__ __forceinline__ void rows_store32(uint8_t* p, const uint4& a, const uint4& b, bool st32)
+{
+    if (st32) asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" :: "l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+    else { reinterpret_cast<uint4*>(p)[0] = a; reinterpret_cast<uint4*>(p)[1] = b; }
+}
+
+template <int kMode, bool kOqf>
+__device__ __forceinline__ void rows_epi_tile(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
+                                              uint32_t tmem_empty_bar, int lane)
+{
+    const float oqf = P.epi.o_qf;
+    const bool st32 = P.st32 != 0;
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32(t_row, ra);
+#pragma unroll 1
+    for (int c0 = 0; c0 < kRCols; c0 += 64) {
+        const int i = c0 >> 6;                                   // output column of the x-block
+        const bool ok = row_ok && i < x_left;
+        uint8_t* px = out_row + (int64_t)i * P.out_px;
+        tmem_ld_wait();
+        tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);
+        if (ok) { uint4 o0, o1; fast_chunk32<false, false, kMode, kOqf>(ra, &aux->bias_i[0], &aux->quant[0], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf); rows_store32(px, o0, o1, st32); }
+        tmem_ld_wait();
+        if (c0 + 64 < kRCols) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
+        else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        if (ok) { uint4 o0, o1; fast_chunk32<false, false, kMode, kOqf>(rb, &aux->bias_i[32], &aux->quant[32], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf); rows_store32(px + 32, o0, o1, st32); }
+    }
+}
+
+__device__ __noinline__ void rows_epi_tile_wide(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
+                                                uint32_t tmem_empty_bar, int lane)
+{
+#pragma unroll 1
+    for (int c0 = 0; c0 < kRCols; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 >= kRCols) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        const int i = c0 >> 6, f0 = c0 & 63;
+        if (row_ok && i < x_left) rows_chunk_wide(P.epi, aux, r, f0, out_row + (int64_t)i * P.out_px + f0);
+    }
+}
+
+__global__ void __launch_bounds__(kRThreads, 1)
+conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw);
+    const uint32_t b_base = base;
+    const uint32_t a_base = base + (uint32_t)P.b_bytes;
+    RowsAux* aux = reinterpret_cast<RowsAux*>(smem + P.b_bytes + P.stages * P.a_stage_bytes + 4096);
+    volatile uint32_t* s_abort = &aux->abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const EpiCfg& c = P.epi;
+    const int v = (int)(blockIdx.x & 1u);                            // parity of the x-blocks this CTA works on
+    const int ctas_v = ((int)gridDim.x + 1 - v) >> 1, bv = (int)(blockIdx.x >> 1);
+    const int my_tiles = P.total[v] > bv ? (P.total[v] - bv + ctas_v - 1) / ctas_v : 0;
+    const int chunks = P.C * P.kh;
+
+    if (tid == 0) {
+        for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4); }
+        mbar_init(smem_u32(&aux->b_full), 1); mbar_init(smem_u32(&aux->drain), 1);
+        aux->abort = 0u; aux->wide = 0u;
+        mbar_fence_init();
+        prefetch_tensormap(&P.tmA[0]); prefetch_tensormap(&P.tmA[1]); prefetch_tensormap(&P.tmB);
+    }
+    if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), 512u); tmem_relinquish(); }
+    __syncthreads();
+    for (int j = tid; j < kROfm; j += kRThreads) {
+        const int32_t bi = c.bias_dtype != CLDNN_B200_NONE ? ((const int32_t*)P.bias)[j] : 0;
+        const float q = P.quant[j];
+        aux->bias_i[j] = bi; aux->quant[j] = q;
+        // the conversion-free epilogue is exact while every dequantised value stays below 2^22
+        if (!(__fmul_rn(__fmul_rn(__fadd_rn(P.acc_bound, fabsf((float)bi)), fabsf(q)), P.mul_oqf ? fabsf(c.o_qf) : 1.0f) < 4.0e6f)) atomicOr(&aux->wide, 1u);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        const bool leader = elect_one();
+        if (leader && my_tiles > 0) {
+            // the banded filter rows of this CTA's parity, once
+            const uint32_t bf = smem_u32(&aux->b_full);
+            mbar_expect_tx(bf, (uint32_t)P.b_bytes);
+            for (int g = 0; g < chunks; ++g) tma_load_2d(b_base + (uint32_t)g * (uint32_t)(kRCols * 32), &P.tmB, bf, 0, (v * chunks + g) * kRCols);
+        }
+        int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
+            const int u = P.u0[v] + 16 * t.jv, y0 = t.ty * 128;
+            for (int ky = 0; ky < P.kh; ++ky) {
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrRows + 1u))) { ok = false; break; }
+                if (leader) {
+                    const uint32_t full = smem_u32(&aux->full[stage]);
+                    mbar_expect_tx(full, (uint32_t)P.a_stage_bytes);
+                    tma_load_4d(a_base + (uint32_t)(stage * P.a_stage_bytes), &P.tmA[P.row_r[ky]], full, u, y0 + P.row_q[ky], 0, t.n);
+                }
+                ++issued;
+                if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) {
+            // unwind: let the copies already in flight land before the CTA's shared memory goes away
+            int st = stage; uint32_t ph = phase;
+            const int pending = issued < P.stages ? (int)issued : P.stages;
+            for (int i = 0; i < pending; ++i) {
+                if (--st < 0) { st = P.stages - 1; ph ^= 1u; }
+                const uint64_t t0 = globaltimer();
+                while (!mbar_try_wait(smem_u32(&aux->full[st]), ph) && globaltimer() - t0 < 100000000ull) { }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        const bool leader = elect_one();
+        int stage = 0; uint32_t phase = 0; bool ok = true;
+        if (my_tiles > 0) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrRows + 2u));
+        for (int it = 0; it < my_tiles && ok; ++it) {
+            const int acc = it & 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(it >> 1) & 1u)) ^ 1u, s_abort, P.status, kErrRows + 3u))) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kRCols);
+            uint32_t accf = 0u;
+            uint32_t b_addr = b_base;
+            for (int ky = 0; ky < P.kh; ++ky) {
+                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrRows + 4u))) { ok = false; break; }
+                tc_fence_after();
+                if (leader) {
+                    uint32_t a_addr = a_base + (uint32_t)(stage * P.a_stage_bytes);
+                    for (int ch = 0; ch < P.C; ++ch, a_addr += (uint32_t)P.a_chan_bytes, b_addr += (uint32_t)(kRCols * 32)) {
+                        mma_i8_ss(d_tmem, make_smem_desc(a_addr, 256u, 6u), make_smem_desc(b_addr, 256u, 6u), P.idesc, accf);
+                        accf = 1u;
+                    }
+                    tc_commit(smem_u32(&aux->empty[stage]));
+                }
+                if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+            }
+            if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[acc]));
+        }
+        // drain: every issued MMA must have retired before tensor memory is released
+        if (leader) tc_commit(smem_u32(&aux->drain));
+        const uint64_t t0 = globaltimer();
+        while (!mbar_try_wait(smem_u32(&aux->drain), 0u)) {
+            if (globaltimer() - t0 > kWaitLimitNs) { atomicCAS(P.status, 0u, kErrRows + 5u); break; }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------ epilogue ----------------------------------
+        const int ew = warp - 4, quad = ew & 3, group = ew >> 2;
+        const int row = quad * 32 + lane;
+        const bool wide = aux->wide != 0u;
+        for (int it = group; it < my_tiles; it += 2) {
+            const int acc = it & 1;                                  // = group
+            const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
+            const int y = t.ty * 128 + row, x0 = 4 * t.j;
+            const bool row_ok = y < P.P;
+            const int x_left = P.Q - x0;
+            uint8_t* out_row = P.out + P.out_off + (int64_t)t.n * P.out_pb + (int64_t)y * P.out_py + (int64_t)x0 * P.out_px;
+            if (!mbar_wait(smem_u32(&aux->tmem_full[acc]), (uint32_t)(it >> 1) & 1u, s_abort, P.status, kErrRows)) break;
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kRCols);
+            const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
+            if (wide) rows_epi_tile_wide(P, aux, t_row, out_row, row_ok, x_left, te, lane);
+            else switch (P.mode) {
+                case 0: rows_epi_tile<0, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
+                case 1: rows_epi_tile<1, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
+                case 2: rows_epi_tile<2, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
+                case 4: rows_epi_tile<0, true>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
+                default: rows_epi_tile<1, true>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512u); }
+}
+
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn r_encode_tiled = nullptr;
+static bool rows_load_entry_point()
+{
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* fn = nullptr; cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr) == cudaSuccess && qr == cudaDriverEntryPointSuccess)
+            r_encode_tiled = (EncodeTiledFn)fn;
+        (void)cudaGetLastError();
+    });
+    return r_encode_tiled != nullptr;
+}
+
+static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
+// window start of the first x-block of parity v, and where in the window its first tap lies
+static void rows_window(int pad_x, int v, int& u0, int& off)
+{
+    u0 = floor_div(8 * v - pad_x, 16) * 16;
+    off = 8 * v - pad_x - u0;
+}
+
+bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why)
+{
+    auto no = [&](const char* m) { if (why) *why = m; return false; };
+    if (!is_int8(p.in.dtype) || p.w_dtype != CLDNN_B200_I8) return no("8-bit activations and weights only");
+    if (p.groups != 1 || p.fused_eltw) return no("plain convolution only");
+    if (p.epilogue_order != CLDNN_B200_EPILOGUE_REF) return no("reference epilogue order only");
+    if (p.in.px != 1 || p.in.py % 16 || p.in.pf % 16 || p.in.pb % 16 || p.in.offset % 16) return no("row form: planar input with 16-byte aligned pitches");
+    if (p.out.pf != 1 || !is_int8(p.out.dtype)) return no("output must be 8-bit byxf");
+    if (p.out.px % 16 || p.out.py % 16 || p.out.pb % 16 || p.out.offset % 16) return no("output pitches must be 16-byte aligned");
+    if (p.stride_x != 2 || p.stride_y != 2 || p.dil_x != 1 || p.dil_y != 1) return no("row form: stride 2, no dilation");
+    if (p.ofm != kROfm || p.out.f != p.ofm || p.in.f != p.ifm) return no("row form: 64 output features");
+    if (p.kh < 1 || p.kh > 16 || p.kw < 1 || p.ifm < 1 || p.ifm * p.kh > 24) return no("row form: C * kh up to 24");
+    if (p.in.x < 32 || p.in.y < 2) return no("row form: image at least 32 wide");
+    for (int v = 0; v < 2; ++v) { int u0, off; rows_window(p.pad_x, v, u0, off); if (off + 6 + p.kw - 1 > 31) return no("row form: the filter window exceeds 32 columns"); }
+    if (p.pad_x < 0 || p.pad_y < 0) return no("row form: non-negative padding");
+    if (!p.quantization || p.i_qf != 1.0f) return no("row form: per-feature quantisation factors, no input factor");
+    const bool mul_oqf = p.calibration || p.o_qf != 1.0f;
+    if (mul_oqf && !(!p.calibration && p.o_qf > 0.0f && (p.out.dtype == CLDNN_B200_U8 || p.act != CLDNN_B200_ACT_RELU))) return no("row form: output factor not in the conversion-free set");
+    if (p.act != CLDNN_B200_ACT_NONE && p.act != CLDNN_B200_ACT_RELU) return no("row form: activation none or ReLU");
+    if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32) return no("row form: 32-bit integer bias");
+    if (make_epi_cfg(p).dont_dequantize_bias) return no("row form: bias in the accumulator's scale");
+    const int P_ = (p.in.y + 2 * p.pad_y - p.kh) / p.stride_y + 1, Q_ = (p.in.x + 2 * p.pad_x - p.kw) / p.stride_x + 1;
+    if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
+    return true;
+}
+
+size_t first_rows_scratch(const cldnn_b200_conv_params& p) { return (size_t)2 * p.ifm * p.kh * kRCols * 32; }
+
+int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p_in, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+{
+    const cldnn_b200_conv_params p = simplified_conv_params(p_in);
+    std::string why;
+    if (!first_rows_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_first: " + why);
+    if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: input, output and weights are required");
+    if (p.bias_dtype != CLDNN_B200_NONE && !a->bias) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: bias_dtype set but no bias pointer");
+    if (!a->weights_quantization_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: quantization set but no factors");
+    const size_t need = first_rows_scratch(p);
+    if (!a->scratch || a->scratch_bytes < need) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: needs " + std::to_string(need) + " bytes of scratch for the packed weights");
+    if (((uintptr_t)a->scratch | (uintptr_t)a->output | (uintptr_t)a->input0) & 15) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: input, scratch and output must be 16-byte aligned");
+    if (!rows_load_entry_point()) return fail(CLDNN_B200_ERROR, "conv_i8_first: cuTensorMapEncodeTiled is not available");
+
+    RowsParams P{};
+    P.N = p.in.b; P.C = p.ifm; P.P = p.out.y; P.Q = p.out.x; P.kh = p.kh; P.ofm = p.ofm;
+    P.tiles_y = (P.P + 127) / 128;
+    const int tiles_x = (P.Q + 3) / 4;
+    P.jcount[0] = (tiles_x + 1) / 2; P.jcount[1] = tiles_x / 2;
+    int off[2];
+    for (int v = 0; v < 2; ++v) { rows_window(p.pad_x, v, P.u0[v], off[v]); P.total[v] = P.N * P.tiles_y * P.jcount[v]; }
+    for (int ky = 0; ky < p.kh; ++ky) { const int t = ky - p.pad_y; P.row_r[ky] = t & 1; P.row_q[ky] = (t - (t & 1)) / 2; }
+    // rows of one box: all 128 of the tile, or (one tile of rows) only those the image has, in whole 8-row groups; the MMA still
+    // reads 128 rows per feature -- the surplus are the next feature's or stage's bytes, and feed accumulator rows nothing reads
+    const int box_rows = P.tiles_y == 1 ? (P.P + 7) / 8 * 8 : 128;
+    P.a_chan_bytes = box_rows * 32; P.a_stage_bytes = p.ifm * P.a_chan_bytes; P.b_bytes = p.ifm * p.kh * kRCols * 32;
+    const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
+    if (max_smem < 1024 + 4096 + (size_t)P.b_bytes + sizeof(RowsAux) + 2 * (size_t)P.a_stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory for the row form");
+    P.stages = (int)std::min<size_t>(kRMaxStages, (max_smem - 1024 - 4096 - P.b_bytes - sizeof(RowsAux)) / P.a_stage_bytes);
+    const size_t smem = 1024 + (size_t)P.b_bytes + (size_t)P.stages * P.a_stage_bytes + 4096 + sizeof(RowsAux);   // 4 KB: the last feature's surplus rows
+    const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;
+    P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(kRCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
+    P.epi = make_epi_cfg(p);
+    P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
+    P.mode = (p.out.dtype == CLDNN_B200_U8 ? 0 : (p.act == CLDNN_B200_ACT_RELU ? 2 : 1)) + (P.mul_oqf ? 4 : 0);
+    P.acc_bound = (float)p.ifm * (float)p.kh * (float)p.kw * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
+    P.st32 = (((uintptr_t)a->output + (uintptr_t)p.out.offset) % 32 == 0 && p.out.px % 32 == 0 && p.out.py % 32 == 0 && p.out.pb % 32 == 0) ? 1 : 0;
+    P.out = (uint8_t*)a->output; P.bias = a->bias; P.quant = a->weights_quantization_factors;
+    P.status = ctx->d_status;
+
+    for (int r = 0; r < 2; ++r) {
+        const int rows_r = (p.in.y - r + 1) / 2;
+        cuuint64_t dims[4] = {(cuuint64_t)p.in.x, (cuuint64_t)rows_r, (cuuint64_t)p.ifm, (cuuint64_t)p.in.b};
+        cuuint64_t strides[3] = {(cuuint64_t)(2 * p.in.py), (cuuint64_t)p.in.pf, (cuuint64_t)p.in.pb};
+        cuuint32_t box[4] = {32u, (cuuint32_t)box_rows, (cuuint32_t)p.ifm, 1u};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        void* ptr = (char*)const_cast<void*>(a->input0) + p.in.offset + (int64_t)r * p.in.py;
+        const CUresult cr = r_encode_tiled(&P.tmA[r], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                           CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "conv_i8_first: tensor map of the input rows refused (" + std::to_string((int)cr) + ")");
+    }
+    {
+        cuuint64_t dims[2] = {32u, (cuuint64_t)(2 * p.ifm * p.kh * kRCols)};
+        cuuint64_t strides[1] = {32u};
+        cuuint32_t box[2] = {32u, (cuuint32_t)kRCols};
+        cuuint32_t es[2] = {1, 1};
+        const CUresult cr = r_encode_tiled(&P.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->scratch, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                           CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "conv_i8_first: tensor map of the filter rows refused (" + std::to_string((int)cr) + ")");
+    }
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel, ctx->device, smem));
+    int grid = ctx->prop.multiProcessorCount & ~1;
+    if (grid < 2) grid = 2;
+    const int most = std::max(P.total[0], P.total[1]);
+    if (grid > 2 * most) grid = 2 * most;
+
+    // pack the filter once, on the context's stream, before anything that is prepared here can run
+    const int pack_total = 2 * p.ifm * p.kh * kRCols * 32;
+    rows_pack_weights<<<(pack_total + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
+                                                                         p.ifm, p.kh, p.kw, off[0], off[1], (uint8_t*)a->scratch);
+    B200_CUDA(cudaGetLastError());
+    out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_first_rows_kernel<<<grid, kRThreads, smem, s>>>(P); return cudaGetLastError(); };
+    out->launches = 1;
+    return CLDNN_B200_SUCCESS;
+}
+
+}  // namespace b200

@@ -1,0 +1,10 @@
+// Row form of the first-layer convolution (conv_i8_first_rows.cu): tuning variant 4 of conv_i8_first.
+#pragma once
+#include <string>
+#include "engine.hpp"
+
+namespace b200 {
+bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why);
+size_t first_rows_scratch(const cldnn_b200_conv_params& p);
+int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out);
+}

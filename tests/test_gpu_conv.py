@@ -259,6 +259,62 @@ def test_conv_i8_first_plain_variants(eng):
                 _exact(eng, case, "conv_i8_first", tune=tune)
 
 
+ROW_FORM = {
+    # geometries the row form of the first-layer kernel takes: stride 2, 64 output features, 16-byte aligned row pitch
+    "resnet_conv1": dict(N=2, C=3, K=64, H=224, W=224, kh=7, kw=7, stride=2, pad=3),
+    "odd_height_many_tiles": dict(N=9, C=3, K=64, H=97, W=144, kh=7, kw=7, stride=2, pad=3),     # more tiles than a CTA's rings hold
+    "two_row_tiles": dict(N=2, C=3, K=64, H=300, W=64, kh=7, kw=7, stride=2, pad=3),               # 150 output rows: two tiles of 128
+    "four_features_5x5": dict(N=2, C=4, K=64, H=40, W=48, kh=5, kw=5, stride=2, pad=2),
+    "stem_3x3": dict(N=3, C=3, K=64, H=66, W=80, kh=3, kw=3, stride=2, pad=1),
+    "no_pad_4x6": dict(N=1, C=3, K=64, H=30, W=32, kh=4, kw=6, stride=2, pad=0),
+    "one_feature": dict(N=2, C=1, K=64, H=33, W=32, kh=7, kw=7, stride=2, pad=3),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ROW_FORM))
+def test_conv_i8_first_row_form_matches_oracle(eng, name):
+    """Tuning variant 4 of conv_i8_first (output rows as GEMM rows, the raw image rows as the TMA-loaded operand, the filter
+    as banded matrices): every conversion-free epilogue variant, a signed image, a uniform O_QF, and the float-domain path."""
+    geom = ROW_FORM[name]
+    k = eng.kernel("conv_i8_first")
+    variants = [dict(out_dtype=np.uint8), dict(out_dtype=np.uint8, act=abi.ACT_NONE), dict(act=abi.ACT_NONE), dict(),
+                dict(in_dtype=np.int8, out_dtype=np.uint8), dict(out_dtype=np.uint8, o_qf=2.5), dict(act=abi.ACT_NONE, o_qf=16.0),
+                dict(out_dtype=np.uint8, bias="none")]
+    for i, extra in enumerate(variants):
+        case = cases.make_conv_case(80 + i, fmt="bfyx", f_align=1, out_fmt="byxf", scale_lo=2.0 ** -13, scale_hi=2.0 ** -10, **geom, **extra)
+        p = cases.copy_params(case.p); p.tune = 4
+        assert k.supports(p), (name, extra)
+        want = _exact(eng, case, "conv_i8_first", tune=4)
+        assert len(np.unique(want[:case.out_elems])) > 16
+    wide = cases.make_conv_case(90, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, scale_lo=2.0 ** -12, scale_hi=2.0 ** -10, **geom)
+    wide.quant[5] = 900.0
+    _exact(eng, wide, "conv_i8_first", tune=4)
+    assert eng.device_status() == 0
+
+
+def test_conv_i8_first_row_form_refusals(eng):
+    """What the row form does not take is refused by `supports` (the tuner then never offers it): other strides, feature counts,
+    row pitches that are not a multiple of 16 bytes, epilogues outside the conversion-free set."""
+    k = eng.kernel("conv_i8_first")
+    def sup(**kw):
+        geom = dict(N=1, C=3, K=64, H=64, W=64, kh=7, kw=7, stride=2, pad=3)
+        extra = {}
+        for key, val in kw.items():
+            (geom if key in geom else extra)[key] = val
+        case = cases.make_conv_case(95, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=extra.pop("out_dtype", np.uint8), **geom, **extra)
+        p = cases.copy_params(case.p); p.tune = 4
+        return k.supports(p)
+    assert sup()
+    assert not sup(stride=1)
+    assert not sup(K=32)
+    assert not sup(W=72)                     # 72-byte rows
+    assert not sup(C=4)                      # 4 x 7 filter rows: more than shared memory holds
+    assert not sup(bias="f32")
+    assert not sup(calib=True)
+    assert not sup(act=abi.ACT_CLAMP)
+    assert not sup(kw=14)                    # the window of four outputs no longer fits 32 columns
+
+
 def test_conv_ref_layouts_and_groups(eng):
     _exact(eng, cases.make_conv_case(5, 1, 128, 128, 28, 28, fmt="bfyx", f_align=1), "conv_ref")
     _exact(eng, cases.make_conv_case(6, 2, 16, 24, 9, 9, fmt="yxfb", f_align=1), "conv_ref")
