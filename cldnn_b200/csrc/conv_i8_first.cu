@@ -392,18 +392,19 @@ constexpr int kTuneRows = 4;
 static bool first_supports(const void* vp)
 {
     const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
-    if (p.tune == kTuneRows) return first_rows_plan(simplified_conv_params(p), nullptr);
+    if (p.tune >= kTuneRows) return first_rows_plan(simplified_conv_params(p), nullptr);
     return first_plan(p, nullptr);
 }
 // tune 0 / 2: as many CTAs per SM as fit (at most two), 1: one CTA per SM with the double-buffered epilogue,
 // 3: up to three CTAs per SM (72 registers per thread: more warps against the latency of the patch loads),
-// 4: the row form (conv_i8_first_rows.cu: output rows as GEMM rows, the raw image as the TMA-loaded operand)
-static int first_tune_count(const void*) { return 5; }
+// 4, 5: the row form (conv_i8_first_rows.cu: output rows as GEMM rows, the raw image rows as the TMA-loaded operand) with two / four
+// epilogue warp groups
+static int first_tune_count(const void*) { return 6; }
 static int first_kp(const cldnn_b200_conv_params& p) { return (p.ifm * p.kh * 8 + 31) / 32 * 32; }
 static size_t first_scratch(const void* vp)
 {
     const auto& p = *(const cldnn_b200_conv_params*)vp;
-    if (p.tune == kTuneRows) return first_rows_scratch(p);
+    if (p.tune >= kTuneRows) return first_rows_scratch(p);
     return (size_t)p.ofm * first_kp(p);
 }
 
@@ -484,7 +485,7 @@ static cudaError_t first_pack(const cldnn_b200_conv_params& p, const cldnn_b200_
 static int32_t first_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
     const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
-    if (p.tune == kTuneRows) return first_rows_prepare(ctx, p, a, out);
+    if (p.tune >= kTuneRows) return first_rows_prepare(ctx, p, a, out);
     FirstParams P; int grid = 0; size_t smem = 0;
     const int32_t st = first_setup(ctx, p, a, a->scratch, a->scratch_bytes, P, grid, smem);
     if (st != CLDNN_B200_SUCCESS) return st;

@@ -31,7 +31,7 @@ namespace b200 {
 
 using namespace ptx;
 
-constexpr int kRThreads = 384;
+constexpr int rows_threads(int groups) { return 128 + 128 * groups; }
 constexpr int kRMaxStages = 4;
 constexpr int kRCols = 256;                     // four output columns x 64 features
 constexpr int kROfm = 64;
@@ -44,11 +44,14 @@ struct RowsParams {
     int32_t tiles_y, jcount[2], total[2];       // x-blocks of even / odd index per row of tiles, tiles per variant
     int32_t u0[2];                              // window start of the first x-block of each parity
     int32_t row_q[16], row_r[16];               // filter row ky reads input rows 2 (y + row_q) + row_r
-    int32_t stages, a_chan_bytes, a_stage_bytes, b_bytes;   // one feature's rows of a stage (box rows x 32), C of them, the filter image
+    int32_t stages, a_plane_bytes, a_stage_bytes, b_bytes;  // one (row parity, feature) plane of a stage, 2 C of them, the filter image
     int32_t st32;                                       // output rows are 32-byte aligned: one 32-byte store per 32 features
     uint32_t idesc;
     int64_t out_px, out_py, out_pb, out_off;
     int32_t mul_oqf, mode;                      // mode: 0 u8, 1 s8, 2 s8 after ReLU; +4 with a uniform O_QF
+    int32_t pad_bytes;                          // behind the last stage: what the last plane's 128-row reads may touch
+    int32_t m_lo;                               // first row of a plane relative to the tile's first output row
+    int32_t groups;                             // epilogue warp groups: 2 (a tile each) or 4 (half the columns of a tile each)
     float acc_bound;
     uint8_t* out; const void* bias; const float* quant;
     uint32_t* status;
@@ -135,30 +138,54 @@ __device__ __forceinline__ void rows_epi_tile(const RowsParams& P, const RowsAux
     }
 }
 
-__device__ __noinline__ void rows_epi_tile_wide(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
-                                                uint32_t tmem_empty_bar, int lane)
+// the same over columns [c_lo, c_lo + 128) with one register array (four epilogue groups: 96 registers per thread)
+template <int kMode, bool kOqf>
+__device__ __forceinline__ void rows_epi_half(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
+                                              uint32_t tmem_empty_bar, int lane, int c_lo)
 {
+    const float oqf = P.epi.o_qf;
+    const bool st32 = P.st32 != 0;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kRCols; c0 += 32) {
+    for (int c0 = c_lo; c0 < c_lo + 128; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + (uint32_t)c0, r);
         tmem_ld_wait();
-        if (c0 + 32 >= kRCols) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        if (c0 + 32 >= c_lo + 128) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        const int i = c0 >> 6, f0 = c0 & 63;
+        if (row_ok && i < x_left) {
+            uint4 o0, o1;
+            fast_chunk32<false, false, kMode, kOqf>(r, &aux->bias_i[f0], &aux->quant[f0], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf);
+            rows_store32(out_row + (int64_t)i * P.out_px + f0, o0, o1, st32);
+        }
+    }
+}
+
+__device__ __noinline__ void rows_epi_tile_wide(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
+                                                uint32_t tmem_empty_bar, int lane, int c_lo, int c_hi)
+{
+#pragma unroll 1
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 >= c_hi) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
         const int i = c0 >> 6, f0 = c0 & 63;
         if (row_ok && i < x_left) rows_chunk_wide(P.epi, aux, r, f0, out_row + (int64_t)i * P.out_px + f0);
     }
 }
 
-__global__ void __launch_bounds__(kRThreads, 1)
+template <int G>
+__global__ void __launch_bounds__(rows_threads(G), 1)
 conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
 {
+    constexpr int kRThreads = 128 + 128 * G;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* smem = smem_raw + (base - raw);
     const uint32_t b_base = base;
     const uint32_t a_base = base + (uint32_t)P.b_bytes;
-    RowsAux* aux = reinterpret_cast<RowsAux*>(smem + P.b_bytes + P.stages * P.a_stage_bytes + 4096);
+    RowsAux* aux = reinterpret_cast<RowsAux*>(smem + P.b_bytes + P.stages * P.a_stage_bytes + P.pad_bytes);
     volatile uint32_t* s_abort = &aux->abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const EpiCfg& c = P.epi;
@@ -169,7 +196,7 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
 
     if (tid == 0) {
         for (int s = 0; s < P.stages; ++s) { mbar_init(smem_u32(&aux->full[s]), 1); mbar_init(smem_u32(&aux->empty[s]), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 4); }
+        for (int a = 0; a < 2; ++a) { mbar_init(smem_u32(&aux->tmem_full[a]), 1); mbar_init(smem_u32(&aux->tmem_empty[a]), 2 * G); }
         mbar_init(smem_u32(&aux->b_full), 1); mbar_init(smem_u32(&aux->drain), 1);
         aux->abort = 0u; aux->wide = 0u;
         mbar_fence_init();
@@ -202,16 +229,17 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
         for (int it = 0; it < my_tiles && ok; ++it) {
             const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
             const int u = P.u0[v] + 16 * t.jv, y0 = t.ty * 128;
-            for (int ky = 0; ky < P.kh; ++ky) {
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrRows + 1u))) { ok = false; break; }
-                if (leader) {
-                    const uint32_t full = smem_u32(&aux->full[stage]);
-                    mbar_expect_tx(full, (uint32_t)P.a_stage_bytes);
-                    tma_load_4d(a_base + (uint32_t)(stage * P.a_stage_bytes), &P.tmA[P.row_r[ky]], full, u, y0 + P.row_q[ky], 0, t.n);
-                }
-                ++issued;
-                if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrRows + 1u))) { ok = false; break; }
+            if (leader) {
+                // the tile's input rows, once: the even-indexed ones and the odd-indexed ones as two boxes of C planes each
+                const uint32_t full = smem_u32(&aux->full[stage]);
+                const uint32_t dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
+                mbar_expect_tx(full, (uint32_t)P.a_stage_bytes);
+                tma_load_4d(dst, &P.tmA[0], full, u, y0 + P.m_lo, 0, t.n);
+                tma_load_4d(dst + (uint32_t)(P.C * P.a_plane_bytes), &P.tmA[1], full, u, y0 + P.m_lo, 0, t.n);
             }
+            ++issued;
+            if (++stage == P.stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) {
             // unwind: let the copies already in flight land before the CTA's shared memory goes away
@@ -233,21 +261,23 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(it >> 1) & 1u)) ^ 1u, s_abort, P.status, kErrRows + 3u))) { ok = false; break; }
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + (uint32_t)(acc * kRCols);
-            uint32_t accf = 0u;
-            uint32_t b_addr = b_base;
-            for (int ky = 0; ky < P.kh; ++ky) {
-                if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrRows + 4u))) { ok = false; break; }
-                tc_fence_after();
-                if (leader) {
-                    uint32_t a_addr = a_base + (uint32_t)(stage * P.a_stage_bytes);
-                    for (int ch = 0; ch < P.C; ++ch, a_addr += (uint32_t)P.a_chan_bytes, b_addr += (uint32_t)(kRCols * 32)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->full[stage]), phase, s_abort, P.status, kErrRows + 4u))) { ok = false; break; }
+            tc_fence_after();
+            if (leader) {
+                // filter row ky of feature ch reads plane (row parity, ch) from row row_q - m_lo on: a descriptor start address
+                // shifted by whole rows inside the swizzle pattern reads what TMA wrote (the swizzle is a function of the address)
+                const uint32_t a_stage = a_base + (uint32_t)(stage * P.a_stage_bytes);
+                uint32_t accf = 0u, b_addr = b_base;
+                for (int ky = 0; ky < P.kh; ++ky) {
+                    uint32_t a_addr = a_stage + (uint32_t)(P.row_r[ky] * P.C * P.a_plane_bytes) + (uint32_t)((P.row_q[ky] - P.m_lo) * 32);
+                    for (int ch = 0; ch < P.C; ++ch, a_addr += (uint32_t)P.a_plane_bytes, b_addr += (uint32_t)(kRCols * 32)) {
                         mma_i8_ss(d_tmem, make_smem_desc(a_addr, 256u, 6u), make_smem_desc(b_addr, 256u, 6u), P.idesc, accf);
                         accf = 1u;
                     }
-                    tc_commit(smem_u32(&aux->empty[stage]));
                 }
-                if (++stage == P.stages) { stage = 0; phase ^= 1u; }
+                tc_commit(smem_u32(&aux->empty[stage]));
             }
+            if (++stage == P.stages) { stage = 0; phase ^= 1u; }
             if (ok && leader) tc_commit(smem_u32(&aux->tmem_full[acc]));
         }
         // drain: every issued MMA must have retired before tensor memory is released
@@ -258,9 +288,11 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
         }
     } else if (warp >= 4) {
         // ------------------------------ epilogue ----------------------------------
-        const int ew = warp - 4, quad = ew & 3, group = ew >> 2;
+        // two groups: a tile each in turn; four: the two of an accumulator share its tiles by column halves
+        const int ew = warp - 4, quad = ew & 3, group = (ew >> 2) & 1, half = ew >> 3;
         const int row = quad * 32 + lane;
         const bool wide = aux->wide != 0u;
+        const int c_lo = G == 4 ? 128 * half : 0, c_hi = G == 4 ? c_lo + 128 : kRCols;
         for (int it = group; it < my_tiles; it += 2) {
             const int acc = it & 1;                                  // = group
             const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
@@ -272,7 +304,14 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kRCols);
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
-            if (wide) rows_epi_tile_wide(P, aux, t_row, out_row, row_ok, x_left, te, lane);
+            if (wide) rows_epi_tile_wide(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo, c_hi);
+            else if (G == 4) switch (P.mode) {
+                case 0: rows_epi_half<0, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
+                case 1: rows_epi_half<1, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
+                case 2: rows_epi_half<2, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
+                case 4: rows_epi_half<0, true>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
+                default: rows_epi_half<1, true>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
+            }
             else switch (P.mode) {
                 case 0: rows_epi_tile<0, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
                 case 1: rows_epi_tile<1, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane); break;
@@ -312,6 +351,23 @@ static void rows_window(int pad_x, int v, int& u0, int& off)
     off = 8 * v - pad_x - u0;
 }
 
+// shared-memory geometry of a stage: rows per plane, bytes behind the last stage that the MMAs' 128-row reads may touch
+struct RowsGeom { int m_lo, plane_rows, pad_bytes; size_t b_bytes, stage_bytes; };
+static RowsGeom rows_geom(const cldnn_b200_conv_params& p)
+{
+    RowsGeom g;
+    g.m_lo = floor_div(-p.pad_y, 2);
+    const int q_max = floor_div(p.kh - 1 - p.pad_y, 2);
+    const int rows_in_tile = p.out.y <= 128 ? p.out.y : 128;
+    g.plane_rows = (rows_in_tile + q_max - g.m_lo + 7) / 8 * 8;
+    const int surplus = q_max - g.m_lo + 128 - g.plane_rows;
+    g.pad_bytes = surplus > 0 ? (surplus * 32 + 255) / 256 * 256 : 0;
+    g.b_bytes = (size_t)p.ifm * p.kh * kRCols * 32;
+    g.stage_bytes = (size_t)2 * p.ifm * g.plane_rows * 32;
+    return g;
+}
+constexpr size_t kRowsSmemLimit = 227 * 1024;          // opt-in shared memory per CTA on sm_100
+
 bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why)
 {
     auto no = [&](const char* m) { if (why) *why = m; return false; };
@@ -335,6 +391,9 @@ bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why)
     if (make_epi_cfg(p).dont_dequantize_bias) return no("row form: bias in the accumulator's scale");
     const int P_ = (p.in.y + 2 * p.pad_y - p.kh) / p.stride_y + 1, Q_ = (p.in.x + 2 * p.pad_x - p.kw) / p.stride_x + 1;
     if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
+    const RowsGeom g = rows_geom(p);
+    if (g.plane_rows > 256) return no("row form: filter too tall");
+    if (1024 + g.b_bytes + 2 * g.stage_bytes + g.pad_bytes + sizeof(RowsAux) > kRowsSmemLimit) return no("row form: filter image and two stages of rows exceed shared memory");
     return true;
 }
 
@@ -361,14 +420,18 @@ int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     int off[2];
     for (int v = 0; v < 2; ++v) { rows_window(p.pad_x, v, P.u0[v], off[v]); P.total[v] = P.N * P.tiles_y * P.jcount[v]; }
     for (int ky = 0; ky < p.kh; ++ky) { const int t = ky - p.pad_y; P.row_r[ky] = t & 1; P.row_q[ky] = (t - (t & 1)) / 2; }
-    // rows of one box: all 128 of the tile, or (one tile of rows) only those the image has, in whole 8-row groups; the MMA still
-    // reads 128 rows per feature -- the surplus are the next feature's or stage's bytes, and feed accumulator rows nothing reads
-    const int box_rows = P.tiles_y == 1 ? (P.P + 7) / 8 * 8 : 128;
-    P.a_chan_bytes = box_rows * 32; P.a_stage_bytes = p.ifm * P.a_chan_bytes; P.b_bytes = p.ifm * p.kh * kRCols * 32;
+    // A plane holds the input rows of one parity that the tile's output rows touch: rows m_lo .. rows_in_tile - 1 + q_max of that
+    // parity's numbering, in whole 8-row groups.  The MMA reads 128 rows from its start row whatever the plane holds: the surplus
+    // are the next plane's bytes (or the pad behind the last stage) and feed accumulator rows that nothing reads.
+    const RowsGeom g = rows_geom(p);
+    const int plane_rows = g.plane_rows;
+    P.m_lo = g.m_lo;
+    P.a_plane_bytes = plane_rows * 32; P.a_stage_bytes = (int32_t)g.stage_bytes; P.b_bytes = (int32_t)g.b_bytes;
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
-    if (max_smem < 1024 + 4096 + (size_t)P.b_bytes + sizeof(RowsAux) + 2 * (size_t)P.a_stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory for the row form");
-    P.stages = (int)std::min<size_t>(kRMaxStages, (max_smem - 1024 - 4096 - P.b_bytes - sizeof(RowsAux)) / P.a_stage_bytes);
-    const size_t smem = 1024 + (size_t)P.b_bytes + (size_t)P.stages * P.a_stage_bytes + 4096 + sizeof(RowsAux);   // 4 KB: the last feature's surplus rows
+    if (max_smem < 1024 + g.b_bytes + 2 * g.stage_bytes + g.pad_bytes + sizeof(RowsAux)) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory for the row form");
+    P.stages = (int)std::min<size_t>(kRMaxStages, (max_smem - 1024 - g.pad_bytes - g.b_bytes - sizeof(RowsAux)) / g.stage_bytes);
+    P.pad_bytes = g.pad_bytes;
+    const size_t smem = 1024 + g.b_bytes + (size_t)P.stages * g.stage_bytes + g.pad_bytes + sizeof(RowsAux);
     const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;
     P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(kRCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
@@ -384,7 +447,7 @@ int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
         const int rows_r = (p.in.y - r + 1) / 2;
         cuuint64_t dims[4] = {(cuuint64_t)p.in.x, (cuuint64_t)rows_r, (cuuint64_t)p.ifm, (cuuint64_t)p.in.b};
         cuuint64_t strides[3] = {(cuuint64_t)(2 * p.in.py), (cuuint64_t)p.in.pf, (cuuint64_t)p.in.pb};
-        cuuint32_t box[4] = {32u, (cuuint32_t)box_rows, (cuuint32_t)p.ifm, 1u};
+        cuuint32_t box[4] = {32u, (cuuint32_t)plane_rows, (cuuint32_t)p.ifm, 1u};
         cuuint32_t es[4] = {1, 1, 1, 1};
         void* ptr = (char*)const_cast<void*>(a->input0) + p.in.offset + (int64_t)r * p.in.py;
         const CUresult cr = r_encode_tiled(&P.tmA[r], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -400,7 +463,9 @@ int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
                                            CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "conv_i8_first: tensor map of the filter rows refused (" + std::to_string((int)cr) + ")");
     }
-    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel, ctx->device, smem));
+    P.groups = p_in.tune == 5 ? 4 : 2;
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<2>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<4>, ctx->device, smem));
     int grid = ctx->prop.multiProcessorCount & ~1;
     if (grid < 2) grid = 2;
     const int most = std::max(P.total[0], P.total[1]);
@@ -411,7 +476,11 @@ int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     rows_pack_weights<<<(pack_total + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
                                                                          p.ifm, p.kh, p.kw, off[0], off[1], (uint8_t*)a->scratch);
     B200_CUDA(cudaGetLastError());
-    out->fn = [P, grid, smem](cudaStream_t s) { conv_i8_first_rows_kernel<<<grid, kRThreads, smem, s>>>(P); return cudaGetLastError(); };
+    out->fn = [P, grid, smem](cudaStream_t s) {
+        if (P.groups == 4) conv_i8_first_rows_kernel<4><<<grid, rows_threads(4), smem, s>>>(P);
+        else conv_i8_first_rows_kernel<2><<<grid, rows_threads(2), smem, s>>>(P);
+        return cudaGetLastError();
+    };
     out->launches = 1;
     return CLDNN_B200_SUCCESS;
 }

@@ -285,10 +285,12 @@ def test_conv_i8_first_row_form_matches_oracle(eng, name):
         p = cases.copy_params(case.p); p.tune = 4
         assert k.supports(p), (name, extra)
         want = _exact(eng, case, "conv_i8_first", tune=4)
+        _exact(eng, case, "conv_i8_first", tune=5)           # four epilogue groups: two share a tile by column halves
         assert len(np.unique(want[:case.out_elems])) > 16
     wide = cases.make_conv_case(90, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, scale_lo=2.0 ** -12, scale_hi=2.0 ** -10, **geom)
     wide.quant[5] = 900.0
     _exact(eng, wide, "conv_i8_first", tune=4)
+    _exact(eng, wide, "conv_i8_first", tune=5)
     assert eng.device_status() == 0
 
 
