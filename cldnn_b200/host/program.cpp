@@ -943,6 +943,15 @@ void network_impl::prepare_kernel(node* n)
                 cldnn_b200_kernel k = eng->kernel(kn);
                 if (cldnn_b200_kernel_supports(k, &cp, sizeof(cp), &yes) == CLDNN_B200_SUCCESS && yes &&
                     cldnn_b200_kernel_scratch_bytes(k, &cp, sizeof(cp), &sbytes) == CLDNN_B200_SUCCESS) {
+                    // the workspace serves whichever tuning variant is chosen: the variants pack the weights differently
+                    int32_t variants = 0;
+                    if (cldnn_b200_kernel_tune_count(k, &cp, sizeof(cp), &variants) != CLDNN_B200_SUCCESS) variants = 0;
+                    for (int32_t t = 1; t < variants; ++t) {
+                        cp.tune = t; size_t b = 0; int32_t ok_t = 0;
+                        if (cldnn_b200_kernel_supports(k, &cp, sizeof(cp), &ok_t) == CLDNN_B200_SUCCESS && ok_t &&
+                            cldnn_b200_kernel_scratch_bytes(k, &cp, sizeof(cp), &b) == CLDNN_B200_SUCCESS && b > sbytes) sbytes = b;
+                    }
+                    cp.tune = 0;
                     n->scratch = new_block(eng, sbytes);
                     a.scratch = n->scratch->dev; a.scratch_bytes = n->scratch->bytes;
                     finish({kn}, &cp, sizeof(cp), [&](int tn) { cp.tune = tn; });
