@@ -1,19 +1,22 @@
 // conv_i8_first, row form: the first convolution of an 8-bit image network (few planar input features, stride 2,
-// 64 output features) as a GEMM whose rows are OUTPUT ROWS and whose operand is the raw image, so that no thread
+// 64 or 32 output features) as a GEMM whose rows are OUTPUT ROWS and whose operand is the raw image, so that no thread
 // ever assembles an im2col operand:
 //
 //   D[y, (i, f)] = sum over (ky, c)  A_(ky,c)[y, 0..31] . T_(ky,c)[(i, f), 0..31]
 //
-// for the four output columns x = 4j + i of one "x-block" j.  A_(ky,c)[y, :] are 32 consecutive bytes of input row
-// 2y + ky - pad_y of feature c, starting at a 16-byte aligned column u(j) -- exactly what one TMA box of 32 bytes x
-// 128 rows x C features delivers (every second row through the row pitch, zero fill outside the image = the padding).
-// T_(ky,c) is the filter row (ky, c) laid out as a banded (Toeplitz) matrix: T[(i, f), k] = w[f][c][ky][k - off - 2i].
-// The window of 32 columns holds the 13 + (kw - 7) the four outputs need at offset `off`, which depends only on the
-// parity of j (13 and 5 for a 7-wide filter with padding 3): two variants of T, and a CTA works on x-blocks of one
-// parity only, so it keeps one variant resident in shared memory (C * kh * 8 KB; 168 KB for 7x7x3).
-// The tensor core multiplies ~4.6 x the taps that exist (32-column window for a 7-tap filter); in exchange the
-// per-tile work of the general first-layer kernel's four builder warps disappears, and what remains per tile of
-// 128 rows x 4 columns is C * kh MMAs (M 128, N 256, K 32), kh TMA copies and the requantising epilogue.
+// for the output columns x = XB j + i of one "x-block" j (XB = 256 / features: four columns of 64 features, eight of 32).
+// A_(ky,c)[y, :] are 32 consecutive bytes of input row 2y + ky - pad_y of feature c, starting at a 16-byte aligned column
+// u(j).  The input rows a tile touches come in once per tile, as two TMA boxes of 32 bytes x rows x C features: the
+// even-indexed rows and the odd-indexed ones (every second row through the row pitch; zero fill outside the image = the
+// padding); filter row ky then reads its parity's plane from row floor((ky - pad_y) / 2) on, by a descriptor start address
+// shifted by whole rows.  T_(ky,c) is the filter row (ky, c) laid out as a banded (Toeplitz) matrix:
+// T[(i, f), k] = w[f][c][ky][k - off - 2i].  The window of 32 columns holds the 2 (XB - 1) + kw the outputs of a block need
+// at offset `off`, which depends only on the parity of j (13 and 5 for a 7-wide filter with padding 3 and XB = 4): two
+// variants of T, and a CTA works on x-blocks of one parity only, so it keeps one variant resident in shared memory
+// (C * kh * 8 KB; 168 KB for 7x7x3).
+// The tensor core multiplies several times the taps that exist (a 32-column window per filter row: 4.6 x for 7 taps); in
+// exchange the per-tile work of the general first-layer kernel's four builder warps disappears, and what remains per tile
+// of 128 rows x XB columns is C * kh MMAs (M 128, N 256, K 32), two TMA copies and the requantising epilogue.
 //
 // Roles: warp 0 issues the copies, warp 1 the MMAs, warps 4..11 are two epilogue groups taking tiles in turn (one
 // accumulator of 256 columns each).  The operation order of the epilogue is the reference's
@@ -34,13 +37,14 @@ using namespace ptx;
 constexpr int rows_threads(int groups) { return 128 + 128 * groups; }
 constexpr int kRMaxStages = 4;
 constexpr int kRCols = 256;                     // four output columns x 64 features
-constexpr int kROfm = 64;
+constexpr int kROfm = 64;                       // at most; 32 features make x-blocks of eight output columns
 constexpr uint32_t kErrRows = 0x58u;
 
 struct RowsParams {
     alignas(64) CUtensorMap tmA[2];             // input rows of even / odd index
     alignas(64) CUtensorMap tmB;                // banded filter rows, both variants
     int32_t N, C, P, Q, kh, ofm;
+    int32_t ofm_shift, xb;                      // log2(ofm); output columns of an x-block = 256 / ofm
     int32_t tiles_y, jcount[2], total[2];       // x-blocks of even / odd index per row of tiles, tiles per variant
     int32_t u0[2];                              // window start of the first x-block of each parity
     int32_t row_q[16], row_r[16];               // filter row ky reads input rows 2 (y + row_q) + row_r
@@ -67,7 +71,7 @@ struct RowsAux {
 
 // filter [ofm][C][kh][kw] (any pitches) -> [variant][ky * C + c][n = i * 64 + f][k = 0..31], zero outside the band
 __global__ void rows_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t pi, int64_t py, int64_t px, int64_t off,
-                                  int C, int kh, int kw, int off0, int off1, uint8_t* __restrict__ dst)
+                                  int C, int kh, int kw, int ofm, int off0, int off1, uint8_t* __restrict__ dst)
 {
     const int chunks = C * kh;
     const int total = 2 * chunks * kRCols * 32;
@@ -76,7 +80,7 @@ __global__ void rows_pack_weights(const int8_t* __restrict__ w, int64_t po, int6
         const int n = r % kRCols; r /= kRCols;
         const int g = r % chunks; const int v = r / chunks;
         const int ky = g / C, c = g - ky * C;
-        const int i = n / kROfm, f = n - i * kROfm;
+        const int i = n / ofm, f = n - i * ofm;
         const int kx = k - (v ? off1 : off0) - 2 * i;
         int8_t val = 0;
         if (kx >= 0 && kx < kw) val = w[off + f * po + c * pi + ky * py + kx * px];
@@ -125,16 +129,16 @@ __device__ __forceinline__ void rows_epi_tile(const RowsParams& P, const RowsAux
     tmem_ld_32x32(t_row, ra);
 #pragma unroll 1
     for (int c0 = 0; c0 < kRCols; c0 += 64) {
-        const int i = c0 >> 6;                                   // output column of the x-block
-        const bool ok = row_ok && i < x_left;
-        uint8_t* px = out_row + (int64_t)i * P.out_px;
+        // two chunks of 32 columns: the two halves of one pixel's 64 features, or two pixels of 32 features
+        const int ia = c0 >> P.ofm_shift, ib = (c0 + 32) >> P.ofm_shift;
+        const int fa = c0 & (P.ofm - 1), fb = (c0 + 32) & (P.ofm - 1);
         tmem_ld_wait();
         tmem_ld_32x32(t_row + (uint32_t)(c0 + 32), rb);
-        if (ok) { uint4 o0, o1; fast_chunk32<false, false, kMode, kOqf>(ra, &aux->bias_i[0], &aux->quant[0], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf); rows_store32(px, o0, o1, st32); }
+        if (row_ok && ia < x_left) { uint4 o0, o1; fast_chunk32<false, false, kMode, kOqf>(ra, &aux->bias_i[fa], &aux->quant[fa], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf); rows_store32(out_row + (int64_t)ia * P.out_px + fa, o0, o1, st32); }
         tmem_ld_wait();
         if (c0 + 64 < kRCols) tmem_ld_32x32(t_row + (uint32_t)(c0 + 64), ra);
         else { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
-        if (ok) { uint4 o0, o1; fast_chunk32<false, false, kMode, kOqf>(rb, &aux->bias_i[32], &aux->quant[32], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf); rows_store32(px + 32, o0, o1, st32); }
+        if (row_ok && ib < x_left) { uint4 o0, o1; fast_chunk32<false, false, kMode, kOqf>(rb, &aux->bias_i[fb], &aux->quant[fb], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf); rows_store32(out_row + (int64_t)ib * P.out_px + fb, o0, o1, st32); }
     }
 }
 
@@ -151,7 +155,7 @@ __device__ __forceinline__ void rows_epi_half(const RowsParams& P, const RowsAux
         tmem_ld_32x32(t_row + (uint32_t)c0, r);
         tmem_ld_wait();
         if (c0 + 32 >= c_lo + 128) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
-        const int i = c0 >> 6, f0 = c0 & 63;
+        const int i = c0 >> P.ofm_shift, f0 = c0 & (P.ofm - 1);
         if (row_ok && i < x_left) {
             uint4 o0, o1;
             fast_chunk32<false, false, kMode, kOqf>(r, &aux->bias_i[f0], &aux->quant[f0], &o0, &o1, 0u, kMagicBits, kMagicBits, oqf);
@@ -169,7 +173,7 @@ __device__ __noinline__ void rows_epi_tile_wide(const RowsParams& P, const RowsA
         tmem_ld_32x32(t_row + (uint32_t)c0, r);
         tmem_ld_wait();
         if (c0 + 32 >= c_hi) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
-        const int i = c0 >> 6, f0 = c0 & 63;
+        const int i = c0 >> P.ofm_shift, f0 = c0 & (P.ofm - 1);
         if (row_ok && i < x_left) rows_chunk_wide(P.epi, aux, r, f0, out_row + (int64_t)i * P.out_px + f0);
     }
 }
@@ -204,7 +208,7 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
     }
     if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), 512u); tmem_relinquish(); }
     __syncthreads();
-    for (int j = tid; j < kROfm; j += kRThreads) {
+    for (int j = tid; j < P.ofm; j += kRThreads) {
         const int32_t bi = c.bias_dtype != CLDNN_B200_NONE ? ((const int32_t*)P.bias)[j] : 0;
         const float q = P.quant[j];
         aux->bias_i[j] = bi; aux->quant[j] = q;
@@ -228,7 +232,7 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
         int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
         for (int it = 0; it < my_tiles && ok; ++it) {
             const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
-            const int u = P.u0[v] + 16 * t.jv, y0 = t.ty * 128;
+            const int u = P.u0[v] + 4 * P.xb * t.jv, y0 = t.ty * 128;
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrRows + 1u))) { ok = false; break; }
             if (leader) {
                 // the tile's input rows, once: the even-indexed ones and the odd-indexed ones as two boxes of C planes each
@@ -296,7 +300,7 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
         for (int it = group; it < my_tiles; it += 2) {
             const int acc = it & 1;                                  // = group
             const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
-            const int y = t.ty * 128 + row, x0 = 4 * t.j;
+            const int y = t.ty * 128 + row, x0 = P.xb * t.j;
             const bool row_ok = y < P.P;
             const int x_left = P.Q - x0;
             uint8_t* out_row = P.out + P.out_off + (int64_t)t.n * P.out_pb + (int64_t)y * P.out_py + (int64_t)x0 * P.out_px;
@@ -345,10 +349,10 @@ static bool rows_load_entry_point()
 
 static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
 // window start of the first x-block of parity v, and where in the window its first tap lies
-static void rows_window(int pad_x, int v, int& u0, int& off)
+static void rows_window(int pad_x, int xb, int v, int& u0, int& off)
 {
-    u0 = floor_div(8 * v - pad_x, 16) * 16;
-    off = 8 * v - pad_x - u0;
+    u0 = floor_div(2 * xb * v - pad_x, 16) * 16;
+    off = 2 * xb * v - pad_x - u0;
 }
 
 // shared-memory geometry of a stage: rows per plane, bytes behind the last stage that the MMAs' 128-row reads may touch
@@ -378,10 +382,11 @@ bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why)
     if (p.out.pf != 1 || !is_int8(p.out.dtype)) return no("output must be 8-bit byxf");
     if (p.out.px % 16 || p.out.py % 16 || p.out.pb % 16 || p.out.offset % 16) return no("output pitches must be 16-byte aligned");
     if (p.stride_x != 2 || p.stride_y != 2 || p.dil_x != 1 || p.dil_y != 1) return no("row form: stride 2, no dilation");
-    if (p.ofm != kROfm || p.out.f != p.ofm || p.in.f != p.ifm) return no("row form: 64 output features");
+    if ((p.ofm != 64 && p.ofm != 32) || p.out.f != p.ofm || p.in.f != p.ifm) return no("row form: 32 or 64 output features");
+    const int xb = kRCols / p.ofm;
     if (p.kh < 1 || p.kh > 16 || p.kw < 1 || p.ifm < 1 || p.ifm * p.kh > 24) return no("row form: C * kh up to 24");
     if (p.in.x < 32 || p.in.y < 2) return no("row form: image at least 32 wide");
-    for (int v = 0; v < 2; ++v) { int u0, off; rows_window(p.pad_x, v, u0, off); if (off + 6 + p.kw - 1 > 31) return no("row form: the filter window exceeds 32 columns"); }
+    for (int v = 0; v < 2; ++v) { int u0, off; rows_window(p.pad_x, xb, v, u0, off); if (off + 2 * (xb - 1) + p.kw - 1 > 31) return no("row form: the filter window exceeds 32 columns"); }
     if (p.pad_x < 0 || p.pad_y < 0) return no("row form: non-negative padding");
     if (!p.quantization || p.i_qf != 1.0f) return no("row form: per-feature quantisation factors, no input factor");
     const bool mul_oqf = p.calibration || p.o_qf != 1.0f;
@@ -415,10 +420,11 @@ int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     RowsParams P{};
     P.N = p.in.b; P.C = p.ifm; P.P = p.out.y; P.Q = p.out.x; P.kh = p.kh; P.ofm = p.ofm;
     P.tiles_y = (P.P + 127) / 128;
-    const int tiles_x = (P.Q + 3) / 4;
+    P.xb = kRCols / p.ofm; P.ofm_shift = p.ofm == 64 ? 6 : 5;
+    const int tiles_x = (P.Q + P.xb - 1) / P.xb;
     P.jcount[0] = (tiles_x + 1) / 2; P.jcount[1] = tiles_x / 2;
     int off[2];
-    for (int v = 0; v < 2; ++v) { rows_window(p.pad_x, v, P.u0[v], off[v]); P.total[v] = P.N * P.tiles_y * P.jcount[v]; }
+    for (int v = 0; v < 2; ++v) { rows_window(p.pad_x, P.xb, v, P.u0[v], off[v]); P.total[v] = P.N * P.tiles_y * P.jcount[v]; }
     for (int ky = 0; ky < p.kh; ++ky) { const int t = ky - p.pad_y; P.row_r[ky] = t & 1; P.row_q[ky] = (t - (t & 1)) / 2; }
     // A plane holds the input rows of one parity that the tile's output rows touch: rows m_lo .. rows_in_tile - 1 + q_max of that
     // parity's numbering, in whole 8-row groups.  The MMA reads 128 rows from its start row whatever the plane holds: the surplus
@@ -474,7 +480,7 @@ int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_param
     // pack the filter once, on the context's stream, before anything that is prepared here can run
     const int pack_total = 2 * p.ifm * p.kh * kRCols * 32;
     rows_pack_weights<<<(pack_total + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
-                                                                         p.ifm, p.kh, p.kw, off[0], off[1], (uint8_t*)a->scratch);
+                                                                         p.ifm, p.kh, p.kw, p.ofm, off[0], off[1], (uint8_t*)a->scratch);
     B200_CUDA(cudaGetLastError());
     out->fn = [P, grid, smem](cudaStream_t s) {
         if (P.groups == 4) conv_i8_first_rows_kernel<4><<<grid, rows_threads(4), smem, s>>>(P);

@@ -268,6 +268,8 @@ ROW_FORM = {
     "stem_3x3": dict(N=3, C=3, K=64, H=66, W=80, kh=3, kw=3, stride=2, pad=1),
     "no_pad_4x6": dict(N=1, C=3, K=64, H=30, W=32, kh=4, kw=6, stride=2, pad=0),
     "one_feature": dict(N=2, C=1, K=64, H=33, W=32, kh=7, kw=7, stride=2, pad=3),
+    "stem_32_features": dict(N=5, C=3, K=32, H=66, W=80, kh=3, kw=3, stride=2, pad=1),              # x-blocks of eight columns
+    "32_features_5x5": dict(N=2, C=3, K=32, H=50, W=112, kh=5, kw=5, stride=2, pad=3),
 }
 
 
@@ -308,7 +310,9 @@ def test_conv_i8_first_row_form_refusals(eng):
         return k.supports(p)
     assert sup()
     assert not sup(stride=1)
-    assert not sup(K=32)
+    assert sup(K=32, kh=3, kw=3, pad=1)      # 32 features: x-blocks of eight columns, a 3-wide filter still fits the window
+    assert not sup(K=32)                     # ... a 7-wide one does not
+    assert not sup(K=96)
     assert not sup(W=72)                     # 72-byte rows
     assert not sup(C=4)                      # 4 x 7 filter rows: more than shared memory holds
     assert not sup(bias="f32")
