@@ -293,15 +293,22 @@ def run_vgg_layers(args, peaks):
         k = E.kernel(kernel)
         if not k.supports(p):
             return None
-        sb = C.c_size_t()
-        E.lib.cldnn_b200_kernel_scratch_bytes(k.handle, C.byref(p), C.sizeof(p), C.byref(sb))
-        scratch = E.alloc(sb.value) if sb.value else None
-        best = None
+        # one workspace for every tile shape / variant of the kernel: the largest any of them asks for
+        tunes, sb = [], C.c_size_t()
+        need = 0
         for tune in range(1 if k.tune_count(p) > 1 else 0, k.tune_count(p)):
             q = abi.ConvParams.from_buffer_copy(bytes(p))
             q.tune = tune
             if not k.supports(q):
                 continue
+            E.lib.cldnn_b200_kernel_scratch_bytes(k.handle, C.byref(q), C.sizeof(q), C.byref(sb))
+            need = max(need, sb.value)
+            tunes.append(q)
+        sb = C.c_size_t(need)
+        scratch = E.alloc(need) if need else None
+        best = None
+        for q in tunes:
+            tune = q.tune
             pr = k.prepare(q, args_for(scratch))
             ns = pr.time_ns(3, runs)
             pr.destroy()

@@ -35,6 +35,7 @@
 #include "engine.hpp"
 #include "sm100_ptx.cuh"
 #include "conv_epilogue.cuh"
+#include "conv_i8_first_rows.hpp"
 
 namespace b200 {
 
@@ -477,18 +478,32 @@ static bool ftc_plan(const cldnn_b200_conv_params& p, std::string* why)
     if ((int64_t)p.ifm * p.in.pf + (int64_t)p.kh * p.dil_y * p.in.py + (int64_t)p.kw * p.dil_x * p.in.px > 0x7fffffffLL) return no("input too large");
     return true;
 }
-static bool ftc_supports(const void* vp) { return ftc_plan(*(const cldnn_b200_conv_params*)vp, nullptr); }
-static int ftc_tune_count(const void*) { return 1; }
+// tuning variants: 0 / 1 the gather kernel of this file; 2 / 3 the row form of conv_i8_first_rows.cu (fp16 here; 8-bit layers reach
+// it through conv_i8_first) with two / four epilogue warp groups
+static bool ftc_rows(const cldnn_b200_conv_params& p) { return p.tune >= 2 && p.in.dtype == CLDNN_B200_F16; }
+static bool ftc_supports(const void* vp)
+{
+    const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
+    if (p.tune >= 2) return ftc_rows(p) && first_rows_plan(p, nullptr);
+    return ftc_plan(p, nullptr);
+}
+static int ftc_tune_count(const void*) { return 4; }
 // packed weights followed by the gather table
 static size_t ftc_table_offset(const cldnn_b200_conv_params& p) { return ((size_t)p.ofm * ftc_cores(p) * 16 + 255) / 256 * 256; }
 static size_t ftc_scratch(const void* vp)
 {
     const auto& p = *(const cldnn_b200_conv_params*)vp;
+    if (ftc_rows(p)) return first_rows_scratch(p);
     return ftc_table_offset(p) + (size_t)ftc_cores(p) * 2 * sizeof(int4);
 }
 
 static int32_t ftc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
+    if (((const cldnn_b200_conv_params*)vp)->tune >= 2) {
+        const cldnn_b200_conv_params& pr = *(const cldnn_b200_conv_params*)vp;
+        if (!ftc_rows(pr)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_first_tc: the row form is the fp16 variant here");
+        return first_rows_prepare(ctx, pr, a, out, pr.tune == 3 ? 4 : 2);
+    }
     const cldnn_b200_conv_params p = simplified_conv_params(*(const cldnn_b200_conv_params*)vp);
     std::string why;
     if (!ftc_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_first_tc: " + why);

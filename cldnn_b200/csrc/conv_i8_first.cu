@@ -485,7 +485,7 @@ static cudaError_t first_pack(const cldnn_b200_conv_params& p, const cldnn_b200_
 static int32_t first_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
 {
     const cldnn_b200_conv_params& p = *(const cldnn_b200_conv_params*)vp;
-    if (p.tune >= kTuneRows) return first_rows_prepare(ctx, p, a, out);
+    if (p.tune >= kTuneRows) return first_rows_prepare(ctx, p, a, out, p.tune == kTuneRows + 1 ? 4 : 2);
     FirstParams P; int grid = 0; size_t smem = 0;
     const int32_t st = first_setup(ctx, p, a, a->scratch, a->scratch_bytes, P, grid, smem);
     if (st != CLDNN_B200_SUCCESS) return st;

@@ -23,6 +23,7 @@
 // (kernel_selector/core/cl_kernels/fused_conv_eltwise_gpu_ref.cl:65-234); it is the conversion-free form of
 // conv_epilogue.cuh, with the float-domain form per value where a feature's range demands it.
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <mutex>
 #include <string>
 #include "engine.hpp"
@@ -45,6 +46,8 @@ struct RowsParams {
     alignas(64) CUtensorMap tmB;                // banded filter rows, both variants
     int32_t N, C, P, Q, kh, ofm;
     int32_t ofm_shift, xb;                      // log2(ofm); output columns of an x-block = 256 / ofm
+    int32_t planes, ustep;                      // row planes per stage (= vertical stride); window step between x-blocks of one parity
+    int32_t act, bias_dtype; float act_m, act_n;   // fp16 path
     int32_t tiles_y, jcount[2], total[2];       // x-blocks of even / odd index per row of tiles, tiles per variant
     int32_t u0[2];                              // window start of the first x-block of each parity
     int32_t row_q[16], row_r[16];               // filter row ky reads input rows 2 (y + row_q) + row_r
@@ -67,24 +70,28 @@ struct RowsAux {
     uint32_t tmem_base, abort, wide;
     alignas(16) int32_t bias_i[kROfm];
     alignas(16) float quant[kROfm];
+    alignas(16) float bias_f[kROfm];            // fp16 path
 };
 
-// filter [ofm][C][kh][kw] (any pitches) -> [variant][ky * C + c][n = i * 64 + f][k = 0..31], zero outside the band
-__global__ void rows_pack_weights(const int8_t* __restrict__ w, int64_t po, int64_t pi, int64_t py, int64_t px, int64_t off,
-                                  int C, int kh, int kw, int ofm, int off0, int off1, uint8_t* __restrict__ dst)
+// filter [ofm][C][kh][kw] (any pitches) -> [variant][ky * C + c][n = i * ofm + f][k = 0 .. 32 bytes of elements], zero outside the
+// band; `s` = horizontal stride
+template <typename T>
+__global__ void rows_pack_weights(const T* __restrict__ w, int64_t po, int64_t pi, int64_t py, int64_t px, int64_t off,
+                                  int C, int kh, int kw, int ofm, int s, int off0, int off1, T* __restrict__ dst)
 {
+    constexpr int KW = 32 / (int)sizeof(T);                          // window in elements
     const int chunks = C * kh;
-    const int total = 2 * chunks * kRCols * 32;
+    const int total = 2 * chunks * kRCols * KW;
     for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const int k = idx & 31; int r = idx >> 5;
+        const int k = idx % KW; int r = idx / KW;
         const int n = r % kRCols; r /= kRCols;
         const int g = r % chunks; const int v = r / chunks;
         const int ky = g / C, c = g - ky * C;
         const int i = n / ofm, f = n - i * ofm;
-        const int kx = k - (v ? off1 : off0) - 2 * i;
-        int8_t val = 0;
+        const int kx = k - (v ? off1 : off0) - s * i;
+        T val = T(0);
         if (kx >= 0 && kx < kw) val = w[off + f * po + c * pi + ky * py + kx * px];
-        dst[idx] = (uint8_t)val;
+        dst[idx] = val;
     }
 }
 
@@ -164,6 +171,49 @@ __device__ __forceinline__ void rows_epi_half(const RowsParams& P, const RowsAux
     }
 }
 
+__device__ __noinline__ float rows_act_other(int32_t fn, float x, float m, float n) { return act_float(fn, x, m, n); }
+__device__ __forceinline__ float rows_act(int32_t fn, float x, float m, float n)
+{
+    if (fn == CLDNN_B200_ACT_NONE) return x;
+    if (fn == CLDNN_B200_ACT_RELU) return fmaxf(0.0f, x);
+    return rows_act_other(fn, x, m, n);
+}
+
+// fp16: fp32 accumulators + bias -> activation -> one rounding to half; 32 columns = 64 output bytes per trip
+__device__ __forceinline__ void rows_epi_f16(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
+                                             uint32_t tmem_empty_bar, int lane, int c_lo, int c_hi)
+{
+    const bool st32 = P.st32 != 0;
+#pragma unroll 1
+    for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 >= c_hi) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
+        const int i = c0 >> P.ofm_shift, f0 = c0 & (P.ofm - 1);
+        if (row_ok && i < x_left) {
+            uint4 o[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float4 b0 = *reinterpret_cast<const float4*>(&aux->bias_f[f0 + 8 * w]), b1 = *reinterpret_cast<const float4*>(&aux->bias_f[f0 + 8 * w + 4]);
+                const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const float v0 = rows_act(P.act, __uint_as_float(r[8 * w + 2 * h]) + bb[2 * h], P.act_m, P.act_n);
+                    const float v1 = rows_act(P.act, __uint_as_float(r[8 * w + 2 * h + 1]) + bb[2 * h + 1], P.act_m, P.act_n);
+                    const __half2 hv = __floats2half2_rn(v0, v1);
+                    ow[h] = *reinterpret_cast<const uint32_t*>(&hv);
+                }
+                o[w] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+            uint8_t* dst = out_row + (int64_t)i * P.out_px + 2 * f0;
+            rows_store32(dst, o[0], o[1], st32);
+            rows_store32(dst + 32, o[2], o[3], st32);
+        }
+    }
+}
+
 __device__ __noinline__ void rows_epi_tile_wide(const RowsParams& P, const RowsAux* aux, uint32_t t_row, uint8_t* out_row, bool row_ok, int x_left,
                                                 uint32_t tmem_empty_bar, int lane, int c_lo, int c_hi)
 {
@@ -178,7 +228,7 @@ __device__ __noinline__ void rows_epi_tile_wide(const RowsParams& P, const RowsA
     }
 }
 
-template <int G>
+template <int G, bool kHalf>
 __global__ void __launch_bounds__(rows_threads(G), 1)
 conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
 {
@@ -209,6 +259,7 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
     if (warp == 1) { tmem_alloc(smem_u32(&aux->tmem_base), 512u); tmem_relinquish(); }
     __syncthreads();
     for (int j = tid; j < P.ofm; j += kRThreads) {
+        if (kHalf) { aux->bias_f[j] = P.bias_dtype != CLDNN_B200_NONE ? load_as_float(P.bias, P.bias_dtype, j) : 0.0f; continue; }
         const int32_t bi = c.bias_dtype != CLDNN_B200_NONE ? ((const int32_t*)P.bias)[j] : 0;
         const float q = P.quant[j];
         aux->bias_i[j] = bi; aux->quant[j] = q;
@@ -232,15 +283,16 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
         int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
         for (int it = 0; it < my_tiles && ok; ++it) {
             const RowsTile t = rows_tile(P, v, bv + it * ctas_v);
-            const int u = P.u0[v] + 4 * P.xb * t.jv, y0 = t.ty * 128;
+            const int u = P.u0[v] + P.ustep * t.jv, y0 = t.ty * 128;
             if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1u, s_abort, P.status, kErrRows + 1u))) { ok = false; break; }
             if (leader) {
-                // the tile's input rows, once: the even-indexed ones and the odd-indexed ones as two boxes of C planes each
+                // the tile's input rows, once: with a vertical stride of two the even-indexed ones and the odd-indexed ones as
+                // two boxes of C planes each
                 const uint32_t full = smem_u32(&aux->full[stage]);
                 const uint32_t dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
                 mbar_expect_tx(full, (uint32_t)P.a_stage_bytes);
                 tma_load_4d(dst, &P.tmA[0], full, u, y0 + P.m_lo, 0, t.n);
-                tma_load_4d(dst + (uint32_t)(P.C * P.a_plane_bytes), &P.tmA[1], full, u, y0 + P.m_lo, 0, t.n);
+                if (P.planes == 2) tma_load_4d(dst + (uint32_t)(P.C * P.a_plane_bytes), &P.tmA[1], full, u, y0 + P.m_lo, 0, t.n);
             }
             ++issued;
             if (++stage == P.stages) { stage = 0; phase ^= 1u; }
@@ -275,7 +327,8 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
                 for (int ky = 0; ky < P.kh; ++ky) {
                     uint32_t a_addr = a_stage + (uint32_t)(P.row_r[ky] * P.C * P.a_plane_bytes) + (uint32_t)((P.row_q[ky] - P.m_lo) * 32);
                     for (int ch = 0; ch < P.C; ++ch, a_addr += (uint32_t)P.a_plane_bytes, b_addr += (uint32_t)(kRCols * 32)) {
-                        mma_i8_ss(d_tmem, make_smem_desc(a_addr, 256u, 6u), make_smem_desc(b_addr, 256u, 6u), P.idesc, accf);
+                        if (kHalf) mma_f16_ss(d_tmem, make_smem_desc(a_addr, 256u, 6u), make_smem_desc(b_addr, 256u, 6u), P.idesc, accf);
+                        else mma_i8_ss(d_tmem, make_smem_desc(a_addr, 256u, 6u), make_smem_desc(b_addr, 256u, 6u), P.idesc, accf);
                         accf = 1u;
                     }
                 }
@@ -308,7 +361,8 @@ conv_i8_first_rows_kernel(const __grid_constant__ RowsParams P)
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * kRCols);
             const uint32_t te = smem_u32(&aux->tmem_empty[acc]);
-            if (wide) rows_epi_tile_wide(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo, c_hi);
+            if (kHalf) rows_epi_f16(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo, c_hi);
+            else if (wide) rows_epi_tile_wide(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo, c_hi);
             else if (G == 4) switch (P.mode) {
                 case 0: rows_epi_half<0, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
                 case 1: rows_epi_half<1, false>(P, aux, t_row, out_row, row_ok, x_left, te, lane, c_lo); break;
@@ -348,26 +402,34 @@ static bool rows_load_entry_point()
 }
 
 static inline int floor_div(int a, int b) { return a >= 0 ? a / b : -((-a + b - 1) / b); }
-// window start of the first x-block of parity v, and where in the window its first tap lies
-static void rows_window(int pad_x, int xb, int v, int& u0, int& off)
-{
-    u0 = floor_div(2 * xb * v - pad_x, 16) * 16;
-    off = 2 * xb * v - pad_x - u0;
-}
 
-// shared-memory geometry of a stage: rows per plane, bytes behind the last stage that the MMAs' 128-row reads may touch
-struct RowsGeom { int m_lo, plane_rows, pad_bytes; size_t b_bytes, stage_bytes; };
+// everything the shapes decide: element size, x-block, windows of the two parities, row planes, shared-memory sizes
+struct RowsGeom {
+    int es, xb, kwin, align;                      // bytes per element; output columns per x-block; window and TMA alignment in elements
+    int u0[2], off[2], ustep;                     // window start of the first x-block of each parity, first tap's place in it, step
+    int planes, m_lo, plane_rows, pad_bytes;      // row planes (vertical stride), first plane row of a tile, rows per plane
+    size_t b_bytes, stage_bytes;
+};
 static RowsGeom rows_geom(const cldnn_b200_conv_params& p)
 {
     RowsGeom g;
-    g.m_lo = floor_div(-p.pad_y, 2);
-    const int q_max = floor_div(p.kh - 1 - p.pad_y, 2);
+    g.es = p.in.dtype == CLDNN_B200_F16 ? 2 : 1;
+    g.xb = kRCols / (p.ofm > 0 ? p.ofm : 64); g.kwin = 32 / g.es; g.align = 16 / g.es;
+    const int s = p.stride_x;
+    for (int v = 0; v < 2; ++v) {
+        const int col0 = s * g.xb * v - p.pad_x;                     // first input column of x-block v
+        g.u0[v] = floor_div(col0, g.align) * g.align; g.off[v] = col0 - g.u0[v];
+    }
+    g.ustep = 2 * s * g.xb;
+    g.planes = p.stride_y;
+    g.m_lo = floor_div(-p.pad_y, p.stride_y);
+    const int q_max = floor_div(p.kh - 1 - p.pad_y, p.stride_y);
     const int rows_in_tile = p.out.y <= 128 ? p.out.y : 128;
     g.plane_rows = (rows_in_tile + q_max - g.m_lo + 7) / 8 * 8;
     const int surplus = q_max - g.m_lo + 128 - g.plane_rows;
     g.pad_bytes = surplus > 0 ? (surplus * 32 + 255) / 256 * 256 : 0;
     g.b_bytes = (size_t)p.ifm * p.kh * kRCols * 32;
-    g.stage_bytes = (size_t)2 * p.ifm * g.plane_rows * 32;
+    g.stage_bytes = (size_t)g.planes * p.ifm * g.plane_rows * 32;
     return g;
 }
 constexpr size_t kRowsSmemLimit = 227 * 1024;          // opt-in shared memory per CTA on sm_100
@@ -375,28 +437,36 @@ constexpr size_t kRowsSmemLimit = 227 * 1024;          // opt-in shared memory p
 bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why)
 {
     auto no = [&](const char* m) { if (why) *why = m; return false; };
-    if (!is_int8(p.in.dtype) || p.w_dtype != CLDNN_B200_I8) return no("8-bit activations and weights only");
+    const bool half = p.in.dtype == CLDNN_B200_F16;
+    if (half) {
+        if (p.w_dtype != CLDNN_B200_F16 || p.out.dtype != CLDNN_B200_F16) return no("fp16 weights and output with fp16 input");
+        if (p.quantization || p.calibration || p.has_o_qf) return no("no quantisation on the fp16 path");
+        if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_F16 && p.bias_dtype != CLDNN_B200_F32) return no("bias type");
+    } else if (!is_int8(p.in.dtype) || p.w_dtype != CLDNN_B200_I8 || !is_int8(p.out.dtype)) return no("fp16, or 8-bit activations, weights and output");
     if (p.groups != 1 || p.fused_eltw) return no("plain convolution only");
     if (p.epilogue_order != CLDNN_B200_EPILOGUE_REF) return no("reference epilogue order only");
-    if (p.in.px != 1 || p.in.py % 16 || p.in.pf % 16 || p.in.pb % 16 || p.in.offset % 16) return no("row form: planar input with 16-byte aligned pitches");
-    if (p.out.pf != 1 || !is_int8(p.out.dtype)) return no("output must be 8-bit byxf");
-    if (p.out.px % 16 || p.out.py % 16 || p.out.pb % 16 || p.out.offset % 16) return no("output pitches must be 16-byte aligned");
-    if (p.stride_x != 2 || p.stride_y != 2 || p.dil_x != 1 || p.dil_y != 1) return no("row form: stride 2, no dilation");
+    const int es = half ? 2 : 1;
+    if (p.in.px != 1 || (p.in.py * es) % 16 || (p.in.pf * es) % 16 || (p.in.pb * es) % 16 || (p.in.offset * es) % 16) return no("row form: planar input with 16-byte aligned pitches");
+    if (p.out.pf != 1) return no("output must be byxf");
+    if ((p.out.px * es) % 16 || (p.out.py * es) % 16 || (p.out.pb * es) % 16 || (p.out.offset * es) % 16) return no("output pitches must be 16-byte aligned");
+    if (p.stride_x != p.stride_y || (p.stride_x != 1 && p.stride_x != 2) || p.dil_x != 1 || p.dil_y != 1) return no("row form: stride 1 or 2, no dilation");
     if ((p.ofm != 64 && p.ofm != 32) || p.out.f != p.ofm || p.in.f != p.ifm) return no("row form: 32 or 64 output features");
-    const int xb = kRCols / p.ofm;
     if (p.kh < 1 || p.kh > 16 || p.kw < 1 || p.ifm < 1 || p.ifm * p.kh > 24) return no("row form: C * kh up to 24");
-    if (p.in.x < 32 || p.in.y < 2) return no("row form: image at least 32 wide");
-    for (int v = 0; v < 2; ++v) { int u0, off; rows_window(p.pad_x, xb, v, u0, off); if (off + 2 * (xb - 1) + p.kw - 1 > 31) return no("row form: the filter window exceeds 32 columns"); }
     if (p.pad_x < 0 || p.pad_y < 0) return no("row form: non-negative padding");
-    if (!p.quantization || p.i_qf != 1.0f) return no("row form: per-feature quantisation factors, no input factor");
-    const bool mul_oqf = p.calibration || p.o_qf != 1.0f;
-    if (mul_oqf && !(!p.calibration && p.o_qf > 0.0f && (p.out.dtype == CLDNN_B200_U8 || p.act != CLDNN_B200_ACT_RELU))) return no("row form: output factor not in the conversion-free set");
-    if (p.act != CLDNN_B200_ACT_NONE && p.act != CLDNN_B200_ACT_RELU) return no("row form: activation none or ReLU");
-    if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32) return no("row form: 32-bit integer bias");
-    if (make_epi_cfg(p).dont_dequantize_bias) return no("row form: bias in the accumulator's scale");
+    const RowsGeom g = rows_geom(p);
+    if (g.ustep % g.align) return no("row form: x-blocks do not step by whole 16-byte units");
+    if (p.in.x < g.kwin || p.in.y < p.stride_y) return no("row form: image narrower than a window");
+    for (int v = 0; v < 2; ++v) if (g.off[v] + p.stride_x * (g.xb - 1) + p.kw - 1 > g.kwin - 1) return no("row form: the filter window exceeds 32 bytes of columns");
+    if (!half) {
+        if (!p.quantization || p.i_qf != 1.0f) return no("row form: per-feature quantisation factors, no input factor");
+        const bool mul_oqf = p.calibration || p.o_qf != 1.0f;
+        if (mul_oqf && !(!p.calibration && p.o_qf > 0.0f && (p.out.dtype == CLDNN_B200_U8 || p.act != CLDNN_B200_ACT_RELU))) return no("row form: output factor not in the conversion-free set");
+        if (p.act != CLDNN_B200_ACT_NONE && p.act != CLDNN_B200_ACT_RELU) return no("row form: activation none or ReLU");
+        if (p.bias_dtype != CLDNN_B200_NONE && p.bias_dtype != CLDNN_B200_I32) return no("row form: 32-bit integer bias");
+        if (make_epi_cfg(p).dont_dequantize_bias) return no("row form: bias in the accumulator's scale");
+    }
     const int P_ = (p.in.y + 2 * p.pad_y - p.kh) / p.stride_y + 1, Q_ = (p.in.x + 2 * p.pad_x - p.kw) / p.stride_x + 1;
     if (p.out.y != P_ || p.out.x != Q_ || p.out.b != p.in.b) return no("output size does not match the sliding-window rule");
-    const RowsGeom g = rows_geom(p);
     if (g.plane_rows > 256) return no("row form: filter too tall");
     if (1024 + g.b_bytes + 2 * g.stage_bytes + g.pad_bytes + sizeof(RowsAux) > kRowsSmemLimit) return no("row form: filter image and two stages of rows exceed shared memory");
     return true;
@@ -404,87 +474,101 @@ bool first_rows_plan(const cldnn_b200_conv_params& p, std::string* why)
 
 size_t first_rows_scratch(const cldnn_b200_conv_params& p) { return (size_t)2 * p.ifm * p.kh * kRCols * 32; }
 
-int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p_in, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out)
+int32_t first_rows_prepare(cldnn_b200_ctx_impl* ctx, const cldnn_b200_conv_params& p_in, const cldnn_b200_args* a, cldnn_b200_prepared_impl* out, int groups)
 {
-    const cldnn_b200_conv_params p = simplified_conv_params(p_in);
+    const bool half = p_in.in.dtype == CLDNN_B200_F16;
+    const cldnn_b200_conv_params p = half ? p_in : simplified_conv_params(p_in);
     std::string why;
-    if (!first_rows_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_first: " + why);
-    if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: input, output and weights are required");
-    if (p.bias_dtype != CLDNN_B200_NONE && !a->bias) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: bias_dtype set but no bias pointer");
-    if (!a->weights_quantization_factors) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: quantization set but no factors");
+    if (!first_rows_plan(p, &why)) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "first layer: " + why);
+    if (!a->input0 || !a->output || !a->weights) return fail(CLDNN_B200_INVALID_ARG, "first layer: input, output and weights are required");
+    if (p.bias_dtype != CLDNN_B200_NONE && !a->bias) return fail(CLDNN_B200_INVALID_ARG, "first layer: bias_dtype set but no bias pointer");
+    if (!half && !a->weights_quantization_factors) return fail(CLDNN_B200_INVALID_ARG, "first layer: quantization set but no factors");
     const size_t need = first_rows_scratch(p);
-    if (!a->scratch || a->scratch_bytes < need) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: needs " + std::to_string(need) + " bytes of scratch for the packed weights");
-    if (((uintptr_t)a->scratch | (uintptr_t)a->output | (uintptr_t)a->input0) & 15) return fail(CLDNN_B200_INVALID_ARG, "conv_i8_first: input, scratch and output must be 16-byte aligned");
-    if (!rows_load_entry_point()) return fail(CLDNN_B200_ERROR, "conv_i8_first: cuTensorMapEncodeTiled is not available");
+    if (!a->scratch || a->scratch_bytes < need) return fail(CLDNN_B200_INVALID_ARG, "first layer: needs " + std::to_string(need) + " bytes of scratch for the packed weights");
+    if (((uintptr_t)a->scratch | (uintptr_t)a->output | (uintptr_t)a->input0) & 15) return fail(CLDNN_B200_INVALID_ARG, "first layer: input, scratch and output must be 16-byte aligned");
+    if (!rows_load_entry_point()) return fail(CLDNN_B200_ERROR, "first layer: cuTensorMapEncodeTiled is not available");
 
+    const RowsGeom g = rows_geom(p);
+    const int es = g.es;
     RowsParams P{};
     P.N = p.in.b; P.C = p.ifm; P.P = p.out.y; P.Q = p.out.x; P.kh = p.kh; P.ofm = p.ofm;
     P.tiles_y = (P.P + 127) / 128;
-    P.xb = kRCols / p.ofm; P.ofm_shift = p.ofm == 64 ? 6 : 5;
+    P.xb = g.xb; P.ofm_shift = p.ofm == 64 ? 6 : 5;
     const int tiles_x = (P.Q + P.xb - 1) / P.xb;
     P.jcount[0] = (tiles_x + 1) / 2; P.jcount[1] = tiles_x / 2;
-    int off[2];
-    for (int v = 0; v < 2; ++v) { rows_window(p.pad_x, P.xb, v, P.u0[v], off[v]); P.total[v] = P.N * P.tiles_y * P.jcount[v]; }
-    for (int ky = 0; ky < p.kh; ++ky) { const int t = ky - p.pad_y; P.row_r[ky] = t & 1; P.row_q[ky] = (t - (t & 1)) / 2; }
-    // A plane holds the input rows of one parity that the tile's output rows touch: rows m_lo .. rows_in_tile - 1 + q_max of that
-    // parity's numbering, in whole 8-row groups.  The MMA reads 128 rows from its start row whatever the plane holds: the surplus
-    // are the next plane's bytes (or the pad behind the last stage) and feed accumulator rows that nothing reads.
-    const RowsGeom g = rows_geom(p);
+    for (int v = 0; v < 2; ++v) { P.u0[v] = g.u0[v]; P.total[v] = P.N * P.tiles_y * P.jcount[v]; }
+    P.ustep = g.ustep; P.planes = g.planes;
+    for (int ky = 0; ky < p.kh; ++ky) { const int t = ky - p.pad_y; P.row_q[ky] = floor_div(t, p.stride_y); P.row_r[ky] = t - P.row_q[ky] * p.stride_y; }
+    // A plane holds the input rows of one parity (one plane of all rows with stride 1) that the tile's output rows touch, in whole
+    // 8-row groups.  The MMA reads 128 rows from its start row whatever the plane holds: the surplus are the next plane's bytes
+    // (or the pad behind the last stage) and feed accumulator rows that nothing reads.
     const int plane_rows = g.plane_rows;
     P.m_lo = g.m_lo;
     P.a_plane_bytes = plane_rows * 32; P.a_stage_bytes = (int32_t)g.stage_bytes; P.b_bytes = (int32_t)g.b_bytes;
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
-    if (max_smem < 1024 + g.b_bytes + 2 * g.stage_bytes + g.pad_bytes + sizeof(RowsAux)) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_i8_first: not enough shared memory for the row form");
+    if (max_smem < 1024 + g.b_bytes + 2 * g.stage_bytes + g.pad_bytes + sizeof(RowsAux)) return fail(CLDNN_B200_OUT_OF_RESOURCES, "first layer: not enough shared memory for the row form");
     P.stages = (int)std::min<size_t>(kRMaxStages, (max_smem - 1024 - g.pad_bytes - g.b_bytes - sizeof(RowsAux)) / g.stage_bytes);
     P.pad_bytes = g.pad_bytes;
     const size_t smem = 1024 + g.b_bytes + (size_t)P.stages * g.stage_bytes + g.pad_bytes + sizeof(RowsAux);
-    const uint32_t a_fmt = p.in.dtype == CLDNN_B200_U8 ? 0u : 1u;
-    P.idesc = (2u << 4) | (a_fmt << 7) | (1u << 10) | ((uint32_t)(kRCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-    P.out_px = p.out.px; P.out_py = p.out.py; P.out_pb = p.out.pb; P.out_off = p.out.offset;
+    if (half) P.idesc = (1u << 4) | ((uint32_t)(kRCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);          // f16 x f16 -> f32
+    else P.idesc = (2u << 4) | ((p.in.dtype == CLDNN_B200_U8 ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(kRCols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    P.out_px = p.out.px * es; P.out_py = p.out.py * es; P.out_pb = p.out.pb * es; P.out_off = p.out.offset * es;      // bytes
     P.epi = make_epi_cfg(p);
-    P.mul_oqf = (p.calibration || p.o_qf != 1.0f) ? 1 : 0;
+    P.mul_oqf = (!half && (p.calibration || p.o_qf != 1.0f)) ? 1 : 0;
     P.mode = (p.out.dtype == CLDNN_B200_U8 ? 0 : (p.act == CLDNN_B200_ACT_RELU ? 2 : 1)) + (P.mul_oqf ? 4 : 0);
     P.acc_bound = (float)p.ifm * (float)p.kh * (float)p.kw * (p.in.dtype == CLDNN_B200_U8 ? 255.0f : 128.0f) * 128.0f;
-    P.st32 = (((uintptr_t)a->output + (uintptr_t)p.out.offset) % 32 == 0 && p.out.px % 32 == 0 && p.out.py % 32 == 0 && p.out.pb % 32 == 0) ? 1 : 0;
+    P.act = p.act; P.act_m = p.act_m; P.act_n = p.act_n; P.bias_dtype = p.bias_dtype;
+    P.st32 = (((uintptr_t)a->output + (uintptr_t)P.out_off) % 32 == 0 && P.out_px % 32 == 0 && P.out_py % 32 == 0 && P.out_pb % 32 == 0) ? 1 : 0;
     P.out = (uint8_t*)a->output; P.bias = a->bias; P.quant = a->weights_quantization_factors;
     P.status = ctx->d_status;
+    P.groups = groups == 4 ? 4 : 2;
 
-    for (int r = 0; r < 2; ++r) {
-        const int rows_r = (p.in.y - r + 1) / 2;
+    const CUtensorMapDataType dt = half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    for (int r = 0; r < g.planes; ++r) {
+        const int rows_r = (p.in.y - r + g.planes - 1) / g.planes;
         cuuint64_t dims[4] = {(cuuint64_t)p.in.x, (cuuint64_t)rows_r, (cuuint64_t)p.ifm, (cuuint64_t)p.in.b};
-        cuuint64_t strides[3] = {(cuuint64_t)(2 * p.in.py), (cuuint64_t)p.in.pf, (cuuint64_t)p.in.pb};
-        cuuint32_t box[4] = {32u, (cuuint32_t)plane_rows, (cuuint32_t)p.ifm, 1u};
-        cuuint32_t es[4] = {1, 1, 1, 1};
-        void* ptr = (char*)const_cast<void*>(a->input0) + p.in.offset + (int64_t)r * p.in.py;
-        const CUresult cr = r_encode_tiled(&P.tmA[r], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        cuuint64_t strides[3] = {(cuuint64_t)(g.planes * p.in.py * es), (cuuint64_t)(p.in.pf * es), (cuuint64_t)(p.in.pb * es)};
+        cuuint32_t box[4] = {(cuuint32_t)g.kwin, (cuuint32_t)plane_rows, (cuuint32_t)p.ifm, 1u};
+        cuuint32_t est[4] = {1, 1, 1, 1};
+        void* ptr = (char*)const_cast<void*>(a->input0) + (p.in.offset + (int64_t)r * p.in.py) * es;
+        const CUresult cr = r_encode_tiled(&P.tmA[r], dt, 4, ptr, dims, strides, box, est, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                            CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "conv_i8_first: tensor map of the input rows refused (" + std::to_string((int)cr) + ")");
+        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "first layer: tensor map of the input rows refused (" + std::to_string((int)cr) + ")");
     }
+    if (g.planes == 1) P.tmA[1] = P.tmA[0];
     {
-        cuuint64_t dims[2] = {32u, (cuuint64_t)(2 * p.ifm * p.kh * kRCols)};
+        cuuint64_t dims[2] = {(cuuint64_t)g.kwin, (cuuint64_t)(2 * p.ifm * p.kh * kRCols)};
         cuuint64_t strides[1] = {32u};
-        cuuint32_t box[2] = {32u, (cuuint32_t)kRCols};
-        cuuint32_t es[2] = {1, 1};
-        const CUresult cr = r_encode_tiled(&P.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->scratch, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        cuuint32_t box[2] = {(cuuint32_t)g.kwin, (cuuint32_t)kRCols};
+        cuuint32_t est[2] = {1, 1};
+        const CUresult cr = r_encode_tiled(&P.tmB, dt, 2, a->scratch, dims, strides, box, est, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                            CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "conv_i8_first: tensor map of the filter rows refused (" + std::to_string((int)cr) + ")");
+        if (cr != CUDA_SUCCESS) return fail(CLDNN_B200_ERROR, "first layer: tensor map of the filter rows refused (" + std::to_string((int)cr) + ")");
     }
-    P.groups = p_in.tune == 5 ? 4 : 2;
-    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<2>, ctx->device, smem));
-    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<4>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<2, false>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<4, false>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<2, true>, ctx->device, smem));
+    B200_CUDA(raise_smem_limit((const void*)conv_i8_first_rows_kernel<4, true>, ctx->device, smem));
     int grid = ctx->prop.multiProcessorCount & ~1;
     if (grid < 2) grid = 2;
     const int most = std::max(P.total[0], P.total[1]);
     if (grid > 2 * most) grid = 2 * most;
 
     // pack the filter once, on the context's stream, before anything that is prepared here can run
-    const int pack_total = 2 * p.ifm * p.kh * kRCols * 32;
-    rows_pack_weights<<<(pack_total + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
-                                                                         p.ifm, p.kh, p.kw, p.ofm, off[0], off[1], (uint8_t*)a->scratch);
+    const int pack_total = 2 * p.ifm * p.kh * kRCols * g.kwin;
+    if (half) rows_pack_weights<__half><<<(pack_total + 255) / 256, 256, 0, ctx->stream>>>((const __half*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
+                                                                                          p.ifm, p.kh, p.kw, p.ofm, p.stride_x, g.off[0], g.off[1], (__half*)a->scratch);
+    else rows_pack_weights<int8_t><<<(pack_total + 255) / 256, 256, 0, ctx->stream>>>((const int8_t*)a->weights, p.w_po, p.w_pi, p.w_py, p.w_px, p.w_offset,
+                                                                                      p.ifm, p.kh, p.kw, p.ofm, p.stride_x, g.off[0], g.off[1], (int8_t*)a->scratch);
     B200_CUDA(cudaGetLastError());
-    out->fn = [P, grid, smem](cudaStream_t s) {
-        if (P.groups == 4) conv_i8_first_rows_kernel<4><<<grid, rows_threads(4), smem, s>>>(P);
-        else conv_i8_first_rows_kernel<2><<<grid, rows_threads(2), smem, s>>>(P);
+    out->fn = [P, grid, smem, half](cudaStream_t s) {
+        if (half) {
+            if (P.groups == 4) conv_i8_first_rows_kernel<4, true><<<grid, rows_threads(4), smem, s>>>(P);
+            else conv_i8_first_rows_kernel<2, true><<<grid, rows_threads(2), smem, s>>>(P);
+        } else {
+            if (P.groups == 4) conv_i8_first_rows_kernel<4, false><<<grid, rows_threads(4), smem, s>>>(P);
+            else conv_i8_first_rows_kernel<2, false><<<grid, rows_threads(2), smem, s>>>(P);
+        }
         return cudaGetLastError();
     };
     out->launches = 1;

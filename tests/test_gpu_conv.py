@@ -309,7 +309,8 @@ def test_conv_i8_first_row_form_refusals(eng):
         p = cases.copy_params(case.p); p.tune = 4
         return k.supports(p)
     assert sup()
-    assert not sup(stride=1)
+    assert not sup(stride=1)                 # 8-bit x-blocks of four columns at stride 1 step by 8 bytes, TMA needs 16
+    assert not sup(stride=3)
     assert sup(K=32, kh=3, kw=3, pad=1)      # 32 features: x-blocks of eight columns, a 3-wide filter still fits the window
     assert not sup(K=32)                     # ... a 7-wide one does not
     assert not sup(K=96)

@@ -37,9 +37,9 @@ def _f16_case(seed, **kw):
     return cases.make_conv_case(seed, fmt="bfyx", f_align=1, out_fmt="byxf", in_dtype=np.float16, out_dtype=np.float16, quant=False, **kw)
 
 
-def _close(eng, case):
+def _close(eng, case, tune=0):
     want = cases.run_oracle(case).astype(np.float32)
-    got = cases.run_gpu(eng, case, "conv_first_tc").astype(np.float32)
+    got = cases.run_gpu(eng, case, "conv_first_tc", tune).astype(np.float32)
     n = case.out_elems
     scale = float(np.abs(want[:n]).max())
     assert scale > 0
@@ -86,6 +86,46 @@ def test_conv_first_tc_f16_epilogues(eng):
         if extra.get("act") == abi.ACT_RELU_NEGATIVE_SLOPE:
             case.p.act_m = 0.125
         _close(eng, case)
+
+
+ROW_FORM_F16 = {
+    # what the row form (tuning variants 2 / 3: output rows as GEMM rows, image rows by TMA, banded filter matrices) takes in fp16:
+    # stride 1 or 2, 64 output features (eight columns of 32 features do not fit a 16-column window), row pitch a multiple of 16 bytes
+    "vgg_conv1_1": dict(N=2, C=3, K=64, H=64, W=64),
+    "vgg_conv1_1_two_row_tiles": dict(N=3, C=3, K=64, H=224, W=48),
+    "many_tiles_stride2": dict(N=9, C=3, K=64, H=93, W=104, stride=2),
+    "one_feature_5x5": dict(N=3, C=1, K=64, H=19, W=24, kh=5, kw=5, pad=2),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ROW_FORM_F16))
+def test_conv_first_tc_row_form_f16_matches_oracle(eng, name):
+    k = eng.kernel("conv_first_tc")
+    for i, extra in enumerate((dict(), dict(bias="none", act=abi.ACT_NONE), dict(act=abi.ACT_CLAMP))):
+        case = _f16_case(60 + i, **ROW_FORM_F16[name], **extra)
+        for tune in (2, 3):
+            p = cases.copy_params(case.p); p.tune = tune
+            assert k.supports(p), (name, tune)
+            want = _close(eng, case, tune)
+            assert (want != 0).any()
+
+
+def test_conv_first_tc_row_form_refusals(eng):
+    k = eng.kernel("conv_first_tc")
+    def sup(**kw):
+        geom = dict(N=1, C=3, K=64, H=32, W=32)
+        geom.update(kw)
+        p = cases.copy_params(_f16_case(69, **geom).p); p.tune = 2
+        return k.supports(p)
+    assert sup()
+    assert not sup(W=36)                     # 72-byte rows
+    assert not sup(K=96)
+    assert not sup(K=32)
+    assert not sup(stride=4, kh=11, kw=11, pad=0, H=67, W=64)
+    assert not sup(kh=3, kw=9, pad=1)        # four outputs' taps no longer fit sixteen columns
+    case = cases.make_conv_case(70, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, N=1, C=3, K=64, H=32, W=32)
+    p = cases.copy_params(case.p); p.tune = 2
+    assert not k.supports(p)                 # the 8-bit row form is reached through conv_i8_first
 
 
 def test_conv_first_tc_reads_any_input_pitches(eng):
