@@ -349,6 +349,8 @@ CLDNN_B200_API int32_t cldnn_b200_graph_destroy(cldnn_b200_graph g);
  * are enqueued on the context's stream and the call returns without waiting.
  *   - Constants whose packed weights exceed 32 KiB (output features x padded C*kh*8) are refused with
  *     CLDNN_B200_UNSUPPORTED_SIZE; everything "conv_i8_first" refuses is refused here with the same codes.
+ *   - params->tune selects among the kernel's CTAs-per-SM variants (1..3) only: the row form (tune 4 / 5 of "conv_i8_first")
+ *     needs a far larger workspace and is not offered here; those values run the default variant.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
  *     before starting any stream capture on the device.
  *   - All calls on a device share the one array and it keeps the previous call's contents.  Each call rewrites every
