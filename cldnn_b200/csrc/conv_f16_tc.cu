@@ -40,7 +40,12 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxBufs = 4;
 constexpr int kMaxBN = 256;
 constexpr uint32_t kErr = 0x60u;
-enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2 };
+// A_PATCH: stride-1 filters whose weights fit in shared memory beside the ring.  The weights of every tap stay resident; per
+// channel chunk and filter COLUMN one patch of (bh + kh - 1) x bw input pixels is loaded, and the kh taps of that column read it
+// from row r * bw on (128 rows each: the tile's bw x bh pixels under filter row r) -- a third of the activation bytes of one
+// load per tap, and no weight traffic per tile.  The deep-pipeline layers with 64 features are bound by what an SM can take
+// in per clock, so bytes are what counts there.
+enum AMode { A_FLAT = 0, A_IM2COL = 1, A_TILED = 2, A_PATCH = 3 };
 
 struct alignas(64) Params {
     CUtensorMap tmA, tmB, tmO, tmE;
@@ -53,6 +58,7 @@ struct alignas(64) Params {
     int32_t bw, bh, bb, tiles_w, tiles_h;
     int32_t stages, a_stage_bytes, b_stage_bytes, a_tx_bytes, b_tx_bytes, ring_bytes, stage_rows;
     uint32_t sbo, layout_type, idesc, tmem_cols;
+    int32_t b_total_bytes, patch_alloc;      // patch mode: all taps' weights (resident), bytes reserved per patch
     int32_t batch_tiles;                     // batched GEMM view: tiles per batch, the weight 'tap' is the batch index (0 = plain convolution)
     int32_t ofm, fused, bias_dtype, act, eltw_act;
     float act_m, act_n, eltw_m, eltw_n;
@@ -63,6 +69,7 @@ struct alignas(64) Params {
 struct Aux {
     uint64_t full[kMaxStages], empty[kMaxStages];
     uint64_t tmem_full[kMaxBufs], tmem_empty[kMaxBufs], res_full[kMaxBufs], stage_free[kMaxBufs], out_ready[kMaxBufs];
+    uint64_t b_full;                         // patch mode: the resident weights have landed
     uint32_t tmem_base, abort;
     alignas(16) float bias[kGroups][kMaxBN];
 };
@@ -168,6 +175,7 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
             mbar_init(smem_u32(&aux->res_full[a]), 1); mbar_init(smem_u32(&aux->stage_free[a]), 1);
             mbar_init(smem_u32(&aux->out_ready[a]), 4);
         }
+        mbar_init(smem_u32(&aux->b_full), 1);
         aux->abort = 0u;
         mbar_fence_init();
         prefetch_tensormap(&P.tmA); prefetch_tensormap(&P.tmB); prefetch_tensormap(&P.tmO);
@@ -178,7 +186,8 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
-    const bool boxed = P.a_mode == A_TILED;
+    const bool patch = P.a_mode == A_PATCH;
+    const bool boxed = P.a_mode == A_TILED || patch;
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -188,6 +197,14 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
             const bool leader = elect_one();
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
             const int bke = P.bk >> 1;                               // channels per chunk
+            if (patch && leader && blockIdx.x < (unsigned)P.total_tiles) {
+                // every tap's weights, once per CTA (one feature tile in this mode)
+                const uint32_t bf = smem_u32(&aux->b_full);
+                mbar_expect_tx(bf, (uint32_t)P.b_total_bytes);
+                uint32_t dst = b_base;
+                for (int tp = 0; tp < P.kh * P.kw; ++tp)
+                    for (int ch = 0; ch < P.chunks; ++ch, dst += (uint32_t)P.b_stage_bytes) tma_load_3d(dst, &P.tmB, bf, ch * bke, tp, 0);
+            }
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
                 const int n_tile = tile / P.m_tiles, m_tile = tile - n_tile * P.m_tiles;
                 int c_w = 0, c_h = 0, c_n = 0;
@@ -206,7 +223,10 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
                     const uint32_t a_dst = a_base + (uint32_t)(stage * P.a_stage_bytes);
                     const uint32_t b_dst = b_base + (uint32_t)(stage * P.b_stage_bytes);
                     const int c0 = cc * bke;
-                    if (leader) {
+                    if (leader && patch) {
+                        mbar_expect_tx(full, (uint32_t)P.a_tx_bytes);
+                        for (int sc = 0; sc < P.kw; ++sc) tma_load_4d(a_dst + (uint32_t)(sc * P.patch_alloc), &P.tmA, full, c0, c_w + sc, c_h, c_n);
+                    } else if (leader) {
                         mbar_expect_tx(full, (uint32_t)(P.a_tx_bytes + P.b_tx_bytes));
                         if (P.a_mode == A_FLAT) tma_load_2d(a_dst, &P.tmA, full, c0, m_tile * kBM);
                         else if (P.a_mode == A_IM2COL) tma_load_im2col_4d(a_dst, &P.tmA, full, c0, c_w, c_h, c_n, (uint16_t)(s * P.dil_x), (uint16_t)(r * P.dil_y));
@@ -241,6 +261,9 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
             const uint32_t idesc = P.idesc;
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
+            const uint32_t patch_step = (uint32_t)P.patch_alloc >> 4, row_step = (uint32_t)(P.bw * P.bk) >> 4;
+            const uint32_t b_chunk = (uint32_t)P.b_stage_bytes >> 4;
+            if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErr + 7u));
             for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x, ++t) {
                 const int acc = t % NBUF;
                 if (!__all_sync(0xffffffffu, mbar_wait_lean(smem_u32(&aux->tmem_empty[acc]), (((uint32_t)(t / NBUF) & 1u)) ^ 1u, s_abort, P.status, kErr + 1u))) { ok = false; break; }
@@ -249,7 +272,20 @@ conv_f16_tc_kernel(const __grid_constant__ Params P)
                 uint32_t accf = 0u;
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!__all_sync(0xffffffffu, mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErr + 2u))) { ok = false; break; }
-                    if (leader) {
+                    if (leader && patch) {
+                        // channel chunk ks: per filter column sc one patch; its rows r * bw .. r * bw + 127 are the tile under filter row r
+                        uint32_t af = accf;
+                        for (int sc = 0; sc < P.kw; ++sc)
+                            for (int r = 0; r < P.kh; ++r) {
+                                const uint32_t al = a_lo + (uint32_t)sc * patch_step + (uint32_t)r * row_step;
+                                const uint32_t bl = b_lo0 + (uint32_t)((r * P.kw + sc) * P.chunks + ks) * b_chunk;
+                                if (kk == 4) mma_chunk<4>(d_tmem, al, bl, hi, idesc, af);
+                                else if (kk == 2) mma_chunk<2>(d_tmem, al, bl, hi, idesc, af);
+                                else mma_chunk<1>(d_tmem, al, bl, hi, idesc, af);
+                                af = 1u;
+                            }
+                        tc_commit(empty0 + 8u * (uint32_t)stage);
+                    } else if (leader) {
                         if (kk == 4) mma_chunk<4>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else if (kk == 2) mma_chunk<2>(d_tmem, a_lo, b_lo, hi, idesc, accf);
                         else mma_chunk<1>(d_tmem, a_lo, b_lo, hi, idesc, accf);
@@ -414,7 +450,8 @@ static bool f16_driver_entry_points()
 struct F16Plan { int a_mode, bn, bk, bw, bh, bb; };
 static const int kF16TuneBN[3] = {64, 128, 256};
 // tune index -> (addressing mode, feature tile): 1 + mode * 3 + {64, 128, 256}; 0 = automatic
-static int f16_tune_count(const void*) { return 1 + 3 * 3; }
+static int f16_tune_count(const void*) { return 1 + 4 * 3; }           // 1 + 3 * mode + feature tile; modes flat / im2col / tiled / patch
+constexpr size_t kF16PatchWeightBytes = 80 * 1024;                  // largest weight tensor the patch mode keeps resident
 
 static bool f16_dense(const cldnn_b200_tensor& t) { return t.py == t.px * t.x && t.pb == t.py * t.y; }
 
@@ -427,6 +464,21 @@ static void f16_choose_box(int Q, int Pn, int N, int& bw, int& bh, int& bb)
             const double tiles = (double)((Q + w - 1) / w) * ((Pn + h - 1) / h) * ((N + b - 1) / b);
             const double score = ((double)Q * Pn * N) / (tiles * 128.0) + 1e-4 * w + 1e-6 * h;
             if (score > best) { best = score; bw = w; bh = h; bb = b; }
+        }
+}
+
+// patch mode: a tile of tw x th output pixels of one image (tw * th <= 128); fewest wasted tile rows first, then least traffic
+static void f16_choose_patch(int Q, int Pn, int kh, int kw, int& tw, int& th)
+{
+    double best = -1.0; tw = 1; th = 1;
+    for (int w = 1; w <= Q && w <= 128; ++w)
+        for (int h = 1; h <= Pn && w * h <= 128; ++h) {
+            if (h + kh - 1 > 256) continue;
+            const double tiles = (double)((Q + w - 1) / w) * ((Pn + h - 1) / h);
+            const double eff = ((double)Q * Pn) / (tiles * 128.0);
+            const double traffic = tiles * kw * (h + kh - 1) * w / ((double)Q * Pn * kh * kw);   // relative to one load per tap
+            const double score = eff - 0.25 * traffic;
+            if (score > best) { best = score; tw = w; th = h; }
         }
 }
 
@@ -467,10 +519,16 @@ static bool f16_plan(const cldnn_b200_conv_params& p, F16Plan& pl, std::string* 
     if (mode == f16tc::A_TILED && !tiled_ok) return no("tiled addressing needs stride 1 or a pointwise filter");
     if (mode == f16tc::A_IM2COL && !im2col_ok) return no("im2col addressing limits exceeded (or tensor below 128 KiB)");
     if (bn == 0) bn = p.ofm > 128 ? 256 : (p.ofm > 64 ? 128 : 64);
+    if (mode == f16tc::A_PATCH) {
+        if (p.stride_x != 1 || p.stride_y != 1 || p.dil_x != 1 || p.dil_y != 1 || p.kh * p.kw == 1) return no("patch mode needs a stride-1 undilated filter larger than 1x1");
+        if (p.ofm > bn) return no("patch mode keeps one feature tile's weights resident: output features within one tile");
+        if ((size_t)p.kh * p.kw * cs * 2 * bn > kF16PatchWeightBytes) return no("patch mode keeps all weights in shared memory: at most 80 KiB");
+    }
     pl.a_mode = mode; pl.bn = bn; pl.bw = pl.bh = pl.bb = 1;
     if (mode == f16tc::A_TILED) f16_choose_box(p.out.x, p.out.y, p.out.b, pl.bw, pl.bh, pl.bb);
-    // TMA needs the flat output / residual views pixel-dense; the tiled mode takes pitches
-    if (mode != f16tc::A_TILED) {
+    if (mode == f16tc::A_PATCH) f16_choose_patch(p.out.x, p.out.y, p.kh, p.kw, pl.bw, pl.bh);
+    // TMA needs the flat output / residual views pixel-dense; the tiled and patch modes take pitches
+    if (mode != f16tc::A_TILED && mode != f16tc::A_PATCH) {
         if (!f16_dense(p.out)) return no("flat and im2col addressing need a pixel-dense output");
         if (p.fused_eltw && !p.in_out_opt && (!f16_dense(p.eltw) || p.eltw_stride_x != 1 || p.eltw_stride_y != 1)) return no("flat and im2col addressing need a pixel-dense unstrided residual");
     }
@@ -480,7 +538,7 @@ static bool f16_supports(const void* vp) { F16Plan pl; return f16_plan(*(const c
 
 static CUresult f16_pixel_map(CUtensorMap* tm, const F16Plan& pl, void* ptr, const cldnn_b200_tensor& t, int ofm, int sx, int sy)
 {
-    if (pl.a_mode == f16tc::A_TILED) {
+    if (pl.a_mode == f16tc::A_TILED || pl.a_mode == f16tc::A_PATCH) {
         cuuint64_t dims[4] = {(cuuint64_t)ofm, (cuuint64_t)((t.x + sx - 1) / sx), (cuuint64_t)((t.y + sy - 1) / sy), (cuuint64_t)t.b};
         cuuint64_t strides[3] = {(cuuint64_t)(t.px * sx * 2), (cuuint64_t)(t.py * sy * 2), (cuuint64_t)(t.pb * 2)};
         cuuint32_t box[4] = {64, (cuuint32_t)pl.bw, (cuuint32_t)pl.bh, (cuuint32_t)pl.bb};
@@ -548,7 +606,8 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.bn = pl.bn; P.n_tiles = (p.ofm + pl.bn - 1) / pl.bn;
     P.M_total = (int64_t)P.N * P.P * P.Q;
     P.bw = pl.bw; P.bh = pl.bh; P.bb = pl.bb;
-    const bool boxed = pl.a_mode == f16tc::A_TILED;
+    const bool patch = pl.a_mode == f16tc::A_PATCH;
+    const bool boxed = pl.a_mode == f16tc::A_TILED || patch;
     if (boxed) {
         P.tiles_w = (P.Q + pl.bw - 1) / pl.bw; P.tiles_h = (P.P + pl.bh - 1) / pl.bh;
         P.m_tiles = P.tiles_w * P.tiles_h * ((P.N + pl.bb - 1) / pl.bb);
@@ -557,6 +616,15 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.stage_rows = boxed ? pl.bw * pl.bh * pl.bb : f16tc::kBM;
     P.a_stage_bytes = f16tc::kBM * pl.bk; P.b_stage_bytes = pl.bn * pl.bk;
     P.a_tx_bytes = P.stage_rows * pl.bk; P.b_tx_bytes = pl.bn * pl.bk;
+    if (patch) {
+        // a stage holds the kw patches of one channel chunk; the tensor core reads 128 rows from row r * bw, r < kh
+        const int patch_rows = (pl.bh + p.kh - 1) * pl.bw, read_rows = (p.kh - 1) * pl.bw + f16tc::kBM;
+        P.k_steps = P.chunks;
+        P.patch_alloc = (((patch_rows > read_rows ? patch_rows : read_rows) * pl.bk) + 1023) / 1024 * 1024;
+        P.a_tx_bytes = p.kw * patch_rows * pl.bk;
+        P.a_stage_bytes = p.kw * P.patch_alloc;
+        P.b_total_bytes = p.kh * p.kw * P.chunks * P.b_stage_bytes;
+    }
     P.sbo = 8u * (uint32_t)pl.bk;
     P.layout_type = pl.bk == 128 ? 2u : (pl.bk == 64 ? 4u : 6u);
     // instruction descriptor: f32 accumulate, f16 x f16, both K-major, N, M
@@ -568,14 +636,15 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
     P.bias = a->bias; P.status = ctx->d_status;
 
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
-    const size_t stage_bytes = (size_t)P.a_stage_bytes + P.b_stage_bytes;
+    const size_t resident = patch ? (size_t)P.b_total_bytes : 0;
+    const size_t stage_bytes = (size_t)P.a_stage_bytes + (patch ? 0 : P.b_stage_bytes);
     const size_t staging_total = (size_t)2 * f16tc::kBM * (pl.bn > 128 ? 128 : pl.bn) * 2;   // two unit buffers of up to 128 features
     const size_t aux_bytes = sizeof(f16tc::Aux);
-    if (max_smem < 1024 + aux_bytes + staging_total + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_f16_tc: not enough shared memory");
-    int stages = (int)((max_smem - 1024 - aux_bytes - staging_total) / stage_bytes);
+    if (max_smem < 1024 + aux_bytes + staging_total + resident + 2 * stage_bytes) return fail(CLDNN_B200_OUT_OF_RESOURCES, "conv_f16_tc: not enough shared memory");
+    int stages = (int)((max_smem - 1024 - aux_bytes - staging_total - resident) / stage_bytes);
     if (stages > f16tc::kMaxStages) stages = f16tc::kMaxStages;
     P.stages = stages;
-    P.ring_bytes = (int32_t)(stages * stage_bytes);
+    P.ring_bytes = (int32_t)(stages * stage_bytes + resident);
     size_t smem_bytes = 1024 + (size_t)P.ring_bytes + staging_total + aux_bytes;
     const size_t one_cta_floor = max_smem / 2 + 1024;                // one CTA per SM, so tensor-memory allocation never waits
     if (smem_bytes < one_cta_floor) smem_bytes = one_cta_floor;
@@ -598,6 +667,13 @@ static int32_t f16_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn
         cuuint32_t es[4] = {1, (cuuint32_t)p.stride_x, (cuuint32_t)p.stride_y, 1};
         cr = h_encode_im2col(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, in_ptr, dims, strides, lower, upper, (cuuint32_t)bke, (cuuint32_t)f16tc::kBM, es,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (patch) {
+        cuuint64_t dims[4] = {(cuuint64_t)cs, (cuuint64_t)p.in.x, (cuuint64_t)p.in.y, (cuuint64_t)p.in.b};
+        cuuint64_t strides[3] = {(cuuint64_t)(p.in.px * 2), (cuuint64_t)(p.in.py * 2), (cuuint64_t)(p.in.pb * 2)};
+        cuuint32_t box[4] = {(cuuint32_t)bke, (cuuint32_t)pl.bw, (cuuint32_t)(pl.bh + p.kh - 1), 1};
+        cuuint32_t es[4] = {1, 1, 1, 1};
+        cr = h_encode_tiled(&P.tmA, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, in_ptr, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         const int sx = p.stride_x, sy = p.stride_y;
         const bool strided_view = sx != 1 || sy != 1;

@@ -74,6 +74,46 @@ def test_conv_f16_tc_every_tuning_variant(eng, name):
     assert ran >= 3
 
 
+PATCH_MODE = {
+    # geometries the patch mode takes (stride 1, one feature tile, weights within 80 KiB): tunes 10 / 11 / 12
+    "vgg_conv1_2": dict(N=2, C=64, K=64, H=56, W=56),
+    "many_tiles_per_cta": dict(N=40, C=64, K=64, H=56, W=56),                 # ~1000 tiles: every ring wraps several times
+    "ragged_map_32_features": dict(N=3, C=32, K=40, H=19, W=23),
+    "5x5_16_features": dict(N=2, C=16, K=32, H=21, W=20, kh=5, kw=5, pad=2),
+    "no_padding_k128": dict(N=2, C=32, K=128, H=17, W=18, pad=0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(PATCH_MODE))
+def test_conv_f16_tc_patch_mode(eng, name):
+    """Resident weights, one activation patch per filter column (tunes 10..12), plain and with a fused residual."""
+    k = eng.kernel("conv_f16_tc")
+    for extra in (dict(), dict(fused=True, act=abi.ACT_NONE)):
+        kw = dict(F16); kw.update(extra)
+        case = cases.make_conv_case(35, **PATCH_MODE[name], **kw)
+        ran = 0
+        for tune in (10, 11, 12):
+            p = cases.copy_params(case.p); p.tune = tune
+            if not k.supports(p):
+                continue
+            _close(eng, case, "conv_f16_tc", tune)
+            ran += 1
+        assert ran >= 1, name
+    assert eng.device_status() == 0
+
+
+def test_conv_f16_tc_patch_mode_refusals(eng):
+    k = eng.kernel("conv_f16_tc")
+    def sup(**geom):
+        p = cases.copy_params(cases.make_conv_case(36, **geom, **F16).p); p.tune = 10
+        return k.supports(p)
+    assert sup(N=1, C=64, K=64, H=28, W=28)
+    assert not sup(N=1, C=64, K=128, H=28, W=28)              # two feature tiles of 64
+    assert not sup(N=1, C=64, K=64, H=28, W=28, stride=2)
+    assert not sup(N=1, C=64, K=64, H=28, W=28, kh=1, kw=1, pad=0)
+    assert not sup(N=1, C=256, K=64, H=14, W=14)              # 9 x 256 x 64 halves exceed the resident budget
+
+
 EPILOGUES = {
     "no_bias": dict(bias="none"),
     "no_activation": dict(act=abi.ACT_NONE),
