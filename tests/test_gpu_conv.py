@@ -296,6 +296,23 @@ def test_conv_i8_first_row_form_matches_oracle(eng, name):
     assert eng.device_status() == 0
 
 
+def test_conv_i8_first_row_form_reads_a_padded_image(eng):
+    """The image inside a larger buffer (cldnn::padding around the data: row pitch and offset beyond the image, garbage in the
+    margin): the TMA boxes of the row form go by the pitches, and what lies outside the image counts as zero, as in the reference."""
+    geom = dict(N=3, C=3, K=64, H=62, W=64, kh=7, kw=7, stride=2, pad=3)
+    case = cases.make_conv_case(96, fmt="bfyx", f_align=1, out_fmt="byxf", out_dtype=np.uint8, **geom)
+    t, n = abi.tensor(abi.U8, geom["N"], geom["C"], geom["H"], geom["W"], "bfyx", 1, pad_lo=(1, 16), pad_hi=(2, 16))
+    buf = np.random.default_rng(97).integers(1, 256, size=n, dtype=np.int64).astype(np.uint8)
+    buf.reshape(geom["N"], geom["C"], geom["H"] + 3, geom["W"] + 32)[:, :, 1:1 + geom["H"], 16:16 + geom["W"]] = case.x_logical
+    case.p.in_ = t
+    case.inp = buf
+    k = eng.kernel("conv_i8_first")
+    for tune in (3, 4, 5):
+        p = cases.copy_params(case.p); p.tune = tune
+        assert k.supports(p), tune
+        _exact(eng, case, "conv_i8_first", tune=tune)
+
+
 def test_conv_i8_first_row_form_refusals(eng):
     """What the row form does not take is refused by `supports` (the tuner then never offers it): other strides, feature counts,
     row pitches that are not a multiple of 16 bytes, epilogues outside the conversion-free set."""
