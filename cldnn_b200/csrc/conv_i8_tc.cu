@@ -677,8 +677,17 @@ static int32_t tc_prepare(cldnn_b200_ctx_impl* ctx, const void* vp, const cldnn_
     const size_t max_smem = (size_t)ctx->prop.sharedMemPerBlockOptin;
     const bool patch = pl.a_mode == A_PATCH;
     if (patch && !use_fast) return fail(CLDNN_B200_UNSUPPORTED_FORMAT, "conv_i8_tc: the patch mode exists for the specialised epilogue configuration only");
-    const size_t stage_bytes = (size_t)P.a_stage_bytes + (patch ? 0 : P.b_stage_bytes);
-    const size_t resident = patch ? (size_t)P.b_total_bytes : 0;
+    // Small weight tensors stay resident outside the patch mode as well: re-fetching them per tile costs as many memory requests
+    // as the activation tile (a weight box has one row per output feature however few bytes a row holds), which is what
+    // bounds the pointwise layers with few features.
+    constexpr size_t kResidentWeightBytes = 48 * 1024;
+    const size_t b_all = (size_t)P.n_tiles * P.k_steps * P.b_stage_bytes;
+    if (use_fast && !patch && !pl.pair && b_all <= kResidentWeightBytes && P.total_tiles >= 2 * ctx->prop.multiProcessorCount) {
+        P.b_resident = 1; P.b_total_bytes = (int32_t)b_all;
+    }
+    const bool resb = patch || P.b_resident;
+    const size_t stage_bytes = (size_t)P.a_stage_bytes + (resb ? 0 : P.b_stage_bytes);
+    const size_t resident = resb ? (size_t)P.b_total_bytes : 0;
     size_t staging_total = P.staged ? (size_t)P.nbuf * kBM * pl.bn : 0;
     // the specialised kernel's fused path keeps more staging tiles than accumulators (residual loads run further ahead)
     // as long as three operand stages still fit beside them

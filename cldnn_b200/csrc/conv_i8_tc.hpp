@@ -49,6 +49,7 @@ struct alignas(64) TcParams {
     int32_t patch_alloc;                 // bytes reserved per filter column's patch inside a stage (a stage holds the kw patches of one channel chunk)
     int32_t fast_variant;                // conv_i8_tc_fast: (output kind << 1) | ReLU before the residual sum
     int32_t epi_groups;                  // conv_i8_tc_fast: epilogue warp groups per CTA, 2 or 4
+    int32_t b_resident;                  // conv_i8_tc_fast, modes other than patch: the weights of every step and feature tile stay in shared memory
     int32_t pair;                        // conv_i8_tc_fast: CTA pairs (cta_group::2): m_tiles is even, the weight box holds bn / 2 rows
     float acc_bound;                     // K * max|activation| * 128: no accumulator can exceed it in magnitude
     // output / residual addressing for the direct path, in elements

@@ -325,8 +325,12 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // inside a one-lane branch cannot use: the role's instruction count per stage is what bounds small-tile layers.
         {
             const bool leader = ptx::elect_one();
-            if (leader && patch && blockIdx.x < (unsigned)P.total_tiles) {
-                // patch mode: every filter tap of every feature tile, once per CTA
+            // Weights that are small enough stay resident in the other modes too (P.b_resident): a layer with few input and
+            // output features would otherwise fetch the same few KB again for every tile -- as many requests as the
+            // activation tile itself costs, for nothing.
+            const bool resb = patch || P.b_resident != 0;
+            if (leader && resb && blockIdx.x < (unsigned)P.total_tiles) {
+                // every filter tap (and channel chunk) of every feature tile, once per CTA
                 const uint32_t bf = smem_u32(&aux->b_full);
                 mbar_expect_tx(bf, (uint32_t)P.b_total_bytes);
                 uint32_t dst = b_base;
@@ -337,7 +341,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             }
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
             const int stages = P.stages, k_steps = P.k_steps, chunks = P.chunks, bk = P.bk, kw = P.kw;
-            const uint32_t tx = (uint32_t)(patch ? P.a_tx_bytes : P.a_tx_bytes + P.b_tx_bytes);
+            const uint32_t tx = (uint32_t)(resb ? P.a_tx_bytes : P.a_tx_bytes + P.b_tx_bytes);
             const uint32_t a_stage = (uint32_t)P.a_stage_bytes, b_stage = (uint32_t)P.b_stage_bytes;
             const uint32_t full0 = smem_u32(&aux->full[0]), empty0 = smem_u32(&aux->empty[0]);
             TileWalk w; w.init(P, blockIdx.x, gridDim.x);
@@ -365,7 +369,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                         else tma_load_4d_pair(dst, &P.tmA, full_r0, c0, c_w + off_w, c_h + off_h, c_n);
                     } else if (leader) {
                         mbar_expect_tx(full, tx);
-                        if (!patch) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
+                        if (!resb) tma_load_3d(b_base + (uint32_t)stage * b_stage, &P.tmB, full, c0, tap, n0);
                         if (patch) {                                                            // one patch per filter column
                             for (int s = 0; s < kw; ++s) tma_load_4d(dst + (uint32_t)(s * patch_alloc), &P.tmA, full, c0, c_w + s, c_h, c_n);
                         }
@@ -412,7 +416,8 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
             const int patch_kind = (kh == 3 && kw_ == 3) ? (kk == 2 ? 1 : (kk == 4 ? 2 : 0)) : 0;   // 3x3 filters are issued straight-line
             int stage = 0; uint32_t phase = 0; bool ok = true; int t = 0;
             uint32_t a_lo = a_lo0, b_lo = b_lo0;
-            if (patch && blockIdx.x < (unsigned)P.total_tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u));
+            const bool resb = !patch && P.b_resident != 0;                           // resident weights outside the patch mode
+            if ((patch || resb) && blockIdx.x < (unsigned)P.total_tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&aux->b_full), 0u, s_abort, P.status, kErrMma + 2u));
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             for (; walk.valid() && ok; walk.next(), ++t) {
                 const int acc = t % NBUF;
@@ -422,13 +427,15 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                 uint32_t accf = 0u;
                 uint32_t b_col = 0u;                                                   // patch mode: weights of (filter column, channel chunk)
                 if (patch) b_col = b_lo0 + (uint32_t)(walk.n_tile * kh) * b_row_step;
+                uint32_t b_res = b_lo0 + (uint32_t)(walk.n_tile * k_steps) * b_step;  // resident weights: step ks of this feature tile
                 for (int ks = 0; ks < k_steps; ++ks) {
                     if (!__all_sync(0xffffffffu, mbar_wait_lean(full0 + 8u * (uint32_t)stage, phase, s_abort, P.status, kErrMma + 1u))) { ok = false; break; }
                     if (!patch) {
-                        if (kk == 4) { if (leader) mma_chunk<4, kPair>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
-                        else if (kk == 2) { if (leader) mma_chunk<2, kPair>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
-                        else { if (leader) mma_chunk<1, kPair>(d_tmem, a_lo, b_lo, hi, idesc, accf); }
-                        accf = 1u;
+                        const uint32_t b_cur = resb ? b_res : b_lo;
+                        if (kk == 4) { if (leader) mma_chunk<4, kPair>(d_tmem, a_lo, b_cur, hi, idesc, accf); }
+                        else if (kk == 2) { if (leader) mma_chunk<2, kPair>(d_tmem, a_lo, b_cur, hi, idesc, accf); }
+                        else { if (leader) mma_chunk<1, kPair>(d_tmem, a_lo, b_cur, hi, idesc, accf); }
+                        accf = 1u; b_res += b_step;
                     } else {
                         if (patch_kind == 1) { if (leader) patch_issue<3, 3, 2>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf); }
                         else if (patch_kind == 2) { if (leader) patch_issue<3, 3, 4>(d_tmem, a_lo, b_col, patch_step, b_tap_step, row_step, b_row_step, hi, idesc, accf); }
