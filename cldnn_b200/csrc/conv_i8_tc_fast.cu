@@ -315,7 +315,9 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
     griddep_launch_dependents();
-    griddep_wait();                                   // everything below may touch memory the previous kernel wrote or read
+    // Each role waits for the previous kernel of the stream itself, right before it first touches memory that kernel wrote or
+    // read (activations, residual, output).  The weights are constants of the network: the producer starts their resident
+    // copy before it waits, so that copy runs under the previous kernel's tail.  The MMA issuers touch no global memory.
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -339,6 +341,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
                         for (int ch = 0; ch < P.chunks; ++ch, dst += (uint32_t)P.b_stage_bytes)
                             tma_load_3d(dst, &P.tmB, bf, ch * P.bk, tp, nt * BN);
             }
+            griddep_wait();
             int stage = 0; uint32_t phase = 0; int64_t issued = 0; bool ok = true;
             const int stages = P.stages, k_steps = P.k_steps, chunks = P.chunks, bk = P.bk, kw = P.kw;
             const uint32_t tx = (uint32_t)(resb ? P.a_tx_bytes : P.a_tx_bytes + P.b_tx_bytes);
@@ -472,6 +475,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // ------------------------------ TMA store issuer --------------------------
         {
             const bool leader = ptx::elect_one();                    // issues, commits and waits for the stores: bulk groups are per thread
+            griddep_wait();
             int t = 0;
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;            // the output of an im2col tile is addressed by its first pixel index
@@ -502,6 +506,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         // never holds back the operand loads of later tiles.
         if (kFused) {
             const bool leader = ptx::elect_one();
+            griddep_wait();
             int t = 0;
             TileWalk walk; walk.init(P, blockIdx.x, gridDim.x);
             if (P.a_mode == A_IM2COL) walk.mode = A_FLAT;
@@ -529,6 +534,7 @@ conv_i8_tc_fast_kernel(const __grid_constant__ TcParams P)
         }
     } else if (warp >= kFastEpiWarp0) {
         // ------------------------------ epilogue ----------------------------------
+        griddep_wait();                                             // (it reads only constants from global memory, and the status word)
         const int ew = warp - kFastEpiWarp0;
         const int quad = ew & 3;                                    // TMEM lanes 32*quad .. 32*quad+31 (warp index mod 4)
         const int group = ew >> 2;
