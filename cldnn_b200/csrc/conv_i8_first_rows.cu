@@ -1,5 +1,5 @@
-// conv_i8_first, row form: the first convolution of an 8-bit image network (few planar input features, stride 2,
-// 64 or 32 output features) as a GEMM whose rows are OUTPUT ROWS and whose operand is the raw image, so that no thread
+// First layer, row form: the first convolution of an image network (few planar input features; written for the 8-bit case:
+// stride 2, 64 or 32 output features) as a GEMM whose rows are OUTPUT ROWS and whose operand is the raw image, so that no thread
 // ever assembles an im2col operand:
 //
 //   D[y, (i, f)] = sum over (ky, c)  A_(ky,c)[y, 0..31] . T_(ky,c)[(i, f), 0..31]
@@ -18,10 +18,15 @@
 // exchange the per-tile work of the general first-layer kernel's four builder warps disappears, and what remains per tile
 // of 128 rows x XB columns is C * kh MMAs (M 128, N 256, K 32), two TMA copies and the requantising epilogue.
 //
-// Roles: warp 0 issues the copies, warp 1 the MMAs, warps 4..11 are two epilogue groups taking tiles in turn (one
-// accumulator of 256 columns each).  The operation order of the epilogue is the reference's
-// (kernel_selector/core/cl_kernels/fused_conv_eltwise_gpu_ref.cl:65-234); it is the conversion-free form of
-// conv_epilogue.cuh, with the float-domain form per value where a feature's range demands it.
+// The same kernel serves fp16 images (kind::f16, fp32 accumulators, bias + activation + one rounding to half): a window is then
+// 16 columns, and with a vertical stride of 1 there is one plane of all rows instead of two parity planes (VGG's 3x3 first
+// layer).  What fits is decided on the host (first_rows_plan): stride 1 or 2, the window of a block within 32 bytes, x-blocks
+// stepping by whole 16-byte units, the banded matrices and two stages of rows within shared memory.
+//
+// Roles: warp 0 issues the copies, warp 1 the MMAs, warps 4.. are two epilogue groups taking tiles in turn (one accumulator of
+// 256 columns each) or four (the two groups of an accumulator share its tiles by column halves).  The operation order of the
+// 8-bit epilogue is the reference's (kernel_selector/core/cl_kernels/fused_conv_eltwise_gpu_ref.cl:65-234); it is the
+// conversion-free form of conv_epilogue.cuh, with the float-domain form per value where a feature's range demands it.
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <mutex>
@@ -37,7 +42,7 @@ using namespace ptx;
 
 constexpr int rows_threads(int groups) { return 128 + 128 * groups; }
 constexpr int kRMaxStages = 4;
-constexpr int kRCols = 256;                     // four output columns x 64 features
+constexpr int kRCols = 256;                     // accumulator columns of a tile: XB output columns x features
 constexpr int kROfm = 64;                       // at most; 32 features make x-blocks of eight output columns
 constexpr uint32_t kErrRows = 0x58u;
 
